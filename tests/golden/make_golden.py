@@ -1,0 +1,212 @@
+"""Generate the golden fixtures in this directory by RUNNING THE REFERENCE.
+
+Two legs, both writing ``.npz`` files next to this script:
+
+``--leg cpu``  (no GPU needed) imports the reference package from ``--ref-root``
+    with ``MSLK_PYTHON_ONLY=1`` and records, on seeded inputs,
+    * ``quantize_fp8_row`` on CPU tensors (its torch path,
+      ``mslk/quantize/triton/fp8_quantize.py:356-378``),
+    * ``matmul_fp8_row`` CPU fallback (``mslk/gemm/triton/fp8_gemm.py:1190-1201``),
+    * the NVFP4 torch reference ``data_to_nvfp4_with_global_scale`` from the
+      reference's own test (``test/quantize/triton/fp4_quantize_test.py:259-296``),
+      ``_to_blocked``, ``global_scale_nvfp4`` and ``dequantize_nvfp4``.
+``--leg gpu``  (needs a B200) runs the reference's Triton kernels
+    ``triton_quantize_fp8_row`` and ``triton_quantize_nvfp4`` on the same seeded
+    inputs; these are the bit-level pins for the GPU arithmetic.
+
+The inputs are stored with the outputs so the tests do not depend on torch's
+random streams.  bf16 / fp8 tensors are stored as their raw integer views.
+
+Usage:  python tests/golden/make_golden.py --leg cpu --ref-root <path to reference checkout>
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _raw(t: torch.Tensor) -> np.ndarray:
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(np.uint16)
+    if t.dtype in (torch.float8_e4m3fn,):
+        return t.view(torch.uint8).numpy()
+    if hasattr(torch, "float4_e2m1fn_x2") and t.dtype == torch.float4_e2m1fn_x2:
+        return t.view(torch.uint8).numpy()
+    return t.numpy()
+
+
+def _randn_bf16(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g, dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+# (name, shape, kwargs) -- mirrors the case list of the reference's own test
+# test/quantize/triton/fp8_quantize_test.py:145-220 at fixture-friendly sizes.
+FP8_ROW_CASES = [
+    ("r8x300", (8, 300), {}),
+    ("r2x1", (2, 1), {}),
+    ("r2x4101", (2, 4101), {}),
+    ("r3x9000", (3, 9000), {}),                       # > 8192: the reference's two-pass branch
+    ("r16x4096", (16, 4096), {}),
+    ("r4x14336", (4, 14336), {}),
+    ("b4x2x3", (4, 2, 3), {}),
+    ("b4x2x13_align8", (4, 2, 13), {"align_rows_to": 8}),
+    ("b4x2x8_align8", (4, 2, 8), {"align_rows_to": 8}),
+    ("b6x4x2x3", (6, 4, 2, 3), {}),
+    ("b4x2x3_perm", (4, 2, 3), {"permute": (2, 0, 1)}),
+    ("b6x4x2x3_perm", (6, 4, 2, 3), {"permute": (0, 3, 2, 1)}),
+    ("r2x3_ub", (2, 3), {"scale_ub": 1200.0}),
+    ("r8x64_ub_small", (8, 64), {"scale_ub": 1.5}),
+    ("r20x30_jag", (20, 30), {"jagged": True}),
+    ("r20x30_jag_align16", (20, 30), {"jagged": True, "align_rows_to": 16}),
+    ("b6x4x2x3_jag", (6, 4, 2, 3), {"jagged": True}),
+    ("r4x256_tiny", (4, 256), {"scale": 1e-4}),        # amax below eps -> eps floor
+    ("r4x256_zero", (4, 256), {"scale": 0.0}),
+]
+
+NVFP4_CASES = [
+    # test/quantize/triton/fp4_quantize_test.py:198-212 (fixture-sized subset)
+    ("n128x64", (128, 64)), ("n5x64", (5, 64)), ("n128x16", (128, 16)), ("n5x16", (5, 16)),
+    ("n256x64", (256, 64)), ("n128x128", (128, 128)), ("n150x64", (150, 64)),
+    ("n128x144", (128, 144)), ("n1x2048", (1, 2048)), ("n250x512", (250, 512)),
+]
+
+
+def _fp8_inputs(name, shape, kw, seed):
+    a = _randn_bf16(shape, seed, kw.get("scale", 1.0))
+    zs = None
+    if kw.get("jagged"):
+        g = torch.Generator().manual_seed(seed + 1000)
+        grouped = a.view(-1, a.shape[-2], a.shape[-1])
+        zs = torch.randint(0, grouped.shape[1] + 1, (grouped.shape[0],), generator=g)
+        mask = torch.arange(grouped.shape[1]).expand(grouped.shape[0], grouped.shape[1]) >= zs[:, None]
+        grouped[mask] = 0.0
+    if "permute" in kw:
+        a = a.permute(kw["permute"])
+    ub = torch.tensor([kw["scale_ub"]], dtype=torch.float32) if "scale_ub" in kw else None
+    return a, ub, zs
+
+
+def _import_reference(ref_root: str):
+    os.environ["MSLK_PYTHON_ONLY"] = "1"
+    sys.path.insert(0, ref_root)
+    # torch.testing._internal.common_quantized imports `expecttest`, which is not
+    # installed; it only needs the name to exist.
+    if "expecttest" not in sys.modules:
+        stub = types.ModuleType("expecttest")
+        stub.TestCase = __import__("unittest").TestCase
+        sys.modules["expecttest"] = stub
+
+
+def leg_cpu(ref_root: str):
+    _import_reference(ref_root)
+    from mslk.quantize.triton.fp8_quantize import quantize_fp8_row
+    from mslk.gemm.triton.fp8_gemm import matmul_fp8_row
+    from mslk.quantize.triton.legacy.fp4_utils import dequantize_nvfp4, global_scale_nvfp4
+    from mslk.quantize.triton.legacy.primitives import _to_blocked
+
+    out = {}
+    for i, (name, shape, kw) in enumerate(FP8_ROW_CASES):
+        if kw.get("jagged") or "align_rows_to" in kw or "permute" in kw:
+            continue  # the reference's CPU path ignores these options
+        a, ub, _ = _fp8_inputs(name, shape, kw, seed=i)
+        q, s = quantize_fp8_row(a, scale_ub=ub, use_triton=False)
+        out[f"{name}.a"] = _raw(a)
+        out[f"{name}.q"] = _raw(q)
+        out[f"{name}.s"] = _raw(s)
+        if ub is not None:
+            out[f"{name}.ub"] = _raw(ub)
+    np.savez_compressed(os.path.join(HERE, "fp8_row_cpu_path.npz"), **out)
+
+    # CPU GEMM fallback of the reference on reference-quantized inputs
+    out = {}
+    for name, (M, N, K), sw in [("g64x48x256", (64, 48, 256), 0.02), ("g5x33x128", (5, 33, 128), 1.0)]:
+        x = _randn_bf16((M, K), 100)
+        w = _randn_bf16((N, K), 101, sw)
+        xq, xs = quantize_fp8_row(x, use_triton=False)
+        wq, ws = quantize_fp8_row(w, use_triton=False)
+        y = matmul_fp8_row(xq, wq, xs, ws)
+        for k, v in dict(xq=xq, wq=wq, xs=xs, ws=ws, y=y).items():
+            out[f"{name}.{k}"] = _raw(v)
+    np.savez_compressed(os.path.join(HERE, "fp8_gemm_cpu_path.npz"), **out)
+
+    # NVFP4 torch reference from the reference's own test module
+    sys.path.insert(0, os.path.join(ref_root, "test", "quantize", "triton"))
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "_ref_fp4_test", os.path.join(ref_root, "test", "quantize", "triton", "fp4_quantize_test.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = {}
+    for i, (name, shape) in enumerate(NVFP4_CASES):
+        x = _randn_bf16(shape, 200 + i)
+        gs = global_scale_nvfp4(x)
+        q, s, s_dec = mod.data_to_nvfp4_with_global_scale(x, 16)
+        s_blocked = _to_blocked(s)
+        deq = dequantize_nvfp4(q.view(torch.uint8), s_blocked.view(torch.uint8), gs)
+        out[f"{name}.x"] = _raw(x)
+        out[f"{name}.gs"] = _raw(gs.reshape(1))
+        out[f"{name}.q"] = _raw(q)
+        out[f"{name}.s"] = _raw(s)
+        out[f"{name}.s_blocked"] = _raw(s_blocked)
+        out[f"{name}.deq"] = _raw(deq)
+    np.savez_compressed(os.path.join(HERE, "nvfp4_torch_ref.npz"), **out)
+    print("cpu leg written")
+
+
+def leg_gpu(ref_root: str):
+    _import_reference(ref_root)
+    assert torch.cuda.is_available()
+    from mslk.quantize.triton.fp8_quantize import triton_quantize_fp8_row
+    from mslk.quantize.triton.quantize_kernels.nvfp4 import quantize_nvfp4
+    from mslk.quantize.triton.legacy.fp4_utils import global_scale_nvfp4
+
+    out = {}
+    for i, (name, shape, kw) in enumerate(FP8_ROW_CASES):
+        a, ub, zs = _fp8_inputs(name, shape, kw, seed=i)
+        q, s = triton_quantize_fp8_row(
+            a.cuda(), None if ub is None else ub.cuda(), None if zs is None else zs.cuda(),
+            align_rows_to=kw.get("align_rows_to"))
+        torch.cuda.synchronize()
+        out[f"{name}.a"] = _raw(a.contiguous())          # logical (permuted) content, contiguous
+        out[f"{name}.q"] = _raw(q)
+        out[f"{name}.s"] = _raw(s)
+        if ub is not None:
+            out[f"{name}.ub"] = _raw(ub)
+        if zs is not None:
+            out[f"{name}.zs"] = _raw(zs)
+    np.savez_compressed(os.path.join(HERE, "fp8_row_triton_b200.npz"), **out)
+
+    out = {}
+    for i, (name, shape) in enumerate(NVFP4_CASES):
+        x = _randn_bf16(shape, 200 + i)
+        gs = global_scale_nvfp4(x.cuda())
+        q, s = quantize_nvfp4(x.cuda(), gs)
+        torch.cuda.synchronize()
+        out[f"{name}.x"] = _raw(x)
+        out[f"{name}.gs"] = _raw(gs.reshape(1))
+        out[f"{name}.q"] = _raw(q)
+        out[f"{name}.s_blocked"] = _raw(s)
+    np.savez_compressed(os.path.join(HERE, "nvfp4_triton_b200.npz"), **out)
+    print("gpu leg written")
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--leg", choices=["cpu", "gpu"], required=True)
+    ap.add_argument("--ref-root", required=True)
+    ap.add_argument("--out-dir", default=None, help="write here instead of beside this script")
+    args = ap.parse_args()
+    if args.out_dir:
+        HERE = args.out_dir
+        os.makedirs(HERE, exist_ok=True)
+    (leg_cpu if args.leg == "cpu" else leg_gpu)(args.ref_root)

@@ -1,0 +1,212 @@
+"""CPU tests: the oracle against fixtures produced by running the reference
+(tests/golden/make_golden.py) and against torch's own conversions."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import bf16, fp8, load_golden, u8, randn_bf16
+from golden.make_golden import FP8_ROW_CASES, NVFP4_CASES
+
+
+def test_e4m3_encode_matches_torch_exhaustive_grid():
+    # every e4m3 value, every midpoint between neighbours, and +-1 ulp(fp32) around both
+    codes = torch.arange(0, 127, dtype=torch.uint8)
+    vals = codes.view(torch.float8_e4m3fn).float()
+    mids = (vals[:-1] + vals[1:]) / 2
+    pts = torch.cat([vals, mids])
+    pts = torch.cat([pts, torch.nextafter(pts, torch.tensor(1e9)), torch.nextafter(pts, torch.tensor(-1e9))])
+    pts = torch.cat([pts, -pts])
+    want = pts.to(torch.float8_e4m3fn).view(torch.uint8)
+    L = oracle.lib()
+    got = torch.tensor([L.oracle_f32_to_e4m3(ctypes.c_float(v)) for v in pts.tolist()], dtype=torch.uint8)
+    assert torch.equal(got, want)
+    # decode
+    dec = torch.tensor([L.oracle_e4m3_to_f32(int(c)) for c in codes.tolist()])
+    assert torch.equal(dec, vals)
+
+
+def test_e4m3_saturates_finite():
+    L = oracle.lib()
+    for v, c in [(448.0, 0x7E), (463.9, 0x7E), (464.0, 0x7E), (1e30, 0x7E), (-1e30, 0xFE), (float("inf"), 0x7E)]:
+        assert L.oracle_f32_to_e4m3(ctypes.c_float(v)) == c
+
+
+def test_e2m1_rne_ties_to_even():
+    L = oracle.lib()
+    table = {0.0: 0, 0.25: 0, 0.26: 1, 0.5: 1, 0.75: 2, 1.0: 2, 1.25: 2, 1.5: 3, 1.75: 4, 2.0: 4,
+             2.5: 4, 2.51: 5, 3.0: 5, 3.5: 6, 4.0: 6, 5.0: 6, 5.01: 7, 6.0: 7, 100.0: 7}
+    for v, c in table.items():
+        assert L.oracle_f32_to_e2m1(ctypes.c_float(v)) == c, v
+        if v:
+            assert L.oracle_f32_to_e2m1(ctypes.c_float(-v)) == (c | 8), v
+
+
+def test_bf16_round_matches_torch():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(20000, generator=g) * 100
+    x = torch.cat([x, torch.tensor([1.00390625, 1.01171875, 3.3895e38, 0.0, -0.0])])
+    L = oracle.lib()
+    got = torch.tensor([L.oracle_f32_to_bf16(ctypes.c_float(v)) for v in x.tolist()], dtype=torch.int32)
+    want = x.to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+    assert torch.equal(got, want)
+
+
+def test_cpu_path_quantize_matches_reference_fixture():
+    gold = load_golden("fp8_row_cpu_path.npz")
+    assert gold is not None
+    names = sorted({k.split(".")[0] for k in gold.files})
+    assert len(names) >= 8
+    for name in names:
+        a = bf16(gold[f"{name}.a"])
+        ub = torch.from_numpy(gold[f"{name}.ub"]) if f"{name}.ub" in gold.files else None
+        q, s = oracle.quantize_fp8_row_cpu_path(a, ub)
+        assert torch.equal(u8(q), torch.from_numpy(gold[f"{name}.q"])), name
+        assert torch.equal(s.view(torch.int32), torch.from_numpy(gold[f"{name}.s"]).view(torch.int32)), name
+        # and the torch statement used for CPU-baseline timing is the same arithmetic
+        q2, s2 = oracle.quantize_fp8_row_cpu_path_torch(a, ub)
+        assert torch.equal(u8(q2), u8(q)), name
+        assert torch.equal(s2, s), name
+
+
+def test_gpu_arithmetic_quantize_matches_torch_statement():
+    # The C statement of the Triton arithmetic against the same formula written in torch
+    # (fp32 IEEE division twice, clamp, RNE cast).
+    for i, (name, shape, kw) in enumerate(FP8_ROW_CASES):
+        if kw.get("jagged") or "permute" in kw:
+            continue
+        a = randn_bf16(shape, i, kw.get("scale", 1.0))
+        ub = torch.tensor([kw["scale_ub"]]) if "scale_ub" in kw else None
+        q, s = oracle.quantize_fp8_row(a, ub, None, kw.get("align_rows_to"))
+        amax = a.abs().amax(dim=-1).float()
+        cur = torch.clamp(amax, min=1.0 / 512.0)
+        if ub is not None:
+            cur = torch.clamp(cur, max=ub.item())
+        sc = cur / 448.0
+        qq = torch.clamp(a.float() / sc[..., None], -448, 448).to(torch.float8_e4m3fn)
+        K = shape[-1]
+        assert torch.equal(s, sc), name
+        assert torch.equal(u8(q)[..., :K], u8(qq)), name
+        assert (u8(q)[..., K:] == 0).all(), name
+
+
+def test_triton_fixture_pins_gpu_arithmetic():
+    gold = load_golden("fp8_row_triton_b200.npz")
+    if gold is None:
+        pytest.skip("fixture captured on a B200 not present yet")
+    for i, (name, shape, kw) in enumerate(FP8_ROW_CASES):
+        a = bf16(gold[f"{name}.a"])
+        ub = torch.from_numpy(gold[f"{name}.ub"]) if f"{name}.ub" in gold.files else None
+        zs = torch.from_numpy(gold[f"{name}.zs"]) if f"{name}.zs" in gold.files else None
+        q, s = oracle.quantize_fp8_row(a, ub, zs, kw.get("align_rows_to"))
+        assert torch.equal(s.reshape(-1).view(torch.int32),
+                           torch.from_numpy(gold[f"{name}.s"]).reshape(-1).view(torch.int32)), name
+        assert torch.equal(u8(q).reshape(-1), torch.from_numpy(gold[f"{name}.q"]).reshape(-1)), name
+
+
+def test_gemm_oracles_agree_and_match_reference_cpu_fallback():
+    gold = load_golden("fp8_gemm_cpu_path.npz")
+    for name in sorted({k.split(".")[0] for k in gold.files}):
+        xq, wq = fp8(gold[f"{name}.xq"]), fp8(gold[f"{name}.wq"])
+        xs, ws = torch.from_numpy(gold[f"{name}.xs"]), torch.from_numpy(gold[f"{name}.ws"])
+        y_ref = bf16(gold[f"{name}.y"])
+        y_c = oracle.gemm_f8_rowwise(xq, wq, xs, ws)
+        y_t = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws)
+        # C (sequential fp32) vs torch (blocked fp32): same up to fp32 summation order
+        torch.testing.assert_close(y_c.float(), y_t.float(), rtol=1.6e-2, atol=1e-2)
+        # the reference's CPU fallback does a bf16 matmul: tolerance of its own tests
+        torch.testing.assert_close(y_c.float(), y_ref.float(), rtol=1.6e-2, atol=3.5e-2)
+
+
+def test_gemm_oracle_bias_kinds():
+    x = randn_bf16((7, 64), 1)
+    w = randn_bf16((9, 64), 2)
+    xq, xs = oracle.quantize_fp8_row(x)
+    wq, ws = oracle.quantize_fp8_row(w)
+    for bias in (torch.randn(9), torch.randn(9).bfloat16()):
+        y_c = oracle.gemm_f8_rowwise(xq, wq, xs, ws, bias)
+        y_t = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws, bias)
+        torch.testing.assert_close(y_c.float(), y_t.float(), rtol=1.6e-2, atol=1e-2)
+
+
+def test_grouped_oracles_agree():
+    ms = [3, 0, 5, 1]
+    x = randn_bf16((sum(ms), 64), 3)
+    w = randn_bf16((4, 6, 64), 4)
+    xq, xs = oracle.quantize_fp8_row(x)
+    wq, ws = oracle.quantize_fp8_row(w)
+    y_c = oracle.gemm_f8_rowwise_grouped_stacked(xq, wq, xs, ws, ms)
+    y_t = oracle.gemm_f8_rowwise_grouped_stacked_torch(xq, wq, xs, ws, ms)
+    torch.testing.assert_close(y_c.float(), y_t.float(), rtol=1.6e-2, atol=1e-2)
+
+
+def test_nvfp4_quantize_matches_reference_torch_fixture():
+    gold = load_golden("nvfp4_torch_ref.npz")
+    assert gold is not None
+    for name, shape in NVFP4_CASES:
+        x = bf16(gold[f"{name}.x"])
+        gs = torch.from_numpy(gold[f"{name}.gs"])
+        assert torch.equal(oracle.global_scale_nvfp4(x).reshape(1), gs), name
+        q, s = oracle.quantize_nvfp4(x, gs)
+        want_s = torch.from_numpy(gold[f"{name}.s_blocked"]).reshape(-1)
+        assert torch.equal(u8(s).reshape(-1), want_s), name
+        assert torch.equal(q, torch.from_numpy(gold[f"{name}.q"])), name
+        # layout helpers
+        s_plain = fp8(gold[f"{name}.s"])
+        assert torch.equal(oracle.to_blocked(u8(s_plain)), want_s), name
+        assert torch.equal(oracle.from_blocked(want_s, *s_plain.shape), u8(s_plain)), name
+
+
+def test_nvfp4_triton_fixture():
+    gold = load_golden("nvfp4_triton_b200.npz")
+    if gold is None:
+        pytest.skip("fixture captured on a B200 not present yet")
+    for name, shape in NVFP4_CASES:
+        x = bf16(gold[f"{name}.x"])
+        gs = torch.from_numpy(gold[f"{name}.gs"])
+        q, s = oracle.quantize_nvfp4(x, gs)
+        assert torch.equal(u8(s).reshape(-1), torch.from_numpy(gold[f"{name}.s_blocked"]).reshape(-1)), name
+        assert torch.equal(q, torch.from_numpy(gold[f"{name}.q"])), name
+
+
+def test_nvfp4_gemm_oracles_agree_and_dequant_matches_reference():
+    gold = load_golden("nvfp4_torch_ref.npz")
+    name = "n128x64"
+    x = bf16(gold[f"{name}.x"])
+    gs = torch.from_numpy(gold[f"{name}.gs"])
+    q, s = oracle.quantize_nvfp4(x, gs)
+    # dequantize(x) as the reference does it equals fp4*scale/gs
+    true_scale = oracle.from_blocked(u8(s).reshape(-1), 128, 4).view(torch.float8_e4m3fn).float() / gs
+    deq = (oracle.fp4_to_float(q) * true_scale.repeat_interleave(16, 1)).to(torch.bfloat16)
+    # value comparison: the reference's lookup table holds +0 for code 8 (-0)
+    assert torch.equal(deq.float(), bf16(gold[f"{name}.deq"]).float())
+    w = randn_bf16((48, 64), 9)
+    gw = oracle.global_scale_nvfp4(w)
+    wq, sw = oracle.quantize_nvfp4(w, gw)
+    alpha = 1.0 / (gs * gw)
+    y_c = oracle.gemm_nvfp4(q, wq, s, sw, alpha)
+    y_t = oracle.gemm_nvfp4_torch(q, wq, s, sw, alpha)
+    torch.testing.assert_close(y_c.float(), y_t.float(), rtol=1.6e-2, atol=1e-2)
+    torch.testing.assert_close(y_t.float(), (x.float() @ w.float().T), rtol=5e-2, atol=0.5)
+
+
+def test_fma_division_equals_ieee_division():
+    # all bf16 magnitudes in the range that can round to a non-zero e4m3 x a spread of scales
+    g = torch.Generator().manual_seed(0)
+    bits = torch.arange(0x0080, 0x7F80, dtype=torch.int32)  # every positive normal bf16
+    x = (bits << 16).view(torch.float32)
+    total_bad = 0
+    L = oracle.lib()
+    for rep in range(24):
+        amax = torch.exp(torch.rand(x.numel(), generator=g) * 40 - 20).to(torch.bfloat16).float()
+        s = torch.clamp(amax, min=1 / 512) / 448.0
+        keep = (x <= amax * 1.0) & (x / s > 2 ** -12)
+        xs_, ss_ = x[keep].contiguous(), s[keep].contiguous()
+        total_bad += L.oracle_check_fma_division(xs_.data_ptr(), ss_.data_ptr(), xs_.numel())
+    assert total_bad == 0
+    # fp32 inputs too
+    xf = torch.randn(400000, generator=g).abs() + 1e-3
+    sf = (torch.rand(400000, generator=g) * 8 + 1e-2) / 448
+    assert L.oracle_check_fma_division(xf.data_ptr(), sf.data_ptr(), xf.numel()) == 0
