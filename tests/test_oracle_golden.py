@@ -189,7 +189,9 @@ def test_nvfp4_gemm_oracles_agree_and_dequant_matches_reference():
     y_c = oracle.gemm_nvfp4(q, wq, s, sw, alpha)
     y_t = oracle.gemm_nvfp4_torch(q, wq, s, sw, alpha)
     torch.testing.assert_close(y_c.float(), y_t.float(), rtol=1.6e-2, atol=1e-2)
-    torch.testing.assert_close(y_t.float(), (x.float() @ w.float().T), rtol=5e-2, atol=0.5)
+    # sanity against the unquantized product: 4-bit error, so only a norm bound
+    y_full = x.float() @ w.float().T
+    assert (y_t.float() - y_full).norm() / y_full.norm() < 0.2
 
 
 def test_fma_division_equals_ieee_division():
