@@ -1,0 +1,121 @@
+/*
+ * mslk_b200 -- C ABI of the B200 (sm_100a) low-precision GEMM path.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer on the
+ * current CUDA device unless stated otherwise, every function enqueues its
+ * work on `stream` (a cudaStream_t passed as void*) and returns without
+ * synchronising the host, so all entry points may be captured in a CUDA graph.
+ * Return value: 0 on success, non-zero on a rejected argument or a CUDA launch
+ * error; the message is available from mslk_b200_last_error() (thread-local).
+ *
+ * Each entry point names the reference (meta-pytorch/MSLK) interface it
+ * replaces.
+ */
+#ifndef MSLK_B200_H_
+#define MSLK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSLK_B200_ABI_VERSION 1
+
+/* element type codes for high-precision inputs */
+#define MSLK_B200_F32 0
+#define MSLK_B200_BF16 1
+#define MSLK_B200_F16 2
+
+/* bias kinds of f8f8bf16_rowwise */
+#define MSLK_B200_BIAS_NONE 0
+#define MSLK_B200_BIAS_F32 1
+#define MSLK_B200_BIAS_BF16 2
+
+int mslk_b200_abi_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char *mslk_b200_last_error(void);
+
+/*
+ * Reads (and clears) the device-side status word of the current device after
+ * synchronising it.  0 = no kernel reported a problem.  A kernel whose bounded
+ * pipeline wait expired stores a non-zero code here and exits cleanly instead
+ * of hanging.  This call synchronises the device; do not use it under capture.
+ */
+int mslk_b200_device_status(int *status_out);
+
+/*
+ * Per-row FP8 (e4m3fn) quantization.
+ * Replaces: mslk/quantize/triton/fp8_quantize.py:36-207 (_kernel_quantize_fp8_row)
+ *           as launched by triton_quantize_fp8_row (:210-316).
+ *
+ * x is read as a 4-D tensor [B, M, N, K] of `dtype` with ELEMENT strides
+ * sb, sm, sn, sk.  Row r = (b*M + m)*N + n gets
+ *     scale[r] = min(max(amax_r, eps), *scale_ub) / 448      (scale_ub may be NULL)
+ *     q[r, k]  = e4m3_rn_satfinite(x[r, k] / scale[r])        k <  K
+ *     q[r, k]  = 0                                            K <= k < K_out
+ * with IEEE fp32 divisions.  zero_start_index_M (int64 [B*M], may be NULL) marks
+ * rows n >= zero_start_index_M[b*M+m] as all-zero.  q is contiguous
+ * [B*M*N, K_out] bytes, scale is fp32 [B*M*N].
+ */
+int mslk_b200_quantize_fp8_row(const void *x, int dtype, int64_t B, int64_t M, int64_t N,
+                               int64_t K, int64_t K_out, int64_t sb, int64_t sm, int64_t sn,
+                               int64_t sk, const float *scale_ub,
+                               const int64_t *zero_start_index_M, float eps, void *q,
+                               float *scale, void *stream);
+
+/*
+ * Rowwise-scaled FP8 GEMM:  y[m,n] = bf16((x_scale[m] * sum_k xq[m,k]*wq[n,k]) * w_scale[n] (+ bias[n])).
+ * Replaces: csrc/gemm/cutlass/f8f8bf16_rowwise.cu:183-206 (f8f8bf16_rowwise / _out)
+ *           and f8f8bf16_rowwise/f8f8bf16_rowwise_common.cuh:44-346 (the kernel).
+ * xq [M,K] and wq [N,K] are contiguous e4m3fn bytes, K % 16 == 0; y is contiguous
+ * bf16 [M,N].  bias ([N], fp32 or bf16 per bias_kind) may be NULL.
+ */
+int mslk_b200_f8f8bf16_rowwise(const void *xq, const void *wq, const float *x_scale,
+                               const float *w_scale, const void *bias, int bias_kind, void *y,
+                               int64_t M, int64_t N, int64_t K, void *stream);
+
+/*
+ * Grouped (stacked) rowwise FP8 GEMM for MoE experts.
+ * Replaces: csrc/gemm/cutlass/f8f8bf16_rowwise_grouped.cu:342-368
+ *           (f8f8bf16_rowwise_grouped_stacked) with its argument-setup kernel and
+ *           grouped kernel, f8f8bf16_rowwise_grouped_sm100/
+ *           f8f8bf16_rowwise_grouped_common.cuh:148-213,225-606.
+ * xq [total_M,K], wq [G,N,K], x_scale [total_M], w_scale [G*N], y [total_M,N] bf16.
+ * M_sizes is int64 [G] ON THE DEVICE (never read by the host); group g owns rows
+ * [sum_{i<g} M_sizes[i], +M_sizes[g]).  Rows past the sum are left untouched.
+ */
+int mslk_b200_f8f8bf16_rowwise_grouped_stacked(const void *xq, const void *wq,
+                                               const float *x_scale, const float *w_scale,
+                                               const int64_t *M_sizes, int64_t G,
+                                               int64_t total_M, int64_t N, int64_t K, void *y,
+                                               void *stream);
+
+/*
+ * NVFP4 quantization (e2m1 data, one e4m3 scale per 16 elements in the 128x4
+ * swizzled layout, optional fp32 per-tensor global scale read from the device).
+ * Replaces: mslk/quantize/triton/quantize_kernels/nvfp4.py:62-296.
+ * x is bf16 [M,K] with row stride `row_stride` elements, K % 16 == 0.
+ * q is [M, K/2] bytes (element 2j in the low nibble); scales is
+ * [ceil(M/128)*128 * ceil(K/64)*4] bytes and is written completely (padding = 0).
+ */
+int mslk_b200_quantize_nvfp4(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                             const float *global_scale, void *q, void *scales, void *stream);
+
+/*
+ * NVFP4 GEMM:  y = bf16(*global_scale * sum_blocks (sx*sw) * sum_16 x^*w^).
+ * Replaces: csrc/gemm/cutlass/f4f4bf16.cu:6413-6473 (NVFP4 branch) and
+ *           f4f4bf16/f4f4bf16_common.cuh:78-315.
+ * xq [M,K/2], wq [N,K/2] packed e2m1; x_scale / w_scale swizzled e4m3 as produced
+ * by mslk_b200_quantize_nvfp4; global_scale is a device fp32 scalar; K % 32 == 0.
+ */
+int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale,
+                       const void *w_scale, const float *global_scale, void *y, int64_t M,
+                       int64_t N, int64_t K, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSLK_B200_H_ */

@@ -1,0 +1,51 @@
+"""ctypes binding of the C-ABI library ``libmslk_b200.so`` (declared in ``include/mslk_b200.h``).
+
+There is no fallback: if the library is missing or cannot be loaded, importing
+this module raises, and every wrapper raises ``RuntimeError`` with the library's
+own message when a call is rejected.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libmslk_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m mslk_b200.build` (needs nvcc with sm_100a support). "
+        "mslk_b200 has no CPU or eager fallback.")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_i64, _vp, _f32, _int = ctypes.c_int64, ctypes.c_void_p, ctypes.c_float, ctypes.c_int
+
+lib.mslk_b200_abi_version.restype = _int
+lib.mslk_b200_last_error.restype = ctypes.c_char_p
+lib.mslk_b200_device_status.argtypes = [ctypes.POINTER(_int)]
+lib.mslk_b200_device_status.restype = _int
+lib.mslk_b200_quantize_fp8_row.argtypes = [_vp, _int] + [_i64] * 9 + [_vp, _vp, _f32, _vp, _vp, _vp]
+lib.mslk_b200_quantize_fp8_row.restype = _int
+lib.mslk_b200_f8f8bf16_rowwise.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]
+lib.mslk_b200_f8f8bf16_rowwise.restype = _int
+lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]
+lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked.restype = _int
+lib.mslk_b200_quantize_nvfp4.argtypes = [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]
+lib.mslk_b200_quantize_nvfp4.restype = _int
+lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
+lib.mslk_b200_f4f4bf16.restype = _int
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib.mslk_b200_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed (code {rc}): {msg}")
+
+
+def device_status() -> int:
+    """Synchronises the current device and returns (and clears) its kernel status word."""
+    out = _int(0)
+    check(lib.mslk_b200_device_status(ctypes.byref(out)), "mslk_b200_device_status")
+    return out.value

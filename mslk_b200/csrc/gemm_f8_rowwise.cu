@@ -1,0 +1,487 @@
+// Rowwise-scaled FP8 GEMM for sm_100a, dense and grouped (stacked MoE) in one
+// persistent, warp-specialised tcgen05 kernel.
+//
+//   y[m, n] = bf16((x_scale[m] * sum_k xq[m,k] * wq[n,k]) * w_scale[n] (+ bias[n]))
+//
+// Both operands are K-major e4m3 bytes, so an operand tile is a TMA box of
+// {128 bytes of K, rows} written to shared memory with the 128-byte swizzle and
+// consumed in place by tcgen05.mma (kind::f8f6f4, 128 x BN x 32 per instruction,
+// fp32 accumulators in tensor memory).
+//
+// Roles (192 threads, one CTA per SM):
+//   warp 0      TMA producer: fills a kStages-deep ring of {A 128x128, B BNx128} tiles
+//   warp 1      MMA issuer (one elected lane) and owner of the TMEM allocation
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply the row and
+//               column scales (+ bias), convert to bf16 and store
+// Two accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the
+// main loop of tile i+1.
+//
+// Tile scheduler (device side, static round-robin over a linear tile index): the
+// kernel reads the per-group row counts from device memory, builds prefix tables
+// in shared memory and maps tile -> (group, 128-row block, BN-column block).  A
+// dense GEMM is the one-group case.  Groups with zero rows own no tiles.  Tiles
+// of a group are visited in bands of kBandM row blocks so that CTAs running at
+// the same time share operand tiles in L2.  Row blocks may run past the end of
+// their group (or of the tensor: TMA zero-fills); the epilogue masks those rows.
+//
+// Every pipeline wait is bounded (see common.cuh); on expiry the CTA records a
+// status code, drains, frees its tensor memory and returns.
+#include "../../include/mslk_b200.h"
+#include "common.cuh"
+#include "host.h"
+
+namespace mslk_b200 {
+namespace {
+
+constexpr int kBM = 128;          // rows of the output tile (UMMA M)
+constexpr int kBK = 128;          // bytes (= fp8 elements) of K per pipeline stage
+constexpr int kUmmaK = 32;        // K per tcgen05.mma for 8-bit operands
+constexpr int kMaxGroups = 1024;
+constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueThreads = 128;
+constexpr int kBandM = 16;        // row blocks per scheduling band
+
+struct GemmParams {
+  const float *x_scale;
+  const float *w_scale;
+  const void *bias;
+  __nv_bfloat16 *y;
+  const int64_t *m_sizes;  // device, [G]; nullptr = dense (one group of total_m rows)
+  int *status;
+  int bias_kind;
+  int G;
+  int total_m;
+  int N;
+  int K;
+};
+
+template <int BN>
+struct Config {
+  static constexpr int kStageA = kBM * kBK;
+  static constexpr int kStageB = BN * kBK;
+  static constexpr int kStageBytes = kStageA + kStageB;
+  // ring depth: as many stages as fit beside ~16 KB of tables
+  static constexpr int kStages = BN == 256 ? 4 : BN == 128 ? 6 : BN == 64 ? 8 : 10;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr uint32_t kIdesc = (1u << 4)                                   // fp32 accumulate
+                                     | (0u << 7) | (0u << 10)                    // A, B = e4m3
+                                     | (static_cast<uint32_t>(BN >> 3) << 17)    // N
+                                     | (static_cast<uint32_t>(kBM >> 4) << 24);  // M
+};
+
+// Shared-memory carve-up after the operand ring (which starts 1024-byte aligned).
+template <int BN>
+struct SmemTail {
+  float w_scale[4][BN];  // one private copy per epilogue warp (no cross-warp sync in the epilogue)
+  float bias[4][BN];
+  int tile_start[kMaxGroups + 1];
+  int row_start[kMaxGroups + 1];
+  uint64_t full[Config<BN>::kStages];
+  uint64_t empty[Config<BN>::kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int BN>
+constexpr size_t smem_bytes() {
+  return 1024 + static_cast<size_t>(Config<BN>::kStages) * Config<BN>::kStageBytes + sizeof(SmemTail<BN>);
+}
+
+struct Tile {
+  int row0;   // first row of the tile in the stacked X / Y
+  int rows;   // valid rows (1..128)
+  int n0;     // first output column
+  int wrow0;  // first row in WQ viewed as [G*N, K]
+  int ws0;    // first index into w_scale
+};
+
+struct Scheduler {
+  const int *tile_start;
+  const int *row_start;
+  int G, N, n_tiles, bn;
+  int g;
+
+  __device__ __forceinline__ bool get(int tile, Tile &t) {
+    if (tile >= tile_start[G]) return false;
+    while (tile >= tile_start[g + 1]) ++g;
+    const int local = tile - tile_start[g];
+    const int mg = row_start[g + 1] - row_start[g];
+    const int m_tiles = (mg + kBM - 1) / kBM;
+    const int per_band = kBandM * n_tiles;
+    const int band = local / per_band;
+    const int in_band = local - band * per_band;
+    const int first_m = band * kBandM;
+    const int band_m = min(m_tiles - first_m, kBandM);
+    const int n_tile = in_band / band_m;
+    const int m_tile = first_m + (in_band - n_tile * band_m);
+    t.row0 = row_start[g] + m_tile * kBM;
+    t.rows = min(kBM, mg - m_tile * kBM);
+    t.n0 = n_tile * bn;
+    t.wrow0 = g * N + t.n0;
+    t.ws0 = g * N + t.n0;
+    return true;
+  }
+};
+
+template <int BN, int BIAS>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float xs, const float *ws, const float *bs,
+                                               __nv_bfloat16 *dst, bool row_ok, int cols_left, bool vec_ok) {
+  uint32_t packed[16];
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float v0 = (__uint_as_float(acc[j]) * xs) * ws[j];
+    float v1 = (__uint_as_float(acc[j + 1]) * xs) * ws[j + 1];
+    if constexpr (BIAS == MSLK_B200_BIAS_F32) {
+      v0 += bs[j];
+      v1 += bs[j + 1];
+    } else if constexpr (BIAS == MSLK_B200_BIAS_BF16) {
+      // the scaled product is rounded to bf16 first and the add is done in bf16
+      v0 = __bfloat162float(__float2bfloat16_rn(v0)) + bs[j];
+      v1 = __bfloat162float(__float2bfloat16_rn(v1)) + bs[j + 1];
+    }
+    packed[j / 2] = pack_bf16x2(v0, v1);
+  }
+  if (!row_ok) return;
+  if (vec_ok && cols_left >= 32) {
+    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d4[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+  } else {
+    const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
+    uint16_t *d = reinterpret_cast<uint16_t *>(dst);
+    for (int j = 0; j < 32 && j < cols_left; ++j) d[j] = h[j];
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+    gemm_f8_rowwise_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                           const GemmParams p) {
+  using Cfg = Config<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemTail<BN> &S = *reinterpret_cast<SmemTail<BN> *>(ring + static_cast<size_t>(Cfg::kStages) * Cfg::kStageBytes);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int k_blocks = (p.K + kBK - 1) / kBK;
+  volatile int *abort_flag = &S.abort_flag;
+
+  // ------------------------------------------------------------------ setup
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&S.full[s], 1);
+      mbar_init(&S.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&S.tmem_full[a], 1);
+      mbar_init(&S.tmem_empty[a], kNumEpilogueThreads / 32);
+    }
+    S.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 2) {
+    // prefix tables over the groups: rows (clamped to the tensor) and tiles
+    int row_carry = 0, tile_carry = 0;
+    for (int base = 0; base < p.G; base += 32) {
+      const int g = base + lane;
+      long long mg = 0;
+      if (g < p.G) mg = p.m_sizes ? p.m_sizes[g] : p.total_m;
+      if (mg < 0) mg = 0;
+      if (mg > p.total_m) mg = p.total_m;
+      int rows = static_cast<int>(mg);
+      int rsum = rows;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, rsum, o);
+        if (lane >= o) rsum += v;
+      }
+      // clamp so that the stacked rows never run past total_m
+      int start = row_carry + rsum - rows;
+      if (start > p.total_m) start = p.total_m;
+      if (start + rows > p.total_m) rows = p.total_m - start;
+      int tiles = ((rows + kBM - 1) / kBM) * n_tiles;
+      int tsum = tiles;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, tsum, o);
+        if (lane >= o) tsum += v;
+      }
+      if (g < p.G) {
+        S.row_start[g] = start;
+        S.tile_start[g] = tile_carry + tsum - tiles;
+      }
+      row_carry = min(p.total_m, row_carry + __shfl_sync(0xffffffffu, rsum, 31));
+      tile_carry += __shfl_sync(0xffffffffu, tsum, 31);
+    }
+    if (lane == 0) {
+      S.row_start[p.G] = row_carry;
+      S.tile_start[p.G] = tile_carry;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, 0};
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      Tile t;
+      for (int tile = blockIdx.x; ok && sched.get(tile, t); tile += gridDim.x) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t *sa = ring + static_cast<size_t>(stage) * Cfg::kStageBytes;
+          uint8_t *sb = sa + Cfg::kStageA;
+          mbar_arrive_expect_tx(&S.full[stage], Cfg::kStageBytes);
+          tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBK, t.row0);
+          tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBK, t.wrow0);
+          ++issued;
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // bounded drain: give copies already issued time to land before the CTA exits
+        const unsigned long long t0 = globaltimer_ns();
+        const int pending = issued < Cfg::kStages ? static_cast<int>(issued) : Cfg::kStages;
+        for (int i = 0; i < pending; ++i) {
+          int s = stage - 1 - i;
+          uint32_t ph = phase;
+          if (s < 0) {
+            s += Cfg::kStages;
+            ph ^= 1;
+          }
+          while (!mbar_try_wait(&S.full[s], ph)) {
+            if (globaltimer_ns() - t0 > 1000000ull) {
+              atomicCAS(p.status, 0, kStatusDrainTimeout);
+              break;
+            }
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      Tile t;
+      for (int tile = blockIdx.x; ok && sched.get(tile, t); tile += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&S.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(ring + static_cast<size_t>(stage) * Cfg::kStageBytes);
+          const uint64_t da = make_kmajor_sw128_desc(sa);
+          const uint64_t db = make_kmajor_sw128_desc(sa + Cfg::kStageA);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // advancing K inside the 128-byte swizzle row: +32 bytes on the start address
+            mma_f8f6f4(d_tmem, da + static_cast<uint64_t>(k * (kUmmaK >> 4)),
+                       db + static_cast<uint64_t>(k * (kUmmaK >> 4)), Cfg::kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&S.empty[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&S.tmem_full[acc]);  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;             // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+    int local = 0;
+    bool ok = true;
+    Tile t;
+    for (int tile = blockIdx.x; ok && sched.get(tile, t); tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      // stage the column scales (and bias) of this tile in this warp's private buffer
+      float *ws_s = S.w_scale[warp - 2];
+      float *bs_s = S.bias[warp - 2];
+      for (int c = lane; c < BN; c += 32) {
+        const bool in = t.n0 + c < p.N;
+        ws_s[c] = in ? p.w_scale[t.ws0 + c] : 0.f;
+        float b = 0.f;
+        if (in && p.bias_kind == MSLK_B200_BIAS_F32) b = static_cast<const float *>(p.bias)[t.n0 + c];
+        if (in && p.bias_kind == MSLK_B200_BIAS_BF16)
+          b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[t.n0 + c]);
+        bs_s[c] = b;
+      }
+      __syncwarp();
+      const bool row_ok = row_in_tile < t.rows;
+      const float xs = row_ok ? p.x_scale[t.row0 + row_in_tile] : 0.f;
+      // warp-uniform decision: either every lane saw the accumulator complete or the warp leaves
+      const bool got = mbar_wait(&S.tmem_full[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+      if (!__all_sync(0xffffffffu, got)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
+      __nv_bfloat16 *yrow = p.y + static_cast<size_t>(t.row0 + row_in_tile) * p.N + t.n0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int cols_left = p.N - (t.n0 + c * 32);
+        if (cols_left <= 0) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const float *ws = ws_s + c * 32;
+        const float *bs = bs_s + c * 32;
+        if (p.bias_kind == MSLK_B200_BIAS_NONE)
+          epilogue_chunk<BN, MSLK_B200_BIAS_NONE>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+        else if (p.bias_kind == MSLK_B200_BIAS_F32)
+          epilogue_chunk<BN, MSLK_B200_BIAS_F32>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+        else
+          epilogue_chunk<BN, MSLK_B200_BIAS_BF16>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.tmem_empty[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int BN>
+int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  constexpr size_t smem = smem_bytes<BN>();
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_f8_rowwise_kernel<BN>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                            "cudaFuncSetAttribute(gemm_f8_rowwise)"))
+      return rc;
+    attr_set[dev] = true;
+  }
+  gemm_f8_rowwise_kernel<BN><<<grid, kNumThreads, smem, st>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "f8f8bf16_rowwise launch");
+}
+
+int run(const void *xq, const void *wq, const float *xs, const float *ws, const void *bias, int bias_kind, void *y,
+        const int64_t *m_sizes, int64_t G, int64_t total_m, int64_t N, int64_t K, cudaStream_t st,
+        const char *name) {
+  if (total_m < 0 || N < 0 || K < 0 || G < 1) return fail(1, "%s: bad shape", name);
+  if (total_m == 0 || N == 0) return 0;
+  if (G > kMaxGroups) return fail(1, "%s: at most %d groups are supported (got %lld)", name, kMaxGroups, (long long)G);
+  if (total_m > 0x7fffff00LL || G * N > 0x7fffff00LL || K > 0x7fffff00LL)
+    return fail(1, "%s: dimension too large for 32-bit tile coordinates", name);
+  if (!y) return fail(1, "%s: null output pointer", name);
+  if (K == 0) {
+    // empty reduction: the reference returns zeros
+    return check_cuda(cudaMemsetAsync(y, 0, static_cast<size_t>(total_m) * N * 2, st), "memset");
+  }
+  if (!xq || !wq || !xs || !ws) return fail(1, "%s: null pointer argument", name);
+  if (bias_kind != MSLK_B200_BIAS_NONE && !bias) return fail(1, "%s: bias_kind set but bias is null", name);
+  if (K % 16 != 0) return fail(1, "%s: K (%lld) must be a multiple of 16 (TMA row pitch)", name, (long long)K);
+  int *status = device_status_ptr();
+  if (!status) return 2;
+
+  const int sms = sm_count();
+  const int64_t m_tiles_ub = (total_m + kBM - 1) / kBM + (m_sizes ? G : 0);
+  // widest column block that still yields at least one tile per SM
+  int bn = 256;
+  while (bn > 32 && (bn / 2 >= N || m_tiles_ub * ((N + bn - 1) / bn) < sms)) bn /= 2;
+
+  GemmParams p;
+  p.x_scale = xs;
+  p.w_scale = ws;
+  p.bias = bias;
+  p.y = static_cast<__nv_bfloat16 *>(y);
+  p.m_sizes = m_sizes;
+  p.status = status;
+  p.bias_kind = bias_kind;
+  p.G = static_cast<int>(G);
+  p.total_m = static_cast<int>(total_m);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d_bytes(&ta, xq, K, total_m, K, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, K, G * N, K, kBK, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+
+  const int64_t tiles_ub = m_tiles_ub * ((N + bn - 1) / bn);
+  const int grid = static_cast<int>(tiles_ub < sms ? tiles_ub : sms);
+  switch (bn) {
+    case 256: return launch<256>(ta, tb, p, grid, st);
+    case 128: return launch<128>(ta, tb, p, grid, st);
+    case 64: return launch<64>(ta, tb, p, grid, st);
+    default: return launch<32>(ta, tb, p, grid, st);
+  }
+}
+
+}  // namespace
+}  // namespace mslk_b200
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise(const void *xq, const void *wq, const float *x_scale, const float *w_scale,
+                                        const void *bias, int bias_kind, void *y, int64_t M, int64_t N, int64_t K,
+                                        void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  if (bias_kind < 0 || bias_kind > 2) return fail(1, "f8f8bf16_rowwise: bad bias_kind %d", bias_kind);
+  return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, 1, M, N, K, static_cast<cudaStream_t>(stream),
+             "f8f8bf16_rowwise");
+}
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise_grouped_stacked(const void *xq, const void *wq, const float *x_scale,
+                                                        const float *w_scale, const int64_t *M_sizes, int64_t G,
+                                                        int64_t total_M, int64_t N, int64_t K, void *y,
+                                                        void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  if (!M_sizes) return fail(1, "f8f8bf16_rowwise_grouped_stacked: M_sizes is null");
+  return run(xq, wq, x_scale, w_scale, nullptr, MSLK_B200_BIAS_NONE, y, M_sizes, G, total_M, N, K,
+             static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise_grouped_stacked");
+}

@@ -1,0 +1,231 @@
+"""Tensor-level wrappers over the C ABI (ctypes).
+
+These functions take CUDA tensors, allocate outputs with torch's caching
+allocator, and enqueue the kernels on torch's current stream of the tensors'
+device.  They keep the argument meaning and error behaviour of the reference
+operators they stand for:
+
+* ``quantize_fp8_row``       -- ``mslk/quantize/triton/fp8_quantize.py:210-316,319-378``
+* ``f8f8bf16_rowwise``       -- ``csrc/gemm/cutlass/f8f8bf16_rowwise.cu:183-206``
+* ``f8f8bf16_rowwise_grouped_stacked`` -- ``csrc/gemm/cutlass/f8f8bf16_rowwise_grouped.cu:342-368``
+* ``quantize_nvfp4``         -- ``mslk/quantize/triton/quantize_kernels/nvfp4.py:62-149``
+* ``f4f4bf16``               -- ``csrc/gemm/cutlass/f4f4bf16.cu:6413-6473``
+
+CPU tensors are rejected: there is no fallback path.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ._lib import check, lib
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+FP8_DTYPE = torch.float8_e4m3fn
+
+
+def _require_cuda(name: str, *tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(f"{name}: expected CUDA tensors (mslk_b200 has no CPU path), got {t.device}")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"{name}: all tensors must be on the same device ({dev} vs {t.device})")
+    assert dev is not None
+    return dev
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# --------------------------------------------------------------------------- FP8 row quantize
+
+def quantize_fp8_row(
+    a: torch.Tensor,
+    scale_ub: Optional[torch.Tensor] = None,
+    zero_start_index_M: Optional[torch.Tensor] = None,
+    align_rows_to: Optional[int] = None,
+    eps_opt: Optional[float] = 1.0 / 512.0,
+):
+    """Per-row e4m3 quantization; returns ``(a_fp8 [..., K_out], a_scale [...] fp32)``."""
+    if scale_ub is not None and scale_ub.device != a.device:
+        raise Exception("'scale_ub' must be on the same device as 'a'")
+    if zero_start_index_M is not None and zero_start_index_M.device != a.device:
+        raise Exception("'zero_start_index_M' must be on the same device as 'a'")
+    assert a.dim() <= 4, "Only up to 4 dimension input tensor is supported."
+    dev = _require_cuda("quantize_fp8_row", a, scale_ub, zero_start_index_M)
+    if a.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"quantize_fp8_row: unsupported input dtype {a.dtype}")
+    out_shape = list(a.shape)
+    a4 = a
+    while a4.dim() < 4:
+        a4 = a4.unsqueeze(0)
+    B, M, N, K = a4.shape
+    K_out = K
+    if align_rows_to is not None:
+        K_out = (K + align_rows_to - 1) // align_rows_to * align_rows_to
+        out_shape[-1] = K_out
+    zs = None
+    if zero_start_index_M is not None:
+        zs = zero_start_index_M.reshape(B, M).to(torch.int64).contiguous()
+    ub = None
+    if scale_ub is not None:
+        ub = scale_ub if scale_ub.dtype == torch.float32 else scale_ub.to(torch.float32)
+    eps = 1e-12 if eps_opt is None else float(eps_opt)
+    q = torch.empty(out_shape, dtype=FP8_DTYPE, device=dev)
+    s = torch.empty(out_shape[:-1], dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_quantize_fp8_row(
+            _ptr(a4), _DTYPE_CODE[a.dtype], B, M, N, K, K_out,
+            a4.stride(0), a4.stride(1), a4.stride(2), a4.stride(3),
+            _ptr(ub), _ptr(zs), eps, _ptr(q), _ptr(s), _stream(dev)), "quantize_fp8_row")
+    return q, s
+
+
+# --------------------------------------------------------------------------- FP8 rowwise GEMM
+
+def _check_rowwise_args(name, XQ, WQ, x_scale, w_scale):
+    dev = _require_cuda(name, XQ, WQ, x_scale, w_scale)
+    if XQ.dtype != FP8_DTYPE or WQ.dtype != FP8_DTYPE:
+        raise RuntimeError(f"{name}: XQ and WQ must be float8_e4m3fn")
+    if not (XQ.is_contiguous() and WQ.is_contiguous()):
+        raise RuntimeError(f"{name}: XQ and WQ must be contiguous")
+    if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32:
+        raise RuntimeError(f"{name}: x_scale and w_scale must be float32")
+    return dev
+
+
+def f8f8bf16_rowwise_out(XQ, WQ, x_scale, w_scale, output, bias=None, use_fast_accum: bool = True) -> None:
+    """``output[M,N] = bf16((XQ @ WQ.T) * x_scale[:,None] * w_scale[None,:] + bias)``.
+    ``use_fast_accum`` is accepted for signature parity and has no effect (as on the
+    reference's sm_100 path)."""
+    dev = _check_rowwise_args("f8f8bf16_rowwise", XQ, WQ, x_scale, w_scale)
+    K = XQ.shape[-1]
+    M = math.prod(XQ.shape[:-1])
+    N = math.prod(WQ.shape[:-1])
+    if WQ.shape[-1] != K:
+        raise RuntimeError(f"f8f8bf16_rowwise: K mismatch ({K} vs {WQ.shape[-1]})")
+    if x_scale.numel() != M or w_scale.numel() != N:
+        raise RuntimeError("f8f8bf16_rowwise: scale sizes must match M and N")
+    if output.dtype != torch.bfloat16 or output.numel() != M * N or not output.is_contiguous():
+        raise RuntimeError("f8f8bf16_rowwise: output must be a contiguous bfloat16 tensor of M*N elements")
+    kind = 0
+    if bias is not None:
+        _require_cuda("f8f8bf16_rowwise", XQ, bias)
+        if bias.dtype == torch.float32:
+            kind = 1
+        elif bias.dtype == torch.bfloat16:
+            kind = 2
+        else:
+            raise RuntimeError("f8f8bf16_rowwise: bias must be float32 or bfloat16")
+        if bias.numel() != N:
+            raise RuntimeError("f8f8bf16_rowwise: bias must have N elements")
+        bias = bias.contiguous()
+    xs, ws = x_scale.contiguous(), w_scale.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f8f8bf16_rowwise(
+            _ptr(XQ), _ptr(WQ), _ptr(xs), _ptr(ws), _ptr(bias), kind, _ptr(output), M, N, K, _stream(dev)),
+            "f8f8bf16_rowwise")
+
+
+def f8f8bf16_rowwise(XQ, WQ, x_scale, w_scale, bias=None, use_fast_accum: bool = True) -> torch.Tensor:
+    dev = _check_rowwise_args("f8f8bf16_rowwise", XQ, WQ, x_scale, w_scale)
+    N = math.prod(WQ.shape[:-1])
+    out = torch.empty((*XQ.shape[:-1], N), dtype=torch.bfloat16, device=dev)
+    f8f8bf16_rowwise_out(XQ, WQ, x_scale, w_scale, out, bias, use_fast_accum)
+    return out
+
+
+def f8f8bf16_rowwise_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes) -> torch.Tensor:
+    """Stacked grouped GEMM: ``XQ [total_M,K]``, ``WQ [G,N,K]``, ``M_sizes`` int64 [G] on the device."""
+    name = "f8f8bf16_rowwise_grouped_stacked"
+    dev = _check_rowwise_args(name, XQ, WQ, x_scale, w_scale)
+    if M_sizes.device != XQ.device:
+        raise RuntimeError(f"{name}: M_sizes must be on same device as inputs.")
+    if M_sizes.dtype != torch.int64:
+        raise RuntimeError(f"{name}: M_sizes must be int64.")
+    if WQ.dim() != 3 or WQ.shape[0] != M_sizes.numel():
+        raise RuntimeError(f"{name}: WQ must be [G,N,K] with G == M_sizes.numel()")
+    if XQ.dim() != 2 or XQ.shape[1] != WQ.shape[2]:
+        raise RuntimeError(f"{name}: XQ must be [total_M,K] with the K of WQ")
+    G, N, K = WQ.shape
+    total_M = XQ.shape[0]
+    if x_scale.numel() != total_M or w_scale.numel() != G * N:
+        raise RuntimeError(f"{name}: scale sizes must match total_M and G*N")
+    y = torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
+    if total_M == 0:
+        return y
+    xs, ws, ms = x_scale.contiguous(), w_scale.contiguous(), M_sizes.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked(
+            _ptr(XQ), _ptr(WQ), _ptr(xs), _ptr(ws), _ptr(ms), G, total_M, N, K, _ptr(y), _stream(dev)), name)
+    return y
+
+
+# --------------------------------------------------------------------------- NVFP4
+
+def nvfp4_scale_shape(rows: int, K: int):
+    return ((rows + 127) // 128 * 128, (K // 16 + 3) // 4 * 4)
+
+
+def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
+    """Returns ``(xq uint8 [..., K/2], scales float8_e4m3fn [rows_pad, cols_pad] swizzled)``."""
+    dev = _require_cuda("quantize_nvfp4", x, global_scale)
+    if x.dtype != torch.bfloat16:
+        raise RuntimeError("quantize_nvfp4: input must be bfloat16")
+    lead, K = x.shape[:-2], x.shape[-1]
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    assert K % 16 == 0, "N must be divisible by 16 for NVFP4 quantization"
+    pr, pc = nvfp4_scale_shape(M, K)
+    q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    s = torch.empty((pr, pc), dtype=FP8_DTYPE, device=dev)
+    gs = None
+    if global_scale is not None:
+        gs = global_scale.reshape(-1).to(torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_quantize_nvfp4(_ptr(x2), M, K, x2.stride(0), _ptr(gs), _ptr(q), _ptr(s), _stream(dev)),
+              "quantize_nvfp4")
+    return q.view(*lead, -1, K // 2), s.view(*lead, -1, pc)
+
+
+def f4f4bf16(XQ, WQ, x_scale, w_scale, output=None, global_scale=None, mxfp4_block_size: int = 32) -> torch.Tensor:
+    """NVFP4 GEMM (``global_scale`` given).  The MXFP4 modes of the reference operator
+    (``global_scale=None``) are outside this library's scope and raise."""
+    name = "f4f4bf16"
+    dev = _require_cuda(name, XQ, WQ, x_scale, w_scale, global_scale, output)
+    if global_scale is None:
+        raise RuntimeError(f"{name}: only the NVFP4 mode (global_scale given) is implemented")
+    if not (XQ.is_contiguous() and WQ.is_contiguous() and x_scale.is_contiguous() and w_scale.is_contiguous()):
+        raise RuntimeError(f"{name}: XQ, WQ, x_scale and w_scale must be contiguous")
+    M, K = XQ.shape[0], XQ.shape[1] * 2
+    N = WQ.shape[0]
+    if WQ.shape[1] * 2 != K:
+        raise RuntimeError(f"{name}: K mismatch")
+    if N % 16 != 0 or K % 16 != 0:
+        raise RuntimeError(f"{name}: N and K must be multiples of 16")
+    if output is None:
+        output = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    elif output.dtype != torch.bfloat16 or tuple(output.shape) != (M, N) or not output.is_contiguous():
+        raise RuntimeError(f"{name}: output must be a contiguous bfloat16 [M,N] tensor")
+    if M == 0 or N == 0 or K == 0:
+        return output.zero_()
+    gs = global_scale.reshape(-1).to(torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f4f4bf16(_ptr(XQ), _ptr(WQ), _ptr(x_scale), _ptr(w_scale), _ptr(gs), _ptr(output),
+                                     M, N, K, _stream(dev)), name)
+    return output

@@ -1,0 +1,185 @@
+"""GPU parity tests of the rowwise-scaled FP8 GEMM (dense and grouped/stacked) through the C ABI.
+
+Oracle: the reference tests' fp32 formula (dequantize, fp32 matmul, row x column scales),
+test/gemm/triton/grouped_gemm_test.py:124-129.  Tolerance: rtol 1.6e-2 (same file, :138-150),
+atol 1e-2 on unit-variance data.  Small cases are also checked against the scalar-C oracle.
+"""
+import pytest
+import torch
+
+import oracle
+from helpers import randn_bf16
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1.6e-2, 1e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mslk_b200 import ops as _ops
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return _ops
+
+
+def _status():
+    from mslk_b200._lib import device_status
+    return device_status()
+
+
+def _quant(ops, M, N, K, seed, w_std=0.02):
+    x = randn_bf16((M, K), seed).cuda()
+    w = randn_bf16((N, K), seed + 1, w_std).cuda()
+    xq, xs = ops.quantize_fp8_row(x)
+    wq, ws = ops.quantize_fp8_row(w)
+    return xq, wq, xs, ws
+
+
+def _close(y, y_ref, tag):
+    assert y.shape == y_ref.shape and y.dtype == torch.bfloat16, tag
+    # atol is stated for unit-variance data: scale it with the spread of the output
+    scale = max(1.0, float(y_ref.float().std()))
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=RTOL, atol=ATOL * scale, msg=lambda m: f"{tag}: {m}")
+
+
+SMALL = [(1, 32, 128), (5, 33, 128), (7, 48, 144), (16, 64, 256), (128, 256, 256), (256, 128, 256),
+         (129, 257, 512), (100, 8, 64), (3, 1, 32), (130, 520, 1040)]
+
+
+@pytest.mark.parametrize("M,N,K", SMALL)
+def test_small_shapes_vs_c_oracle(ops, M, N, K):
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=M + N + K, w_std=1.0)
+    y = ops.f8f8bf16_rowwise(xq, wq, xs, ws)
+    y_c = oracle.gemm_f8_rowwise(xq.cpu(), wq.cpu(), xs.cpu(), ws.cpu())
+    _close(y.cpu(), y_c, f"{M}x{N}x{K}")
+    assert _status() == 0
+
+
+LLAMA = [(M, N, K) for M in (1, 16, 128, 2048) for (N, K) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336))]
+
+
+@pytest.mark.parametrize("M,N,K", LLAMA + [(4096, 4096, 4096), (2048, 2048, 4096), (4096, 4096, 8192), (8192, 4096, 4096)])
+def test_model_shapes_vs_fp32_formula(ops, M, N, K):
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=1)
+    y = ops.f8f8bf16_rowwise(xq, wq, xs, ws)
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws)
+    _close(y, y_ref, f"{M}x{N}x{K}")
+    assert _status() == 0
+
+
+@pytest.mark.parametrize("bias_dtype", [torch.float32, torch.bfloat16])
+def test_bias(ops, bias_dtype):
+    M, N, K = 200, 384, 512
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=9, w_std=1.0)
+    bias = (torch.randn(N, device="cuda") * 10).to(bias_dtype)
+    y = ops.f8f8bf16_rowwise(xq, wq, xs, ws, bias=bias)
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws, bias)
+    _close(y, y_ref, f"bias {bias_dtype}")
+    y_c = oracle.gemm_f8_rowwise(xq.cpu(), wq.cpu(), xs.cpu(), ws.cpu(), bias.cpu())
+    _close(y.cpu(), y_c, f"bias {bias_dtype} vs C")
+
+
+def test_3d_input_out_variant_and_fast_accum_flag(ops):
+    B, T, N, K = 3, 50, 256, 256
+    x = randn_bf16((B, T, K), 21).cuda()
+    w = randn_bf16((N, K), 22).cuda()
+    xq, xs = ops.quantize_fp8_row(x)
+    wq, ws = ops.quantize_fp8_row(w)
+    y = ops.f8f8bf16_rowwise(xq, wq, xs, ws, use_fast_accum=False)
+    assert y.shape == (B, T, N)
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws)
+    _close(y, y_ref, "3d")
+    out = torch.full((B * T, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.f8f8bf16_rowwise_out(xq, wq, xs, ws, out)
+    assert torch.equal(out.view(B, T, N), y)
+
+
+def test_empty_dims_and_errors(ops):
+    xq, wq, xs, ws = _quant(ops, 4, 32, 64, seed=2)
+    y = ops.f8f8bf16_rowwise(xq[:0], wq, xs[:0], ws)
+    assert y.shape == (0, 32)
+    # K == 0 gives zeros like the reference
+    y = ops.f8f8bf16_rowwise(xq[:, :0].contiguous(), wq[:, :0].contiguous(), xs, ws)
+    assert y.shape == (4, 32) and (y == 0).all()
+    with pytest.raises(RuntimeError, match="float8_e4m3fn"):
+        ops.f8f8bf16_rowwise(xq.view(torch.uint8), wq, xs, ws)
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ops.f8f8bf16_rowwise(xq[:, :40].contiguous(), wq[:, :40].contiguous(), xs, ws)
+    with pytest.raises(RuntimeError, match="float32"):
+        ops.f8f8bf16_rowwise(xq, wq, xs.half(), ws)
+
+
+def test_linearity_in_scales_full_size(ops):
+    # size-independent property at a BASELINE size: doubling x_scale doubles y exactly (power of two),
+    # and the result matches the fp32 formula on a sampled set of rows
+    M, N, K = 8192, 8192, 8192
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=4)
+    y1 = ops.f8f8bf16_rowwise(xq, wq, xs, ws)
+    y2 = ops.f8f8bf16_rowwise(xq, wq, xs * 2, ws)
+    assert torch.equal(y2.float(), y1.float() * 2)
+    rows = torch.arange(0, M, 61, device="cuda")
+    y_ref = oracle.gemm_f8_rowwise_torch(xq[rows], wq, xs[rows], ws)
+    _close(y1[rows], y_ref, "8192^3 sampled rows")
+    assert _status() == 0
+
+
+def _grouped_case(ops, G, m_sizes, N, K, seed):
+    total = sum(m_sizes)
+    x = randn_bf16((total, K), seed).cuda()
+    w = randn_bf16((G, N, K), seed + 1, 0.02).cuda()
+    xq, xs = ops.quantize_fp8_row(x)
+    wq, ws = ops.quantize_fp8_row(w)
+    ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+    y = ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms)
+    y_ref = oracle.gemm_f8_rowwise_grouped_stacked_torch(xq, wq, xs, ws, m_sizes)
+    _close(y, y_ref, f"G={G} {m_sizes[:6]} N={N} K={K}")
+    return xq, wq, xs, ws, ms, y
+
+
+@pytest.mark.parametrize("G,m_sizes,N,K", [
+    (1, [64], 512, 512),
+    (4, [3, 0, 5, 1], 64, 128),
+    (4, [128, 256, 0, 64], 512, 512),
+    (16, [64 * ((i * 7) % 5) for i in range(16)], 1024, 512),
+    (16, [0, 300, 0, 17, 129, 0, 1, 640, 128, 127, 0, 0, 255, 256, 257, 1000], 768, 640),
+    (64, [((i * 37) % 9) * 16 for i in range(64)], 512, 1024),
+])
+def test_grouped_stacked(ops, G, m_sizes, N, K):
+    xq, wq, xs, ws, ms, y = _grouped_case(ops, G, m_sizes, N, K, seed=G + N)
+    # small cases also against the scalar-C oracle
+    if sum(m_sizes) * N * K < 5e8:
+        y_c = oracle.gemm_f8_rowwise_grouped_stacked(xq.cpu(), wq.cpu(), xs.cpu(), ws.cpu(), m_sizes)
+        _close(y.cpu(), y_c, "grouped vs C")
+    assert _status() == 0
+
+
+def test_grouped_all_empty_and_rows_past_sum_untouched(ops):
+    G, N, K = 4, 64, 128
+    x = randn_bf16((10, K), 1).cuda()
+    w = randn_bf16((G, N, K), 2).cuda()
+    xq, xs = ops.quantize_fp8_row(x)
+    wq, ws = ops.quantize_fp8_row(w)
+    y = ops.f8f8bf16_rowwise_grouped_stacked(xq[:0], wq, xs[:0], ws, torch.zeros(G, dtype=torch.int64, device="cuda"))
+    assert y.shape == (0, N)
+    ms = torch.tensor([2, 0, 3, 0], dtype=torch.int64, device="cuda")
+    y = ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms)
+    y_ref = oracle.gemm_f8_rowwise_grouped_stacked_torch(xq[:5], wq, xs[:5], ws, [2, 0, 3, 0])
+    _close(y[:5], y_ref, "partial")
+    with pytest.raises(RuntimeError, match="int64"):
+        ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms.int())
+    assert _status() == 0
+
+
+def test_grouped_moe_shape_zipf(ops):
+    # the MoE configuration at reduced token count: 16 experts, Zipf(1.2) counts with empty experts
+    E, N, K, tokens = 16, 2048, 5120, 4096
+    g = torch.Generator().manual_seed(0)
+    p = (torch.randperm(E, generator=g).float() + 1) ** -1.2
+    counts = torch.bincount(torch.multinomial(p / p.sum(), tokens, replacement=True, generator=g), minlength=E)
+    low = torch.argsort(p)[:2]
+    counts[torch.argmax(counts)] += counts[low].sum()
+    counts[low] = 0
+    m_sizes = counts.tolist()
+    assert sum(m_sizes) == tokens and m_sizes.count(0) >= 2
+    _grouped_case(ops, E, m_sizes, N, K, seed=3)
+    assert _status() == 0
