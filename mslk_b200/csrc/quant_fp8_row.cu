@@ -10,7 +10,11 @@
 // HBM-bound: 2 bytes read + 1 byte written per bf16 element, so the fast path
 // reads every row exactly once with 16-byte loads, keeps it in registers across
 // the amax reduction, and writes 8-byte (bf16/fp16 input) or 4-byte (fp32 input)
-// packed results.  x/scale is evaluated as q0 = x*r, q = fma(fma(-q0, scale, x), r, q0)
+// packed results.  At most four (eight for very long rows) vectors per thread
+// keep the kernel near 40 registers, so an SM holds 1536+ threads and ~96 KB of
+// loads in flight; the per-element instruction count (about 11, mostly on the
+// integer/logic pipe: unpack, packed |max|, e4m3 conversion) is what bounds it
+// once the loads are covered.  x/scale is evaluated as q0 = x*r, q = fma(fma(-q0, scale, x), r, q0)
 // with r = 1/scale correctly rounded; for operands in the guarded range this is
 // the correctly rounded quotient (three FMA-pipe operations instead of a
 // division sequence).  Rows whose scale falls outside the guarded range use a
@@ -102,16 +106,89 @@ __device__ __forceinline__ RowScale make_row_scale(float amax, float eps, const 
   return rs;
 }
 
+// x / scale, correctly rounded.  Fast form: q0 = x*r; d = q0*scale - x (exact in an FMA);
+// q = q0 - d*r.  Written with d = -(residual) so that x = -0 yields -0 like a division does.
+template <bool kFast>
 __device__ __forceinline__ float divide(float x, const RowScale &rs) {
-  if (rs.fast) {
+  if constexpr (kFast) {
     const float q0 = __fmul_rn(x, rs.rcp);
-    const float e = __fmaf_rn(-q0, rs.scale, x);
-    const float q = __fmaf_rn(e, rs.rcp, q0);
-    // the quotient carries the sign of x (scale > 0); the FMA form loses it only for x = -0
-    return __uint_as_float((__float_as_uint(q) & 0x7fffffffu) | (__float_as_uint(x) & 0x80000000u));
+    const float d = __fmaf_rn(q0, rs.scale, -x);
+    return __fmaf_rn(-d, rs.rcp, q0);
+  } else {
+    return __fdiv_rn(x, rs.scale);
   }
-  return __fdiv_rn(x, rs.scale);
 }
+
+// One 16-byte vector of inputs -> packed e4m3 bytes (2 words for 16-bit inputs, 1 for fp32).
+template <typename T, bool kFast>
+__device__ __forceinline__ void quantize_vec(const uint4 &v, const RowScale &rs, uint32_t (&o)[Elem<T>::kPerVec / 4]) {
+  constexpr int kE = Elem<T>::kPerVec;
+  float f[kE];
+  unpack<T>(v, f);
+#pragma unroll
+  for (int j = 0; j < kE / 4; ++j) {
+    const uint32_t lo = cvt_e4m3x2(divide<kFast>(f[4 * j], rs), divide<kFast>(f[4 * j + 1], rs));
+    const uint32_t hi = cvt_e4m3x2(divide<kFast>(f[4 * j + 2], rs), divide<kFast>(f[4 * j + 3], rs));
+    o[j] = lo | (hi << 16);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_quantized(uint8_t *row, int v, const uint32_t (&o)[Elem<T>::kPerVec / 4]) {
+  if constexpr (Elem<T>::kPerVec == 8) {
+    *reinterpret_cast<uint2 *>(row + static_cast<int64_t>(v) * 8) = make_uint2(o[0], o[1]);
+  } else {
+    *reinterpret_cast<uint32_t *>(row + static_cast<int64_t>(v) * 4) = o[0];
+  }
+}
+
+// Running |max| over 16-byte vectors.  16-bit inputs stay packed (sign bits masked off,
+// then one two-lane max per word); the pair is only widened once at the end.
+template <typename T>
+struct AmaxAcc;
+template <>
+struct AmaxAcc<float> {
+  float m = 0.f;
+  __device__ __forceinline__ void add(const uint4 &v) {
+    m = fmaxf(fmaxf(m, fabsf(__uint_as_float(v.x))), fabsf(__uint_as_float(v.y)));
+    m = fmaxf(fmaxf(m, fabsf(__uint_as_float(v.z))), fabsf(__uint_as_float(v.w)));
+  }
+  __device__ __forceinline__ float get() const { return m; }
+};
+template <>
+struct AmaxAcc<__nv_bfloat16> {
+  uint32_t a = 0, b = 0;
+  static __device__ __forceinline__ uint32_t mx(uint32_t acc, uint32_t w) {
+    const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&acc),
+                                     __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w)));
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
+  __device__ __forceinline__ void add(const uint4 &v) {
+    a = mx(mx(a, v.x), v.z);
+    b = mx(mx(b, v.y), v.w);
+  }
+  __device__ __forceinline__ float get() const {
+    const uint32_t m = mx(a, b);
+    return fmaxf(__uint_as_float(m << 16), __uint_as_float(m & 0xffff0000u));
+  }
+};
+template <>
+struct AmaxAcc<__half> {
+  uint32_t a = 0, b = 0;
+  static __device__ __forceinline__ uint32_t mx(uint32_t acc, uint32_t w) {
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2 *>(&acc), __habs2(*reinterpret_cast<const __half2 *>(&w)));
+    return *reinterpret_cast<const uint32_t *>(&r);
+  }
+  __device__ __forceinline__ void add(const uint4 &v) {
+    a = mx(mx(a, v.x), v.z);
+    b = mx(mx(b, v.y), v.w);
+  }
+  __device__ __forceinline__ float get() const {
+    const uint32_t m = mx(a, b);
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&m));
+    return fmaxf(f.x, f.y);
+  }
+};
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -129,9 +206,14 @@ struct QuantParams {
   int64_t M, N, K, K_out;
   int64_t sb, sm, sn, sk;     // element strides of x
   float eps;
+  int uniform_pitch;          // rows are sn elements apart throughout: base = r * sn, no index split needed
 };
 
 __device__ __forceinline__ int64_t row_base(const QuantParams &p, int64_t r, bool &empty) {
+  if (p.uniform_pitch && p.zero_start == nullptr) {
+    empty = false;
+    return r * p.sn;
+  }
   const int64_t mn = p.M * p.N;
   const int64_t b = r / mn, rem = r - b * mn;
   const int64_t m = rem / p.N, n = rem - m * p.N;
@@ -166,7 +248,6 @@ __global__ void __launch_bounds__(kBlock) quant_fp8_row_vec_kernel(const QuantPa
   const T *xr = static_cast<const T *>(p.x) + base;
 
   uint4 v[kVecs];
-  float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < kVecs; ++i) {
     const int vi = t_in_row + i * kThreadsPerRow;
@@ -176,14 +257,10 @@ __global__ void __launch_bounds__(kBlock) quant_fp8_row_vec_kernel(const QuantPa
       v[i] = make_uint4(0, 0, 0, 0);
     }
   }
+  AmaxAcc<T> acc;
 #pragma unroll
-  for (int i = 0; i < kVecs; ++i) {
-    float f[kE];
-    unpack<T>(v[i], f);
-#pragma unroll
-    for (int j = 0; j < kE; ++j) amax = fmaxf(amax, fabsf(f[j]));
-  }
-  amax = warp_max(amax);
+  for (int i = 0; i < kVecs; ++i) acc.add(v[i]);
+  float amax = warp_max(acc.get());
   if constexpr (kWarpsPerRow > 1) {
     const int warp = tid / 32;
     if ((tid & 31) == 0) s_part[warp] = amax;
@@ -200,23 +277,24 @@ __global__ void __launch_bounds__(kBlock) quant_fp8_row_vec_kernel(const QuantPa
   if (t_in_row == 0) p.scale[r] = rs.scale;
 
   uint8_t *qr = p.q + r * p.K_out;
+  if (rs.fast) {
 #pragma unroll
-  for (int i = 0; i < kVecs; ++i) {
-    const int vi = t_in_row + i * kThreadsPerRow;
-    if (vi < nvec_out) {
-      float f[kE];
-      unpack<T>(v[i], f);
-      uint32_t o[kE / 4];
-#pragma unroll
-      for (int j = 0; j < kE / 4; ++j) {
-        const uint32_t lo = cvt_e4m3x2(divide(f[4 * j], rs), divide(f[4 * j + 1], rs));
-        const uint32_t hi = cvt_e4m3x2(divide(f[4 * j + 2], rs), divide(f[4 * j + 3], rs));
-        o[j] = lo | (hi << 16);
+    for (int i = 0; i < kVecs; ++i) {
+      const int vi = t_in_row + i * kThreadsPerRow;
+      if (vi < nvec_out) {
+        uint32_t o[kE / 4];
+        quantize_vec<T, true>(v[i], rs, o);
+        store_quantized<T>(qr, vi, o);
       }
-      if constexpr (kE == 8) {
-        *reinterpret_cast<uint2 *>(qr + static_cast<int64_t>(vi) * 8) = make_uint2(o[0], o[1]);
-      } else {
-        *reinterpret_cast<uint32_t *>(qr + static_cast<int64_t>(vi) * 4) = o[0];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < kVecs; ++i) {
+      const int vi = t_in_row + i * kThreadsPerRow;
+      if (vi < nvec_out) {
+        uint32_t o[kE / 4];
+        quantize_vec<T, false>(v[i], rs, o);
+        store_quantized<T>(qr, vi, o);
       }
     }
   }
@@ -263,7 +341,7 @@ __global__ void __launch_bounds__(kBlock) quant_fp8_row_generic_kernel(const Qua
     uint8_t *qr = p.q + r * p.K_out;
     for (int64_t k = threadIdx.x; k < p.K_out; k += kBlock) {
       const float x = k < k_in ? load_as_float<T>(xr + k * p.sk) : 0.f;
-      qr[k] = static_cast<uint8_t>(cvt_e4m3x2(divide(x, rs), 0.f) & 0xffu);
+      qr[k] = static_cast<uint8_t>(cvt_e4m3x2(divide<false>(x, rs), 0.f) & 0xffu);
     }
   }
 }
@@ -282,15 +360,15 @@ int launch_typed(const QuantParams &p, bool vec_ok, cudaStream_t st) {
   constexpr int kE = Elem<T>::kPerVec;
   if (vec_ok) {
     const int64_t nvec = p.K_out / kE;
-    // one warp per row while a lane holds at most 16 vectors, else one block per row
+    // at most four 16-byte vectors per thread keeps the register count low enough for full
+    // occupancy; longer rows get more threads per row (partial maxima meet in shared memory)
     if (nvec <= 32 * 1) return launch_vec<T, 1, 32, 256>(p, st);
     if (nvec <= 32 * 2) return launch_vec<T, 2, 32, 256>(p, st);
     if (nvec <= 32 * 4) return launch_vec<T, 4, 32, 256>(p, st);
-    if (nvec <= 32 * 8) return launch_vec<T, 8, 32, 256>(p, st);
-    if (nvec <= 32 * 16 && p.rows >= 1024) return launch_vec<T, 16, 32, 128>(p, st);
-    if (nvec <= 256 * 2) return launch_vec<T, 2, 256, 256>(p, st);
+    if (nvec <= 64 * 4) return launch_vec<T, 4, 64, 256>(p, st);
+    if (nvec <= 128 * 4) return launch_vec<T, 4, 128, 256>(p, st);
     if (nvec <= 256 * 4) return launch_vec<T, 4, 256, 256>(p, st);
-    if (nvec <= 256 * 8) return launch_vec<T, 8, 256, 256>(p, st);
+    if (nvec <= 512 * 4) return launch_vec<T, 4, 512, 512>(p, st);
     if (nvec <= 512 * 8) return launch_vec<T, 8, 512, 512>(p, st);
   }
   const int64_t blocks = p.rows < 148 * 16 ? p.rows : 148 * 16;
@@ -329,6 +407,7 @@ MSLK_API int mslk_b200_quantize_fp8_row(const void *x, int dtype, int64_t B, int
   p.sn = sn;
   p.sk = sk;
   p.eps = eps;
+  p.uniform_pitch = ((M == 1 || sm == N * sn) && (B == 1 || sb == M * N * sn)) ? 1 : 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int esz = dtype == MSLK_B200_F32 ? 4 : 2;
   const int per_vec = 16 / esz;
