@@ -1,0 +1,152 @@
+// Definitions shared by the 1-CTA and 2-CTA rowwise FP8 GEMM kernels: launch
+// parameters, the device-side tile scheduler over per-group row counts, and the
+// scale/bias/convert/store step of the epilogue.
+#pragma once
+
+#include "../../include/mslk_b200.h"
+#include "common.cuh"
+#include "host.h"
+
+namespace mslk_b200 {
+namespace gemm_f8 {
+
+constexpr int kBM = 128;          // rows of the output tile (UMMA M)
+constexpr int kBK = 128;          // bytes (= fp8 elements) of K per pipeline stage
+constexpr int kUmmaK = 32;        // K per tcgen05.mma for 8-bit operands
+constexpr int kMaxGroups = 1024;
+constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueThreads = 128;
+constexpr int kBandM = 16;        // row blocks per scheduling band
+
+struct GemmParams {
+  const float *x_scale;
+  const float *w_scale;
+  const void *bias;
+  __nv_bfloat16 *y;
+  const int64_t *m_sizes;  // device, [G]; nullptr = dense (one group of total_m rows)
+  int *status;
+  int bias_kind;
+  int G;
+  int total_m;
+  int N;
+  int K;
+};
+
+// Builds the per-group prefix tables (first stacked row and first linear tile of every
+// group) in shared memory; executed by one full warp.  Row counts come from device memory
+// (m_sizes) and are clamped so that the stacked rows never run past total_m.  `tile_rows`
+// is the row extent of one scheduled tile (128 for the 1-CTA kernel, 256 for a CTA pair).
+__device__ __forceinline__ void build_group_tables(const GemmParams &p, int n_tiles, int tile_rows, int lane,
+                                                   int *row_start, int *tile_start) {
+  int row_carry = 0, tile_carry = 0;
+  for (int base = 0; base < p.G; base += 32) {
+    const int g = base + lane;
+    long long mg = 0;
+    if (g < p.G) mg = p.m_sizes ? p.m_sizes[g] : p.total_m;
+    if (mg < 0) mg = 0;
+    if (mg > p.total_m) mg = p.total_m;
+    int rows = static_cast<int>(mg);
+    int rsum = rows;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, rsum, o);
+      if (lane >= o) rsum += v;
+    }
+    int start = row_carry + rsum - rows;
+    if (start > p.total_m) start = p.total_m;
+    if (start + rows > p.total_m) rows = p.total_m - start;
+    int tiles = ((rows + tile_rows - 1) / tile_rows) * n_tiles;
+    int tsum = tiles;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, tsum, o);
+      if (lane >= o) tsum += v;
+    }
+    if (g < p.G) {
+      row_start[g] = start;
+      tile_start[g] = tile_carry + tsum - tiles;
+    }
+    row_carry = min(p.total_m, row_carry + __shfl_sync(0xffffffffu, rsum, 31));
+    tile_carry += __shfl_sync(0xffffffffu, tsum, 31);
+  }
+  if (lane == 0) {
+    row_start[p.G] = row_carry;
+    tile_start[p.G] = tile_carry;
+  }
+}
+
+struct Tile {
+  int row0;   // first row of the tile in the stacked X / Y
+  int rows;   // valid rows of the scheduled tile (1..tile_rows)
+  int n0;     // first output column
+  int wrow0;  // first row in WQ viewed as [G*N, K]
+  int ws0;    // first index into w_scale
+};
+
+struct Scheduler {
+  const int *tile_start;
+  const int *row_start;
+  int G, N, n_tiles, bn;
+  int tile_rows;  // rows of one scheduled tile: 128 (single CTA) or 256 (CTA pair)
+  int band_m;     // row blocks per band
+  int g;
+
+  __device__ __forceinline__ bool get(int tile, Tile &t) {
+    if (tile >= tile_start[G]) return false;
+    while (tile >= tile_start[g + 1]) ++g;
+    const int local = tile - tile_start[g];
+    const int mg = row_start[g + 1] - row_start[g];
+    const int m_tiles = (mg + tile_rows - 1) / tile_rows;
+    const int per_band = band_m * n_tiles;
+    const int band = local / per_band;
+    const int in_band = local - band * per_band;
+    const int first_m = band * band_m;
+    const int this_band_m = min(m_tiles - first_m, band_m);
+    const int n_tile = in_band / this_band_m;
+    const int m_tile = first_m + (in_band - n_tile * this_band_m);
+    t.row0 = row_start[g] + m_tile * tile_rows;
+    t.rows = min(tile_rows, mg - m_tile * tile_rows);
+    t.n0 = n_tile * bn;
+    t.wrow0 = g * N + t.n0;
+    t.ws0 = g * N + t.n0;
+    return true;
+  }
+};
+
+template <int BN, int BIAS>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float xs, const float *ws, const float *bs,
+                                               __nv_bfloat16 *dst, bool row_ok, int cols_left, bool vec_ok) {
+  uint32_t packed[16];
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    float v0 = (__uint_as_float(acc[j]) * xs) * ws[j];
+    float v1 = (__uint_as_float(acc[j + 1]) * xs) * ws[j + 1];
+    if constexpr (BIAS == MSLK_B200_BIAS_F32) {
+      v0 += bs[j];
+      v1 += bs[j + 1];
+    } else if constexpr (BIAS == MSLK_B200_BIAS_BF16) {
+      // the scaled product is rounded to bf16 first and the add is done in bf16
+      v0 = __bfloat162float(__float2bfloat16_rn(v0)) + bs[j];
+      v1 = __bfloat162float(__float2bfloat16_rn(v1)) + bs[j + 1];
+    }
+    packed[j / 2] = pack_bf16x2(v0, v1);
+  }
+  if (!row_ok) return;
+  if (vec_ok && cols_left >= 32) {
+    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) d4[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+  } else {
+    const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
+    uint16_t *d = reinterpret_cast<uint16_t *>(dst);
+    for (int j = 0; j < 32 && j < cols_left; ++j) d[j] = h[j];
+  }
+}
+
+// Host side: the 2-CTA (cta_group::2) launcher lives in gemm_f8_rowwise_2cta.cu.
+// Returns 0 on success, a non-zero code after recording an error, or -1 when the shape or
+// the device cannot use CTA pairs (the caller then takes the 1-CTA kernel).
+int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cudaStream_t st);
+
+}  // namespace gemm_f8
+}  // namespace mslk_b200

@@ -26,34 +26,13 @@
 //
 // Every pipeline wait is bounded (see common.cuh); on expiry the CTA records a
 // status code, drains, frees its tensor memory and returns.
-#include "../../include/mslk_b200.h"
-#include "common.cuh"
-#include "host.h"
+#include "gemm_f8_common.cuh"
+
+#include <cstdlib>
 
 namespace mslk_b200 {
+namespace gemm_f8 {
 namespace {
-
-constexpr int kBM = 128;          // rows of the output tile (UMMA M)
-constexpr int kBK = 128;          // bytes (= fp8 elements) of K per pipeline stage
-constexpr int kUmmaK = 32;        // K per tcgen05.mma for 8-bit operands
-constexpr int kMaxGroups = 1024;
-constexpr int kNumThreads = 192;
-constexpr int kNumEpilogueThreads = 128;
-constexpr int kBandM = 16;        // row blocks per scheduling band
-
-struct GemmParams {
-  const float *x_scale;
-  const float *w_scale;
-  const void *bias;
-  __nv_bfloat16 *y;
-  const int64_t *m_sizes;  // device, [G]; nullptr = dense (one group of total_m rows)
-  int *status;
-  int bias_kind;
-  int G;
-  int total_m;
-  int N;
-  int K;
-};
 
 template <int BN>
 struct Config {
@@ -87,72 +66,6 @@ struct SmemTail {
 template <int BN>
 constexpr size_t smem_bytes() {
   return 1024 + static_cast<size_t>(Config<BN>::kStages) * Config<BN>::kStageBytes + sizeof(SmemTail<BN>);
-}
-
-struct Tile {
-  int row0;   // first row of the tile in the stacked X / Y
-  int rows;   // valid rows (1..128)
-  int n0;     // first output column
-  int wrow0;  // first row in WQ viewed as [G*N, K]
-  int ws0;    // first index into w_scale
-};
-
-struct Scheduler {
-  const int *tile_start;
-  const int *row_start;
-  int G, N, n_tiles, bn;
-  int g;
-
-  __device__ __forceinline__ bool get(int tile, Tile &t) {
-    if (tile >= tile_start[G]) return false;
-    while (tile >= tile_start[g + 1]) ++g;
-    const int local = tile - tile_start[g];
-    const int mg = row_start[g + 1] - row_start[g];
-    const int m_tiles = (mg + kBM - 1) / kBM;
-    const int per_band = kBandM * n_tiles;
-    const int band = local / per_band;
-    const int in_band = local - band * per_band;
-    const int first_m = band * kBandM;
-    const int band_m = min(m_tiles - first_m, kBandM);
-    const int n_tile = in_band / band_m;
-    const int m_tile = first_m + (in_band - n_tile * band_m);
-    t.row0 = row_start[g] + m_tile * kBM;
-    t.rows = min(kBM, mg - m_tile * kBM);
-    t.n0 = n_tile * bn;
-    t.wrow0 = g * N + t.n0;
-    t.ws0 = g * N + t.n0;
-    return true;
-  }
-};
-
-template <int BN, int BIAS>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float xs, const float *ws, const float *bs,
-                                               __nv_bfloat16 *dst, bool row_ok, int cols_left, bool vec_ok) {
-  uint32_t packed[16];
-#pragma unroll
-  for (int j = 0; j < 32; j += 2) {
-    float v0 = (__uint_as_float(acc[j]) * xs) * ws[j];
-    float v1 = (__uint_as_float(acc[j + 1]) * xs) * ws[j + 1];
-    if constexpr (BIAS == MSLK_B200_BIAS_F32) {
-      v0 += bs[j];
-      v1 += bs[j + 1];
-    } else if constexpr (BIAS == MSLK_B200_BIAS_BF16) {
-      // the scaled product is rounded to bf16 first and the add is done in bf16
-      v0 = __bfloat162float(__float2bfloat16_rn(v0)) + bs[j];
-      v1 = __bfloat162float(__float2bfloat16_rn(v1)) + bs[j + 1];
-    }
-    packed[j / 2] = pack_bf16x2(v0, v1);
-  }
-  if (!row_ok) return;
-  if (vec_ok && cols_left >= 32) {
-    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) d4[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-  } else {
-    const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
-    uint16_t *d = reinterpret_cast<uint16_t *>(dst);
-    for (int j = 0; j < 32 && j < cols_left; ++j) d[j] = h[j];
-  }
 }
 
 template <int BN>
@@ -190,51 +103,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tmem_alloc(&S.tmem_base, Cfg::kTmemCols);
     tmem_relinquish();
   }
-  if (warp == 2) {
-    // prefix tables over the groups: rows (clamped to the tensor) and tiles
-    int row_carry = 0, tile_carry = 0;
-    for (int base = 0; base < p.G; base += 32) {
-      const int g = base + lane;
-      long long mg = 0;
-      if (g < p.G) mg = p.m_sizes ? p.m_sizes[g] : p.total_m;
-      if (mg < 0) mg = 0;
-      if (mg > p.total_m) mg = p.total_m;
-      int rows = static_cast<int>(mg);
-      int rsum = rows;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, rsum, o);
-        if (lane >= o) rsum += v;
-      }
-      // clamp so that the stacked rows never run past total_m
-      int start = row_carry + rsum - rows;
-      if (start > p.total_m) start = p.total_m;
-      if (start + rows > p.total_m) rows = p.total_m - start;
-      int tiles = ((rows + kBM - 1) / kBM) * n_tiles;
-      int tsum = tiles;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, tsum, o);
-        if (lane >= o) tsum += v;
-      }
-      if (g < p.G) {
-        S.row_start[g] = start;
-        S.tile_start[g] = tile_carry + tsum - tiles;
-      }
-      row_carry = min(p.total_m, row_carry + __shfl_sync(0xffffffffu, rsum, 31));
-      tile_carry += __shfl_sync(0xffffffffu, tsum, 31);
-    }
-    if (lane == 0) {
-      S.row_start[p.G] = row_carry;
-      S.tile_start[p.G] = tile_carry;
-    }
-  }
+  if (warp == 2) build_group_tables(p, n_tiles, kBM, lane, S.row_start, S.tile_start);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
 
-  Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, 0};
+  Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, kBM, kBandM, 0};
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -448,6 +323,18 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
 
+  // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs
+  static const int force = [] {
+    const char *e = getenv("MSLK_B200_GEMM_KERNEL");  // "1cta" | "2cta": tuning aid, default = heuristic
+    return !e ? 0 : (e[0] == '2' ? 2 : 1);
+  }();
+  const int64_t pair_tiles = ((total_m + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
+  const bool want_pair = force == 2 || (force == 0 && !m_sizes && bn == 256 && pair_tiles >= sms / 2);
+  if (want_pair) {
+    const int rc = launch_pair_kernel(xq, wq, p, st);
+    if (rc >= 0) return rc;  // -1: pairs unavailable on this device, fall through to one CTA per tile
+  }
+
   CUtensorMap ta, tb;
   if (int rc = make_tmap_2d_bytes(&ta, xq, K, total_m, K, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d_bytes(&tb, wq, K, G * N, K, kBK, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
@@ -463,12 +350,14 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
 }
 
 }  // namespace
+}  // namespace gemm_f8
 }  // namespace mslk_b200
 
 MSLK_API int mslk_b200_f8f8bf16_rowwise(const void *xq, const void *wq, const float *x_scale, const float *w_scale,
                                         const void *bias, int bias_kind, void *y, int64_t M, int64_t N, int64_t K,
                                         void *stream) {
   using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
   clear_error();
   if (bias_kind < 0 || bias_kind > 2) return fail(1, "f8f8bf16_rowwise: bad bias_kind %d", bias_kind);
   return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, 1, M, N, K, static_cast<cudaStream_t>(stream),
@@ -480,6 +369,7 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_grouped_stacked(const void *xq, const vo
                                                         int64_t total_M, int64_t N, int64_t K, void *y,
                                                         void *stream) {
   using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
   clear_error();
   if (!M_sizes) return fail(1, "f8f8bf16_rowwise_grouped_stacked: M_sizes is null");
   return run(xq, wq, x_scale, w_scale, nullptr, MSLK_B200_BIAS_NONE, y, M_sizes, G, total_M, N, K,

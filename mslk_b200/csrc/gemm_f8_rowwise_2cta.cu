@@ -1,0 +1,293 @@
+// Rowwise-scaled FP8 GEMM on CTA pairs (tcgen05 cta_group::2) for sm_100a.
+//
+// Two CTAs on neighbouring SMs (a cluster of 2) compute one 256 x 256 output tile.
+// Each CTA TMA-loads only its own operand slices -- its 128 rows of A and its 128 of
+// the 256 rows of B -- so per SM the ring holds {A 128x128, B 128x128} = 32 KB per
+// K-block instead of 48 KB, and the tensor core reads 8 KB instead of 12 KB of shared
+// memory per instruction.  No load is multicast.
+//
+//   CTA rank 0 ("leader")                      CTA rank 1
+//   warp 0  producer: waits its own empty[s], TMA -> own smem, bytes counted on the
+//           LEADER's full[s] (the leader arms it with the bytes of both CTAs)
+//   warp 1  MMA issuer (cta_group::2, 256x256x32)     (idle; takes part in TMEM alloc)
+//           frees stage s in both CTAs with one tcgen05.commit per CTA,
+//           hands the accumulator to both epilogues the same way
+//   warps 2..5 epilogue on the CTA's own 128 accumulator rows; every epilogue warp of
+//           both CTAs arrives on the leader's tmem_empty barrier
+//
+// The tile scheduler, epilogue arithmetic and bounded waits are those of the 1-CTA
+// kernel (gemm_f8_common.cuh, common.cuh).  Cluster-wide hardware barriers are used
+// only at start-up (barriers initialised before the peer touches them) and at
+// teardown (no MMA may still write the peer's tensor memory when it is freed); every
+// control path of both CTAs reaches them.
+#include "gemm_f8_common.cuh"
+
+namespace mslk_b200 {
+namespace gemm_f8 {
+namespace {
+
+constexpr int kPairBN = 256;            // output columns of the pair tile
+constexpr int kPairRows = 2 * kBM;      // output rows of the pair tile
+constexpr int kStageA = kBM * kBK;      // this CTA's rows of A
+constexpr int kStageB = (kPairBN / 2) * kBK;  // this CTA's half of the B rows
+constexpr int kStageBytes = kStageA + kStageB;
+constexpr int kStages = 6;
+constexpr int kTmemCols = 512;          // two 256-column accumulators
+constexpr int kPairBandM = 8;           // 8 x 256 rows per band, matching 16 x 128 of the 1-CTA kernel
+constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kPairBN >> 3) << 17) |
+                            (static_cast<uint32_t>(kPairRows >> 4) << 24);
+
+struct SmemTail {
+  float w_scale[4][kPairBN];
+  float bias[4][kPairBN];
+  int tile_start[kMaxGroups + 1];
+  int row_start[kMaxGroups + 1];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(SmemTail);
+static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+
+__global__ void __launch_bounds__(kNumThreads, 1)
+    gemm_f8_rowwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemTail &S = *reinterpret_cast<SmemTail *>(ring + static_cast<size_t>(kStages) * kStageBytes);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x / 2;
+  const int num_pairs = gridDim.x / 2;
+  const int n_tiles = (p.N + kPairBN - 1) / kPairBN;
+  const int k_blocks = (p.K + kBK - 1) / kBK;
+  volatile int *abort_flag = &S.abort_flag;
+
+  // ------------------------------------------------------------------ setup
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&S.full[s], 1);
+      mbar_init(&S.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&S.tmem_full[a], 1);
+      mbar_init(&S.tmem_empty[a], 2 * (kNumEpilogueThreads / 32));  // epilogue warps of both CTAs
+    }
+    S.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&S.tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (warp == 2) build_group_tables(p, n_tiles, kPairRows, lane, S.row_start, S.tile_start);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything is signalled on them
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, kPairBN, kPairRows, kPairBandM, 0};
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      Tile t;
+      bool ok = true;
+      for (int tile = pair_id; ok && sched.get(tile, t); tile += num_pairs) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t *sa = ring + static_cast<size_t>(stage) * kStageBytes;
+          uint8_t *sb = sa + kStageA;
+          const uint32_t leader_full = mapa_u32(smem_u32(&S.full[stage]), 0);
+          if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * kStageBytes);
+          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBK, t.row0 + static_cast<int>(rank) * kBM);
+          tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBK, t.wrow0 + static_cast<int>(rank) * (kPairBN / 2));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader only)
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      Tile t;
+      for (int tile = pair_id; ok && sched.get(tile, t); tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&S.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairBN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(ring + static_cast<size_t>(stage) * kStageBytes);
+          const uint64_t da = make_kmajor_sw128_desc(sa);
+          const uint64_t db = make_kmajor_sw128_desc(sa + kStageA);
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            mma_f8f6f4_pair(d_tmem, da + static_cast<uint64_t>(k * (kUmmaK >> 4)),
+                            db + static_cast<uint64_t>(k * (kUmmaK >> 4)), kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // free the stage in both CTAs once these MMAs have read it
+          const uint32_t e = smem_u32(&S.empty[stage]);
+          tc_commit_pair(mapa_u32(e, 0));
+          tc_commit_pair(mapa_u32(e, 1));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        const uint32_t f = smem_u32(&S.tmem_full[acc]);
+        tc_commit_pair(mapa_u32(f, 0));
+        tc_commit_pair(mapa_u32(f, 1));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    const int quad = warp & 3;
+    const int row_in_cta = quad * 32 + lane;
+    const int row_in_tile = static_cast<int>(rank) * kBM + row_in_cta;
+    const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+    int local = 0;
+    Tile t;
+    for (int tile = pair_id; sched.get(tile, t); tile += num_pairs, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      float *ws_s = S.w_scale[warp - 2];
+      float *bs_s = S.bias[warp - 2];
+      for (int c = lane; c < kPairBN; c += 32) {
+        const bool in = t.n0 + c < p.N;
+        ws_s[c] = in ? p.w_scale[t.ws0 + c] : 0.f;
+        float b = 0.f;
+        if (in && p.bias_kind == MSLK_B200_BIAS_F32) b = static_cast<const float *>(p.bias)[t.n0 + c];
+        if (in && p.bias_kind == MSLK_B200_BIAS_BF16)
+          b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[t.n0 + c]);
+        bs_s[c] = b;
+      }
+      __syncwarp();
+      const bool row_ok = row_in_tile < t.rows;
+      const float xs = row_ok ? p.x_scale[t.row0 + row_in_tile] : 0.f;
+      const bool got = mbar_wait(&S.tmem_full[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+      const uint32_t taddr =
+          tmem_base + static_cast<uint32_t>(acc * kPairBN) + (static_cast<uint32_t>(quad * 32) << 16);
+      __nv_bfloat16 *yrow = p.y + static_cast<size_t>(t.row0 + row_in_tile) * p.N + t.n0;
+#pragma unroll 1
+      for (int c = 0; c < kPairBN / 32; ++c) {
+        const int cols_left = p.N - (t.n0 + c * 32);
+        if (cols_left <= 0) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const float *ws = ws_s + c * 32;
+        const float *bs = bs_s + c * 32;
+        if (p.bias_kind == MSLK_B200_BIAS_NONE)
+          epilogue_chunk<kPairBN, MSLK_B200_BIAS_NONE>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+        else if (p.bias_kind == MSLK_B200_BIAS_F32)
+          epilogue_chunk<kPairBN, MSLK_B200_BIAS_F32>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+        else
+          epilogue_chunk<kPairBN, MSLK_B200_BIAS_BF16>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty[acc]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory while the pair may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace
+
+int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cudaStream_t st) {
+  static int max_pairs[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return -1;
+
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+
+  if (max_pairs[dev] == 0) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_f8_rowwise_pair_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(kSmemBytes)),
+                            "cudaFuncSetAttribute(gemm_f8_rowwise_pair)"))
+      return rc;
+    // how many CTA pairs the device can hold at once: a persistent kernel must not launch more
+    cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_f8_rowwise_pair_kernel, &cfg);
+    if (e != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      max_pairs[dev] = -1;
+    } else {
+      max_pairs[dev] = n;
+    }
+  }
+  if (max_pairs[dev] < 0) return -1;
+
+  const int64_t tiles_ub = ((static_cast<int64_t>(p.total_m) + kPairRows - 1) / kPairRows + (p.m_sizes ? p.G : 0)) *
+                           ((p.N + kPairBN - 1) / kPairBN);
+  const int pairs = static_cast<int>(tiles_ub < max_pairs[dev] ? tiles_ub : max_pairs[dev]);
+
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d_bytes(&ta, xq, p.K, p.total_m, p.K, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, p.K, static_cast<uint64_t>(p.G) * p.N, p.K, kBK, kPairBN / 2,
+                                  CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel, ta, tb, p), "f8f8bf16_rowwise pair launch");
+}
+
+}  // namespace gemm_f8
+}  // namespace mslk_b200
