@@ -120,6 +120,14 @@ __device__ __forceinline__ void tma_load_2d_hint(void *smem_dst, const CUtensorM
       : "memory");
 }
 
+// 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // 2-D tiled store shared -> global (bulk group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap *m, const void *smem_src, int c0, int c1) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
@@ -276,6 +284,16 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(1) << 46;                          // descriptor version (Blackwell)
   d |= static_cast<uint64_t>(2) << 61;                          // SWIZZLE_128B
   return d;
+}
+
+// Shared-memory descriptor of one 512-byte scale-factor atom (32 rows of 16 bytes, no
+// swizzle: 8-row groups are 128 bytes apart) for tcgen05.cp.
+__device__ __forceinline__ uint64_t make_sf_atom_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;         // descriptor version (Blackwell)
+  return d;                                    // layout type 0 = no swizzle
 }
 
 // named barrier among a subset of warps

@@ -1,9 +1,340 @@
-// NVFP4 GEMM entry point (block-scaled tcgen05 kernel).
+// NVFP4 GEMM for sm_100a:  y = bf16(alpha * sum_blocks (sx * sw) * sum_16 x^ * w^)
+//
+// Operands are packed e2m1 (two per byte, K-major) with one ue4m3 scale per 16
+// K-elements, stored in 512-byte atoms of 128 rows x 4 scales (the layout the
+// quantizer writes).  The block-scaled tensor-core instruction
+// tcgen05.mma.kind::mxf4nvf4.block_scale.scale_vec::4X consumes 128 x BN x 64 per
+// issue: data tiles straight from 128-byte-swizzled shared memory (a TMA box of
+// {128 bytes = 256 elements of K, rows}), scales from tensor memory, where one
+// atom occupies 4 columns (row i + 32 j of the atom sits in lane i, column j, of
+// every 32-lane quadrant).  tcgen05.cp (32x128b, replicated to the four
+// quadrants) moves an atom from shared to tensor memory; it is issued by the MMA
+// thread right before the instruction that uses it and is ordered with it.
+//
+// Pipeline and roles are those of the FP8 kernel (gemm_f8_rowwise.cu): TMA
+// producer warp, single-thread MMA issuer, four epilogue warps, bounded waits.
+// Per stage (256 K-elements): A 16 KB, B BN/128 x 16 KB, scale atoms 2 KB for A
+// and BN/128 x 2 KB for B (plain bulk copies: four consecutive atoms of one
+// 128-row block are contiguous in memory).
+// Tensor memory: BN = 128 keeps two accumulators (epilogue overlaps the next
+// tile); BN = 256 has room for one accumulator beside the scale columns.
 #include "../../include/mslk_b200.h"
 #include "common.cuh"
 #include "host.h"
 
-MSLK_API int mslk_b200_f4f4bf16(const void *, const void *, const void *, const void *, const float *, void *, int64_t,
-                                int64_t, int64_t, void *) {
-  return mslk_b200::fail(3, "f4f4bf16: kernel not built yet");
+namespace mslk_b200 {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBKBytes = 128;        // bytes of packed K per stage row
+constexpr int kBKElems = 256;        // K elements per stage
+constexpr int kMmaKBytes = 32;       // 64 K-elements per instruction
+constexpr int kAtomBytes = 512;      // 128 rows x 4 scales
+constexpr int kNumThreads = 192;
+
+struct Fp4Params {
+  const uint8_t *sfa;   // swizzled scales of A: [ceil(M/128)][ncb] atoms
+  const uint8_t *sfb;   // swizzled scales of B: [ceil(N/128)][ncb] atoms
+  const float *alpha;   // device scalar
+  __nv_bfloat16 *y;
+  int *status;
+  int M, N, K;
+  int ncb;              // scale atoms per 128-row block = ceil(K / 64)
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kNB = BN / 128;                     // 128-row blocks of B per tile
+  static constexpr int kStageA = kBM * kBKBytes;
+  static constexpr int kStageB = BN * kBKBytes;
+  static constexpr int kStageSFA = 4 * kAtomBytes;
+  static constexpr int kStageSFB = kNB * 4 * kAtomBytes;
+  static constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
+  static constexpr int kStages = BN == 128 ? 6 : 4;
+  static constexpr int kAccStages = BN == 128 ? 2 : 1;
+  static constexpr int kSfaCol = kAccStages * BN;          // first TMEM column of the A scales (16 columns)
+  static constexpr int kSfbCol = kSfaCol + 16;             // B scales: 16 * kNB columns
+  static constexpr int kTmemCols = 512;
+  // block-scaled instruction descriptor: e2m1 x e2m1, ue4m3 scales, K-major, dense K = 64
+  static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (0u << 23) |
+                                     (static_cast<uint32_t>(kBM >> 4) << 24);
+};
+
+template <int BN>
+struct SmemTail {
+  uint64_t full[Cfg<BN>::kStages];
+  uint64_t empty[Cfg<BN>::kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int BN>
+constexpr size_t smem_bytes() {
+  return 1024 + static_cast<size_t>(Cfg<BN>::kStages) * Cfg<BN>::kStageBytes + sizeof(SmemTail<BN>);
+}
+
+// tile index -> (row block, column block), bands of 16 row blocks for L2 reuse
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &m_tile, int &n_tile) {
+  constexpr int kBand = 16;
+  const int per_band = kBand * n_tiles;
+  const int band = tile / per_band;
+  const int in_band = tile - band * per_band;
+  const int first_m = band * kBand;
+  const int band_m = min(m_tiles - first_m, kBand);
+  n_tile = in_band / band_m;
+  m_tile = first_m + (in_band - n_tile * band_m);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+    gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const Fp4Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemTail<BN> &S = *reinterpret_cast<SmemTail<BN> *>(ring + static_cast<size_t>(C::kStages) * C::kStageBytes);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int m_tiles = (p.M + kBM - 1) / kBM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int k_blocks = (p.K + kBKElems - 1) / kBKElems;
+  const int n_row_blocks_b = (p.N + 127) / 128;
+  volatile int *abort_flag = &S.abort_flag;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&S.full[s], 1);
+      mbar_init(&S.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&S.tmem_full[a], 1);
+      mbar_init(&S.tmem_empty[a], 4);
+    }
+    S.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        int m_tile, n_tile;
+        tile_coords(tile, m_tiles, n_tiles, m_tile, n_tile);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t *sa = ring + static_cast<size_t>(stage) * C::kStageBytes;
+          uint8_t *sb = sa + C::kStageA;
+          uint8_t *ssfa = sb + C::kStageB;
+          uint8_t *ssfb = ssfa + C::kStageSFA;
+          const int atoms = min(4, p.ncb - 4 * kb);  // scale atoms (64 K-elements each) left in this K block
+          const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
+          int nb_live = 0;  // 128-row blocks of B that exist for this tile
+          for (int b = 0; b < C::kNB; ++b) nb_live += (n_tile * C::kNB + b) < n_row_blocks_b ? 1 : 0;
+          mbar_arrive_expect_tx(&S.full[stage], C::kStageA + C::kStageB + sf_bytes * (1 + nb_live));
+          tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBKBytes, m_tile * kBM);
+          tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBKBytes, n_tile * BN);
+          bulk_load_1d(ssfa, p.sfa + (static_cast<size_t>(m_tile) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
+                       &S.full[stage]);
+          for (int b = 0; b < nb_live; ++b)
+            bulk_load_1d(ssfb + b * 4 * kAtomBytes,
+                         p.sfb + (static_cast<size_t>(n_tile * C::kNB + b) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
+                         &S.full[stage]);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+        const int acc = local % C::kAccStages;
+        const uint32_t acc_phase = (local / C::kAccStages) & 1;
+        if (!mbar_wait(&S.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(ring + static_cast<size_t>(stage) * C::kStageBytes);
+          const uint32_t sb = sa + C::kStageA;
+          const uint32_t ssfa = sb + C::kStageB;
+          const uint32_t ssfb = ssfa + C::kStageSFA;
+          const uint64_t da = make_kmajor_sw128_desc(sa);
+          const uint64_t db = make_kmajor_sw128_desc(sb);
+          const int atoms = min(4, p.ncb - 4 * kb);
+          for (int k = 0; k < atoms; ++k) {
+            const uint32_t sfa_t = tmem_base + C::kSfaCol + 4 * k;
+            const uint32_t sfb_t = tmem_base + C::kSfbCol + 4 * C::kNB * k;
+            tc_cp_32x128b_warpx4(sfa_t, make_sf_atom_desc(ssfa + k * kAtomBytes));
+#pragma unroll
+            for (int b = 0; b < C::kNB; ++b)
+              tc_cp_32x128b_warpx4(sfb_t + 4 * b, make_sf_atom_desc(ssfb + (b * 4 + k) * kAtomBytes));
+            mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                      db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t, sfb_t,
+                      (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&S.empty[stage]);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&S.tmem_full[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+    const float alpha = *p.alpha;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      int m_tile, n_tile;
+      tile_coords(tile, m_tiles, n_tiles, m_tile, n_tile);
+      const int acc = local % C::kAccStages;
+      const uint32_t acc_phase = (local / C::kAccStages) & 1;
+      const int row = m_tile * kBM + row_in_tile;
+      const bool row_ok = row < p.M;
+      const bool got = mbar_wait(&S.tmem_full[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
+      __nv_bfloat16 *yrow = p.y + static_cast<size_t>(row) * p.N + n_tile * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int cols_left = p.N - (n_tile * BN + c * 32);
+        if (cols_left <= 0) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          packed[j / 2] = pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+        if (row_ok) {
+          __nv_bfloat16 *dst = yrow + c * 32;
+          if (y_vec_ok && cols_left >= 32) {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              d4[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+          } else {
+            const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
+            uint16_t *d = reinterpret_cast<uint16_t *>(dst);
+            for (int j = 0; j < 32 && j < cols_left; ++j) d[j] = h[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.tmem_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int BN>
+int launch(const CUtensorMap &ta, const CUtensorMap &tb, const Fp4Params &p, int grid, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  constexpr size_t smem = smem_bytes<BN>();
+  static_assert(smem <= 232448, "shared memory budget exceeded");
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 static_cast<int>(smem)),
+                            "cudaFuncSetAttribute(gemm_nvfp4)"))
+      return rc;
+    attr_set[dev] = true;
+  }
+  gemm_nvfp4_kernel<BN><<<grid, kNumThreads, smem, st>>>(ta, tb, p);
+  return check_cuda(cudaGetLastError(), "f4f4bf16 launch");
+}
+
+}  // namespace
+}  // namespace mslk_b200
+
+MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                const float *global_scale, void *y, int64_t M, int64_t N, int64_t K, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (M < 0 || N < 0 || K < 0) return fail(1, "f4f4bf16: bad shape");
+  if (M == 0 || N == 0) return 0;
+  if (!y) return fail(1, "f4f4bf16: null output pointer");
+  if (K == 0) return check_cuda(cudaMemsetAsync(y, 0, static_cast<size_t>(M) * N * 2, st), "memset");
+  if (!xq || !wq || !x_scale || !w_scale || !global_scale) return fail(1, "f4f4bf16: null pointer argument");
+  if (K % 32 != 0) return fail(1, "f4f4bf16: K (%lld) must be a multiple of 32 (16-byte rows of packed e2m1)", (long long)K);
+  if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(1, "f4f4bf16: dimension too large");
+  if ((reinterpret_cast<uintptr_t>(x_scale) | reinterpret_cast<uintptr_t>(w_scale)) & 15u)
+    return fail(1, "f4f4bf16: scale tensors must be 16-byte aligned");
+  int *status = device_status_ptr();
+  if (!status) return 2;
+
+  Fp4Params p;
+  p.sfa = static_cast<const uint8_t *>(x_scale);
+  p.sfb = static_cast<const uint8_t *>(w_scale);
+  p.alpha = global_scale;
+  p.y = static_cast<__nv_bfloat16 *>(y);
+  p.status = status;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.ncb = static_cast<int>((K + 63) / 64);
+
+  const int sms = sm_count();
+  const int64_t m_tiles = (M + kBM - 1) / kBM;
+  // 256-wide tiles halve the A traffic per flop but hold one accumulator only; use them when
+  // there are enough tiles to fill the device, 128-wide (double-buffered) otherwise
+  const int bn = (m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d_bytes(&ta, xq, K / 2, M, K / 2, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, K / 2, N, K / 2, kBKBytes, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  const int64_t tiles = m_tiles * ((N + bn - 1) / bn);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  return bn == 256 ? launch<256>(ta, tb, p, grid, st) : launch<128>(ta, tb, p, grid, st);
 }

@@ -1,0 +1,27 @@
+"""NVFP4 quantization with the reference's Python symbols
+(``mslk/quantize/triton/fp4_quantize.py:40-43`` re-exporting ``quantize_kernels/nvfp4.py:62-149``)."""
+
+from typing import Optional
+
+import torch
+
+from ... import gemm as _gemm  # noqa: F401  loads the operator library
+from .fp4_utils import _from_blocked, _to_blocked, global_scale_nvfp4  # noqa: F401
+
+
+def triton_quantize_nvfp4(
+    x: torch.Tensor,
+    global_scale: Optional[torch.Tensor],
+    use_e8m0_scale: bool = False,
+    use_precise_math: bool = True,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Quantize a bf16 tensor to NVFP4: packed e2m1 bytes (viewed as float4_e2m1fn_x2) and
+    e4m3 block scales in the 128x4 swizzled layout.  Only the e4m3-scale, precise-math mode of
+    the reference is implemented (its defaults)."""
+    if use_e8m0_scale or not use_precise_math:
+        raise NotImplementedError("only use_e8m0_scale=False, use_precise_math=True is implemented")
+    assert x.shape[-1] % 16 == 0, "N must be divisible by 16 for NVFP4 quantization"
+    xq, scales = torch.ops.mslk.quantize_nvfp4(x, global_scale)
+    if hasattr(torch, "float4_e2m1fn_x2"):
+        xq = xq.view(torch.float4_e2m1fn_x2)
+    return xq, scales

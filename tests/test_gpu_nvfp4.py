@@ -1,0 +1,103 @@
+"""GPU parity tests of the NVFP4 quantizer (bit-exact) and the NVFP4 GEMM (tolerance) through the C ABI."""
+import pytest
+import torch
+
+import oracle
+from helpers import bf16, load_golden, randn_bf16, u8
+from golden.make_golden import NVFP4_CASES
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mslk_b200 import ops as _ops
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return _ops
+
+
+def _status():
+    from mslk_b200._lib import device_status
+    return device_status()
+
+
+def test_quantize_matches_reference_fixtures(ops):
+    # torch reference of the reference's own test and its Triton kernel run on a B200
+    for fname in ("nvfp4_torch_ref.npz", "nvfp4_triton_b200.npz"):
+        gold = load_golden(fname)
+        assert gold is not None, fname
+        for name, shape in NVFP4_CASES:
+            x = bf16(gold[f"{name}.x"]).cuda()
+            gs = torch.from_numpy(gold[f"{name}.gs"]).cuda()
+            q, s = ops.quantize_nvfp4(x, gs)
+            assert torch.equal(q.cpu(), torch.from_numpy(gold[f"{name}.q"])), (fname, name)
+            assert torch.equal(u8(s.cpu()).reshape(-1), torch.from_numpy(gold[f"{name}.s_blocked"]).reshape(-1)), (fname, name)
+    assert _status() == 0
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (4000, 4096), (4096, 4080), (4000, 4080), (1, 8192), (32, 8192),
+                                   (250, 3584), (128, 16)])
+@pytest.mark.parametrize("use_gs", [True, False])
+def test_quantize_bit_exact_vs_oracle(ops, shape, use_gs):
+    x = randn_bf16(shape, 5)
+    gs = oracle.global_scale_nvfp4(x) if use_gs else None
+    q_ref, s_ref = oracle.quantize_nvfp4(x, gs)
+    q, s = ops.quantize_nvfp4(x.cuda(), None if gs is None else gs.cuda())
+    assert torch.equal(q.cpu(), q_ref)
+    assert torch.equal(u8(s.cpu()), u8(s_ref))
+
+
+def _gemm_case(ops, M, N, K, seed=0):
+    x = randn_bf16((M, K), seed).cuda()
+    w = randn_bf16((N, K), seed + 1).cuda()
+    gx = (448.0 * 6.0) / x.abs().amax().float()
+    gw = (448.0 * 6.0) / w.abs().amax().float()
+    xq, sx = ops.quantize_nvfp4(x, gx)
+    wq, sw = ops.quantize_nvfp4(w, gw)
+    alpha = (1.0 / (gx * gw)).reshape(1)
+    y = ops.f4f4bf16(xq, wq, sx, sw, global_scale=alpha)
+    return x, w, xq, wq, sx, sw, alpha, y
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 64), (1, 256, 2048), (250, 512, 2048),
+                                   (250, 1024, 3584), (130, 144, 320), (512, 2048, 1024), (32, 4096, 8192),
+                                   (300, 272, 96)])
+def test_gemm_vs_fp32_dequant_formula(ops, M, N, K):
+    x, w, xq, wq, sx, sw, alpha, y = _gemm_case(ops, M, N, K)
+    y_ref = oracle.gemm_nvfp4_torch(xq, wq, sx, sw, alpha)
+    scale = max(1.0, float(y_ref.float().std()))
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=1.6e-2, atol=1e-2 * scale)
+    # sanity against the unquantized product (4-bit error: norm bound only; the reference's own
+    # end-to-end tolerance test with its data scales is in test_gpu_torch_ops.py)
+    y_full = x.float() @ w.float().T
+    assert (y.float() - y_full).norm() / y_full.norm() < 0.2
+    assert _status() == 0
+
+
+def test_gemm_small_vs_c_oracle(ops):
+    x, w, xq, wq, sx, sw, alpha, y = _gemm_case(ops, 40, 48, 128, seed=3)
+    y_c = oracle.gemm_nvfp4(xq.cpu(), wq.cpu(), sx.cpu(), sw.cpu(), alpha.cpu())
+    torch.testing.assert_close(y.cpu().float(), y_c.float(), rtol=1.6e-2, atol=1e-2 * max(1.0, float(y_c.float().std())))
+
+
+def test_gemm_large_tiles_and_output_arg(ops):
+    # enough 256-wide tiles to take the single-accumulator configuration
+    M, N, K = 8192, 8192, 1024
+    x, w, xq, wq, sx, sw, alpha, y = _gemm_case(ops, M, N, K, seed=7)
+    rows = torch.arange(0, M, 97, device="cuda")
+    y_ref = oracle.gemm_nvfp4_torch(xq[rows], wq, _rows_of_scales(sx, rows, K), sw, alpha)
+    torch.testing.assert_close(y[rows].float(), y_ref.float(), rtol=1.6e-2, atol=1e-2 * float(y_ref.float().std()))
+    out = torch.empty_like(y)
+    y2 = ops.f4f4bf16(xq, wq, sx, sw, output=out, global_scale=alpha)
+    assert y2.data_ptr() == out.data_ptr() and torch.equal(out, y)
+    with pytest.raises(RuntimeError, match="NVFP4"):
+        ops.f4f4bf16(xq, wq, sx, sw)
+    assert _status() == 0
+
+
+def _rows_of_scales(s_blocked, rows, K):
+    """Blocked scales of a row subset (un-swizzle, pick rows, swizzle again)."""
+    M = s_blocked.shape[0]
+    plain = oracle.from_blocked(u8(s_blocked.cpu()).reshape(-1), M, K // 16)
+    sub = plain[rows.cpu()]
+    return oracle.to_blocked(sub).view(torch.float8_e4m3fn).cuda()
