@@ -78,6 +78,23 @@ int mslk_b200_f8f8bf16_rowwise(const void *xq, const void *wq, const float *x_sc
                                int64_t M, int64_t N, int64_t K, void *stream);
 
 /*
+ * Same operation with caller-provided scratch memory.  For few-token shapes (M <= 32) the
+ * kernel streams the weights with the K dimension split over several CTAs; the partial sums
+ * and their completion tickets live in `workspace`.  mslk_b200_f8f8bf16_rowwise_workspace_bytes
+ * returns the size that enables the split for a shape (0 = no scratch is used).  A null or too
+ * small workspace is legal: the kernel then runs unsplit.  The workspace needs no
+ * initialisation and may be reused by later calls on the same stream; calls that may overlap
+ * on the GPU need separate workspaces.
+ * Replaces: the workspace the reference allocates inside its op,
+ *           csrc/gemm/cutlass/f8f8bf16_rowwise/f8f8bf16_rowwise_common.cuh:316-334.
+ */
+size_t mslk_b200_f8f8bf16_rowwise_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int mslk_b200_f8f8bf16_rowwise_ws(const void *xq, const void *wq, const float *x_scale,
+                                  const float *w_scale, const void *bias, int bias_kind, void *y,
+                                  int64_t M, int64_t N, int64_t K, void *workspace,
+                                  size_t workspace_bytes, void *stream);
+
+/*
  * Grouped (stacked) rowwise FP8 GEMM for MoE experts.
  * Replaces: csrc/gemm/cutlass/f8f8bf16_rowwise_grouped.cu:342-368
  *           (f8f8bf16_rowwise_grouped_stacked) with its argument-setup kernel and

@@ -148,5 +148,15 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float 
 // the device cannot use CTA pairs (the caller then takes the 1-CTA kernel).
 int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cudaStream_t st);
 
+// Host side: the few-token (M <= 32) weight-streaming kernel lives in gemm_f8_rowwise_decode.cu.
+// (The kernel itself handles up to 128 tokens, but beyond 32 the split-K traffic and its serial
+// tail cost more than the small-BN tiles of the general kernel; measured on the Llama-3-8B shapes.)
+// `scratch` (may be null) enables K splitting; its required size comes from decode_scratch_bytes().
+// `scratch_is_clean`: the ticket words are known to be zero (skips the memset).
+constexpr int kDecodeMaxTokens = 32;
+size_t decode_scratch_bytes(int64_t M, int64_t N, int64_t K, int sms);
+int launch_decode_kernel(const void *xq, const void *wq, const GemmParams &p, void *scratch, size_t scratch_bytes,
+                         bool scratch_is_clean, cudaStream_t st);
+
 }  // namespace gemm_f8
 }  // namespace mslk_b200

@@ -286,8 +286,8 @@ int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, in
 }
 
 int run(const void *xq, const void *wq, const float *xs, const float *ws, const void *bias, int bias_kind, void *y,
-        const int64_t *m_sizes, int64_t G, int64_t total_m, int64_t N, int64_t K, cudaStream_t st,
-        const char *name) {
+        const int64_t *m_sizes, int64_t G, int64_t total_m, int64_t N, int64_t K, void *scratch, size_t scratch_bytes,
+        cudaStream_t st, const char *name) {
   if (total_m < 0 || N < 0 || K < 0 || G < 1) return fail(1, "%s: bad shape", name);
   if (total_m == 0 || N == 0) return 0;
   if (G > kMaxGroups) return fail(1, "%s: at most %d groups are supported (got %lld)", name, kMaxGroups, (long long)G);
@@ -322,6 +322,10 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   p.total_m = static_cast<int>(total_m);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
+
+  // few tokens: weight-streaming kernel (operands swapped, optional K split through `scratch`)
+  if (!m_sizes && total_m <= kDecodeMaxTokens && N >= 128)
+    return launch_decode_kernel(xq, wq, p, scratch, scratch_bytes, false, st);
 
   // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs
   static const int force = [] {
@@ -360,8 +364,28 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise(const void *xq, const void *wq, const fl
   using namespace mslk_b200::gemm_f8;
   clear_error();
   if (bias_kind < 0 || bias_kind > 2) return fail(1, "f8f8bf16_rowwise: bad bias_kind %d", bias_kind);
-  return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, 1, M, N, K, static_cast<cudaStream_t>(stream),
-             "f8f8bf16_rowwise");
+  return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, 1, M, N, K, nullptr, 0,
+             static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise");
+}
+
+MSLK_API size_t mslk_b200_f8f8bf16_rowwise_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
+  if (M <= 0 || M > kDecodeMaxTokens || N < 128 || K <= 0) return 0;
+  return decode_scratch_bytes(M, N, K, sm_count());
+}
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise_ws(const void *xq, const void *wq, const float *x_scale, const float *w_scale,
+                                           const void *bias, int bias_kind, void *y, int64_t M, int64_t N, int64_t K,
+                                           void *workspace, size_t workspace_bytes, void *stream) {
+  using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
+  clear_error();
+  if (bias_kind < 0 || bias_kind > 2) return fail(1, "f8f8bf16_rowwise: bad bias_kind %d", bias_kind);
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u))
+    return fail(1, "f8f8bf16_rowwise: workspace must be 16-byte aligned");
+  return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, 1, M, N, K, workspace, workspace_bytes,
+             static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise");
 }
 
 MSLK_API int mslk_b200_f8f8bf16_rowwise_grouped_stacked(const void *xq, const void *wq, const float *x_scale,
@@ -372,6 +396,6 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_grouped_stacked(const void *xq, const vo
   using namespace mslk_b200::gemm_f8;
   clear_error();
   if (!M_sizes) return fail(1, "f8f8bf16_rowwise_grouped_stacked: M_sizes is null");
-  return run(xq, wq, x_scale, w_scale, nullptr, MSLK_B200_BIAS_NONE, y, M_sizes, G, total_M, N, K,
+  return run(xq, wq, x_scale, w_scale, nullptr, MSLK_B200_BIAS_NONE, y, M_sizes, G, total_M, N, K, nullptr, 0,
              static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise_grouped_stacked");
 }

@@ -1,0 +1,327 @@
+// Rowwise-scaled FP8 GEMM for few tokens (decode shapes): weight streaming, HBM-bound.
+//
+// Operands are swapped with respect to the large-M kernels: the 128 accumulator
+// rows (UMMA M) run over WEIGHT rows n, the accumulator columns (UMMA N = BT, the
+// token count padded to 16/32/64/128) over tokens m.  A pipeline stage then holds
+// 16 KB of weights and only BT x 128 bytes of activations, so the shared-memory
+// ring is almost entirely weight bytes in flight (two CTAs per SM, up to ~100 KB
+// each), which is what an HBM-bound kernel needs.
+//
+// One CTA computes one (128 weight rows) x (K range) tile.  When there are fewer
+// 128-row blocks than SMs the K dimension is split over `splits` CTAs:
+//   * every CTA stores its fp32 partial tile to scratch memory,
+//   * bumps a per-(tile, warp) ticket with atomicInc (which wraps to zero after the
+//     last ticket, so the counters need zeroing only once),
+//   * the warp that draws the last ticket sums all partials in split order (the
+//     result does not depend on which CTA finishes last) and runs the epilogue.
+// Scratch layout: [n_tile][split][BT tokens][128 weight rows] fp32, then the
+// tickets [n_tile][4] u32.
+//
+// Roles: warp 0 TMA producer, warp 1 MMA issuer / TMEM owner, warps 2..5 epilogue
+// (thread = weight row).  All pipeline waits are bounded (common.cuh).
+#include "gemm_f8_common.cuh"
+
+namespace mslk_b200 {
+namespace gemm_f8 {
+namespace {
+
+constexpr int kWRows = 128;  // weight rows per tile (UMMA M)
+
+template <int BT>
+struct DCfg {
+  static constexpr int kStageW = kWRows * kBK;
+  static constexpr int kStageX = BT * kBK;
+  static constexpr int kStageBytes = kStageW + kStageX;
+  // two CTAs per SM: keep each below ~110 KB
+  static constexpr int kStages = BT <= 32 ? 5 : BT == 64 ? 4 : 3;
+  static constexpr int kTmemCols = BT < 32 ? 32 : BT;
+  static constexpr uint32_t kIdesc =
+      (1u << 4) | (static_cast<uint32_t>(BT >> 3) << 17) | (static_cast<uint32_t>(kWRows >> 4) << 24);
+};
+
+template <int BT>
+struct DSmemTail {
+  uint64_t full[DCfg<BT>::kStages];
+  uint64_t empty[DCfg<BT>::kStages];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int BT>
+constexpr size_t decode_smem_bytes() {
+  return 1024 + static_cast<size_t>(DCfg<BT>::kStages) * DCfg<BT>::kStageBytes + sizeof(DSmemTail<BT>);
+}
+
+struct DecodeParams {
+  const float *x_scale;
+  const float *w_scale;
+  const void *bias;
+  __nv_bfloat16 *y;
+  float *partials;         // scratch (splits > 1)
+  unsigned int *tickets;   // scratch (splits > 1), zero before first use, self-resetting
+  int *status;
+  int bias_kind;
+  int M, N, K;
+  int splits;
+  int kb_per_split;        // K blocks (of 128) per split
+};
+
+template <int BT>
+__global__ void __launch_bounds__(kNumThreads, 2)
+    gemm_f8_rowwise_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                                  const DecodeParams p) {
+  using C = DCfg<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  DSmemTail<BT> &S = *reinterpret_cast<DSmemTail<BT> *>(ring + static_cast<size_t>(C::kStages) * C::kStageBytes);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const int n_tile = blockIdx.x;
+  const int split = blockIdx.y;
+  const int k_blocks_total = (p.K + kBK - 1) / kBK;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = min(k_blocks_total, kb0 + p.kb_per_split);
+  const int my_kb = max(0, kb1 - kb0);
+  volatile int *abort_flag = &S.abort_flag;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_w);
+    prefetch_tensormap(&tmap_x);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&S.full[s], 1);
+      mbar_init(&S.empty[s], 1);
+    }
+    mbar_init(&S.acc_full, 1);
+    S.abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) break;
+        uint8_t *sw = ring + static_cast<size_t>(stage) * C::kStageBytes;
+        uint8_t *sx = sw + C::kStageW;
+        mbar_arrive_expect_tx(&S.full[stage], C::kStageBytes);
+        tma_load_2d(sw, &tmap_w, &S.full[stage], kb * kBK, n_tile * kWRows);
+        tma_load_2d(sx, &tmap_x, &S.full[stage], kb * kBK, 0);
+        if (++stage == C::kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < my_kb; ++i) {
+        if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sw = smem_u32(ring + static_cast<size_t>(stage) * C::kStageBytes);
+        const uint64_t dw = make_kmajor_sw128_desc(sw);
+        const uint64_t dx = make_kmajor_sw128_desc(sw + C::kStageW);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k)
+          mma_f8f6f4(tmem_base, dw + static_cast<uint64_t>(k * (kUmmaK >> 4)),
+                     dx + static_cast<uint64_t>(k * (kUmmaK >> 4)), C::kIdesc, (i | k) != 0 ? 1u : 0u);
+        tc_commit(&S.empty[stage]);
+        if (++stage == C::kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) tc_commit(&S.acc_full);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue: thread = weight row
+    const int quad = warp & 3;
+    const int n = n_tile * kWRows + quad * 32 + lane;
+    const bool n_ok = n < p.N;
+    float acc[BT];
+    bool have = false;
+    if (my_kb > 0) {
+      const bool got = mbar_wait(&S.acc_full, 0, abort_flag, p.status, kStatusEpilogueTimeout);
+      have = __all_sync(0xffffffffu, got);
+    }
+    if (have) {
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+      if constexpr (BT >= 32) {
+#pragma unroll
+        for (int c = 0; c < BT / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = __uint_as_float(r[j]);
+        }
+      } else {
+        uint32_t r[32];  // only the first BT columns are meaningful (32 columns are allocated)
+        tmem_ld_32x32(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < BT; ++j) acc[j] = __uint_as_float(r[j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < BT; ++j) acc[j] = 0.f;
+    }
+    const bool aborted = (my_kb > 0) && !have;
+
+    bool do_epilogue = !aborted;
+    if (p.splits > 1 && !aborted) {
+      float *mine = p.partials + ((static_cast<size_t>(n_tile) * p.splits + split) * BT) * kWRows + quad * 32 + lane;
+#pragma unroll
+      for (int m = 0; m < BT; ++m)
+        if (m < p.M) mine[static_cast<size_t>(m) * kWRows] = acc[m];
+      __threadfence();
+      __syncwarp();
+      unsigned int ticket = 0;
+      if (lane == 0) ticket = atomicInc(p.tickets + n_tile * 4 + quad, static_cast<unsigned int>(p.splits - 1));
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      do_epilogue = ticket == static_cast<unsigned int>(p.splits - 1);
+      if (do_epilogue) {
+        __threadfence();
+        const float *base = p.partials + (static_cast<size_t>(n_tile) * p.splits * BT) * kWRows + quad * 32 + lane;
+#pragma unroll
+        for (int m = 0; m < BT; ++m) acc[m] = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+          const float *ps = base + static_cast<size_t>(s) * BT * kWRows;
+#pragma unroll
+          for (int m = 0; m < BT; ++m)
+            if (m < p.M) acc[m] += __ldcg(ps + static_cast<size_t>(m) * kWRows);
+        }
+      }
+    }
+    if (do_epilogue && n_ok) {
+      const float ws = p.w_scale[n];
+      float bias_f = 0.f;
+      if (p.bias_kind == MSLK_B200_BIAS_F32) bias_f = static_cast<const float *>(p.bias)[n];
+      if (p.bias_kind == MSLK_B200_BIAS_BF16) bias_f = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[n]);
+#pragma unroll
+      for (int m = 0; m < BT; ++m) {
+        if (m < p.M) {
+          float v = (acc[m] * p.x_scale[m]) * ws;
+          if (p.bias_kind == MSLK_B200_BIAS_F32) v += bias_f;
+          if (p.bias_kind == MSLK_B200_BIAS_BF16) v = __bfloat162float(__float2bfloat16_rn(v)) + bias_f;
+          p.y[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int BT>
+int launch_decode(const CUtensorMap &tw, const CUtensorMap &tx, const DecodeParams &p, int n_tiles, cudaStream_t st) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  constexpr size_t smem = decode_smem_bytes<BT>();
+  static_assert(smem <= 113 * 1024, "two CTAs per SM need at most ~113 KB each");
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_f8_rowwise_decode_kernel<BT>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                            "cudaFuncSetAttribute(gemm_f8_rowwise_decode)"))
+      return rc;
+    attr_set[dev] = true;
+  }
+  gemm_f8_rowwise_decode_kernel<BT><<<dim3(n_tiles, p.splits, 1), kNumThreads, smem, st>>>(tw, tx, p);
+  return check_cuda(cudaGetLastError(), "f8f8bf16_rowwise decode launch");
+}
+
+}  // namespace
+
+int decode_token_tile(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
+
+// Number of K splits for a decode-shaped problem: enough CTAs for about two per SM, each
+// split keeping at least four K blocks.
+int decode_splits(int64_t N, int64_t K, int sms) {
+  const int64_t n_tiles = (N + kWRows - 1) / kWRows;
+  const int64_t k_blocks = (K + kBK - 1) / kBK;
+  int64_t s = (2 * sms + n_tiles - 1) / n_tiles;
+  if (s > k_blocks / 4) s = k_blocks / 4;
+  if (s > 32) s = 32;
+  if (s < 1) s = 1;
+  return static_cast<int>(s);
+}
+
+size_t decode_scratch_bytes(int64_t M, int64_t N, int64_t K, int sms) {
+  const int splits = decode_splits(N, K, sms);
+  if (splits <= 1) return 0;
+  const int64_t n_tiles = (N + kWRows - 1) / kWRows;
+  const size_t partial = static_cast<size_t>(n_tiles) * splits * decode_token_tile(M) * kWRows * sizeof(float);
+  return partial + static_cast<size_t>(n_tiles) * 4 * sizeof(unsigned int);
+}
+
+int launch_decode_kernel(const void *xq, const void *wq, const GemmParams &gp, void *scratch, size_t scratch_bytes,
+                         bool scratch_is_clean, cudaStream_t st) {
+  const int sms = sm_count();
+  const int64_t n_tiles = (static_cast<int64_t>(gp.N) + kWRows - 1) / kWRows;
+  const int k_blocks = (gp.K + kBK - 1) / kBK;
+  int splits = decode_splits(gp.N, gp.K, sms);
+  const int bt = decode_token_tile(gp.total_m);
+  const size_t partial_bytes = static_cast<size_t>(n_tiles) * splits * bt * kWRows * sizeof(float);
+  const size_t ticket_bytes = static_cast<size_t>(n_tiles) * 4 * sizeof(unsigned int);
+  if (splits > 1 && (!scratch || scratch_bytes < partial_bytes + ticket_bytes)) splits = 1;  // no scratch: one CTA per tile
+
+  DecodeParams p;
+  p.x_scale = gp.x_scale;
+  p.w_scale = gp.w_scale;
+  p.bias = gp.bias;
+  p.y = gp.y;
+  p.status = gp.status;
+  p.bias_kind = gp.bias_kind;
+  p.M = gp.total_m;
+  p.N = gp.N;
+  p.K = gp.K;
+  p.splits = splits;
+  p.kb_per_split = (k_blocks + splits - 1) / splits;
+  p.partials = nullptr;
+  p.tickets = nullptr;
+  if (splits > 1) {
+    p.partials = static_cast<float *>(scratch);
+    p.tickets = reinterpret_cast<unsigned int *>(static_cast<uint8_t *>(scratch) + partial_bytes);
+    if (!scratch_is_clean)
+      if (int rc = check_cuda(cudaMemsetAsync(p.tickets, 0, ticket_bytes, st), "zero split-K tickets")) return rc;
+  }
+
+  CUtensorMap tw, tx;
+  if (int rc = make_tmap_2d_bytes(&tw, wq, gp.K, gp.N, gp.K, kBK, kWRows, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tx, xq, gp.K, gp.total_m, gp.K, kBK, bt, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  switch (bt) {
+    case 16: return launch_decode<16>(tw, tx, p, static_cast<int>(n_tiles), st);
+    case 32: return launch_decode<32>(tw, tx, p, static_cast<int>(n_tiles), st);
+    case 64: return launch_decode<64>(tw, tx, p, static_cast<int>(n_tiles), st);
+    default: return launch_decode<128>(tw, tx, p, static_cast<int>(n_tiles), st);
+  }
+}
+
+}  // namespace gemm_f8
+}  // namespace mslk_b200

@@ -1,0 +1,173 @@
+"""Shape-level micro-benchmarks of the individual kernels (one JSON line per case).
+
+    python -m mslk_b200.microbench quantize_fp8_row --shape 8192,4096
+    python -m mslk_b200.microbench f8f8bf16_rowwise --shape 8192,8192,8192
+    python -m mslk_b200.microbench grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
+    python -m mslk_b200.microbench f4f4bf16 --shape 8192,8192,8192
+    python -m mslk_b200.microbench quantize_nvfp4 --shape 8192,8192
+    python -m mslk_b200.microbench sweep          # the Llama-3-8B sweep: M x (N,K), quantize + GEMM
+
+Timing: CUDA events around `--iters` launches after `--warmup` launches, on torch's current
+stream.  Inputs rotate through enough buffers to exceed the 126 MB L2 (`--rotate-mb`, default 512).
+With `--graph` the launches are captured in one CUDA graph first, which removes the host launch
+cost from small cases.  `--iters 1 --warmup 0 --rotate-mb 0` gives a minimal run to profile.
+Synthetic data: activations bf16 ~N(0,1), weights ~N(0, --w-std).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+
+def _time(fn, n_variants, iters, warmup, graph):
+    for i in range(warmup):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
+                for i in range(iters):
+                    fn(i % n_variants)
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        e1.record()
+    else:
+        e0.record()
+        for i in range(iters):
+            fn(i % n_variants)
+        e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3  # seconds per launch
+
+
+def _variants(bytes_per_variant, rotate_mb):
+    if rotate_mb <= 0:
+        return 1
+    return max(1, min(16, math.ceil(rotate_mb * 1e6 / max(1, bytes_per_variant))))
+
+
+def _randn(shape, std=1.0):
+    return (torch.randn(shape, device="cuda", dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+def bench_quantize_fp8_row(ops, M, K, args):
+    nv = _variants(M * K * 2, args.rotate_mb)
+    xs = [_randn((M, K)) for _ in range(nv)]
+    sec = _time(lambda i: ops.quantize_fp8_row(xs[i]), nv, args.iters, args.warmup, args.graph)
+    byts = 3.0 * M * K + 4.0 * M
+    return {"op": "quantize_fp8_row", "M": M, "K": K, "us": sec * 1e6, "GBps": byts / sec / 1e9, "bytes": byts}
+
+
+def bench_f8f8bf16_rowwise(ops, M, N, K, args):
+    nv = _variants(N * K, args.rotate_mb)
+    xq, xs = ops.quantize_fp8_row(_randn((M, K)))
+    ws = [ops.quantize_fp8_row(_randn((N, K), args.w_std)) for _ in range(nv)]
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    sec = _time(lambda i: ops.f8f8bf16_rowwise_out(xq, ws[i][0], xs, ws[i][1], y), nv, args.iters, args.warmup, args.graph)
+    flops = 2.0 * M * N * K
+    byts = M * K + N * K + 2.0 * M * N + 4.0 * (M + N)
+    return {"op": "f8f8bf16_rowwise", "M": M, "N": N, "K": K, "us": sec * 1e6, "TFLOPs": flops / sec / 1e12,
+            "GBps": byts / sec / 1e9}
+
+
+def zipf_counts(experts, tokens, seed=0, s=1.2, n_empty=2):
+    """Per-expert token counts: top-1 routing with Zipf(s) expert popularity, the `n_empty` least popular
+    experts forced to zero tokens (their tokens go to the most popular one)."""
+    g = torch.Generator().manual_seed(seed)
+    p = (torch.randperm(experts, generator=g).float() + 1) ** -s
+    counts = torch.bincount(torch.multinomial(p / p.sum(), tokens, replacement=True, generator=g), minlength=experts)
+    low = torch.argsort(p)[:n_empty]
+    counts[torch.argmax(counts)] += counts[low].sum()
+    counts[low] = 0
+    return counts
+
+
+def bench_grouped(ops, E, tokens, N, K, args):
+    counts = zipf_counts(E, tokens)
+    xq, xs = ops.quantize_fp8_row(_randn((tokens, K)))
+    wq, ws = ops.quantize_fp8_row(_randn((E, N, K), args.w_std))
+    ms = counts.to(torch.int64).cuda()
+    sec = _time(lambda i: ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws.view(-1), ms), 1, args.iters,
+                args.warmup, args.graph)
+    flops = 2.0 * tokens * N * K
+    return {"op": "f8f8bf16_rowwise_grouped_stacked", "E": E, "tokens": tokens, "N": N, "K": K,
+            "counts": counts.tolist(), "us": sec * 1e6, "TFLOPs": flops / sec / 1e12}
+
+
+def bench_quantize_nvfp4(ops, M, K, args):
+    nv = _variants(M * K * 2, args.rotate_mb)
+    xs = [_randn((M, K)) for _ in range(nv)]
+    gs = (448.0 * 6.0) / xs[0].abs().amax().float()
+    sec = _time(lambda i: ops.quantize_nvfp4(xs[i], gs), nv, args.iters, args.warmup, args.graph)
+    byts = 2.0 * M * K + M * K / 2 + M * K / 16
+    return {"op": "quantize_nvfp4", "M": M, "K": K, "us": sec * 1e6, "GBps": byts / sec / 1e9}
+
+
+def bench_f4f4bf16(ops, M, N, K, args):
+    nv = _variants(N * K // 2, args.rotate_mb)
+    x = _randn((M, K))
+    gx = (448.0 * 6.0) / x.abs().amax().float()
+    xq, sx = ops.quantize_nvfp4(x, gx)
+    ws = []
+    for _ in range(nv):
+        w = _randn((N, K))
+        gw = (448.0 * 6.0) / w.abs().amax().float()
+        wq, sw = ops.quantize_nvfp4(w, gw)
+        ws.append((wq, sw, (1.0 / (gx * gw)).reshape(1)))
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    sec = _time(lambda i: ops.f4f4bf16(xq, ws[i][0], sx, ws[i][1], output=y, global_scale=ws[i][2]), nv, args.iters,
+                args.warmup, args.graph)
+    flops = 2.0 * M * N * K
+    byts = M * K / 2 + N * K / 2 + (M + N) * K / 16 + 2.0 * M * N
+    return {"op": "f4f4bf16", "M": M, "N": N, "K": K, "us": sec * 1e6, "TFLOPs": flops / sec / 1e12,
+            "GBps": byts / sec / 1e9}
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "grouped", "f4f4bf16", "quantize_nvfp4", "sweep"])
+    ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
+    ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--rotate-mb", type=float, default=512.0)
+    ap.add_argument("--w-std", type=float, default=0.02)
+    ap.add_argument("--graph", action="store_true")
+    args = ap.parse_args()
+    from . import ops
+    from ._lib import device_status
+    shape = [int(v) for v in args.shape.split(",")] if args.shape else None
+    out = []
+    if args.op == "quantize_fp8_row":
+        out.append(bench_quantize_fp8_row(ops, *(shape or [8192, 4096]), args))
+    elif args.op == "f8f8bf16_rowwise":
+        out.append(bench_f8f8bf16_rowwise(ops, *(shape or [8192, 8192, 8192]), args))
+    elif args.op == "grouped":
+        out.append(bench_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
+    elif args.op == "quantize_nvfp4":
+        out.append(bench_quantize_nvfp4(ops, *(shape or [8192, 8192]), args))
+    elif args.op == "f4f4bf16":
+        out.append(bench_f4f4bf16(ops, *(shape or [8192, 8192, 8192]), args))
+    else:
+        for M in (1, 16, 128, 2048, 8192):
+            for N, K in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
+                out.append(bench_quantize_fp8_row(ops, M, K, args))
+                out.append(bench_f8f8bf16_rowwise(ops, M, N, K, args))
+    status = device_status()
+    for r in out:
+        r["device_status"] = status
+        print(json.dumps(r), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -183,3 +183,41 @@ def test_grouped_moe_shape_zipf(ops):
     assert sum(m_sizes) == tokens and m_sizes.count(0) >= 2
     _grouped_case(ops, E, m_sizes, N, K, seed=3)
     assert _status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 3, 16, 17, 32, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(128, 128), (1000, 512), (4096, 4096), (6144, 1024)])
+def test_few_token_shapes_split_and_unsplit(ops, M, N, K):
+    # M <= 32 takes the weight-streaming kernel (with scratch the K dimension is split); larger M the general one
+    from mslk_b200._lib import lib, check
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=M + N, w_std=1.0)
+    bias = torch.randn(N, device="cuda") if (M + N) % 2 else None
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws, bias)
+    y = ops.f8f8bf16_rowwise(xq, wq, xs, ws, bias=bias)            # scratch from the allocator (split when useful)
+    _close(y, y_ref, f"decode split {M}x{N}x{K}")
+    y2 = torch.empty_like(y)
+    check(lib.mslk_b200_f8f8bf16_rowwise(xq.data_ptr(), wq.data_ptr(), xs.data_ptr(), ws.data_ptr(),
+                                         None if bias is None else bias.data_ptr(), 0 if bias is None else 1,
+                                         y2.data_ptr(), M, N, K, torch.cuda.current_stream().cuda_stream), "plain")
+    _close(y2, y_ref, f"decode unsplit {M}x{N}x{K}")
+    # the split result does not depend on CTA finishing order: repeated calls are bit-identical
+    y3 = ops.f8f8bf16_rowwise(xq, wq, xs, ws, bias=bias)
+    assert torch.equal(y3, y)
+    assert _status() == 0
+
+
+def test_workspace_reuse_and_dirty_scratch(ops):
+    from mslk_b200._lib import lib, check
+    M, N, K = 8, 4096, 4096
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=5)
+    nbytes = lib.mslk_b200_f8f8bf16_rowwise_workspace_bytes(M, N, K)
+    assert nbytes > 0
+    scratch = torch.full((nbytes,), 0xAB, dtype=torch.uint8, device="cuda")   # deliberately dirty
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws)
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        check(lib.mslk_b200_f8f8bf16_rowwise_ws(xq.data_ptr(), wq.data_ptr(), xs.data_ptr(), ws.data_ptr(), None, 0,
+                                                y.data_ptr(), M, N, K, scratch.data_ptr(), nbytes, st), "ws")
+        _close(y, y_ref, "dirty scratch")
+    assert _status() == 0
