@@ -286,15 +286,19 @@ def run_ours(args, rank, world, local_rank):
         gemm_flops = step_flops()
         gemm_ms = sum(g_ms)
         achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
-        fp8_peak = 2.0 * peaks["bf16_sustained"]
+        # a timed region of a few hundred ms never reaches the power cap: compare with the burst figure;
+        # a region of seconds runs power-capped: compare with the sustained one
+        long_run = ms_max >= 2000.0
+        fp8_peak = 2.0 * (peaks["bf16_sustained"] if long_run else peaks["bf16_burst"])
         q_bytes = sum(3.0 * M_TOKENS * L["k"] + 4.0 * M_TOKENS for L in layers)
         q_gbs = q_bytes / (sum(q_ms) * 1e-3) / 1e9
         line = base_line(args, world)
         line.update({
             "value": value, "ms_per_step": per_step_ms, "gpu_launches": 2 * len(layers) * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "gemm_f8_rowwise_kernel<256>", "achieved": achieved,
+            "roofline": {"bound": "tensor", "kernel": "gemm_f8_rowwise_pair_kernel", "achieved": achieved,
                          "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": None,
-                         "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} peaks (fp8 issues at twice the bf16 rate)",
+                         "peak_source": f"2 x bf16_tflops{'_sustained' if long_run else ' (burst)'} of {peaks['source']} peaks "
+                                        "(the fp8 tensor rate is twice the bf16 rate)",
                          "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
                          "flops_per_step": gemm_flops, "ms_per_step_in_kernel": gemm_ms},
             "roofline_quantize": {"bound": "hbm", "kernel": "quant_fp8_row_vec_kernel", "achieved": q_gbs,
