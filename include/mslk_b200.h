@@ -95,6 +95,24 @@ int mslk_b200_f8f8bf16_rowwise_ws(const void *xq, const void *wq, const float *x
                                   size_t workspace_bytes, void *stream);
 
 /*
+ * The few-token GEMM for hosts that cannot allocate device memory when they call (all HBM
+ * already handed to a KV-cache pool, a memory plan frozen at start-up, or a thread that must
+ * not run cudaMalloc because it stalls the device).  The split-K scratch is an 8 MiB array
+ * built into the library image (held by every GPU that loads the library until exit); the call
+ * allocates and frees nothing.  Serves 1 <= M <= 128, N >= 128, K % 16 == 0 as long as the
+ * split-K scratch of the shape fits the 8 MiB (always true for M <= 32; for more tokens only
+ * small N*K do); a shape that needs more is rejected with a message, never truncated.  The first call on a
+ * device looks up the array's device address: make that call outside stream capture.  All calls
+ * on a GPU share the array -- the tickets in it are cleared on the stream before each launch,
+ * the partial sums are overwritten -- so calls that could overlap on one GPU must be ordered
+ * by the caller.  Same arithmetic and arguments as mslk_b200_f8f8bf16_rowwise.
+ * This entry point has no counterpart in the reference (its op always allocates its workspace).
+ */
+int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, const float *x_scale,
+                                       const float *w_scale, const void *bias, int bias_kind,
+                                       void *y, int64_t M, int64_t N, int64_t K, void *stream);
+
+/*
  * Grouped (stacked) rowwise FP8 GEMM for MoE experts.
  * Replaces: csrc/gemm/cutlass/f8f8bf16_rowwise_grouped.cu:342-368
  *           (f8f8bf16_rowwise_grouped_stacked) with its argument-setup kernel and

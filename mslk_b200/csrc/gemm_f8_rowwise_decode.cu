@@ -21,6 +21,8 @@
 // (thread = weight row).  All pipeline waits are bounded (common.cuh).
 #include "gemm_f8_common.cuh"
 
+#include <mutex>
+
 namespace mslk_b200 {
 namespace gemm_f8 {
 namespace {
@@ -325,3 +327,101 @@ int launch_decode_kernel(const void *xq, const void *wq, const GemmParams &gp, v
 
 }  // namespace gemm_f8
 }  // namespace mslk_b200
+
+// ---------------------------------------------------------------------------
+// Few-token GEMM with built-in scratch: for callers that must not allocate.
+//
+// Some hosts of this library cannot obtain device memory at call time: a serving
+// engine that has handed all free HBM to its KV-cache pool at start-up (a late
+// cudaMalloc simply fails there), a runtime whose memory plan is fixed before
+// the first request, or a plugin called from a thread that is forbidden to
+// touch the allocator because cudaMalloc/cudaFree synchronise the whole device.
+// For them the split-K scratch of the weight-streaming kernel lives in the
+// array below, which is part of the library image: every GPU that loads the
+// library carries these 8 MiB until the process exits, and nothing is
+// allocated or freed by the call.
+//
+// The host cannot use the array's name as a pointer (on the host it is only a
+// handle for the symbol); the device address is looked up once per device with
+// cudaGetSymbolAddress, with that device current.  The look-up happens in the
+// first call made on a device, so make that first call outside stream capture.
+//
+// All calls on a device share the one array.  The partial sums left by the
+// previous call are simply overwritten; the completion tickets must start at
+// zero and are cleared on the stream before every launch.  Two calls that can
+// run at the same time on one GPU (different streams, or graph branches) would
+// mix their partial sums and tickets: keep such calls ordered.
+// ---------------------------------------------------------------------------
+namespace mslk_b200 {
+namespace gemm_f8 {
+namespace {
+
+constexpr size_t kBuiltinScratchBytes = 8u << 20;  // 8 MiB: every shape with M <= 32, smaller ones up to M = 128
+constexpr int kNoAllocMaxTokens = 128;             // what the weight-streaming kernel itself can take
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+constexpr int kMaxDevicesTracked = 64;
+std::mutex g_builtin_mu;
+void *g_builtin_ptr[kMaxDevicesTracked];
+
+// Device address of g_builtin_scratch on the current device (looked up once per device).
+int builtin_scratch_ptr(void **out) {
+  int dev = 0;
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
+  if (dev < 0 || dev >= kMaxDevicesTracked) return fail(2, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_builtin_mu);
+  if (!g_builtin_ptr[dev]) {
+    void *ptr = nullptr;
+    if (int rc = check_cuda(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_builtin_scratch),
+                            "cudaGetSymbolAddress(built-in scratch)"))
+      return rc;
+    g_builtin_ptr[dev] = ptr;
+  }
+  *out = g_builtin_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+}  // namespace gemm_f8
+}  // namespace mslk_b200
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, const float *x_scale,
+                                                const float *w_scale, const void *bias, int bias_kind, void *y,
+                                                int64_t M, int64_t N, int64_t K, void *stream) {
+  using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
+  clear_error();
+  const char *name = "f8f8bf16_rowwise_noalloc";
+  if (bias_kind < 0 || bias_kind > 2) return fail(1, "%s: bad bias_kind %d", name, bias_kind);
+  if (M < 1 || M > kNoAllocMaxTokens)
+    return fail(1, "%s: this entry point serves 1..%d tokens (got M=%lld); use f8f8bf16_rowwise for more", name,
+                kNoAllocMaxTokens, (long long)M);
+  if (N < 128 || N > 0x7fffff00LL) return fail(1, "%s: N (%lld) must be at least 128", name, (long long)N);
+  if (K < 16 || K > 0x7fffff00LL || K % 16 != 0)
+    return fail(1, "%s: K (%lld) must be a positive multiple of 16", name, (long long)K);
+  if (!xq || !wq || !x_scale || !w_scale || !y) return fail(1, "%s: null pointer argument", name);
+  if (bias_kind != MSLK_B200_BIAS_NONE && !bias) return fail(1, "%s: bias_kind set but bias is null", name);
+  const size_t need = decode_scratch_bytes(M, N, K, sm_count());
+  if (need > kBuiltinScratchBytes)
+    return fail(1, "%s: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in buffer holds %zu", name,
+                (long long)M, (long long)N, (long long)K, need, kBuiltinScratchBytes);
+  void *scratch = nullptr;
+  if (int rc = builtin_scratch_ptr(&scratch)) return rc;
+  int *status = device_status_ptr();
+  if (!status) return 2;
+  GemmParams p;
+  p.x_scale = x_scale;
+  p.w_scale = w_scale;
+  p.bias = bias;
+  p.y = static_cast<__nv_bfloat16 *>(y);
+  p.m_sizes = nullptr;
+  p.status = status;
+  p.bias_kind = bias_kind;
+  p.G = 1;
+  p.total_m = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  // scratch_is_clean = false: the tickets are zeroed on the stream before the launch
+  return launch_decode_kernel(xq, wq, p, scratch, kBuiltinScratchBytes, false, static_cast<cudaStream_t>(stream));
+}
+
