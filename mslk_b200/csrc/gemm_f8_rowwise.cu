@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
       int stage = 0;
       uint32_t phase = 0;
       long long issued = 0;
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;

@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (both CTAs)
-    if (lane == 0) {
+    if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
       int stage = 0;
       uint32_t phase = 0;
       Tile t;
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader only)
-    if (leader && lane == 0) {
+    if (leader && elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;

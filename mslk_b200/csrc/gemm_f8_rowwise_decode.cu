@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kNumThreads, 2)
   const uint32_t tmem_base = S.tmem_base;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
       int stage = 0;
       uint32_t phase = 0;
       for (int kb = kb0; kb < kb1; ++kb) {
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(kNumThreads, 2)
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;

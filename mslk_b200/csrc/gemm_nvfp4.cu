@@ -22,6 +22,8 @@
 #include "common.cuh"
 #include "host.h"
 
+#include <cstdlib>
+
 namespace mslk_b200 {
 namespace {
 
@@ -52,8 +54,9 @@ struct Cfg {
   static constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
   static constexpr int kStages = BN == 128 ? 6 : 4;
   static constexpr int kAccStages = BN == 128 ? 2 : 1;
-  static constexpr int kSfaCol = kAccStages * BN;          // first TMEM column of the A scales (16 columns)
-  static constexpr int kSfbCol = kSfaCol + 16;             // B scales: 16 * kNB columns
+  static constexpr int kSfaCol = kAccStages * BN;          // first TMEM column of the scale area
+  static constexpr int kSfCols = 16 + 16 * kNB;            // one set: A scales (16 columns) + B scales (16 * kNB)
+  static_assert(kSfaCol + 2 * kSfCols <= 512, "two scale column sets must fit beside the accumulators");
   static constexpr int kTmemCols = 512;
   // block-scaled instruction descriptor: e2m1 x e2m1, ue4m3 scales, K-major, dense K = 64
   static constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (0u << 23) |
@@ -131,7 +134,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    if (lane == 0) {
+    if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -170,52 +173,85 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int local = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
-        const int acc = local % C::kAccStages;
-        const uint32_t acc_phase = (local / C::kAccStages) & 1;
-        if (!mbar_wait(&S.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
-          ok = false;
-          break;
+    // The K blocks of all tiles of this CTA form one stream.  The scale atoms of block i+1 are
+    // copied to tensor memory (into the other of two column sets) BEFORE the instructions of
+    // block i are issued, so the copies run behind those instructions instead of in front of
+    // the ones that need them.
+    if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
+      struct Pos {
+        int tile, kb, stage, local;
+        uint32_t phase;
+      };
+      auto advance = [&](Pos &q) {
+        if (++q.kb == k_blocks) {
+          q.kb = 0;
+          q.tile += gridDim.x;
+          ++q.local;
         }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+        if (++q.stage == C::kStages) {
+          q.stage = 0;
+          q.phase ^= 1;
+        }
+      };
+      auto copy_scales = [&](const Pos &q, int buf) {
+        const uint32_t sa = smem_u32(ring + static_cast<size_t>(q.stage) * C::kStageBytes);
+        const uint32_t ssfa = sa + C::kStageA + C::kStageB;
+        const uint32_t ssfb = ssfa + C::kStageSFA;
+        const uint32_t sfa_t = tmem_base + C::kSfaCol + buf * C::kSfCols;
+        const uint32_t sfb_t = sfa_t + 16;
+        const int atoms = min(4, p.ncb - 4 * q.kb);
+        for (int k = 0; k < atoms; ++k) {
+          tc_cp_32x128b_warpx4(sfa_t + 4 * k, make_sf_atom_desc(ssfa + k * kAtomBytes));
+#pragma unroll
+          for (int b = 0; b < C::kNB; ++b)
+            tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * k + 4 * b, make_sf_atom_desc(ssfb + (b * 4 + k) * kAtomBytes));
+        }
+      };
+      Pos pos{static_cast<int>(blockIdx.x), 0, 0, 0, 0u};
+      bool ok = pos.tile < num_tiles;
+      if (ok) {
+        ok = mbar_wait(&S.full[pos.stage], pos.phase, abort_flag, p.status, kStatusMmaTimeout);
+        if (ok) {
+          tc_fence_after();
+          copy_scales(pos, 0);
+        }
+      }
+      int n = 0;
+      while (ok && pos.tile < num_tiles) {
+        Pos nxt = pos;
+        advance(nxt);
+        if (nxt.tile < num_tiles) {
+          if (!mbar_wait(&S.full[nxt.stage], nxt.phase, abort_flag, p.status, kStatusMmaTimeout)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(ring + static_cast<size_t>(stage) * C::kStageBytes);
-          const uint32_t sb = sa + C::kStageA;
-          const uint32_t ssfa = sb + C::kStageB;
-          const uint32_t ssfb = ssfa + C::kStageSFA;
-          const uint64_t da = make_kmajor_sw128_desc(sa);
-          const uint64_t db = make_kmajor_sw128_desc(sb);
-          const int atoms = min(4, p.ncb - 4 * kb);
-          for (int k = 0; k < atoms; ++k) {
-            const uint32_t sfa_t = tmem_base + C::kSfaCol + 4 * k;
-            const uint32_t sfb_t = tmem_base + C::kSfbCol + 4 * C::kNB * k;
-            tc_cp_32x128b_warpx4(sfa_t, make_sf_atom_desc(ssfa + k * kAtomBytes));
-#pragma unroll
-            for (int b = 0; b < C::kNB; ++b)
-              tc_cp_32x128b_warpx4(sfb_t + 4 * b, make_sf_atom_desc(ssfb + (b * 4 + k) * kAtomBytes));
-            mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                      db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t, sfb_t,
-                      (kb | k) != 0 ? 1u : 0u);
-          }
-          tc_commit(&S.empty[stage]);
-          if (++stage == C::kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          copy_scales(nxt, (n + 1) & 1);
         }
-        if (!ok) break;
-        tc_commit(&S.tmem_full[acc]);
+        const int acc = pos.local % C::kAccStages;
+        if (pos.kb == 0) {
+          const uint32_t acc_phase = (pos.local / C::kAccStages) & 1;
+          if (!mbar_wait(&S.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+        }
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        const uint32_t sa = smem_u32(ring + static_cast<size_t>(pos.stage) * C::kStageBytes);
+        const uint64_t da = make_kmajor_sw128_desc(sa);
+        const uint64_t db = make_kmajor_sw128_desc(sa + C::kStageA);
+        const uint32_t sfa_t = tmem_base + C::kSfaCol + (n & 1) * C::kSfCols;
+        const uint32_t sfb_t = sfa_t + 16;
+        const int atoms = min(4, p.ncb - 4 * pos.kb);
+        for (int k = 0; k < atoms; ++k)
+          mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                    db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t + 4 * k,
+                    sfb_t + 4 * C::kNB * k, (pos.kb | k) != 0 ? 1u : 0u);
+        tc_commit(&S.empty[pos.stage]);
+        if (pos.kb == k_blocks - 1) tc_commit(&S.tmem_full[acc]);
+        pos = nxt;
+        ++n;
       }
     }
     __syncwarp();
@@ -238,34 +274,41 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
       __nv_bfloat16 *yrow = p.y + static_cast<size_t>(row) * p.N + n_tile * BN;
-#pragma unroll 1
+      // Drain the whole accumulator into registers (already scaled and packed to bf16) and hand
+      // it back to the MMA warp BEFORE the global stores: with a single accumulator the next
+      // tile's main loop would otherwise wait for the store phase as well.
+      uint32_t packed[BN / 2];
+#pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
-        const int cols_left = p.N - (n_tile * BN + c * 32);
-        if (cols_left <= 0) break;
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        uint32_t packed[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2)
-          packed[j / 2] = pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
-        if (row_ok) {
+          packed[c * 16 + j / 2] = pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.tmem_empty[acc]);
+      if (row_ok) {
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          const int cols_left = p.N - (n_tile * BN + c * 32);
           __nv_bfloat16 *dst = yrow + c * 32;
           if (y_vec_ok && cols_left >= 32) {
             uint4 *d4 = reinterpret_cast<uint4 *>(dst);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              d4[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-          } else {
-            const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
+              d4[j] = make_uint4(packed[c * 16 + 4 * j], packed[c * 16 + 4 * j + 1], packed[c * 16 + 4 * j + 2],
+                                 packed[c * 16 + 4 * j + 3]);
+          } else if (cols_left > 0) {
             uint16_t *d = reinterpret_cast<uint16_t *>(dst);
-            for (int j = 0; j < 32 && j < cols_left; ++j) d[j] = h[j];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < cols_left) d[j] = static_cast<uint16_t>(packed[c * 16 + j / 2] >> ((j & 1) * 16));
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&S.tmem_empty[acc]);
     }
   }
 
@@ -330,7 +373,8 @@ MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_sc
   const int64_t m_tiles = (M + kBM - 1) / kBM;
   // 256-wide tiles halve the A traffic per flop but hold one accumulator only; use them when
   // there are enough tiles to fill the device, 128-wide (double-buffered) otherwise
-  const int bn = (m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
+  int bn = (m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
+  if (const char *e = getenv("MSLK_B200_NVFP4_BN")) bn = atoi(e) == 128 ? 128 : 256;  // tuning aid
   CUtensorMap ta, tb;
   if (int rc = make_tmap_2d_bytes(&ta, xq, K / 2, M, K / 2, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d_bytes(&tb, wq, K / 2, N, K / 2, kBKBytes, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
