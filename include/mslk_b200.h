@@ -78,6 +78,22 @@ int mslk_b200_f8f8bf16_rowwise(const void *xq, const void *wq, const float *x_sc
                                int64_t M, int64_t N, int64_t K, void *stream);
 
 /*
+ * N-sharded GEMM fused with the all-gather of its output (tensor parallelism inside one node).
+ * Rank `rank` of `world` (<= 8) holds the weight rows [rank*N_local, (rank+1)*N_local) and computes
+ * its [M, N_local] column block; the kernel's epilogue stores that block at column rank*N_local of
+ * EVERY rank's row-major [M, world*N_local] bf16 output: y_bases is a HOST array of `world` device
+ * pointers, y_bases[rank] the local buffer, the others peer-mapped buffers of the other GPUs
+ * (plain stores over NVLink, no separate collective, no re-layout copy).  The caller synchronises
+ * the ranks afterwards (any barrier on the same streams) before a rank reads columns it did not
+ * write.  New with respect to the reference, whose operator is single-GPU
+ * (csrc/gemm/cutlass/f8f8bf16_rowwise.cu:183-206).
+ */
+int mslk_b200_f8f8bf16_rowwise_allgather(const void *xq, const void *wq_shard, const float *x_scale,
+                                         const float *w_scale_shard, const void *bias_shard,
+                                         int bias_kind, void *const *y_bases, int world, int rank,
+                                         int64_t M, int64_t N_local, int64_t K, void *stream);
+
+/*
  * Same operation with caller-provided scratch memory.  For few-token shapes (M <= 32) the
  * kernel streams the weights with the K dimension split over several CTAs; the partial sums
  * and their completion tickets live in `workspace`.  mslk_b200_f8f8bf16_rowwise_workspace_bytes

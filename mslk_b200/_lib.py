@@ -34,6 +34,9 @@ lib.mslk_b200_f8f8bf16_rowwise_workspace_bytes.argtypes = [_i64, _i64, _i64]
 lib.mslk_b200_f8f8bf16_rowwise_workspace_bytes.restype = ctypes.c_size_t
 lib.mslk_b200_f8f8bf16_rowwise_ws.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp, ctypes.c_size_t, _vp]
 lib.mslk_b200_f8f8bf16_rowwise_ws.restype = _int
+lib.mslk_b200_f8f8bf16_rowwise_allgather.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, ctypes.POINTER(_vp), _int, _int,
+                                                     _i64, _i64, _i64, _vp]
+lib.mslk_b200_f8f8bf16_rowwise_allgather.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f8f8bf16_rowwise_noalloc.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]

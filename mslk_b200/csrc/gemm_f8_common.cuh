@@ -30,7 +30,24 @@ struct GemmParams {
   int total_m;
   int N;
   int K;
+  // Output placement: y (and y_extra[0..n_extra)) are row-major with a pitch of ldy elements; the
+  // N columns of this problem start at column col0.  Defaults: ldy = N, col0 = 0, n_extra = 0.
+  // The extra destinations may be buffers of peer GPUs (plain stores over NVLink): that is how the
+  // N-sharded GEMM delivers its column block to every rank without a separate all-gather.
+  __nv_bfloat16 *y_extra[7];
+  int n_extra;
+  int ldy;
+  int col0;
+  int tma_store;  // pair kernel: full 32-row slabs leave through shared memory and TMA stores
 };
+
+inline void default_placement(GemmParams &p) {
+  p.n_extra = 0;
+  p.ldy = p.N;
+  p.col0 = 0;
+  p.tma_store = 0;
+  for (auto &e : p.y_extra) e = nullptr;
+}
 
 // Builds the per-group prefix tables (first stacked row and first linear tile of every
 // group) in shared memory; executed by one full warp.  Row counts come from device memory
@@ -113,10 +130,10 @@ struct Scheduler {
   }
 };
 
-template <int BN, int BIAS>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float xs, const float *ws, const float *bs,
-                                               __nv_bfloat16 *dst, bool row_ok, int cols_left, bool vec_ok) {
-  uint32_t packed[16];
+// 32 accumulator columns of one row -> 16 packed bf16 pairs: (acc * xs) * ws (+ bias)
+template <int BIAS>
+__device__ __forceinline__ void epilogue_pack(const uint32_t (&acc)[32], float xs, const float *ws, const float *bs,
+                                              uint32_t (&packed)[16]) {
 #pragma unroll
   for (int j = 0; j < 32; j += 2) {
     float v0 = (__uint_as_float(acc[j]) * xs) * ws[j];
@@ -131,15 +148,35 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float 
     }
     packed[j / 2] = pack_bf16x2(v0, v1);
   }
+}
+
+__device__ __forceinline__ void epilogue_pack_any(int bias_kind, const uint32_t (&acc)[32], float xs, const float *ws,
+                                                  const float *bs, uint32_t (&packed)[16]) {
+  if (bias_kind == MSLK_B200_BIAS_NONE) epilogue_pack<MSLK_B200_BIAS_NONE>(acc, xs, ws, bs, packed);
+  else if (bias_kind == MSLK_B200_BIAS_F32) epilogue_pack<MSLK_B200_BIAS_F32>(acc, xs, ws, bs, packed);
+  else epilogue_pack<MSLK_B200_BIAS_BF16>(acc, xs, ws, bs, packed);
+}
+
+template <int BN, int BIAS>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float xs, const float *ws, const float *bs,
+                                               const GemmParams &p, size_t elem_off, bool row_ok, int cols_left,
+                                               bool vec_ok) {
+  uint32_t packed[16];
+  epilogue_pack<BIAS>(acc, xs, ws, bs, packed);
   if (!row_ok) return;
-  if (vec_ok && cols_left >= 32) {
-    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+  for (int dsti = -1; dsti < p.n_extra; ++dsti) {
+    __nv_bfloat16 *dst = (dsti < 0 ? p.y : p.y_extra[dsti]) + elem_off;
+    if (vec_ok && cols_left >= 32) {
+      uint4 *d4 = reinterpret_cast<uint4 *>(dst);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) d4[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-  } else {
-    const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
-    uint16_t *d = reinterpret_cast<uint16_t *>(dst);
-    for (int j = 0; j < 32 && j < cols_left; ++j) d[j] = h[j];
+      for (int j = 0; j < 4; ++j)
+        d4[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+    } else {
+      uint16_t *d = reinterpret_cast<uint16_t *>(dst);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < cols_left) d[j] = static_cast<uint16_t>(packed[j / 2] >> ((j & 1) * 16));
+    }
   }
 }
 

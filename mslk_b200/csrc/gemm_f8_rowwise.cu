@@ -205,7 +205,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;             // TMEM lane quadrant this warp may read
     const int row_in_tile = quad * 32 + lane;
-    const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+    bool y_vec_ok = (p.ldy % 8 == 0) && (p.col0 % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+    for (int d = 0; d < p.n_extra; ++d) y_vec_ok = y_vec_ok && ((reinterpret_cast<uintptr_t>(p.y_extra[d]) & 15u) == 0);
     int local = 0;
     bool ok = true;
     Tile t;
@@ -235,7 +236,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
-      __nv_bfloat16 *yrow = p.y + static_cast<size_t>(t.row0 + row_in_tile) * p.N + t.n0;
+      const size_t yoff = static_cast<size_t>(t.row0 + row_in_tile) * p.ldy + p.col0 + t.n0;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int cols_left = p.N - (t.n0 + c * 32);
@@ -246,11 +247,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const float *ws = ws_s + c * 32;
         const float *bs = bs_s + c * 32;
         if (p.bias_kind == MSLK_B200_BIAS_NONE)
-          epilogue_chunk<BN, MSLK_B200_BIAS_NONE>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+          epilogue_chunk<BN, MSLK_B200_BIAS_NONE>(r, xs, ws, bs, p, yoff + c * 32, row_ok, cols_left, y_vec_ok);
         else if (p.bias_kind == MSLK_B200_BIAS_F32)
-          epilogue_chunk<BN, MSLK_B200_BIAS_F32>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+          epilogue_chunk<BN, MSLK_B200_BIAS_F32>(r, xs, ws, bs, p, yoff + c * 32, row_ok, cols_left, y_vec_ok);
         else
-          epilogue_chunk<BN, MSLK_B200_BIAS_BF16>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+          epilogue_chunk<BN, MSLK_B200_BIAS_BF16>(r, xs, ws, bs, p, yoff + c * 32, row_ok, cols_left, y_vec_ok);
       }
       tc_fence_before();
       __syncwarp();
@@ -287,7 +288,7 @@ int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, in
 
 int run(const void *xq, const void *wq, const float *xs, const float *ws, const void *bias, int bias_kind, void *y,
         const int64_t *m_sizes, int64_t G, int64_t total_m, int64_t N, int64_t K, void *scratch, size_t scratch_bytes,
-        cudaStream_t st, const char *name) {
+        cudaStream_t st, const char *name, const GemmParams *placement = nullptr) {
   if (total_m < 0 || N < 0 || K < 0 || G < 1) return fail(1, "%s: bad shape", name);
   if (total_m == 0 || N == 0) return 0;
   if (G > kMaxGroups) return fail(1, "%s: at most %d groups are supported (got %lld)", name, kMaxGroups, (long long)G);
@@ -322,9 +323,16 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   p.total_m = static_cast<int>(total_m);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
+  default_placement(p);
+  if (placement) {
+    p.n_extra = placement->n_extra;
+    p.ldy = placement->ldy;
+    p.col0 = placement->col0;
+    for (int i = 0; i < 7; ++i) p.y_extra[i] = placement->y_extra[i];
+  }
 
   // few tokens: weight-streaming kernel (operands swapped, optional K split through `scratch`)
-  if (!m_sizes && total_m <= kDecodeMaxTokens && N >= 128)
+  if (!m_sizes && !placement && total_m <= kDecodeMaxTokens && N >= 128)
     return launch_decode_kernel(xq, wq, p, scratch, scratch_bytes, false, st);
 
   // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs
@@ -366,6 +374,32 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise(const void *xq, const void *wq, const fl
   if (bias_kind < 0 || bias_kind > 2) return fail(1, "f8f8bf16_rowwise: bad bias_kind %d", bias_kind);
   return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, 1, M, N, K, nullptr, 0,
              static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise");
+}
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise_allgather(const void *xq, const void *wq_shard, const float *x_scale,
+                                                  const float *w_scale_shard, const void *bias_shard, int bias_kind,
+                                                  void *const *y_bases, int world, int rank, int64_t M,
+                                                  int64_t N_local, int64_t K, void *stream) {
+  using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
+  clear_error();
+  const char *name = "f8f8bf16_rowwise_allgather";
+  if (bias_kind < 0 || bias_kind > 2) return fail(1, "%s: bad bias_kind %d", name, bias_kind);
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(1, "%s: need 1 <= world <= 8 and 0 <= rank < world", name);
+  if (!y_bases) return fail(1, "%s: y_bases is null", name);
+  for (int r = 0; r < world; ++r)
+    if (!y_bases[r]) return fail(1, "%s: y_bases[%d] is null", name, r);
+  if (N_local * world > 0x7fffff00LL) return fail(1, "%s: N too large", name);
+  GemmParams place;
+  place.N = static_cast<int>(N_local);
+  default_placement(place);
+  place.ldy = static_cast<int>(N_local * world);
+  place.col0 = static_cast<int>(N_local * rank);
+  // peers in ring order starting after this rank, so that the ranks do not all write to the same peer first
+  for (int i = 1; i < world; ++i) place.y_extra[i - 1] = static_cast<__nv_bfloat16 *>(y_bases[(rank + i) % world]);
+  place.n_extra = world - 1;
+  return run(xq, wq_shard, x_scale, w_scale_shard, bias_shard, bias_kind, y_bases[rank], nullptr, 1, M, N_local, K,
+             nullptr, 0, static_cast<cudaStream_t>(stream), name, &place);
 }
 
 MSLK_API size_t mslk_b200_f8f8bf16_rowwise_workspace_bytes(int64_t M, int64_t N, int64_t K) {

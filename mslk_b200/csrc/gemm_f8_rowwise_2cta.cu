@@ -22,6 +22,8 @@
 // control path of both CTAs reaches them.
 #include "gemm_f8_common.cuh"
 
+#include <cstring>
+
 namespace mslk_b200 {
 namespace gemm_f8 {
 namespace {
@@ -31,11 +33,19 @@ constexpr int kPairRows = 2 * kBM;      // output rows of the pair tile
 constexpr int kStageA = kBM * kBK;      // this CTA's rows of A
 constexpr int kStageB = (kPairBN / 2) * kBK;  // this CTA's half of the B rows
 constexpr int kStageBytes = kStageA + kStageB;
-constexpr int kStages = 6;
+constexpr int kStages = 5;
+constexpr int kOutCols = 64;                       // columns of one staged output slab (128-byte rows)
+constexpr int kOutSlabBytes = 32 * kOutCols * 2;   // 32 rows x 64 bf16
+constexpr int kOutStageBytes = 4 * 2 * kOutSlabBytes;  // four epilogue warps, double-buffered
 constexpr int kTmemCols = 512;          // two 256-column accumulators
 constexpr int kPairBandM = 8;           // 8 x 256 rows per band, matching 16 x 128 of the 1-CTA kernel
 constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kPairBN >> 3) << 17) |
                             (static_cast<uint32_t>(kPairRows >> 4) << 24);
+
+// Tensor maps of the output buffers (own + up to 7 further destinations), box {64 columns, 32 rows}.
+struct OutMaps {
+  CUtensorMap m[8];
+};
 
 struct SmemTail {
   float w_scale[4][kPairBN];
@@ -50,15 +60,16 @@ struct SmemTail {
   int abort_flag;
 };
 
-constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(SmemTail);
+constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + kOutStageBytes + sizeof(SmemTail);
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 
 __global__ void __launch_bounds__(kNumThreads, 1)
     gemm_f8_rowwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                                const GemmParams p) {
+                                const __grid_constant__ OutMaps ymaps, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SmemTail &S = *reinterpret_cast<SmemTail *>(ring + static_cast<size_t>(kStages) * kStageBytes);
+  uint8_t *out_stage = ring + static_cast<size_t>(kStages) * kStageBytes;  // 1024-byte aligned slabs
+  SmemTail &S = *reinterpret_cast<SmemTail *>(out_stage + kOutStageBytes);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -178,8 +189,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int quad = warp & 3;
     const int row_in_cta = quad * 32 + lane;
     const int row_in_tile = static_cast<int>(rank) * kBM + row_in_cta;
-    const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+    bool y_vec_ok = (p.ldy % 8 == 0) && (p.col0 % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
+    for (int d = 0; d < p.n_extra; ++d) y_vec_ok = y_vec_ok && ((reinterpret_cast<uintptr_t>(p.y_extra[d]) & 15u) == 0);
     int local = 0;
+    uint32_t slab_seq = 0;
     Tile t;
     for (int tile = pair_id; sched.get(tile, t); tile += num_pairs, ++local) {
       const int acc = local & 1;
@@ -203,27 +216,64 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + static_cast<uint32_t>(acc * kPairBN) + (static_cast<uint32_t>(quad * 32) << 16);
-      __nv_bfloat16 *yrow = p.y + static_cast<size_t>(t.row0 + row_in_tile) * p.N + t.n0;
+      const int slab_row0 = static_cast<int>(rank) * kBM + quad * 32;   // first row of this warp's 32-row slab in the tile
+      if (p.tma_store && slab_row0 + 32 <= t.rows) {
+        // Full slab: scale in registers, stage 32 x 64 bf16 in shared memory (128-byte rows, 128-byte
+        // swizzle), and let TMA write 128-byte row segments to every destination.
+        uint8_t *bufs = out_stage + (warp - 2) * 2 * kOutSlabBytes;
 #pragma unroll 1
-      for (int c = 0; c < kPairBN / 32; ++c) {
-        const int cols_left = p.N - (t.n0 + c * 32);
-        if (cols_left <= 0) break;
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const float *ws = ws_s + c * 32;
-        const float *bs = bs_s + c * 32;
-        if (p.bias_kind == MSLK_B200_BIAS_NONE)
-          epilogue_chunk<kPairBN, MSLK_B200_BIAS_NONE>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
-        else if (p.bias_kind == MSLK_B200_BIAS_F32)
-          epilogue_chunk<kPairBN, MSLK_B200_BIAS_F32>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
-        else
-          epilogue_chunk<kPairBN, MSLK_B200_BIAS_BF16>(r, xs, ws, bs, yrow + c * 32, row_ok, cols_left, y_vec_ok);
+        for (int c2 = 0; c2 < kPairBN / kOutCols; ++c2) {
+          if (t.n0 + c2 * kOutCols >= p.N) break;
+          uint8_t *buf = bufs + (slab_seq++ & 1) * kOutSlabBytes;  // alternates across tiles too
+          if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done with it
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32], packed[16];
+            tmem_ld_32x32(taddr + c2 * kOutCols + h * 32, r);
+            tmem_ld_wait();
+            epilogue_pack_any(p.bias_kind, r, xs, ws_s + c2 * kOutCols + h * 32, bs_s + c2 * kOutCols + h * 32, packed);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int chunk = (h * 4 + q) ^ (lane & 7);
+              *reinterpret_cast<uint4 *>(buf + lane * 128 + chunk * 16) =
+                  make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int x = p.col0 + t.n0 + c2 * kOutCols;
+            const int y = t.row0 + slab_row0;
+            for (int d = 0; d <= p.n_extra; ++d) tma_store_2d(&ymaps.m[d], buf, x, y);
+            tma_store_commit();
+          }
+        }
+      } else {
+        const size_t yoff = static_cast<size_t>(t.row0 + row_in_tile) * p.ldy + p.col0 + t.n0;
+#pragma unroll 1
+        for (int c = 0; c < kPairBN / 32; ++c) {
+          const int cols_left = p.N - (t.n0 + c * 32);
+          if (cols_left <= 0) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const float *ws = ws_s + c * 32;
+          const float *bs = bs_s + c * 32;
+          if (p.bias_kind == MSLK_B200_BIAS_NONE)
+            epilogue_chunk<kPairBN, MSLK_B200_BIAS_NONE>(r, xs, ws, bs, p, yoff + c * 32, row_ok, cols_left, y_vec_ok);
+          else if (p.bias_kind == MSLK_B200_BIAS_F32)
+            epilogue_chunk<kPairBN, MSLK_B200_BIAS_F32>(r, xs, ws, bs, p, yoff + c * 32, row_ok, cols_left, y_vec_ok);
+          else
+            epilogue_chunk<kPairBN, MSLK_B200_BIAS_BF16>(r, xs, ws, bs, p, yoff + c * 32, row_ok, cols_left, y_vec_ok);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty[acc]), 0));
     }
+    if (lane == 0) tma_store_wait<0>();  // every staged slab has been written out before the CTA leaves
+    __syncwarp();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -285,8 +335,30 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
                                   CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
 
+  // Output through shared memory + TMA stores when every destination allows it: 16-byte aligned
+  // bases and row pitch, column window aligned to 8 and a multiple of the 64-column slab (a slab
+  // must never spill into a neighbouring column block).
+  GemmParams q = p;
+  OutMaps ymaps;
+  memset(&ymaps, 0, sizeof(ymaps));
+  bool tma_ok = (q.ldy % 8 == 0) && (q.col0 % 8 == 0) && (q.N % kOutCols == 0);
+  for (int d = 0; d <= q.n_extra && tma_ok; ++d) {
+    const void *base = d == 0 ? static_cast<const void *>(q.y) : static_cast<const void *>(q.y_extra[d - 1]);
+    tma_ok = (reinterpret_cast<uintptr_t>(base) & 15u) == 0;
+  }
+  if (tma_ok) {
+    for (int d = 0; d <= q.n_extra; ++d) {
+      const void *base = d == 0 ? static_cast<const void *>(q.y) : static_cast<const void *>(q.y_extra[d - 1]);
+      if (int rc = make_tmap_2d_bf16(&ymaps.m[d], base, q.ldy, q.total_m, static_cast<uint64_t>(q.ldy) * 2, kOutCols, 32,
+                                     CU_TENSOR_MAP_SWIZZLE_128B))
+        return rc;
+    }
+  }
+  q.tma_store = tma_ok ? 1 : 0;
+
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel, ta, tb, p), "f8f8bf16_rowwise pair launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel, ta, tb, ymaps, q),
+                    "f8f8bf16_rowwise pair launch");
 }
 
 }  // namespace gemm_f8

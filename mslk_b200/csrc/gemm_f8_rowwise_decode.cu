@@ -421,6 +421,7 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, 
   p.total_m = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
+  default_placement(p);
   // scratch_is_clean = false: the tickets are zeroed on the stream before the launch
   return launch_decode_kernel(xq, wq, p, scratch, kBuiltinScratchBytes, false, static_cast<cudaStream_t>(stream));
 }

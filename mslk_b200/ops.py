@@ -233,3 +233,32 @@ def f4f4bf16(XQ, WQ, x_scale, w_scale, output=None, global_scale=None, mxfp4_blo
         check(lib.mslk_b200_f4f4bf16(_ptr(XQ), _ptr(WQ), _ptr(x_scale), _ptr(w_scale), _ptr(gs), _ptr(output),
                                      M, N, K, _stream(dev)), name)
     return output
+
+
+# --------------------------------------------------------------------------- fused GEMM + all-gather
+
+def f8f8bf16_rowwise_allgather(XQ, WQ_shard, x_scale, w_scale_shard, out_ptrs, rank: int, out_local: torch.Tensor,
+                               bias_shard=None) -> torch.Tensor:
+    """N-sharded GEMM whose epilogue writes this rank's ``[M, N/P]`` column block into the
+    ``[M, N]`` output buffer of every rank (``out_ptrs``: device pointers of all ranks' buffers,
+    e.g. ``torch.distributed._symmetric_memory`` ``buffer_ptrs``; ``out_local`` is this rank's).
+    Ranks must synchronise afterwards before reading columns written by peers."""
+    import ctypes
+    dev = _check_rowwise_args("f8f8bf16_rowwise_allgather", XQ, WQ_shard, x_scale, w_scale_shard)
+    M, K = XQ.shape
+    n_local = WQ_shard.shape[0]
+    world = len(out_ptrs)
+    if out_local.dtype != torch.bfloat16 or tuple(out_local.shape) != (M, n_local * world) or not out_local.is_contiguous():
+        raise RuntimeError("f8f8bf16_rowwise_allgather: out_local must be a contiguous bfloat16 [M, N] tensor")
+    if int(out_ptrs[rank]) != out_local.data_ptr():
+        raise RuntimeError("f8f8bf16_rowwise_allgather: out_ptrs[rank] must be the address of out_local")
+    kind = 0
+    if bias_shard is not None:
+        kind = 1 if bias_shard.dtype == torch.float32 else 2
+    arr = (ctypes.c_void_p * world)(*[int(p) for p in out_ptrs])
+    xs, ws = x_scale.contiguous(), w_scale_shard.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f8f8bf16_rowwise_allgather(
+            _ptr(XQ), _ptr(WQ_shard), _ptr(xs), _ptr(ws), _ptr(bias_shard), kind, arr, world, rank,
+            M, n_local, K, _stream(dev)), "f8f8bf16_rowwise_allgather")
+    return out_local

@@ -221,3 +221,22 @@ def test_workspace_reuse_and_dirty_scratch(ops):
                                                 y.data_ptr(), M, N, K, scratch.data_ptr(), nbytes, st), "ws")
         _close(y, y_ref, "dirty scratch")
     assert _status() == 0
+
+
+@pytest.mark.parametrize("M,N_local,K,world", [(300, 256, 512, 2), (4096, 2048, 1024, 4), (64, 520, 256, 3)])
+def test_fused_allgather_placement_emulated_on_one_gpu(ops, M, N_local, K, world):
+    # the ranks' output buffers are emulated by `world` buffers on this GPU; every "rank" writes its
+    # column block into all of them, so each buffer must end up holding the unsharded result
+    xq, wq, xs, ws = _quant(ops, M, N_local * world, K, seed=7)
+    bias = torch.randn(N_local * world, device="cuda")
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws, bias)
+    bufs = [torch.zeros((M, N_local * world), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptrs = [b.data_ptr() for b in bufs]
+    for r in range(world):
+        sl = slice(r * N_local, (r + 1) * N_local)
+        ops.f8f8bf16_rowwise_allgather(xq, wq[sl].contiguous(), xs, ws[sl].contiguous(), ptrs, r, bufs[r],
+                                       bias_shard=bias[sl].contiguous())
+    for b in bufs:
+        _close(b, y_ref, "fused all-gather placement")
+    assert all(torch.equal(b, bufs[0]) for b in bufs)
+    assert _status() == 0
