@@ -94,6 +94,25 @@ int mslk_b200_f8f8bf16_rowwise_allgather(const void *xq, const void *wq_shard, c
                                          int64_t M, int64_t N_local, int64_t K, void *stream);
 
 /*
+ * K-sharded GEMM fused with the data movement of a reduce-scatter over the token dimension.
+ * Rank `rank` of `world` multiplies its K slices (xq_kshard [M, K_local], wq_kshard [N, K_local];
+ * x_scale / w_scale are the scales of the UNSHARDED rows, so the scaled partial products add up)
+ * and its epilogue deposits rows [o*M/world, (o+1)*M/world) of the partial product in slot `rank`
+ * of owner o's staging buffer: stage_bases is a HOST array of `world` device pointers to bf16
+ * [world, M/world, N] buffers (stage_bases[rank] local, the others peer-mapped), written with TMA
+ * stores over NVLink tile by tile while the GEMM runs.  After the ranks have synchronised, every
+ * rank calls mslk_b200_reduce_slots_bf16 on its own staging buffer to get its [M/world, N] rows of
+ * the sum (fp32 accumulation in rank order).  Needs M % (32*world) == 0, N % 64 == 0.
+ * New with respect to the reference (single-GPU operator).
+ */
+int mslk_b200_f8f8bf16_rowwise_scatter(const void *xq_kshard, const void *wq_kshard,
+                                       const float *x_scale, const float *w_scale,
+                                       void *const *stage_bases, int world, int rank, int64_t M,
+                                       int64_t N, int64_t K_local, void *stream);
+int mslk_b200_reduce_slots_bf16(const void *slots_base, int slots, int64_t rows, int64_t cols,
+                                void *out, void *stream);
+
+/*
  * Same operation with caller-provided scratch memory.  For few-token shapes (M <= 32) the
  * kernel streams the weights with the K dimension split over several CTAs; the partial sums
  * and their completion tickets live in `workspace`.  mslk_b200_f8f8bf16_rowwise_workspace_bytes

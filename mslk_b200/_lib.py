@@ -37,6 +37,10 @@ lib.mslk_b200_f8f8bf16_rowwise_ws.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_allgather.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, ctypes.POINTER(_vp), _int, _int,
                                                      _i64, _i64, _i64, _vp]
 lib.mslk_b200_f8f8bf16_rowwise_allgather.restype = _int
+lib.mslk_b200_f8f8bf16_rowwise_scatter.argtypes = [_vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _int, _int, _i64, _i64, _i64, _vp]
+lib.mslk_b200_f8f8bf16_rowwise_scatter.restype = _int
+lib.mslk_b200_reduce_slots_bf16.argtypes = [_vp, _int, _i64, _i64, _vp, _vp]
+lib.mslk_b200_reduce_slots_bf16.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_noalloc.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f8f8bf16_rowwise_noalloc.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]

@@ -39,6 +39,12 @@ struct GemmParams {
   int ldy;
   int col0;
   int tma_store;  // pair kernel: full 32-row slabs leave through shared memory and TMA stores
+  // Row-scatter mode (K-sharded GEMM feeding a reduce-scatter): rs_rows > 0 sends every 32-row slab
+  // to ONE destination, the owner of its rows (owner = row / rs_rows; destinations are y, y_extra[0..]
+  // in rank order), at row rs_slot * rs_rows + row % rs_rows of that destination's
+  // [world * rs_rows, N] staging buffer; the owner sums the slots afterwards.
+  int rs_rows;
+  int rs_slot;
 };
 
 inline void default_placement(GemmParams &p) {
@@ -46,6 +52,8 @@ inline void default_placement(GemmParams &p) {
   p.ldy = p.N;
   p.col0 = 0;
   p.tma_store = 0;
+  p.rs_rows = 0;
+  p.rs_slot = 0;
   for (auto &e : p.y_extra) e = nullptr;
 }
 

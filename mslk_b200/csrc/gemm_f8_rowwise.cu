@@ -329,6 +329,8 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
     p.ldy = placement->ldy;
     p.col0 = placement->col0;
     for (int i = 0; i < 7; ++i) p.y_extra[i] = placement->y_extra[i];
+    p.rs_rows = placement->rs_rows;
+    p.rs_slot = placement->rs_slot;
   }
 
   // few tokens: weight-streaming kernel (operands swapped, optional K split through `scratch`)
@@ -341,10 +343,11 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
     return !e ? 0 : (e[0] == '2' ? 2 : 1);
   }();
   const int64_t pair_tiles = ((total_m + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
-  const bool want_pair = force == 2 || (force == 0 && !m_sizes && bn == 256 && pair_tiles >= sms / 2);
+  const bool want_pair = force == 2 || p.rs_rows > 0 || (force == 0 && !m_sizes && bn == 256 && pair_tiles >= sms / 2);
   if (want_pair) {
     const int rc = launch_pair_kernel(xq, wq, p, st);
     if (rc >= 0) return rc;  // -1: pairs unavailable on this device, fall through to one CTA per tile
+    if (p.rs_rows > 0) return fail(2, "%s: the row-scatter GEMM needs CTA pairs, which this device cannot run", name);
   }
 
   CUtensorMap ta, tb;
@@ -400,6 +403,30 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_allgather(const void *xq, const void *wq
   place.n_extra = world - 1;
   return run(xq, wq_shard, x_scale, w_scale_shard, bias_shard, bias_kind, y_bases[rank], nullptr, 1, M, N_local, K,
              nullptr, 0, static_cast<cudaStream_t>(stream), name, &place);
+}
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise_scatter(const void *xq_kshard, const void *wq_kshard, const float *x_scale,
+                                                const float *w_scale, void *const *stage_bases, int world, int rank,
+                                                int64_t M, int64_t N, int64_t K_local, void *stream) {
+  using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
+  clear_error();
+  const char *name = "f8f8bf16_rowwise_scatter";
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(1, "%s: need 1 <= world <= 8 and 0 <= rank < world", name);
+  if (!stage_bases) return fail(1, "%s: stage_bases is null", name);
+  for (int r = 0; r < world; ++r)
+    if (!stage_bases[r]) return fail(1, "%s: stage_bases[%d] is null", name, r);
+  if (M <= 0 || M % (32 * world) != 0) return fail(1, "%s: M (%lld) must be a positive multiple of 32*world", name, (long long)M);
+  if (N % 64 != 0) return fail(1, "%s: N (%lld) must be a multiple of 64", name, (long long)N);
+  GemmParams place;
+  place.N = static_cast<int>(N);
+  default_placement(place);
+  for (int i = 1; i < world; ++i) place.y_extra[i - 1] = static_cast<__nv_bfloat16 *>(stage_bases[i]);
+  place.n_extra = world - 1;
+  place.rs_rows = static_cast<int>(M / world);
+  place.rs_slot = rank;
+  return run(xq_kshard, wq_kshard, x_scale, w_scale, nullptr, MSLK_B200_BIAS_NONE, stage_bases[0], nullptr, 1, M, N,
+             K_local, nullptr, 0, static_cast<cudaStream_t>(stream), name, &place);
 }
 
 MSLK_API size_t mslk_b200_f8f8bf16_rowwise_workspace_bytes(int64_t M, int64_t N, int64_t K) {

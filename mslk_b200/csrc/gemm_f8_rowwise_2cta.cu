@@ -245,7 +245,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (lane == 0) {
             const int x = p.col0 + t.n0 + c2 * kOutCols;
             const int y = t.row0 + slab_row0;
-            for (int d = 0; d <= p.n_extra; ++d) tma_store_2d(&ymaps.m[d], buf, x, y);
+            if (p.rs_rows > 0) {
+              const int owner = y / p.rs_rows;
+              tma_store_2d(&ymaps.m[owner], buf, x, p.rs_slot * p.rs_rows + (y - owner * p.rs_rows));
+            } else {
+              for (int d = 0; d <= p.n_extra; ++d) tma_store_2d(&ymaps.m[d], buf, x, y);
+            }
             tma_store_commit();
           }
         }
@@ -355,6 +360,8 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
     }
   }
   q.tma_store = tma_ok ? 1 : 0;
+  if (q.rs_rows > 0 && (!tma_ok || q.rs_rows % 32 != 0 || q.total_m % 32 != 0))
+    return fail(1, "row-scatter GEMM needs 16-byte aligned buffers, N %% 64 == 0 and rows per rank %% 32 == 0");
 
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel, ta, tb, ymaps, q),

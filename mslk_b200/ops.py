@@ -262,3 +262,35 @@ def f8f8bf16_rowwise_allgather(XQ, WQ_shard, x_scale, w_scale_shard, out_ptrs, r
             _ptr(XQ), _ptr(WQ_shard), _ptr(xs), _ptr(ws), _ptr(bias_shard), kind, arr, world, rank,
             M, n_local, K, _stream(dev)), "f8f8bf16_rowwise_allgather")
     return out_local
+
+
+# --------------------------------------------------------------------------- fused GEMM + reduce-scatter
+
+def f8f8bf16_rowwise_scatter(XQ_kshard, WQ_kshard, x_scale, w_scale, stage_ptrs, rank: int) -> None:
+    """K-sharded GEMM whose epilogue deposits each owner's rows of the partial product in slot
+    ``rank`` of that owner's ``[world, M/world, N]`` bf16 staging buffer (``stage_ptrs``: device
+    pointers of all ranks' staging buffers).  Follow with a cross-rank barrier and
+    :func:`reduce_slots` on the local staging buffer."""
+    import ctypes
+    dev = _check_rowwise_args("f8f8bf16_rowwise_scatter", XQ_kshard, WQ_kshard, x_scale, w_scale)
+    M, K = XQ_kshard.shape
+    N = WQ_kshard.shape[0]
+    world = len(stage_ptrs)
+    arr = (ctypes.c_void_p * world)(*[int(p) for p in stage_ptrs])
+    xs, ws = x_scale.contiguous(), w_scale.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f8f8bf16_rowwise_scatter(_ptr(XQ_kshard), _ptr(WQ_kshard), _ptr(xs), _ptr(ws), arr, world,
+                                                     rank, M, N, K, _stream(dev)), "f8f8bf16_rowwise_scatter")
+
+
+def reduce_slots(stage: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[rows, N] = sum_s stage[s]`` for a contiguous bf16 ``[slots, rows, N]`` tensor (fp32 accumulation)."""
+    dev = _require_cuda("reduce_slots", stage)
+    slots, rows, cols = stage.shape
+    if stage.dtype != torch.bfloat16 or not stage.is_contiguous():
+        raise RuntimeError("reduce_slots: stage must be a contiguous bfloat16 [slots, rows, N] tensor")
+    if out is None:
+        out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_reduce_slots_bf16(_ptr(stage), slots, rows, cols, _ptr(out), _stream(dev)), "reduce_slots")
+    return out

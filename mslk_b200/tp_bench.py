@@ -117,6 +117,30 @@ def bench_ffn70b(ops, par, rank, world, device, args):
                    "gemm_tflops": flops / ms_gemm / 1e9, "with_collective_ms": ms_full,
                    "with_collective_tflops": flops / ms_full / 1e9,
                    "scattered_bytes_per_gpu": (world - 1) * (M_TOKENS // world) * N * 2}
+    # ---- same, fused: partial rows leave the epilogue straight into the owners' staging slots
+    if world > 1:
+        import torch.distributed._symmetric_memory as symm_mem
+        y_ref = row.forward(xq_k, xs).clone()
+        rows = M_TOKENS // world
+        stage = symm_mem.empty((world, rows, N), dtype=torch.bfloat16, device=device)
+        hdl = symm_mem.rendezvous(stage, dist.group.WORLD)
+        ptrs = list(hdl.buffer_ptrs)
+        y_out = torch.empty((rows, N), dtype=torch.bfloat16, device=device)
+
+        def fused():
+            ops.f8f8bf16_rowwise_scatter(xq_k, wq_k, xs, ws, ptrs, rank)
+            hdl.barrier()                       # every rank's partial rows have landed
+            ops.reduce_slots(stage, y_out)
+            hdl.barrier()                       # nobody overwrites a slot that is still being summed
+
+        fused()
+        torch.cuda.synchronize()
+        err = float((y_out.float() - y_ref.float()).abs().max())
+        ok = bool(torch.allclose(y_out.float(), y_ref.float(), rtol=1.6e-2, atol=1e-2 * max(1.0, float(y_ref.float().std()))))
+        ms_fused = _timed(fused, args.steps, args.warmup, device)
+        out["down"].update({"fused_epilogue_scatter_ms": ms_fused, "fused_epilogue_scatter_tflops": flops / ms_fused / 1e9,
+                            "fused_within_tolerance_of_nccl_path": ok, "fused_max_abs_diff": err})
+        del stage, hdl
     return out
 
 

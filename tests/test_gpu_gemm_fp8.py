@@ -240,3 +240,24 @@ def test_fused_allgather_placement_emulated_on_one_gpu(ops, M, N_local, K, world
         _close(b, y_ref, "fused all-gather placement")
     assert all(torch.equal(b, bufs[0]) for b in bufs)
     assert _status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,world", [(512, 256, 1024, 2), (1024, 1024, 2048, 4), (768, 320, 768, 3)])
+def test_fused_reduce_scatter_emulated_on_one_gpu(ops, M, N, K, world):
+    # K-sharded partial products are deposited by each "rank" into the owners' staging slots, then
+    # every owner sums its slots: together the owners hold the unsharded result
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=11)
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws)
+    rows = M // world
+    stages = [torch.full((world, rows, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptrs = [s.data_ptr() for s in stages]
+    kl = K // world
+    for r in range(world):
+        ops.f8f8bf16_rowwise_scatter(xq[:, r * kl:(r + 1) * kl].contiguous(), wq[:, r * kl:(r + 1) * kl].contiguous(),
+                                     xs, ws, ptrs, r)
+    y = torch.cat([ops.reduce_slots(s) for s in stages], dim=0)
+    _close(y, y_ref, "fused reduce-scatter")
+    # slot contents are the individual partial products
+    part0 = oracle.gemm_f8_rowwise_torch(xq[:, :kl].contiguous(), wq[:, :kl].contiguous(), xs, ws)
+    _close(stages[1][0], part0[rows:2 * rows], "slot of rank 0 in owner 1")
+    assert _status() == 0
