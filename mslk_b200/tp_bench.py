@@ -120,27 +120,40 @@ def bench_ffn70b(ops, par, rank, world, device, args):
     # ---- same, fused: partial rows leave the epilogue straight into the owners' staging slots
     if world > 1:
         import torch.distributed._symmetric_memory as symm_mem
-        y_ref = row.forward(xq_k, xs).clone()
         rows = M_TOKENS // world
-        stage = symm_mem.empty((world, rows, N), dtype=torch.bfloat16, device=device)
-        hdl = symm_mem.rendezvous(stage, dist.group.WORLD)
-        ptrs = list(hdl.buffer_ptrs)
+        # fp32 reference of the unsharded product for this rank's rows: all-reduce of fp32 partials
+        ref = (xq_k.float() @ wq_k.float().T) * xs[:, None] * ws[None, :]
+        dist.all_reduce(ref)
+        ref = ref[rank * rows:(rank + 1) * rows]
+        y_nccl = row.forward(xq_k, xs).float()
+        # two staging buffers used alternately: one cross-rank barrier per call is then enough (a slot
+        # is rewritten two calls later, after its owner's reduction has been passed by a barrier)
+        stages, handles = [], []
+        for _ in range(2):
+            st = symm_mem.empty((world, rows, N), dtype=torch.bfloat16, device=device)
+            handles.append(symm_mem.rendezvous(st, dist.group.WORLD))
+            stages.append(st)
         y_out = torch.empty((rows, N), dtype=torch.bfloat16, device=device)
+        turn = [0]
 
         def fused():
-            ops.f8f8bf16_rowwise_scatter(xq_k, wq_k, xs, ws, ptrs, rank)
-            hdl.barrier()                       # every rank's partial rows have landed
-            ops.reduce_slots(stage, y_out)
-            hdl.barrier()                       # nobody overwrites a slot that is still being summed
+            i = turn[0] & 1
+            turn[0] += 1
+            ops.f8f8bf16_rowwise_scatter(xq_k, wq_k, xs, ws, list(handles[i].buffer_ptrs), rank)
+            handles[i].barrier()                # every rank's partial rows have landed
+            ops.reduce_slots(stages[i], y_out)
 
         fused()
         torch.cuda.synchronize()
-        err = float((y_out.float() - y_ref.float()).abs().max())
-        ok = bool(torch.allclose(y_out.float(), y_ref.float(), rtol=1.6e-2, atol=1e-2 * max(1.0, float(y_ref.float().std()))))
+        scale = max(1.0, float(ref.std()))
         ms_fused = _timed(fused, args.steps, args.warmup, device)
-        out["down"].update({"fused_epilogue_scatter_ms": ms_fused, "fused_epilogue_scatter_tflops": flops / ms_fused / 1e9,
-                            "fused_within_tolerance_of_nccl_path": ok, "fused_max_abs_diff": err})
-        del stage, hdl
+        torch.cuda.synchronize()
+        out["down"].update({
+            "fused_epilogue_scatter_ms": ms_fused, "fused_epilogue_scatter_tflops": flops / ms_fused / 1e9,
+            "fused_within_tolerance_of_fp32_reference": bool(torch.allclose(y_out.float(), ref, rtol=1.6e-2, atol=1e-2 * scale)),
+            "max_abs_err_vs_fp32_reference": {"fused": float((y_out.float() - ref).abs().max()),
+                                              "nccl_bf16_reduce_scatter": float((y_nccl - ref).abs().max())}})
+        del stages, handles, ref
     return out
 
 
