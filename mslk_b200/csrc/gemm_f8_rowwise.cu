@@ -333,8 +333,10 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
     p.rs_slot = placement->rs_slot;
   }
 
-  // few tokens: weight-streaming kernel (operands swapped, optional K split through `scratch`)
-  if (!m_sizes && !placement && total_m <= kDecodeMaxTokens && N >= 128)
+  // few tokens AND scratch given: weight-streaming kernel with the K dimension split.  Opt-in: on
+  // the shapes measured (Llama-3-8B projections, M = 1..32) the 32-column tiles of the general
+  // kernel below finish sooner than split + partial sums + tickets, so no scratch = general kernel.
+  if (!m_sizes && !placement && scratch && total_m <= kDecodeMaxTokens && N >= 128)
     return launch_decode_kernel(xq, wq, p, scratch, scratch_bytes, false, st);
 
   // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs

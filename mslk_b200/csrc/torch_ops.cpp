@@ -64,14 +64,8 @@ void rowwise_impl(const at::Tensor &XQ, const at::Tensor &WQ, const at::Tensor &
   }
   c10::cuda::CUDAGuard guard(XQ.device());
   const at::Tensor xs = x_scale.contiguous(), ws = w_scale.contiguous();
-  // scratch for the split-K path of few-token shapes: from the caching allocator, like the
-  // reference's own workspace (f8f8bf16_rowwise_common.cuh:321-322)
-  const size_t ws_bytes = mslk_b200_f8f8bf16_rowwise_workspace_bytes(M, N, K);
-  at::Tensor workspace;
-  if (ws_bytes) workspace = at::empty({static_cast<int64_t>(ws_bytes)}, XQ.options().dtype(at::kByte));
-  check_rc(mslk_b200_f8f8bf16_rowwise_ws(XQ.data_ptr(), WQ.data_ptr(), xs.data_ptr<float>(), ws.data_ptr<float>(),
-                                         kind ? b.data_ptr() : nullptr, kind, out.data_ptr(), M, N, K,
-                                         ws_bytes ? workspace.data_ptr() : nullptr, ws_bytes, stream_of(XQ)),
+  check_rc(mslk_b200_f8f8bf16_rowwise(XQ.data_ptr(), WQ.data_ptr(), xs.data_ptr<float>(), ws.data_ptr<float>(),
+                                      kind ? b.data_ptr() : nullptr, kind, out.data_ptr(), M, N, K, stream_of(XQ)),
            "f8f8bf16_rowwise");
 }
 

@@ -135,13 +135,9 @@ def f8f8bf16_rowwise_out(XQ, WQ, x_scale, w_scale, output, bias=None, use_fast_a
         bias = bias.contiguous()
     xs, ws = x_scale.contiguous(), w_scale.contiguous()
     with torch.cuda.device(dev):
-        # scratch for the split-K path of few-token shapes, from the caching allocator like the
-        # reference's own workspace
-        nbytes = lib.mslk_b200_f8f8bf16_rowwise_workspace_bytes(M, N, K)
-        workspace = torch.empty((nbytes,), dtype=torch.uint8, device=dev) if nbytes else None
-        check(lib.mslk_b200_f8f8bf16_rowwise_ws(
-            _ptr(XQ), _ptr(WQ), _ptr(xs), _ptr(ws), _ptr(bias), kind, _ptr(output), M, N, K,
-            _ptr(workspace), nbytes, _stream(dev)), "f8f8bf16_rowwise")
+        check(lib.mslk_b200_f8f8bf16_rowwise(
+            _ptr(XQ), _ptr(WQ), _ptr(xs), _ptr(ws), _ptr(bias), kind, _ptr(output), M, N, K, _stream(dev)),
+            "f8f8bf16_rowwise")
 
 
 def f8f8bf16_rowwise(XQ, WQ, x_scale, w_scale, bias=None, use_fast_accum: bool = True) -> torch.Tensor:

@@ -188,12 +188,23 @@ def test_grouped_moe_shape_zipf(ops):
 @pytest.mark.parametrize("M", [1, 3, 16, 17, 32, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 128), (1000, 512), (4096, 4096), (6144, 1024)])
 def test_few_token_shapes_split_and_unsplit(ops, M, N, K):
-    # M <= 32 takes the weight-streaming kernel (with scratch the K dimension is split); larger M the general one
+    # with scratch, M <= 32 takes the weight-streaming split-K kernel; without, the general kernel
     from mslk_b200._lib import lib, check
     xq, wq, xs, ws = _quant(ops, M, N, K, seed=M + N, w_std=1.0)
     bias = torch.randn(N, device="cuda") if (M + N) % 2 else None
     y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws, bias)
-    y = ops.f8f8bf16_rowwise(xq, wq, xs, ws, bias=bias)            # scratch from the allocator (split when useful)
+    st = torch.cuda.current_stream().cuda_stream
+    bptr, bkind = (None, 0) if bias is None else (bias.data_ptr(), 1)
+
+    def split_call():
+        nbytes = lib.mslk_b200_f8f8bf16_rowwise_workspace_bytes(M, N, K)
+        scratch = torch.empty((max(nbytes, 16),), dtype=torch.uint8, device="cuda")
+        out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        check(lib.mslk_b200_f8f8bf16_rowwise_ws(xq.data_ptr(), wq.data_ptr(), xs.data_ptr(), ws.data_ptr(), bptr, bkind,
+                                                out.data_ptr(), M, N, K, scratch.data_ptr(), nbytes, st), "ws")
+        return out
+
+    y = split_call()                                                # weight-streaming kernel, K split when useful
     _close(y, y_ref, f"decode split {M}x{N}x{K}")
     y2 = torch.empty_like(y)
     check(lib.mslk_b200_f8f8bf16_rowwise(xq.data_ptr(), wq.data_ptr(), xs.data_ptr(), ws.data_ptr(),
@@ -201,8 +212,7 @@ def test_few_token_shapes_split_and_unsplit(ops, M, N, K):
                                          y2.data_ptr(), M, N, K, torch.cuda.current_stream().cuda_stream), "plain")
     _close(y2, y_ref, f"decode unsplit {M}x{N}x{K}")
     # the split result does not depend on CTA finishing order: repeated calls are bit-identical
-    y3 = ops.f8f8bf16_rowwise(xq, wq, xs, ws, bias=bias)
-    assert torch.equal(y3, y)
+    assert torch.equal(split_call(), y)
     assert _status() == 0
 
 
