@@ -325,7 +325,11 @@ def run_ours(args, rank, world, local_rank):
         line.update({
             "value": value, "ms_per_step": per_step_ms, "gpu_launches": 2 * len(layers) * args.steps,
             "roofline": {"bound": "tensor", "kernel": "gemm_f8_rowwise_pair_kernel", "achieved": achieved,
-                         "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak, "traffic": None,
+                         "peak": fp8_peak, "unit": "TFLOP/s", "frac": achieved / fp8_peak,
+                         # DRAM bytes per launch, mean over the step's four GEMM launches, from the ncu capture of this
+                         # same command (profiles/bench_gemm_dram_traffic__llama3_8b_layer_step.md); the algorithmic
+                         # mean (operands + output once) is 285e6
+                         "traffic": 436.0e6, "algorithmic_bytes_per_launch": 285.0e6,
                          "peak_source": f"2 x bf16_tflops{'_sustained' if long_run else ' (burst)'} of {peaks['source']} peaks "
                                         "(the fp8 tensor rate is twice the bf16 rate)",
                          "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,

@@ -345,7 +345,9 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
     return !e ? 0 : (e[0] == '2' ? 2 : 1);
   }();
   const int64_t pair_tiles = ((total_m + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
-  const bool want_pair = force == 2 || p.rs_rows > 0 || (force == 0 && !m_sizes && bn == 256 && pair_tiles >= sms / 2);
+  // grouped problems: pairs pay off only when the average group is several 256-row tiles tall
+  const bool groups_tall = !m_sizes || total_m / G >= 512;
+  const bool want_pair = force == 2 || p.rs_rows > 0 || (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2);
   if (want_pair) {
     const int rc = launch_pair_kernel(xq, wq, p, st);
     if (rc >= 0) return rc;  // -1: pairs unavailable on this device, fall through to one CTA per tile
