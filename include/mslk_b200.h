@@ -187,6 +187,31 @@ int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale,
                        const void *w_scale, const float *global_scale, void *y, int64_t M,
                        int64_t N, int64_t K, void *stream);
 
+/*
+ * Fused SwiGLU + per-row FP8 quantization:  y = x0 * sigmoid(x0) * x1 (fp32),
+ *     rmax = min(max(max_k |y|, 1e-12), *scale_ub)        (scale_ub may be NULL)
+ *     q[r, k] = e4m3_rn_satfinite(y * (448 / rmax)),  inv_scale[r] = 1 / (448 / rmax).
+ * Replaces: mslk/moe/activation.py:72-133 (silu_mul_quant) and its kernel
+ *           _mslk_silu_mul_quant (:220-294); sigmoid and the divisions use the same
+ *           approximate instructions that kernel lowers to, so outputs agree bit for bit.
+ * x0, x1: [T, D] of `dtype` (MSLK_B200_BF16 or MSLK_B200_F16), unit inner stride, row
+ * strides stride0 / stride1 in elements.  q: [T, D] bytes contiguous; inv_scale: fp32 [T].
+ * valid_token_count (device int32 scalar, may be NULL): rows >= *valid_token_count are
+ * neither read nor written.
+ */
+int mslk_b200_silu_mul_quant(const void *x0, const void *x1, int dtype, int64_t T, int64_t D,
+                             int64_t stride0, int64_t stride1, const float *scale_ub,
+                             const int *valid_token_count, void *q, float *inv_scale,
+                             void *stream);
+
+/*
+ * SwiGLU without quantization: y = x0 * sigmoid(x0) * x1, y [T, D] contiguous in the
+ * input dtype.  Replaces: mslk/moe/activation.py:25-69 (silu_mul), kernel :181-217.
+ */
+int mslk_b200_silu_mul(const void *x0, const void *x1, int dtype, int64_t T, int64_t D,
+                       int64_t stride0, int64_t stride1, const int *valid_token_count, void *y,
+                       void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -3,7 +3,7 @@
 ``install()`` registers this package's mirror modules under the reference's module names in
 ``sys.modules``, so code written against MSLK's FP8-rowwise / NVFP4 path
 (``torch.ops.mslk.f8f8bf16_rowwise``, ``mslk.quantize.triton.fp8_quantize.quantize_fp8_row``,
-``mslk.quantize.triton.fp4_quantize.triton_quantize_nvfp4``, ``mslk.quantize.triton.fp4_utils.*``)
+``mslk.quantize.triton.fp4_quantize.triton_quantize_nvfp4``, ``mslk.quantize.triton.fp4_utils.*``, ``mslk.moe.activation.silu_mul_quant``)
 runs unchanged on the B200 kernels.  It refuses to shadow a real ``mslk`` that is already imported.
 """
 
@@ -18,6 +18,8 @@ _ALIASES = {
     "mslk.quantize.triton.fp8_quantize": "mslk_b200.quantize.triton.fp8_quantize",
     "mslk.quantize.triton.fp4_quantize": "mslk_b200.quantize.triton.fp4_quantize",
     "mslk.quantize.triton.fp4_utils": "mslk_b200.quantize.triton.fp4_utils",
+    "mslk.moe": "mslk_b200.moe",
+    "mslk.moe.activation": "mslk_b200.moe.activation",
 }
 
 

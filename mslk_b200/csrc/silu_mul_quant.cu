@@ -1,0 +1,308 @@
+// Fused SwiGLU + per-row FP8 quantization for sm_100a:  y = x0 * sigmoid(x0) * x1, then
+// (q, inv_scale) = rowwise e4m3 quantization of y.  This is the step between the gate+up and
+// the down projection of an FFN (the reference's Triton kernel: mslk/moe/activation.py:220-294).
+//
+// Arithmetic, operation for operation as the reference's kernel lowers on NVIDIA GPUs:
+//     e      = ex2.approx(-x0 * log2(e))             sigmoid(x0) = 1 / (1 + e), division = div.full
+//     y      = (x0 * sigmoid) * x1                    fp32
+//     rmax   = min(max(max_k |y|, 1e-12), *scale_ub)
+//     yscale = 448 / rmax                             div.full;  inv_scale = 1 / yscale (div.full)
+//     q      = e4m3_rn_satfinite(y * yscale)
+// (Note the differences from quantize_fp8_row: reciprocal scale applied by multiplication,
+// floor 1e-12, the INVERSE scale is what is stored.)
+//
+// HBM-bound: 4 bytes read + 1 byte written per element (bf16 inputs).  One block per row; each
+// thread keeps its share of y in registers (fp32) across the row-max reduction, so x0/x1 are read
+// once.  Rows at or beyond *valid_token_count are left untouched.
+#include "../../include/mslk_b200.h"
+#include "common.cuh"
+#include "host.h"
+
+#include <algorithm>
+
+namespace mslk_b200 {
+namespace {
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float div_full(float a, float b) {
+  float r;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float silu_mul(float x0, float x1) {
+  const float e = ex2_approx(__fmul_rn(-x0, 1.4426950408889634f));
+  const float sig = div_full(1.0f, __fadd_rn(1.0f, e));
+  return __fmul_rn(__fmul_rn(x0, sig), x1);
+}
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]);
+template <>
+__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4 &v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void unpack8<__half>(const uint4 &v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 p = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+    f[2 * i] = p.x;
+    f[2 * i + 1] = p.y;
+  }
+}
+
+__device__ __forceinline__ uint4 ld_stream_v4(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+struct SiluParams {
+  const void *x0;
+  const void *x1;
+  uint8_t *q;
+  float *inv_scale;
+  const float *scale_ub;
+  const int *valid_token_count;
+  int64_t T, D, stride0, stride1;
+};
+
+template <int kBlock>
+__device__ __forceinline__ float block_max(float v, float *s_part) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x / 32] = v;
+  __syncthreads();
+  float m = 0.f;
+#pragma unroll
+  for (int w = 0; w < kBlock / 32; ++w) m = fmaxf(m, s_part[w]);
+  return m;
+}
+
+// Vector path: D % 8 == 0, 16-byte aligned rows; kVecs 8-element vectors per thread.
+template <typename T, int kVecs, int kBlock>
+__global__ void __launch_bounds__(kBlock) silu_mul_quant_vec_kernel(const SiluParams p) {
+  __shared__ float s_part[kBlock / 32];
+  const int64_t row = blockIdx.x;
+  if (p.valid_token_count && row >= *p.valid_token_count) return;
+  const T *r0 = static_cast<const T *>(p.x0) + row * p.stride0;
+  const T *r1 = static_cast<const T *>(p.x1) + row * p.stride1;
+  const int nvec = static_cast<int>(p.D / 8);
+  uint4 a[kVecs], b[kVecs];
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    const int v = threadIdx.x + i * kBlock;
+    if (v < nvec) {
+      a[i] = ld_stream_v4(r0 + static_cast<int64_t>(v) * 8);
+      b[i] = ld_stream_v4(r1 + static_cast<int64_t>(v) * 8);
+    } else {
+      a[i] = make_uint4(0, 0, 0, 0);
+      b[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  float y[kVecs][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    float f0[8], f1[8];
+    unpack8<T>(a[i], f0);
+    unpack8<T>(b[i], f1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      y[i][j] = silu_mul(f0[j], f1[j]);
+      amax = fmaxf(amax, fabsf(y[i][j]));
+    }
+  }
+  amax = block_max<kBlock>(amax, s_part);
+  float rmax = fmaxf(amax, 1e-12f);
+  if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
+  const float y_scale = div_full(448.0f, rmax);
+  if (threadIdx.x == 0) p.inv_scale[row] = div_full(1.0f, y_scale);
+  uint8_t *qr = p.q + row * p.D;
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    const int v = threadIdx.x + i * kBlock;
+    if (v < nvec) {
+      uint32_t o[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = cvt_e4m3x2(__fmul_rn(y[i][4 * h], y_scale), __fmul_rn(y[i][4 * h + 1], y_scale));
+        const uint32_t hi = cvt_e4m3x2(__fmul_rn(y[i][4 * h + 2], y_scale), __fmul_rn(y[i][4 * h + 3], y_scale));
+        o[h] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint2 *>(qr + static_cast<int64_t>(v) * 8) = make_uint2(o[0], o[1]);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(const T *p);
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(const __nv_bfloat16 *p) {
+  return __bfloat162float(*p);
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(const __half *p) {
+  return __half2float(*p);
+}
+
+// General path (any D / alignment): two passes, y recomputed in the second.
+template <typename T, int kBlock>
+__global__ void __launch_bounds__(kBlock) silu_mul_quant_generic_kernel(const SiluParams p) {
+  __shared__ float s_part[kBlock / 32];
+  const int64_t row = blockIdx.x;
+  if (p.valid_token_count && row >= *p.valid_token_count) return;
+  const T *r0 = static_cast<const T *>(p.x0) + row * p.stride0;
+  const T *r1 = static_cast<const T *>(p.x1) + row * p.stride1;
+  float amax = 0.f;
+  for (int64_t k = threadIdx.x; k < p.D; k += kBlock) amax = fmaxf(amax, fabsf(silu_mul(to_f32<T>(r0 + k), to_f32<T>(r1 + k))));
+  amax = block_max<kBlock>(amax, s_part);
+  float rmax = fmaxf(amax, 1e-12f);
+  if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
+  const float y_scale = div_full(448.0f, rmax);
+  if (threadIdx.x == 0) p.inv_scale[row] = div_full(1.0f, y_scale);
+  uint8_t *qr = p.q + row * p.D;
+  for (int64_t k = threadIdx.x; k < p.D; k += kBlock) {
+    const float y = silu_mul(to_f32<T>(r0 + k), to_f32<T>(r1 + k));
+    qr[k] = static_cast<uint8_t>(cvt_e4m3x2(__fmul_rn(y, y_scale), 0.f) & 0xffu);
+  }
+}
+
+template <typename T, int kVecs, int kBlock>
+int launch_vec(const SiluParams &p, cudaStream_t st) {
+  silu_mul_quant_vec_kernel<T, kVecs, kBlock><<<static_cast<unsigned>(p.T), kBlock, 0, st>>>(p);
+  return check_cuda(cudaGetLastError(), "silu_mul_quant launch");
+}
+
+template <typename T>
+int launch_typed(const SiluParams &p, bool vec_ok, cudaStream_t st) {
+  if (vec_ok) {
+    const int64_t nvec = p.D / 8;
+    if (nvec <= 256 * 1) return launch_vec<T, 1, 256>(p, st);
+    if (nvec <= 256 * 2) return launch_vec<T, 2, 256>(p, st);
+    if (nvec <= 256 * 3) return launch_vec<T, 3, 256>(p, st);
+    if (nvec <= 256 * 4) return launch_vec<T, 4, 256>(p, st);
+    if (nvec <= 512 * 4) return launch_vec<T, 4, 512>(p, st);
+    if (nvec <= 1024 * 4) return launch_vec<T, 4, 1024>(p, st);
+  }
+  silu_mul_quant_generic_kernel<T, 256><<<static_cast<unsigned>(p.T), 256, 0, st>>>(p);
+  return check_cuda(cudaGetLastError(), "silu_mul_quant launch");
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  return pack_bf16x2(lo, hi);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) {
+  return __float2half_rn(v);
+}
+
+// y = x0 * sigmoid(x0) * x1 without quantization (the reference's _mslk_silu_mul,
+// mslk/moe/activation.py:181-217): elementwise, output in the input dtype, contiguous [T, D].
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const SiluParams p, T *__restrict__ y) {
+  const int64_t valid = p.valid_token_count ? min(static_cast<int64_t>(*p.valid_token_count), p.T) : p.T;
+  const T *x0 = static_cast<const T *>(p.x0);
+  const T *x1 = static_cast<const T *>(p.x1);
+  const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (kVec) {
+    const int64_t per_row = p.D / 8, total = valid * per_row;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+      const int64_t row = i / per_row, v = i - row * per_row;
+      float f0[8], f1[8];
+      unpack8<T>(ld_stream_v4(x0 + row * p.stride0 + v * 8), f0);
+      unpack8<T>(ld_stream_v4(x1 + row * p.stride1 + v * 8), f1);
+      uint4 o;
+      o.x = pack2<T>(silu_mul(f0[0], f1[0]), silu_mul(f0[1], f1[1]));
+      o.y = pack2<T>(silu_mul(f0[2], f1[2]), silu_mul(f0[3], f1[3]));
+      o.z = pack2<T>(silu_mul(f0[4], f1[4]), silu_mul(f0[5], f1[5]));
+      o.w = pack2<T>(silu_mul(f0[6], f1[6]), silu_mul(f0[7], f1[7]));
+      *reinterpret_cast<uint4 *>(y + row * p.D + v * 8) = o;
+    }
+  } else {
+    const int64_t total = valid * p.D;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
+      const int64_t row = i / p.D, k = i - row * p.D;
+      y[i] = from_f32<T>(silu_mul(to_f32<T>(x0 + row * p.stride0 + k), to_f32<T>(x1 + row * p.stride1 + k)));
+    }
+  }
+}
+
+template <typename T>
+int launch_silu_mul(const SiluParams &p, bool vec_ok, void *y, cudaStream_t st) {
+  const int64_t work = vec_ok ? p.T * (p.D / 8) : p.T * p.D;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+  const unsigned blocks = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((work + 255) / 256, cap)));
+  if (vec_ok)
+    silu_mul_kernel<T, true><<<blocks, 256, 0, st>>>(p, static_cast<T *>(y));
+  else
+    silu_mul_kernel<T, false><<<blocks, 256, 0, st>>>(p, static_cast<T *>(y));
+  return check_cuda(cudaGetLastError(), "silu_mul launch");
+}
+
+}  // namespace
+}  // namespace mslk_b200
+
+MSLK_API int mslk_b200_silu_mul_quant(const void *x0, const void *x1, int dtype, int64_t T, int64_t D, int64_t stride0,
+                                      int64_t stride1, const float *scale_ub, const int *valid_token_count, void *q,
+                                      float *inv_scale, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  if (T < 0 || D < 0) return fail(1, "silu_mul_quant: bad shape");
+  if (T == 0 || D == 0) return 0;
+  if (T > 0x7fffffffLL) return fail(1, "silu_mul_quant: too many rows");
+  if (!x0 || !x1 || !q || !inv_scale) return fail(1, "silu_mul_quant: null pointer argument");
+  if (dtype != MSLK_B200_BF16 && dtype != MSLK_B200_F16) return fail(1, "silu_mul_quant: inputs must be bf16 or fp16");
+  SiluParams p{x0, x1, static_cast<uint8_t *>(q), inv_scale, scale_ub, valid_token_count, T, D, stride0, stride1};
+  const bool vec_ok = D % 8 == 0 && stride0 % 8 == 0 && stride1 % 8 == 0 &&
+                      ((reinterpret_cast<uintptr_t>(x0) | reinterpret_cast<uintptr_t>(x1)) & 15u) == 0 &&
+                      (reinterpret_cast<uintptr_t>(q) & 7u) == 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == MSLK_B200_BF16 ? launch_typed<__nv_bfloat16>(p, vec_ok, st) : launch_typed<__half>(p, vec_ok, st);
+}
+
+MSLK_API int mslk_b200_silu_mul(const void *x0, const void *x1, int dtype, int64_t T, int64_t D, int64_t stride0,
+                                int64_t stride1, const int *valid_token_count, void *y, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  if (T < 0 || D < 0) return fail(1, "silu_mul: bad shape");
+  if (T == 0 || D == 0) return 0;
+  if (!x0 || !x1 || !y) return fail(1, "silu_mul: null pointer argument");
+  if (dtype != MSLK_B200_BF16 && dtype != MSLK_B200_F16) return fail(1, "silu_mul: inputs must be bf16 or fp16");
+  SiluParams p{x0, x1, nullptr, nullptr, nullptr, valid_token_count, T, D, stride0, stride1};
+  const bool vec_ok = D % 8 == 0 && stride0 % 8 == 0 && stride1 % 8 == 0 &&
+                      ((reinterpret_cast<uintptr_t>(x0) | reinterpret_cast<uintptr_t>(x1) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == MSLK_B200_BF16 ? launch_silu_mul<__nv_bfloat16>(p, vec_ok, y, st) : launch_silu_mul<__half>(p, vec_ok, y, st);
+}

@@ -5,6 +5,7 @@
     python -m mslk_b200.microbench grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
     python -m mslk_b200.microbench f4f4bf16 --shape 8192,8192,8192
     python -m mslk_b200.microbench quantize_nvfp4 --shape 8192,8192
+    python -m mslk_b200.microbench silu_mul_quant --shape 16384,14336      # T,D; also times the unfused pair
     python -m mslk_b200.microbench sweep          # the Llama-3-8B sweep: M x (N,K), quantize + GEMM
 
 Timing: CUDA events around `--iters` launches after `--warmup` launches, on torch's current
@@ -79,6 +80,17 @@ def bench_f8f8bf16_rowwise(ops, M, N, K, args):
             "GBps": byts / sec / 1e9}
 
 
+def bench_silu_mul_quant(ops, T, D, args):
+    nv = _variants(T * D * 4, args.rotate_mb)
+    xs = [_randn((T, 2 * D)) for _ in range(nv)]
+    sec = _time(lambda i: ops.silu_mul_quant(xs[i][:, :D], xs[i][:, D:]), nv, args.iters, args.warmup, args.graph)
+    sec_unfused = _time(lambda i: ops.quantize_fp8_row(ops.silu_mul(xs[i][:, :D], xs[i][:, D:])), nv, args.iters,
+                        args.warmup, args.graph)
+    byts = 5.0 * T * D + 4.0 * T
+    return {"op": "silu_mul_quant", "T": T, "D": D, "us": sec * 1e6, "GBps": byts / sec / 1e9, "bytes": byts,
+            "unfused_silu_mul_then_quantize_us": sec_unfused * 1e6}
+
+
 def zipf_counts(experts, tokens, seed=0, s=1.2, n_empty=2):
     """Per-expert token counts: top-1 routing with Zipf(s) expert popularity, the `n_empty` least popular
     experts forced to zero tokens (their tokens go to the most popular one)."""
@@ -134,7 +146,8 @@ def bench_f4f4bf16(ops, M, N, K, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "grouped", "f4f4bf16", "quantize_nvfp4", "sweep"])
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "grouped", "f4f4bf16", "quantize_nvfp4", "silu_mul_quant",
+                                   "sweep"])
     ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--tokens", type=int, default=16384)
@@ -156,6 +169,8 @@ def main():
         out.append(bench_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
     elif args.op == "quantize_nvfp4":
         out.append(bench_quantize_nvfp4(ops, *(shape or [8192, 8192]), args))
+    elif args.op == "silu_mul_quant":
+        out.append(bench_silu_mul_quant(ops, *(shape or [16384, 14336]), args))
     elif args.op == "f4f4bf16":
         out.append(bench_f4f4bf16(ops, *(shape or [8192, 8192, 8192]), args))
     else:

@@ -10,6 +10,7 @@ operators they stand for:
 * ``f8f8bf16_rowwise_grouped_stacked`` -- ``csrc/gemm/cutlass/f8f8bf16_rowwise_grouped.cu:342-368``
 * ``quantize_nvfp4``         -- ``mslk/quantize/triton/quantize_kernels/nvfp4.py:62-149``
 * ``f4f4bf16``               -- ``csrc/gemm/cutlass/f4f4bf16.cu:6413-6473``
+* ``silu_mul`` / ``silu_mul_quant`` -- ``mslk/moe/activation.py:25-69,72-133``
 
 CPU tensors are rejected: there is no fallback path.
 """
@@ -290,3 +291,47 @@ def reduce_slots(stage: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
     with torch.cuda.device(dev):
         check(lib.mslk_b200_reduce_slots_bf16(_ptr(stage), slots, rows, cols, _ptr(out), _stream(dev)), "reduce_slots")
     return out
+
+
+# --------------------------------------------------------------------------- SwiGLU (+ FP8 row quantize)
+
+def _check_silu_args(name, x0, x1, valid_token_count):
+    assert x0.ndim == 2 and x0.stride(1) == 1
+    assert x1.ndim == 2 and x1.stride(1) == 1
+    assert x0.shape == x1.shape
+    assert x0.dtype == x1.dtype
+    dev = _require_cuda(name, x0, x1, valid_token_count)
+    if x0.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"{name}: inputs must be bfloat16 or float16, got {x0.dtype}")
+    if valid_token_count is not None and valid_token_count.dtype != torch.int32:
+        valid_token_count = valid_token_count.to(torch.int32)
+    return dev, valid_token_count
+
+
+def silu_mul(x0: torch.Tensor, x1: torch.Tensor, valid_token_count: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x0 * sigmoid(x0) * x1`` for ``[T, D]`` inputs; rows at or past ``valid_token_count`` are not written."""
+    dev, vtc = _check_silu_args("silu_mul", x0, x1, valid_token_count)
+    T, D = x0.shape
+    out = torch.empty((T, D), dtype=x0.dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_silu_mul(_ptr(x0), _ptr(x1), _DTYPE_CODE[x0.dtype], T, D, x0.stride(0), x1.stride(0),
+                                     _ptr(vtc), _ptr(out), _stream(dev)), "silu_mul")
+    return out
+
+
+def silu_mul_quant(x0: torch.Tensor, x1: torch.Tensor, scale_ub: Optional[torch.Tensor] = None,
+                   valid_token_count: Optional[torch.Tensor] = None):
+    """Fused ``quantize_fp8_row(x0 * sigmoid(x0) * x1)``: returns ``(y_fp8 [T, D], inverse scale fp32 [T])``."""
+    dev, vtc = _check_silu_args("silu_mul_quant", x0, x1, valid_token_count)
+    _require_cuda("silu_mul_quant", x0, scale_ub)
+    ub = None
+    if scale_ub is not None:
+        ub = scale_ub if scale_ub.dtype == torch.float32 else scale_ub.to(torch.float32)
+    T, D = x0.shape
+    out = torch.empty((T, D), dtype=FP8_DTYPE, device=dev)
+    inv_scale = torch.empty((T,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_silu_mul_quant(_ptr(x0), _ptr(x1), _DTYPE_CODE[x0.dtype], T, D, x0.stride(0),
+                                           x1.stride(0), _ptr(ub), _ptr(vtc), _ptr(out), _ptr(inv_scale),
+                                           _stream(dev)), "silu_mul_quant")
+    return out, inv_scale

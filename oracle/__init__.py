@@ -72,6 +72,10 @@ def lib() -> ctypes.CDLL:
         L.oracle_gemm_nvfp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
         L.oracle_gemm_nvfp4.restype = None
         L.oracle_check_fma_division.argtypes = [vp, vp, i64]
+        L.oracle_silu_mul.argtypes = [vp, vp, i32, i64, i64, i64, i64, i64, vp]
+        L.oracle_silu_mul.restype = None
+        L.oracle_silu_mul_quant.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i64, vp, vp]
+        L.oracle_silu_mul_quant.restype = None
         L.oracle_check_fma_division.restype = i64
         _lib = L
     return _lib
@@ -314,3 +318,40 @@ def gemm_nvfp4(xq, wq, x_scale, w_scale, global_scale):
     sw = w_scale.contiguous().view(torch.uint8)
     lib().oracle_gemm_nvfp4(_p(xq), _p(wq), _p(sx), _p(sw), _p(gs), M, N, K, _p(y))
     return y
+
+
+# --------------------------------------------------------------------------
+# fused SwiGLU (+ per-row FP8 quantize)
+# --------------------------------------------------------------------------
+
+def silu_mul(x0: torch.Tensor, x1: torch.Tensor, valid_token_count: Optional[int] = None) -> torch.Tensor:
+    """fp32 ``x0 * sigmoid(x0) * x1`` (``mslk/moe/activation.py:181-217``); rows past the count stay 0."""
+    x0, x1 = _cpu(x0), _cpu(x1)
+    assert x0.dim() == 2 and x0.shape == x1.shape and x0.dtype == x1.dtype and x0.stride(1) == 1 and x1.stride(1) == 1
+    T, D = x0.shape
+    y = torch.zeros((T, D), dtype=torch.float32)
+    valid = T if valid_token_count is None else int(valid_token_count)
+    if T and D:
+        lib().oracle_silu_mul(_p(x0), _p(x1), DTYPE_CODE[x0.dtype], T, D, x0.stride(0), x1.stride(0), valid, _p(y))
+    return y
+
+
+def silu_mul_quant(x0: torch.Tensor, x1: torch.Tensor, scale_ub: Optional[torch.Tensor] = None,
+                   valid_token_count: Optional[int] = None):
+    """Statement of ``mslk/moe/activation.py:220-294`` with exact ``expf`` / IEEE division in the sigmoid.
+
+    Returns ``(q float8_e4m3fn [T, D], inverse scale fp32 [T])``; rows past the count are 0.  The GPU
+    kernels use approximate exp2 / division, so agreement with them is to within one e4m3 code on a
+    small fraction of elements (rounding boundaries) and a few ulps on the scale, not bit for bit.
+    """
+    x0, x1 = _cpu(x0), _cpu(x1)
+    assert x0.dim() == 2 and x0.shape == x1.shape and x0.dtype == x1.dtype and x0.stride(1) == 1 and x1.stride(1) == 1
+    T, D = x0.shape
+    q = torch.zeros((T, D), dtype=torch.uint8)
+    s = torch.zeros((T,), dtype=torch.float32)
+    ub = None if scale_ub is None else _cpu(scale_ub).to(torch.float32).contiguous()
+    valid = T if valid_token_count is None else int(valid_token_count)
+    if T and D:
+        lib().oracle_silu_mul_quant(_p(x0), _p(x1), DTYPE_CODE[x0.dtype], T, D, x0.stride(0), x1.stride(0),
+                                    _p(ub), valid, _p(q), _p(s))
+    return q.view(torch.float8_e4m3fn), s

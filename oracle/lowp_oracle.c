@@ -406,3 +406,47 @@ ORACLE_API int64_t oracle_check_fma_division(const float *x, const float *s, int
   }
   return bad;
 }
+
+/* ------------------------------------------------------------------------ */
+/* fused SwiGLU + per-row FP8 quantize                                       */
+/* mslk/moe/activation.py:220-294 (_mslk_silu_mul_quant), :181-217 (silu_mul) */
+/* ------------------------------------------------------------------------ */
+
+/* y = x0 * sigmoid(x0) * x1 in fp32.  The reference's GPU kernel evaluates the
+ * sigmoid with the hardware's approximate exp2 and an approximate division, which no
+ * CPU can restate bit for bit; this function uses correctly rounded expf and IEEE
+ * division instead, so it agrees with the GPU to a few fp32 ulps (the captured GPU
+ * fixtures, not this function, pin the exact bits). */
+static inline float silu_mul_f32(float x0, float x1) {
+  float sig = 1.0f / (1.0f + expf(-x0));
+  return (x0 * sig) * x1;
+}
+
+ORACLE_API void oracle_silu_mul(const void *x0, const void *x1, int dtype, int64_t T, int64_t D, int64_t stride0,
+                                int64_t stride1, int64_t valid, float *y) {
+  for (int64_t t = 0; t < T && t < valid; ++t)
+    for (int64_t k = 0; k < D; ++k)
+      y[t * D + k] = silu_mul_f32(load_elem(x0, dtype, t * stride0 + k), load_elem(x1, dtype, t * stride1 + k));
+}
+
+/* Rows >= valid are left untouched.  scale_ub may be NULL.  inv_scale = 1 / (448 / rmax),
+ * q = e4m3(y * (448 / rmax)) -- multiplication by the reciprocal scale, as the reference. */
+ORACLE_API void oracle_silu_mul_quant(const void *x0, const void *x1, int dtype, int64_t T, int64_t D, int64_t stride0,
+                                      int64_t stride1, const float *scale_ub, int64_t valid, uint8_t *q,
+                                      float *inv_scale) {
+  float *y = (float *)malloc(sizeof(float) * (size_t)(D > 0 ? D : 1));
+  for (int64_t t = 0; t < T && t < valid; ++t) {
+    float amax = 0.f;
+    for (int64_t k = 0; k < D; ++k) {
+      y[k] = silu_mul_f32(load_elem(x0, dtype, t * stride0 + k), load_elem(x1, dtype, t * stride1 + k));
+      float a = fabsf(y[k]);
+      if (a > amax) amax = a;
+    }
+    float rmax = amax > 1e-12f ? amax : 1e-12f;
+    if (scale_ub && rmax > *scale_ub) rmax = *scale_ub;
+    float y_scale = 448.0f / rmax;
+    inv_scale[t] = 1.0f / y_scale;
+    for (int64_t k = 0; k < D; ++k) q[t * D + k] = oracle_f32_to_e4m3(y[k] * y_scale);
+  }
+  free(y);
+}

@@ -10,6 +10,7 @@ Two legs, both writing ``.npz`` files next to this script:
     * the NVFP4 torch reference ``data_to_nvfp4_with_global_scale`` from the
       reference's own test (``test/quantize/triton/fp4_quantize_test.py:259-296``),
       ``_to_blocked``, ``global_scale_nvfp4`` and ``dequantize_nvfp4``.
+``--leg gpu_silu``  (needs a B200) runs the reference's fused ``silu_mul_quant`` (``mslk/moe/activation.py``).
 ``--leg gpu``  (needs a B200) runs the reference's Triton kernels
     ``triton_quantize_fp8_row`` and ``triton_quantize_nvfp4`` on the same seeded
     inputs; these are the bit-level pins for the GPU arithmetic.
@@ -200,13 +201,59 @@ def leg_gpu(ref_root: str):
     print("gpu leg written")
 
 
+# (T, D, scale_ub, valid tokens or None, contiguous) -- after test/moe/activation_test.py:97-168
+SILU_CASES = [
+    ("s1x5120", 1, 5120, None, None, True),
+    ("s128x5120", 128, 5120, None, None, True),
+    ("s128x7168_ub", 128, 7168, 1200.0, None, True),
+    ("s64x8192_strided", 64, 8192, None, None, False),
+    ("s200x1024_partial", 200, 1024, None, 100, True),
+    ("s16x14336_ub_small", 16, 14336, 0.05, None, True),
+    ("s8x256_tiny", 8, 256, None, None, True),
+]
+
+
+def silu_inputs(name, T, D, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((T, 2 * D), generator=g, dtype=torch.float32).to(torch.bfloat16)
+    if "tiny" in name:
+        x = (x.float() * 1e-7).to(torch.bfloat16)      # row maxima below the 1e-12 floor of the scale
+    else:
+        x = torch.sign(x) * torch.clamp(torch.abs(x), 0.01, 2.0)
+    return x
+
+
+def leg_gpu_silu(ref_root: str):
+    """silu_mul_quant of the reference (Triton, mslk/moe/activation.py:72-294) on a B200."""
+    _import_reference(ref_root)
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_ref_activation", os.path.join(ref_root, "mslk", "moe", "activation.py"))
+    act = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(act)
+    out = {}
+    for i, (name, T, D, ub, valid, contiguous) in enumerate(SILU_CASES):
+        x = silu_inputs(name, T, D, 400 + i).cuda()
+        x0, x1 = x[:, :D], x[:, D:]
+        if contiguous:
+            x0, x1 = x0.contiguous(), x1.contiguous()
+        ubt = None if ub is None else torch.tensor([ub], dtype=torch.float32, device="cuda")
+        vt = None if valid is None else torch.tensor([valid], dtype=torch.int32, device="cuda")
+        q, s = act.silu_mul_quant(x0, x1, ubt, vt)
+        torch.cuda.synchronize()
+        out[f"{name}.x"] = _raw(x)
+        out[f"{name}.q"] = _raw(q)
+        out[f"{name}.s"] = _raw(s)
+    np.savez_compressed(os.path.join(HERE, "silu_mul_quant_triton_b200.npz"), **out)
+    print("gpu silu leg written")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--leg", choices=["cpu", "gpu"], required=True)
+    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu"], required=True)
     ap.add_argument("--ref-root", required=True)
     ap.add_argument("--out-dir", default=None, help="write here instead of beside this script")
     args = ap.parse_args()
     if args.out_dir:
         HERE = args.out_dir
         os.makedirs(HERE, exist_ok=True)
-    (leg_cpu if args.leg == "cpu" else leg_gpu)(args.ref_root)
+    {"cpu": leg_cpu, "gpu": leg_gpu, "gpu_silu": leg_gpu_silu}[args.leg](args.ref_root)

@@ -212,3 +212,44 @@ def test_fma_division_equals_ieee_division():
     xf = torch.randn(400000, generator=g).abs() + 1e-3
     sf = (torch.rand(400000, generator=g) * 8 + 1e-2) / 448
     assert L.oracle_check_fma_division(xf.data_ptr(), sf.data_ptr(), xf.numel()) == 0
+
+
+def test_silu_mul_quant_oracle_against_torch_expression():
+    # mslk/moe/activation.py:220-294 restated with exact expf; test/moe/activation_test.py:97-168 tolerance
+    g = torch.Generator().manual_seed(5)
+    x0 = torch.randn((37, 640), generator=g).to(torch.bfloat16)
+    x1 = torch.randn((37, 640), generator=g).to(torch.bfloat16)
+    ub = torch.tensor([1200.0])
+    q, s = oracle.silu_mul_quant(x0, x1, ub, 20)
+    ref = x0.float() * torch.sigmoid(x0.float()) * x1.float()
+    torch.testing.assert_close(q[:20].float() * s[:20, None], ref[:20], rtol=1e-1, atol=1e-3)
+    assert bool((q.view(torch.uint8)[20:] == 0).all()) and bool((s[20:] == 0).all())
+    # inverse scale = row max / 448 up to two roundings; the largest element maps to +-448
+    torch.testing.assert_close(s[:20], ref[:20].abs().amax(dim=1) / 448.0, rtol=1e-6, atol=0)
+    assert bool((q[:20].float().abs().amax(dim=1) == 448.0).all())
+    # the upper bound clamps the row maximum, the floor 1e-12 keeps an all-zero row finite
+    q2, s2 = oracle.silu_mul_quant(x0, x1, torch.tensor([0.05]))
+    torch.testing.assert_close(s2, torch.full((37,), 1.0 / (448.0 / 0.05)), rtol=1e-6, atol=0)
+    z = torch.zeros((2, 64), dtype=torch.bfloat16)
+    q3, s3 = oracle.silu_mul_quant(z, z)
+    assert bool((q3.view(torch.uint8) == 0).all()) and bool(torch.isfinite(s3).all()) and bool((s3 > 0).all())
+    torch.testing.assert_close(oracle.silu_mul(x0, x1), ref, rtol=1e-6, atol=1e-7)
+
+
+def test_silu_mul_quant_triton_fixture_close_to_oracle():
+    gold = load_golden("silu_mul_quant_triton_b200.npz")
+    if gold is None:
+        pytest.skip("fixture captured from the reference's Triton kernel not present")
+    from golden.make_golden import SILU_CASES
+    for name, T, D, ub, valid, contiguous in SILU_CASES:
+        x = bf16(gold[f"{name}.x"]).reshape(T, 2 * D)
+        n = T if valid is None else valid
+        q, s = oracle.silu_mul_quant(x[:, :D], x[:, D:], None if ub is None else torch.tensor([ub]), valid)
+        s_g = torch.from_numpy(gold[f"{name}.s"]).reshape(T)
+        q_g = torch.from_numpy(gold[f"{name}.q"]).reshape(T, D)
+        torch.testing.assert_close(s[:n], s_g[:n], rtol=2e-6, atol=0)
+        a, b = q.view(torch.uint8)[:n].to(torch.int16), q_g[:n].to(torch.int16)
+        oa = torch.where((a & 0x80) != 0, -(a & 0x7f), a & 0x7f)
+        ob = torch.where((b & 0x80) != 0, -(b & 0x7f), b & 0x7f)
+        d = (oa - ob).abs()
+        assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 2e-3, name
