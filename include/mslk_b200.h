@@ -166,6 +166,19 @@ int mslk_b200_f8f8bf16_rowwise_grouped_stacked(const void *xq, const void *wq,
                                                void *stream);
 
 /*
+ * Batched rowwise-scaled FP8 GEMM:  y[b] = f8f8bf16_rowwise(xq[b], wq[b], x_scale[b], w_scale[b], bias[b]).
+ * Replaces: csrc/gemm/cutlass/f8f8bf16_rowwise_batched.cu:20-139 and
+ *           f8f8bf16_rowwise_batched/f8f8bf16_rowwise_batched_common.cuh:40-340.
+ * xq [B,M,K], wq [B,N,K] e4m3 contiguous; x_scale [B,M], w_scale [B,N] fp32; bias [B,N]
+ * (kind as for mslk_b200_f8f8bf16_rowwise, may be NULL); y [B,M,N] bf16.  One launch: the
+ * batches are scheduled as B equal groups of the grouped kernel.  B <= 1024.
+ */
+int mslk_b200_f8f8bf16_rowwise_batched(const void *xq, const void *wq, const float *x_scale,
+                                       const float *w_scale, const void *bias, int bias_kind,
+                                       void *y, int64_t B, int64_t M, int64_t N, int64_t K,
+                                       void *stream);
+
+/*
  * NVFP4 quantization (e2m1 data, one e4m3 scale per 16 elements in the 128x4
  * swizzled layout, optional fp32 per-tensor global scale read from the device).
  * Replaces: mslk/quantize/triton/quantize_kernels/nvfp4.py:62-296.

@@ -49,6 +49,8 @@ lib.mslk_b200_quantize_nvfp4.argtypes = [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _
 lib.mslk_b200_quantize_nvfp4.restype = _int
 lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f4f4bf16.restype = _int
+lib.mslk_b200_f8f8bf16_rowwise_batched.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp]
+lib.mslk_b200_f8f8bf16_rowwise_batched.restype = _int
 lib.mslk_b200_silu_mul_quant.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]
 lib.mslk_b200_silu_mul_quant.restype = _int
 lib.mslk_b200_silu_mul.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp]

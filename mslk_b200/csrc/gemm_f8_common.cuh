@@ -23,11 +23,12 @@ struct GemmParams {
   const float *w_scale;
   const void *bias;
   __nv_bfloat16 *y;
-  const int64_t *m_sizes;  // device, [G]; nullptr = dense (one group of total_m rows)
+  const int64_t *m_sizes;  // device, [G]; nullptr = G groups of group_m rows each (dense: G = 1)
   int *status;
   int bias_kind;
   int G;
   int total_m;
+  int group_m;  // rows of every group when m_sizes is null (batched GEMM); total_m for the dense case
   int N;
   int K;
   // Output placement: y (and y_extra[0..n_extra)) are row-major with a pitch of ldy elements; the
@@ -67,7 +68,7 @@ __device__ __forceinline__ void build_group_tables(const GemmParams &p, int n_ti
   for (int base = 0; base < p.G; base += 32) {
     const int g = base + lane;
     long long mg = 0;
-    if (g < p.G) mg = p.m_sizes ? p.m_sizes[g] : p.total_m;
+    if (g < p.G) mg = p.m_sizes ? p.m_sizes[g] : p.group_m;
     if (mg < 0) mg = 0;
     if (mg > p.total_m) mg = p.total_m;
     int rows = static_cast<int>(mg);

@@ -220,9 +220,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const bool in = t.n0 + c < p.N;
         ws_s[c] = in ? p.w_scale[t.ws0 + c] : 0.f;
         float b = 0.f;
-        if (in && p.bias_kind == MSLK_B200_BIAS_F32) b = static_cast<const float *>(p.bias)[t.n0 + c];
+        if (in && p.bias_kind == MSLK_B200_BIAS_F32) b = static_cast<const float *>(p.bias)[t.ws0 + c];
         if (in && p.bias_kind == MSLK_B200_BIAS_BF16)
-          b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[t.n0 + c]);
+          b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[t.ws0 + c]);
         bs_s[c] = b;
       }
       __syncwarp();
@@ -306,7 +306,10 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   if (!status) return 2;
 
   const int sms = sm_count();
-  const int64_t m_tiles_ub = (total_m + kBM - 1) / kBM + (m_sizes ? G : 0);
+  // upper bound of the row blocks: exact for equal groups, one ragged block per group otherwise
+  const int64_t group_m = total_m / G;
+  if (!m_sizes && group_m * G != total_m) return fail(1, "%s: rows are not a multiple of the batch count", name);
+  const int64_t m_tiles_ub = m_sizes ? (total_m + kBM - 1) / kBM + G : G * ((group_m + kBM - 1) / kBM);
   // widest column block that still yields at least one tile per SM
   int bn = 256;
   while (bn > 32 && (bn / 2 >= N || m_tiles_ub * ((N + bn - 1) / bn) < sms)) bn /= 2;
@@ -321,6 +324,7 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   p.bias_kind = bias_kind;
   p.G = static_cast<int>(G);
   p.total_m = static_cast<int>(total_m);
+  p.group_m = static_cast<int>(group_m);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   default_placement(p);
@@ -336,7 +340,7 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   // few tokens AND scratch given: weight-streaming kernel with the K dimension split.  Opt-in: on
   // the shapes measured (Llama-3-8B projections, M = 1..32) the 32-column tiles of the general
   // kernel below finish sooner than split + partial sums + tickets, so no scratch = general kernel.
-  if (!m_sizes && !placement && scratch && total_m <= kDecodeMaxTokens && N >= 128)
+  if (!m_sizes && G == 1 && !placement && scratch && total_m <= kDecodeMaxTokens && N >= 128)
     return launch_decode_kernel(xq, wq, p, scratch, scratch_bytes, false, st);
 
   // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs
@@ -344,7 +348,8 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
     const char *e = getenv("MSLK_B200_GEMM_KERNEL");  // "1cta" | "2cta": tuning aid, default = heuristic
     return !e ? 0 : (e[0] == '2' ? 2 : 1);
   }();
-  const int64_t pair_tiles = ((total_m + 2 * kBM - 1) / (2 * kBM)) * ((N + 255) / 256);
+  const int64_t pair_tiles = (m_sizes ? (total_m + 2 * kBM - 1) / (2 * kBM) : G * ((group_m + 2 * kBM - 1) / (2 * kBM))) *
+                             ((N + 255) / 256);
   // grouped problems: pairs pay off only when the average group is several 256-row tiles tall
   const bool groups_tall = !m_sizes || total_m / G >= 512;
   const bool want_pair = force == 2 || p.rs_rows > 0 || (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2);
@@ -463,4 +468,18 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_grouped_stacked(const void *xq, const vo
   if (!M_sizes) return fail(1, "f8f8bf16_rowwise_grouped_stacked: M_sizes is null");
   return run(xq, wq, x_scale, w_scale, nullptr, MSLK_B200_BIAS_NONE, y, M_sizes, G, total_M, N, K, nullptr, 0,
              static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise_grouped_stacked");
+}
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise_batched(const void *xq, const void *wq, const float *x_scale,
+                                                const float *w_scale, const void *bias, int bias_kind, void *y,
+                                                int64_t B, int64_t M, int64_t N, int64_t K, void *stream) {
+  using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
+  clear_error();
+  if (bias_kind < 0 || bias_kind > 2) return fail(1, "f8f8bf16_rowwise_batched: bad bias_kind %d", bias_kind);
+  if (B < 0 || M < 0) return fail(1, "f8f8bf16_rowwise_batched: bad shape");
+  if (B == 0 || M == 0) return 0;
+  // B equal groups of M stacked rows, group b multiplying its own weight block wq[b]
+  return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, B, B * M, N, K, nullptr, 0,
+             static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise_batched");
 }

@@ -203,9 +203,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const bool in = t.n0 + c < p.N;
         ws_s[c] = in ? p.w_scale[t.ws0 + c] : 0.f;
         float b = 0.f;
-        if (in && p.bias_kind == MSLK_B200_BIAS_F32) b = static_cast<const float *>(p.bias)[t.n0 + c];
+        if (in && p.bias_kind == MSLK_B200_BIAS_F32) b = static_cast<const float *>(p.bias)[t.ws0 + c];
         if (in && p.bias_kind == MSLK_B200_BIAS_BF16)
-          b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[t.n0 + c]);
+          b = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.bias)[t.ws0 + c]);
         bs_s[c] = b;
       }
       __syncwarp();
@@ -330,7 +330,9 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
   }
   if (max_pairs[dev] < 0) return -1;
 
-  const int64_t tiles_ub = ((static_cast<int64_t>(p.total_m) + kPairRows - 1) / kPairRows + (p.m_sizes ? p.G : 0)) *
+  const int64_t row_blocks_ub = p.m_sizes ? (static_cast<int64_t>(p.total_m) + kPairRows - 1) / kPairRows + p.G
+                                          : static_cast<int64_t>(p.G) * ((p.group_m + kPairRows - 1) / kPairRows);
+  const int64_t tiles_ub = row_blocks_ub *
                            ((p.N + kPairBN - 1) / kPairBN);
   const int pairs = static_cast<int>(tiles_ub < max_pairs[dev] ? tiles_ub : max_pairs[dev]);
 

@@ -419,6 +419,7 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, 
   p.bias_kind = bias_kind;
   p.G = 1;
   p.total_m = static_cast<int>(M);
+  p.group_m = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   default_placement(p);

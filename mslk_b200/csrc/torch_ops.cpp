@@ -110,6 +110,51 @@ at::Tensor f8f8bf16_rowwise_grouped_stacked(at::Tensor XQ, at::Tensor WQ, at::Te
   return Y;
 }
 
+// ------------------------------------------------------------------ batched
+// csrc/gemm/cutlass/f8f8bf16_rowwise_batched.cu:20-139: 3-D inputs only, fp32 bias, optional output.
+at::Tensor f8f8bf16_rowwise_batched(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor w_scale,
+                                    std::optional<at::Tensor> bias, bool use_fast_accum,
+                                    std::optional<at::Tensor> output) {
+  const char *n = "f8f8bf16_rowwise_batched";
+  TORCH_CHECK(use_fast_accum, "f8f8bf16_rowwise_batched only supports fast_accum=True");
+  TORCH_CHECK(XQ.dim() == 3 && WQ.dim() == 3, "FP8 rowwise batched GEMM only supports 3D inputs");
+  TORCH_CHECK(XQ.is_cuda() && XQ.is_contiguous() && WQ.is_cuda() && WQ.is_contiguous(), n,
+              ": XQ and WQ must be contiguous CUDA tensors");
+  TORCH_CHECK(XQ.dtype() == at::kFloat8_e4m3fn, "XQ must be FP8 e4m3fn");
+  TORCH_CHECK(WQ.dtype() == at::kFloat8_e4m3fn, "WQ must be FP8 e4m3fn");
+  TORCH_CHECK(x_scale.dtype() == at::kFloat && w_scale.dtype() == at::kFloat, "Scale tensors must be float32.");
+  const int64_t B = XQ.size(0), M = XQ.size(1), N = WQ.size(1), K = WQ.size(2);
+  TORCH_CHECK(WQ.size(0) == B, n, ": XQ and WQ disagree on the batch count");
+  if (M == 0 || N == 0 || K == 0) return at::zeros({B, M, N}, XQ.options().dtype(at::kBFloat16));
+  TORCH_CHECK(XQ.size(2) == K, n, ": XQ and WQ disagree on K");
+  TORCH_CHECK(x_scale.is_cuda() && w_scale.is_cuda() && x_scale.numel() == B * M && w_scale.numel() == B * N, n,
+              ": scales must be CUDA tensors of B*M and B*N elements");
+  at::Tensor b;
+  int kind = MSLK_B200_BIAS_NONE;
+  if (bias.has_value()) {
+    b = bias->contiguous();
+    TORCH_CHECK(b.dtype() == at::kFloat, "Bias type must be float32 if provided.");
+    TORCH_CHECK(b.is_cuda() && b.numel() == B * N, n, ": bias must be a CUDA tensor of B*N elements");
+    kind = MSLK_B200_BIAS_F32;
+  }
+  at::Tensor Y;
+  if (output.has_value()) {
+    Y = *output;
+    TORCH_CHECK(Y.dtype() == at::kBFloat16);
+    TORCH_CHECK(Y.is_cuda() && Y.is_contiguous() && Y.numel() == B * M * N, n,
+                ": output must be a contiguous CUDA tensor of B*M*N elements");
+  } else {
+    Y = at::empty({B, M, N}, XQ.options().dtype(at::kBFloat16));
+  }
+  c10::cuda::CUDAGuard guard(XQ.device());
+  const at::Tensor xs = x_scale.contiguous(), ws = w_scale.contiguous();
+  check_rc(mslk_b200_f8f8bf16_rowwise_batched(XQ.data_ptr(), WQ.data_ptr(), xs.data_ptr<float>(), ws.data_ptr<float>(),
+                                              kind ? b.data_ptr() : nullptr, kind, Y.data_ptr(), B, M, N, K,
+                                              stream_of(XQ)),
+           n);
+  return Y;
+}
+
 // ------------------------------------------------------------------ NVFP4 GEMM
 at::Tensor f4f4bf16(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor w_scale,
                     std::optional<at::Tensor> output, std::optional<at::Tensor> global_scale,
@@ -220,6 +265,9 @@ TORCH_LIBRARY_FRAGMENT(mslk, m) {
       "f8f8bf16_rowwise_out(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output, Tensor? "
       "bias=None, bool use_fast_accum=True) -> ()");
   m.def(
+      "f8f8bf16_rowwise_batched(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor? bias=None, bool "
+      "use_fast_accum=True, Tensor(a!)? output=None) -> Tensor");
+  m.def(
       "f8f8bf16_rowwise_grouped_stacked(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor M_sizes) -> "
       "Tensor");
   m.def(
@@ -237,6 +285,7 @@ TORCH_LIBRARY_FRAGMENT(mslk, m) {
 TORCH_LIBRARY_IMPL(mslk, CPU, m) {
   m.impl("f8f8bf16_rowwise", f8f8bf16_rowwise);
   m.impl("f8f8bf16_rowwise_out", f8f8bf16_rowwise_out);
+  m.impl("f8f8bf16_rowwise_batched", f8f8bf16_rowwise_batched);
   m.impl("f8f8bf16_rowwise_grouped_stacked", f8f8bf16_rowwise_grouped_stacked);
   m.impl("f4f4bf16", f4f4bf16);
   m.impl("quantize_fp8_row", quantize_fp8_row);
@@ -247,6 +296,7 @@ TORCH_LIBRARY_IMPL(mslk, CPU, m) {
 TORCH_LIBRARY_IMPL(mslk, CUDA, m) {
   m.impl("f8f8bf16_rowwise", f8f8bf16_rowwise);
   m.impl("f8f8bf16_rowwise_out", f8f8bf16_rowwise_out);
+  m.impl("f8f8bf16_rowwise_batched", f8f8bf16_rowwise_batched);
   m.impl("f8f8bf16_rowwise_grouped_stacked", f8f8bf16_rowwise_grouped_stacked);
   m.impl("f4f4bf16", f4f4bf16);
   m.impl("quantize_fp8_row", quantize_fp8_row);

@@ -2,8 +2,8 @@
 
 Mirror of the reference's ``mslk/gemm/__init__.py:15-26``: after ``import mslk_b200.gemm``
 (or ``import mslk.gemm`` once :func:`mslk_b200.compat.install` has run) the operators
-``torch.ops.mslk.{f8f8bf16_rowwise, f8f8bf16_rowwise_out, f8f8bf16_rowwise_grouped_stacked,
-f4f4bf16}`` exist, backed by the sm_100a kernels.  Importing fails loudly if the native
+``torch.ops.mslk.{f8f8bf16_rowwise, f8f8bf16_rowwise_out, f8f8bf16_rowwise_batched,
+f8f8bf16_rowwise_grouped_stacked, f4f4bf16}`` exist, backed by the sm_100a kernels.  Importing fails loudly if the native
 libraries have not been built.
 """
 

@@ -1,6 +1,6 @@
 """Fake (meta) kernels: output shapes and dtypes for ``torch.compile`` / ``torch.export``.
 
-Shape rules follow the reference's ``mslk/gemm/_meta.py:28-67,116-128,234-247``.
+Shape rules follow the reference's ``mslk/gemm/_meta.py:28-67,68-83,116-128,234-247``.
 """
 
 from typing import Optional
@@ -18,6 +18,12 @@ def _f8f8bf16_rowwise_fake(XQ, WQ, x_scale, w_scale, bias: Optional[torch.Tensor
 def _f8f8bf16_rowwise_out_fake(XQ, WQ, x_scale, w_scale, output, bias: Optional[torch.Tensor] = None,
                                use_fast_accum: bool = True) -> None:
     return None
+
+
+@torch.library.register_fake("mslk::f8f8bf16_rowwise_batched")
+def _f8f8bf16_rowwise_batched_fake(XQ, WQ, x_scale, w_scale, bias: Optional[torch.Tensor] = None,
+                                   use_fast_accum: bool = True, output: Optional[torch.Tensor] = None):
+    return torch.empty((XQ.shape[0], XQ.shape[1], WQ.shape[1]), dtype=torch.bfloat16, device=XQ.device)
 
 
 @torch.library.register_fake("mslk::f8f8bf16_rowwise_grouped_stacked")

@@ -7,6 +7,7 @@ operators they stand for:
 
 * ``quantize_fp8_row``       -- ``mslk/quantize/triton/fp8_quantize.py:210-316,319-378``
 * ``f8f8bf16_rowwise``       -- ``csrc/gemm/cutlass/f8f8bf16_rowwise.cu:183-206``
+* ``f8f8bf16_rowwise_batched`` -- ``csrc/gemm/cutlass/f8f8bf16_rowwise_batched.cu:20-139``
 * ``f8f8bf16_rowwise_grouped_stacked`` -- ``csrc/gemm/cutlass/f8f8bf16_rowwise_grouped.cu:342-368``
 * ``quantize_nvfp4``         -- ``mslk/quantize/triton/quantize_kernels/nvfp4.py:62-149``
 * ``f4f4bf16``               -- ``csrc/gemm/cutlass/f4f4bf16.cu:6413-6473``
@@ -147,6 +148,46 @@ def f8f8bf16_rowwise(XQ, WQ, x_scale, w_scale, bias=None, use_fast_accum: bool =
     out = torch.empty((*XQ.shape[:-1], N), dtype=torch.bfloat16, device=dev)
     f8f8bf16_rowwise_out(XQ, WQ, x_scale, w_scale, out, bias, use_fast_accum)
     return out
+
+
+def f8f8bf16_rowwise_batched(XQ, WQ, x_scale, w_scale, bias=None, use_fast_accum: bool = True,
+                             output: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y[b] = f8f8bf16_rowwise(XQ[b], WQ[b], x_scale[b], w_scale[b], bias[b])`` in one launch.
+    ``XQ [B,M,K]``, ``WQ [B,N,K]``, ``x_scale [B,M]``, ``w_scale [B,N]``, fp32 ``bias [B,N]``."""
+    name = "f8f8bf16_rowwise_batched"
+    if not use_fast_accum:
+        raise RuntimeError("f8f8bf16_rowwise_batched only supports fast_accum=True")
+    if XQ.dim() != 3 or WQ.dim() != 3:
+        raise RuntimeError("FP8 rowwise batched GEMM only supports 3D inputs")
+    dev = _check_rowwise_args(name, XQ, WQ, x_scale, w_scale)
+    B, M, K = XQ.shape
+    N = WQ.shape[1]
+    if WQ.shape[0] != B:
+        raise RuntimeError(f"{name}: XQ and WQ disagree on the batch count")
+    if M == 0 or N == 0 or K == 0:
+        return torch.zeros((B, M, N), dtype=torch.bfloat16, device=dev)
+    if WQ.shape[2] != K:
+        raise RuntimeError(f"{name}: XQ and WQ disagree on K")
+    if x_scale.numel() != B * M or w_scale.numel() != B * N:
+        raise RuntimeError(f"{name}: scale sizes must match B*M and B*N")
+    kind = 0
+    if bias is not None:
+        _require_cuda(name, XQ, bias)
+        if bias.dtype != torch.float32:
+            raise RuntimeError("Bias type must be float32 if provided.")
+        if bias.numel() != B * N:
+            raise RuntimeError(f"{name}: bias must have B*N elements")
+        bias = bias.contiguous()
+        kind = 1
+    if output is None:
+        output = torch.empty((B, M, N), dtype=torch.bfloat16, device=dev)
+    elif output.dtype != torch.bfloat16 or output.numel() != B * M * N or not output.is_contiguous():
+        raise RuntimeError(f"{name}: output must be a contiguous bfloat16 tensor of B*M*N elements")
+    xs, ws = x_scale.contiguous(), w_scale.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f8f8bf16_rowwise_batched(
+            _ptr(XQ), _ptr(WQ), _ptr(xs), _ptr(ws), _ptr(bias), kind, _ptr(output), B, M, N, K, _stream(dev)), name)
+    return output
 
 
 def f8f8bf16_rowwise_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes) -> torch.Tensor:

@@ -271,3 +271,65 @@ def test_fused_reduce_scatter_emulated_on_one_gpu(ops, M, N, K, world):
     part0 = oracle.gemm_f8_rowwise_torch(xq[:, :kl].contiguous(), wq[:, :kl].contiguous(), xs, ws)
     _close(stages[1][0], part0[rows:2 * rows], "slot of rank 0 in owner 1")
     assert _status() == 0
+
+
+# ------------------------------------------------------------------ batched (3D x 3D)
+
+def _batched_case(ops, B, M, N, K, with_bias, seed):
+    # test/gemm/gemm_test.py:507-597: x ~ U[0,1)*0.1, w ~ U[0,1)*0.01, fp32 bias [B, N]
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.rand((B, M, K), generator=g) * 0.1).to(torch.bfloat16).cuda()
+    w = (torch.rand((B, N, K), generator=g) * 0.01).to(torch.bfloat16).cuda()
+    bias = torch.randn((B, N), generator=g).cuda() if with_bias else None
+    xq, xs = ops.quantize_fp8_row(x)
+    wq, ws = ops.quantize_fp8_row(w)
+    assert xs.shape == (B, M) and ws.shape == (B, N)
+    return x, w, bias, xq, wq, xs, ws
+
+
+@pytest.mark.parametrize("B,M,N,K,with_bias", [
+    (1, 256, 128, 256, False),     # the reference's cases
+    (4, 4096, 256, 512, False),
+    (4, 2048, 256, 512, True),
+    (3, 100, 72, 144, True),       # ragged rows and columns: tiles straddle batch boundaries
+    (5, 1, 40, 64, False),
+    (2, 300, 1000, 640, True),
+    (8, 512, 1024, 1024, False),   # tall enough for CTA pairs
+    (16, 130, 8, 32, False),
+])
+def test_batched_equals_loop_over_dense(ops, B, M, N, K, with_bias):
+    x, w, bias, xq, wq, xs, ws = _batched_case(ops, B, M, N, K, with_bias, seed=B * 1000 + M)
+    y = ops.f8f8bf16_rowwise_batched(xq, wq, xs, ws, bias)
+    assert y.shape == (B, M, N) and y.dtype == torch.bfloat16
+    # the reference's tolerance against the unquantized bmm
+    y_ref = torch.bmm(x.float(), w.float().transpose(1, 2))
+    if bias is not None:
+        y_ref += bias.unsqueeze(1)
+    torch.testing.assert_close(y.float(), y_ref, atol=8.0e-2, rtol=8.0e-2)
+    # the same quantized operands through the dense operator, batch by batch
+    for b in range(B):
+        y_b = ops.f8f8bf16_rowwise(xq[b], wq[b], xs[b], ws[b], None if bias is None else bias[b])
+        _close(y[b], y_b, f"batch {b} vs dense operator")
+        y_o = oracle.gemm_f8_rowwise_torch(xq[b].cpu(), wq[b].cpu(), xs[b].cpu(), ws[b].cpu(),
+                                           None if bias is None else bias[b].cpu())
+        _close(y[b].cpu(), y_o, f"batch {b} vs fp32 formula")
+    assert _status() == 0
+
+
+def test_batched_output_argument_empty_dims_and_errors(ops):
+    x, w, bias, xq, wq, xs, ws = _batched_case(ops, 2, 64, 128, 128, False, seed=1)
+    import mslk_b200.gemm  # noqa: F401  registers torch.ops.mslk.*
+    out = torch.full((2, 64, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    y = torch.ops.mslk.f8f8bf16_rowwise_batched(xq, wq, xs, ws, None, True, out)
+    assert y.data_ptr() == out.data_ptr()
+    assert torch.equal(out, ops.f8f8bf16_rowwise_batched(xq, wq, xs, ws))
+    assert ops.f8f8bf16_rowwise_batched(xq[:, :0], wq, xs[:, :0], ws).shape == (2, 0, 128)
+    z = ops.f8f8bf16_rowwise_batched(xq[:, :, :0].contiguous(), wq[:, :, :0].contiguous(), xs, ws)
+    assert z.shape == (2, 64, 128) and float(z.float().abs().max()) == 0.0
+    with pytest.raises(RuntimeError, match="3D"):
+        ops.f8f8bf16_rowwise_batched(xq[0], wq, xs, ws)
+    with pytest.raises(RuntimeError, match="fast_accum"):
+        torch.ops.mslk.f8f8bf16_rowwise_batched(xq, wq, xs, ws, None, False)
+    with pytest.raises(RuntimeError, match="float32"):
+        ops.f8f8bf16_rowwise_batched(xq, wq, xs, ws, torch.zeros((2, 128), dtype=torch.bfloat16, device="cuda"))
+    assert _status() == 0

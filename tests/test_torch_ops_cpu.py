@@ -17,11 +17,17 @@ def test_schemas_match_reference_strings(mslk):
     want = {
         "f8f8bf16_rowwise": "mslk::f8f8bf16_rowwise(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor? bias=None, bool use_fast_accum=True) -> Tensor",
         "f8f8bf16_rowwise_out": "mslk::f8f8bf16_rowwise_out(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output, Tensor? bias=None, bool use_fast_accum=True) -> ()",
+        "f8f8bf16_rowwise_batched": "mslk::f8f8bf16_rowwise_batched(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor? bias=None, bool use_fast_accum=True, Tensor(a!)? output=None) -> Tensor",
         "f8f8bf16_rowwise_grouped_stacked": "mslk::f8f8bf16_rowwise_grouped_stacked(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor M_sizes) -> Tensor",
         "f4f4bf16": "mslk::f4f4bf16(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor? output=None, Tensor? global_scale=None, int mxfp4_block_size=32) -> Tensor",
     }
     for name, schema in want.items():
         assert str(getattr(mslk, name).default._schema) == schema
+    import importlib
+    importlib.import_module("mslk.moe.activation")   # mslk/moe/activation.py:137-176 defines these from Python
+    assert str(mslk.silu_mul.default._schema) == "mslk::silu_mul(Tensor x0, Tensor x1, Tensor? valid_token_count=None) -> Tensor"
+    assert str(mslk.silu_mul_quant.default._schema) == (
+        "mslk::silu_mul_quant(Tensor x0, Tensor x1, Tensor? scale_ub=None, Tensor? valid_token_count=None) -> (Tensor, Tensor)")
 
 
 def test_reference_module_paths_resolve(mslk):
@@ -44,6 +50,9 @@ def test_fake_kernels_infer_shapes(mslk):
     y = mslk.f8f8bf16_rowwise_grouped_stacked(xq.view(150, 256), wg, xs, torch.empty((512,), device="meta"),
                                               torch.empty((4,), dtype=torch.int64, device="meta"))
     assert y.shape == (150, 128)
+    y = mslk.f8f8bf16_rowwise_batched(xq, torch.empty((3, 128, 256), dtype=f8, device="meta"),
+                                      torch.empty((3, 50), device="meta"), torch.empty((3, 128), device="meta"))
+    assert y.shape == (3, 50, 128) and y.dtype == torch.bfloat16
     y = mslk.f4f4bf16(torch.empty((5, 64), dtype=torch.uint8, device="meta"), torch.empty((32, 64), dtype=torch.uint8, device="meta"),
                       torch.empty((128, 8), dtype=f8, device="meta"), torch.empty((128, 8), dtype=f8, device="meta"),
                       None, torch.empty((1,), device="meta"))
