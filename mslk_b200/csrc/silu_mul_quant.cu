@@ -4,6 +4,7 @@
 //
 // Arithmetic, operation for operation as the reference's kernel lowers on NVIDIA GPUs:
 //     e      = ex2.approx(-x0 * log2(e))             sigmoid(x0) = 1 / (1 + e), division = div.full
+//                                                     (evaluated by an equivalent shorter sequence, see silu_mul)
 //     y      = (x0 * sigmoid) * x1                    fp32
 //     rmax   = min(max(max_k |y|, 1e-12), *scale_ub)
 //     yscale = 448 / rmax                             div.full;  inv_scale = 1 / yscale (div.full)
@@ -23,9 +24,14 @@
 namespace mslk_b200 {
 namespace {
 
-__device__ __forceinline__ float ex2_approx(float x) {
+__device__ __forceinline__ float ex2_approx_ftz(float x) {
   float r;
-  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float rcp_approx_ftz(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
 __device__ __forceinline__ float div_full(float a, float b) {
@@ -33,10 +39,34 @@ __device__ __forceinline__ float div_full(float a, float b) {
   asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
   return r;
 }
+// The reference's kernel lowers sigmoid(x) to  div.full(1, 1 + ex2.approx(-x * log2(e))).  Two
+// substitutions keep every result bit identical while shortening the instruction sequence (both
+// were checked exhaustively on a B200, over all 2^32 inputs of the first and every divisor in
+// [1, +inf] of the second):
+//   * 1 + ex2.approx(t) == 1 + ex2.approx.ftz(t): the variants differ only where the exponential is
+//     subnormal, which the addition to 1 absorbs;
+//   * div.full(1, d) == rcp.approx.ftz(d) for 1 <= d <= 2^126; larger d (x below about -87.3)
+//     need the range scaling of div.full.
+// kFast = true asserts x >= -87 (so that d < 2^126); callers test that per vector of inputs.
+template <bool kFast>
 __device__ __forceinline__ float silu_mul(float x0, float x1) {
-  const float e = ex2_approx(__fmul_rn(-x0, 1.4426950408889634f));
-  const float sig = div_full(1.0f, __fadd_rn(1.0f, e));
+  const float e = ex2_approx_ftz(__fmul_rn(-x0, 1.4426950408889634f));
+  const float d = __fadd_rn(1.0f, e);
+  const float sig = kFast ? rcp_approx_ftz(d) : div_full(1.0f, d);
   return __fmul_rn(__fmul_rn(x0, sig), x1);
+}
+constexpr float kFastSigmoidMinX = -87.0f;
+
+// y[j] = silu_mul(f0[j], f1[j]) for 8 elements; one range test for the whole vector
+__device__ __forceinline__ void silu_mul8(const float (&f0)[8], const float (&f1)[8], float (&y)[8]) {
+  const float lo = fminf(fminf(fminf(f0[0], f0[1]), fminf(f0[2], f0[3])), fminf(fminf(f0[4], f0[5]), fminf(f0[6], f0[7])));
+  if (lo >= kFastSigmoidMinX) {   // false for NaN as well: the general form handles it
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = silu_mul<true>(f0[j], f1[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = silu_mul<false>(f0[j], f1[j]);
+  }
 }
 __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
   uint16_t r;
@@ -84,22 +114,25 @@ struct SiluParams {
   int64_t T, D, stride0, stride1;
 };
 
-template <int kBlock>
+// Maximum over the block (blockDim.x a multiple of 32, at most 1024); s_part holds 32 floats.
 __device__ __forceinline__ float block_max(float v, float *s_part) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   if ((threadIdx.x & 31) == 0) s_part[threadIdx.x / 32] = v;
   __syncthreads();
-  float m = 0.f;
+  const int warps = blockDim.x / 32;
+  float m = (threadIdx.x & 31) < warps ? s_part[threadIdx.x & 31] : 0.f;
 #pragma unroll
-  for (int w = 0; w < kBlock / 32; ++w) m = fmaxf(m, s_part[w]);
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   return m;
 }
 
-// Vector path: D % 8 == 0, 16-byte aligned rows; kVecs 8-element vectors per thread.
-template <typename T, int kVecs, int kBlock>
-__global__ void __launch_bounds__(kBlock) silu_mul_quant_vec_kernel(const SiluParams p) {
-  __shared__ float s_part[kBlock / 32];
+// Vector path: D % 8 == 0, 16-byte aligned rows; kVecs 8-element vectors per thread, the block size
+// chosen by the host so that kVecs * blockDim.x covers the row with less than one warp of slack.
+template <typename T, int kVecs, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads) silu_mul_quant_vec_kernel(const SiluParams p) {
+  __shared__ float s_part[32];
+  const int kBlock = blockDim.x;
   const int64_t row = blockIdx.x;
   if (p.valid_token_count && row >= *p.valid_token_count) return;
   const T *r0 = static_cast<const T *>(p.x0) + row * p.stride0;
@@ -125,12 +158,11 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_vec_kernel(const SiluPa
     unpack8<T>(a[i], f0);
     unpack8<T>(b[i], f1);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      y[i][j] = silu_mul(f0[j], f1[j]);
-      amax = fmaxf(amax, fabsf(y[i][j]));
-    }
+    silu_mul8(f0, f1, y[i]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[i][j]));
   }
-  amax = block_max<kBlock>(amax, s_part);
+  amax = block_max(amax, s_part);
   float rmax = fmaxf(amax, 1e-12f);
   if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
   const float y_scale = div_full(448.0f, rmax);
@@ -166,41 +198,43 @@ __device__ __forceinline__ float to_f32<__half>(const __half *p) {
 // General path (any D / alignment): two passes, y recomputed in the second.
 template <typename T, int kBlock>
 __global__ void __launch_bounds__(kBlock) silu_mul_quant_generic_kernel(const SiluParams p) {
-  __shared__ float s_part[kBlock / 32];
+  __shared__ float s_part[32];
   const int64_t row = blockIdx.x;
   if (p.valid_token_count && row >= *p.valid_token_count) return;
   const T *r0 = static_cast<const T *>(p.x0) + row * p.stride0;
   const T *r1 = static_cast<const T *>(p.x1) + row * p.stride1;
   float amax = 0.f;
-  for (int64_t k = threadIdx.x; k < p.D; k += kBlock) amax = fmaxf(amax, fabsf(silu_mul(to_f32<T>(r0 + k), to_f32<T>(r1 + k))));
-  amax = block_max<kBlock>(amax, s_part);
+  for (int64_t k = threadIdx.x; k < p.D; k += kBlock) amax = fmaxf(amax, fabsf(silu_mul<false>(to_f32<T>(r0 + k), to_f32<T>(r1 + k))));
+  amax = block_max(amax, s_part);
   float rmax = fmaxf(amax, 1e-12f);
   if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
   const float y_scale = div_full(448.0f, rmax);
   if (threadIdx.x == 0) p.inv_scale[row] = div_full(1.0f, y_scale);
   uint8_t *qr = p.q + row * p.D;
   for (int64_t k = threadIdx.x; k < p.D; k += kBlock) {
-    const float y = silu_mul(to_f32<T>(r0 + k), to_f32<T>(r1 + k));
+    const float y = silu_mul<false>(to_f32<T>(r0 + k), to_f32<T>(r1 + k));
     qr[k] = static_cast<uint8_t>(cvt_e4m3x2(__fmul_rn(y, y_scale), 0.f) & 0xffu);
   }
 }
 
-template <typename T, int kVecs, int kBlock>
-int launch_vec(const SiluParams &p, cudaStream_t st) {
-  silu_mul_quant_vec_kernel<T, kVecs, kBlock><<<static_cast<unsigned>(p.T), kBlock, 0, st>>>(p);
+template <typename T, int kVecs>
+int launch_vec(const SiluParams &p, int64_t nvec, cudaStream_t st) {
+  const int threads = static_cast<int>((nvec + kVecs - 1) / kVecs + 31) / 32 * 32;
+  if (threads <= 512)
+    silu_mul_quant_vec_kernel<T, kVecs, 512><<<static_cast<unsigned>(p.T), threads, 0, st>>>(p);
+  else
+    silu_mul_quant_vec_kernel<T, kVecs, 1024><<<static_cast<unsigned>(p.T), threads, 0, st>>>(p);
   return check_cuda(cudaGetLastError(), "silu_mul_quant launch");
 }
 
 template <typename T>
 int launch_typed(const SiluParams &p, bool vec_ok, cudaStream_t st) {
-  if (vec_ok) {
-    const int64_t nvec = p.D / 8;
-    if (nvec <= 256 * 1) return launch_vec<T, 1, 256>(p, st);
-    if (nvec <= 256 * 2) return launch_vec<T, 2, 256>(p, st);
-    if (nvec <= 256 * 3) return launch_vec<T, 3, 256>(p, st);
-    if (nvec <= 256 * 4) return launch_vec<T, 4, 256>(p, st);
-    if (nvec <= 512 * 4) return launch_vec<T, 4, 512>(p, st);
-    if (nvec <= 1024 * 4) return launch_vec<T, 4, 1024>(p, st);
+  const int64_t nvec = p.D / 8;
+  if (vec_ok && nvec <= 4 * 1024) {
+    // four vectors per thread once that still gives a block of 128 threads; fewer for short rows
+    if (nvec >= 4 * 128) return launch_vec<T, 4>(p, nvec, st);
+    if (nvec >= 2 * 64) return launch_vec<T, 2>(p, nvec, st);
+    return launch_vec<T, 1>(p, nvec, st);
   }
   silu_mul_quant_generic_kernel<T, 256><<<static_cast<unsigned>(p.T), 256, 0, st>>>(p);
   return check_cuda(cudaGetLastError(), "silu_mul_quant launch");
@@ -243,18 +277,20 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const SiluParams p, T *__
       float f0[8], f1[8];
       unpack8<T>(ld_stream_v4(x0 + row * p.stride0 + v * 8), f0);
       unpack8<T>(ld_stream_v4(x1 + row * p.stride1 + v * 8), f1);
+      float r[8];
+      silu_mul8(f0, f1, r);
       uint4 o;
-      o.x = pack2<T>(silu_mul(f0[0], f1[0]), silu_mul(f0[1], f1[1]));
-      o.y = pack2<T>(silu_mul(f0[2], f1[2]), silu_mul(f0[3], f1[3]));
-      o.z = pack2<T>(silu_mul(f0[4], f1[4]), silu_mul(f0[5], f1[5]));
-      o.w = pack2<T>(silu_mul(f0[6], f1[6]), silu_mul(f0[7], f1[7]));
+      o.x = pack2<T>(r[0], r[1]);
+      o.y = pack2<T>(r[2], r[3]);
+      o.z = pack2<T>(r[4], r[5]);
+      o.w = pack2<T>(r[6], r[7]);
       *reinterpret_cast<uint4 *>(y + row * p.D + v * 8) = o;
     }
   } else {
     const int64_t total = valid * p.D;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
       const int64_t row = i / p.D, k = i - row * p.D;
-      y[i] = from_f32<T>(silu_mul(to_f32<T>(x0 + row * p.stride0 + k), to_f32<T>(x1 + row * p.stride1 + k)));
+      y[i] = from_f32<T>(silu_mul<false>(to_f32<T>(x0 + row * p.stride0 + k), to_f32<T>(x1 + row * p.stride1 + k)));
     }
   }
 }

@@ -2,6 +2,7 @@
 
     python -m mslk_b200.microbench quantize_fp8_row --shape 8192,4096
     python -m mslk_b200.microbench f8f8bf16_rowwise --shape 8192,8192,8192
+    python -m mslk_b200.microbench batched --shape 8,2048,4096,4096          # B,M,N,K
     python -m mslk_b200.microbench grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
     python -m mslk_b200.microbench f4f4bf16 --shape 8192,8192,8192
     python -m mslk_b200.microbench quantize_nvfp4 --shape 8192,8192
@@ -91,6 +92,24 @@ def bench_silu_mul_quant(ops, T, D, args):
             "unfused_silu_mul_then_quantize_us": sec_unfused * 1e6}
 
 
+def bench_batched(ops, B, M, N, K, args):
+    xq, xs = ops.quantize_fp8_row(_randn((B, M, K)))
+    nv = _variants(B * N * K, args.rotate_mb)
+    ws = [ops.quantize_fp8_row(_randn((B, N, K), args.w_std)) for _ in range(nv)]
+    y = torch.empty((B, M, N), dtype=torch.bfloat16, device="cuda")
+    sec = _time(lambda i: ops.f8f8bf16_rowwise_batched(xq, ws[i][0], xs, ws[i][1], output=y), nv, args.iters,
+                args.warmup, args.graph)
+
+    def loop(i):
+        for b in range(B):
+            ops.f8f8bf16_rowwise_out(xq[b], ws[i][0][b], xs[b], ws[i][1][b], y[b])
+    sec_loop = _time(loop, nv, args.iters, args.warmup, args.graph)
+    flops = 2.0 * B * M * N * K
+    return {"op": "f8f8bf16_rowwise_batched", "B": B, "M": M, "N": N, "K": K, "us": sec * 1e6,
+            "TFLOPs": flops / sec / 1e12, "loop_over_dense_us": sec_loop * 1e6,
+            "loop_over_dense_TFLOPs": flops / sec_loop / 1e12}
+
+
 def zipf_counts(experts, tokens, seed=0, s=1.2, n_empty=2):
     """Per-expert token counts: top-1 routing with Zipf(s) expert popularity, the `n_empty` least popular
     experts forced to zero tokens (their tokens go to the most popular one)."""
@@ -146,7 +165,7 @@ def bench_f4f4bf16(ops, M, N, K, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "grouped", "f4f4bf16", "quantize_nvfp4", "silu_mul_quant",
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "batched", "grouped", "f4f4bf16", "quantize_nvfp4", "silu_mul_quant",
                                    "sweep"])
     ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
     ap.add_argument("--experts", type=int, default=16)
@@ -165,6 +184,8 @@ def main():
         out.append(bench_quantize_fp8_row(ops, *(shape or [8192, 4096]), args))
     elif args.op == "f8f8bf16_rowwise":
         out.append(bench_f8f8bf16_rowwise(ops, *(shape or [8192, 8192, 8192]), args))
+    elif args.op == "batched":
+        out.append(bench_batched(ops, *(shape or [8, 2048, 4096, 4096]), args))
     elif args.op == "grouped":
         out.append(bench_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
     elif args.op == "quantize_nvfp4":

@@ -204,12 +204,13 @@ def leg_gpu(ref_root: str):
 # (T, D, scale_ub, valid tokens or None, contiguous) -- after test/moe/activation_test.py:97-168
 SILU_CASES = [
     ("s1x5120", 1, 5120, None, None, True),
-    ("s128x5120", 128, 5120, None, None, True),
-    ("s128x7168_ub", 128, 7168, 1200.0, None, True),
-    ("s64x8192_strided", 64, 8192, None, None, False),
+    ("s32x5120", 32, 5120, None, None, True),
+    ("s32x7168_ub", 32, 7168, 1200.0, None, True),
+    ("s16x8192_strided", 16, 8192, None, None, False),
     ("s200x1024_partial", 200, 1024, None, 100, True),
     ("s16x14336_ub_small", 16, 14336, 0.05, None, True),
     ("s8x256_tiny", 8, 256, None, None, True),
+    ("s32x2048_wide", 32, 2048, None, None, True),
 ]
 
 
@@ -218,6 +219,8 @@ def silu_inputs(name, T, D, seed):
     x = torch.randn((T, 2 * D), generator=g, dtype=torch.float32).to(torch.bfloat16)
     if "tiny" in name:
         x = (x.float() * 1e-7).to(torch.bfloat16)      # row maxima below the 1e-12 floor of the scale
+    elif "wide" in name:
+        x = (x.float() * 60.0).to(torch.bfloat16)      # gate values below -87.3: exp(-x) beyond 2^126
     else:
         x = torch.sign(x) * torch.clamp(torch.abs(x), 0.01, 2.0)
     return x
@@ -240,7 +243,10 @@ def leg_gpu_silu(ref_root: str):
         vt = None if valid is None else torch.tensor([valid], dtype=torch.int32, device="cuda")
         q, s = act.silu_mul_quant(x0, x1, ubt, vt)
         torch.cuda.synchronize()
-        out[f"{name}.x"] = _raw(x)
+        if valid is not None:          # rows past the count are never written: keep the file small
+            q.view(torch.uint8)[valid:] = 0
+            s[valid:] = 0
+        # the inputs are not stored: silu_inputs() regenerates them from the seed
         out[f"{name}.q"] = _raw(q)
         out[f"{name}.s"] = _raw(s)
     np.savez_compressed(os.path.join(HERE, "silu_mul_quant_triton_b200.npz"), **out)

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import bf16, load_golden, u8
+from helpers import load_golden, u8
 from golden.make_golden import SILU_CASES, silu_inputs
 
 pytestmark = pytest.mark.gpu
@@ -57,7 +57,7 @@ def test_triton_fixture_bit_exact(ops):
     if gold is None:
         pytest.skip("fixture captured from the reference's Triton kernel not present")
     for i, (name, T, D, ub, valid, contiguous) in enumerate(SILU_CASES):
-        x0, x1, ubt, vt = _case_inputs(i, name, T, D, ub, valid, contiguous, bf16(gold[f"{name}.x"]).reshape(T, 2 * D))
+        x0, x1, ubt, vt = _case_inputs(i, name, T, D, ub, valid, contiguous)
         q, s = ops.silu_mul_quant(x0, x1, ubt, vt)
         n = T if valid is None else valid
         s_ref = torch.from_numpy(gold[f"{name}.s"]).reshape(T)

@@ -240,9 +240,9 @@ def test_silu_mul_quant_triton_fixture_close_to_oracle():
     gold = load_golden("silu_mul_quant_triton_b200.npz")
     if gold is None:
         pytest.skip("fixture captured from the reference's Triton kernel not present")
-    from golden.make_golden import SILU_CASES
-    for name, T, D, ub, valid, contiguous in SILU_CASES:
-        x = bf16(gold[f"{name}.x"]).reshape(T, 2 * D)
+    from golden.make_golden import SILU_CASES, silu_inputs
+    for i, (name, T, D, ub, valid, contiguous) in enumerate(SILU_CASES):
+        x = silu_inputs(name, T, D, 400 + i)
         n = T if valid is None else valid
         q, s = oracle.silu_mul_quant(x[:, :D], x[:, D:], None if ub is None else torch.tensor([ub]), valid)
         s_g = torch.from_numpy(gold[f"{name}.s"]).reshape(T)
