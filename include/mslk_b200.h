@@ -225,6 +225,65 @@ int mslk_b200_silu_mul(const void *x0, const void *x1, int dtype, int64_t T, int
                        int64_t stride0, int64_t stride1, const int *valid_token_count, void *y,
                        void *stream);
 
+/* element type code of int32 tensors, accepted by the scatter-add entry points only */
+#define MSLK_B200_I32 3
+
+/*
+ * Token gather (MoE dispatch):  out[i, :] = dtype(f32(x[tok[i], :]) * f32(scores[tok[i], exp[i]])), i < a.
+ * Replaces: mslk/moe/gather_scatter.py:18-93 (gather_scale_dense_tokens), kernel :431-486.
+ * x [T, D] contiguous bf16/fp16; token_indices / expert_indices [a] of 32- or 64-bit integers
+ * (`*_index_bits`); scores [T, E] of scores_dtype (MSLK_B200_F32/BF16/F16) with element strides
+ * stride_t, stride_e; out [a, D] in the dtype of x.  Rows i >= *valid_token_count (device int32,
+ * may be NULL) are skipped.  An index outside [0, T) x [0, E) skips the row and sets bit 0x100
+ * of the device status word.
+ */
+int mslk_b200_gather_scale_dense_tokens(const void *x, int dtype, int64_t T, int64_t D,
+                                        const void *token_indices, int token_index_bits,
+                                        const void *expert_indices, int expert_index_bits,
+                                        const void *scores, int scores_dtype, int64_t E,
+                                        int64_t stride_t, int64_t stride_e, int64_t a,
+                                        const int *valid_token_count, void *out, void *stream);
+
+/*
+ * The same gather fused with per-row FP8 quantization:  v = f32(x[tok[i]]) * score,
+ *     rmax = min(max(max_k |v|, 1e-12), *scale_ub),  os = 448 / rmax,
+ *     q[i, k] = e4m3_rn_satfinite(v[k] * os),  inv_scale[i] = 1 / os.
+ * Replaces: mslk/moe/gather_scatter.py:96-169 (gather_scale_quant_dense_tokens), kernel :537-655
+ * (same approximate divisions, so q and inv_scale agree bit for bit).  q [a, D] bytes, inv_scale fp32 [a].
+ */
+int mslk_b200_gather_scale_quant_dense_tokens(const void *x, int dtype, int64_t T, int64_t D,
+                                              const void *token_indices, int token_index_bits,
+                                              const void *expert_indices, int expert_index_bits,
+                                              const void *scores, int scores_dtype, int64_t E,
+                                              int64_t stride_t, int64_t stride_e, int64_t a,
+                                              const float *scale_ub, const int *valid_token_count,
+                                              void *q, float *inv_scale, void *stream);
+
+/*
+ * Token scatter-add (MoE combine):  out_tokens[tok[i], :] += in_tokens[i, :] for i < min(a, *valid_token_count),
+ * atomically, in the tensors' dtype (MSLK_B200_BF16 / F16 / F32 / I32; 16-byte vector reductions).
+ * Replaces: mslk/moe/gather_scatter.py:172-226 (scatter_add_dense_tokens), kernel :489-526.
+ * out_tokens [T, D], in_tokens [a, D] contiguous.  With several contributions per output row the
+ * floating-point sum depends on the order the atomics land in, as it does in the reference.
+ * An index outside [0, T) skips the row and sets bit 0x200 of the device status word.
+ */
+int mslk_b200_scatter_add_dense_tokens(void *out_tokens, int64_t T, const void *in_tokens, int dtype,
+                                       int64_t a, int64_t D, const void *token_indices,
+                                       int token_index_bits, const int *valid_token_count,
+                                       void *stream);
+
+/*
+ * Scatter-add of expert-parallel padded buffers:  for every stacked row i < sum(token_counts),
+ * out_tokens[tok[i], :] += in_tokens[rank(i), i, :], rank(i) = (expert owning row i) / (E / EP).
+ * Replaces: mslk/moe/gather_scatter.py:229-282 (scatter_add_padded_tokens), kernel :677-740.
+ * in_tokens [EP, T_K, D], token_counts [E] (32- or 64-bit, on the device), token_indices [T_K],
+ * out_tokens [T, D].  E % EP == 0, E <= 1024.
+ */
+int mslk_b200_scatter_add_padded_tokens(const void *in_tokens, int dtype, int64_t EP, int64_t T_K,
+                                        int64_t D, const void *token_counts, int count_bits,
+                                        int64_t E, const void *token_indices, int token_index_bits,
+                                        void *out_tokens, int64_t T, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

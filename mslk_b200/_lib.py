@@ -51,6 +51,16 @@ lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i6
 lib.mslk_b200_f4f4bf16.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_batched.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f8f8bf16_rowwise_batched.restype = _int
+lib.mslk_b200_gather_scale_dense_tokens.argtypes = [_vp, _int, _i64, _i64, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64,
+                                                    _i64, _vp, _vp, _vp]
+lib.mslk_b200_gather_scale_dense_tokens.restype = _int
+lib.mslk_b200_gather_scale_quant_dense_tokens.argtypes = [_vp, _int, _i64, _i64, _vp, _int, _vp, _int, _vp, _int, _i64, _i64,
+                                                          _i64, _i64, _vp, _vp, _vp, _vp, _vp]
+lib.mslk_b200_gather_scale_quant_dense_tokens.restype = _int
+lib.mslk_b200_scatter_add_dense_tokens.argtypes = [_vp, _i64, _vp, _int, _i64, _i64, _vp, _int, _vp, _vp]
+lib.mslk_b200_scatter_add_dense_tokens.restype = _int
+lib.mslk_b200_scatter_add_padded_tokens.argtypes = [_vp, _int, _i64, _i64, _i64, _vp, _int, _i64, _vp, _int, _vp, _i64, _vp]
+lib.mslk_b200_scatter_add_padded_tokens.restype = _int
 lib.mslk_b200_silu_mul_quant.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp]
 lib.mslk_b200_silu_mul_quant.restype = _int
 lib.mslk_b200_silu_mul.argtypes = [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp, _vp]

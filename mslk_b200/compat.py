@@ -20,6 +20,7 @@ _ALIASES = {
     "mslk.quantize.triton.fp4_utils": "mslk_b200.quantize.triton.fp4_utils",
     "mslk.moe": "mslk_b200.moe",
     "mslk.moe.activation": "mslk_b200.moe.activation",
+    "mslk.moe.gather_scatter": "mslk_b200.moe.gather_scatter",
 }
 
 

@@ -12,6 +12,8 @@ operators they stand for:
 * ``quantize_nvfp4``         -- ``mslk/quantize/triton/quantize_kernels/nvfp4.py:62-149``
 * ``f4f4bf16``               -- ``csrc/gemm/cutlass/f4f4bf16.cu:6413-6473``
 * ``silu_mul`` / ``silu_mul_quant`` -- ``mslk/moe/activation.py:25-69,72-133``
+* ``gather_scale_dense_tokens``, ``gather_scale_quant_dense_tokens``, ``scatter_add_dense_tokens``,
+  ``scatter_add_padded_tokens`` -- ``mslk/moe/gather_scatter.py:18-282``
 
 CPU tensors are rejected: there is no fallback path.
 """
@@ -376,3 +378,120 @@ def silu_mul_quant(x0: torch.Tensor, x1: torch.Tensor, scale_ub: Optional[torch.
                                            x1.stride(0), _ptr(ub), _ptr(vtc), _ptr(out), _ptr(inv_scale),
                                            _stream(dev)), "silu_mul_quant")
     return out, inv_scale
+
+
+# --------------------------------------------------------------------------- MoE token gather / scatter
+
+_SCATTER_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2, torch.int32: 3}
+
+
+def _index_bits(name: str, t: torch.Tensor) -> int:
+    if t.dtype == torch.int32:
+        return 32
+    if t.dtype == torch.int64:
+        return 64
+    raise RuntimeError(f"{name}: index tensors must be int32 or int64, got {t.dtype}")
+
+
+def _valid_count(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if t is not None and t.dtype != torch.int32:
+        t = t.to(torch.int32)
+    return t
+
+
+def _gather_args(name, x, token_indices, expert_indices, scores, valid_token_count):
+    dev = _require_cuda(name, x, token_indices, expert_indices, scores, valid_token_count)
+    assert x.dim() == 2 and scores.dim() == 2
+    T, D = x.shape
+    E = scores.shape[1]
+    a = token_indices.shape[0]
+    assert x.is_contiguous()
+    assert token_indices.is_contiguous()
+    assert expert_indices.is_contiguous()
+    assert tuple(token_indices.shape) == (a,)
+    assert tuple(expert_indices.shape) == (a,)
+    assert tuple(scores.shape) == (T, E)
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"{name}: x must be bfloat16 or float16, got {x.dtype}")
+    if scores.dtype not in _DTYPE_CODE:
+        raise RuntimeError(f"{name}: unsupported scores dtype {scores.dtype}")
+    return dev, T, D, E, a
+
+
+def gather_scale_dense_tokens(x, token_indices, expert_indices, scores, valid_token_count=None) -> torch.Tensor:
+    """``out[i] = x[token_indices[i]] * scores[token_indices[i], expert_indices[i]]`` -> ``[a, D]`` in ``x.dtype``."""
+    name = "gather_scale_dense_tokens"
+    dev, T, D, E, a = _gather_args(name, x, token_indices, expert_indices, scores, valid_token_count)
+    out = torch.empty((a, D), device=dev, dtype=x.dtype)
+    if a == 0 or D == 0:
+        return out
+    vtc = _valid_count(valid_token_count)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_gather_scale_dense_tokens(
+            _ptr(x), _DTYPE_CODE[x.dtype], T, D, _ptr(token_indices), _index_bits(name, token_indices),
+            _ptr(expert_indices), _index_bits(name, expert_indices), _ptr(scores), _DTYPE_CODE[scores.dtype], E,
+            scores.stride(0), scores.stride(1), a, _ptr(vtc), _ptr(out), _stream(dev)), name)
+    return out
+
+
+def gather_scale_quant_dense_tokens(x, token_indices, expert_indices, scores, scale_ub=None, valid_token_count=None):
+    """The same gather followed by per-row FP8 quantization: ``(fp8 [a, D], inverse scale fp32 [a])``."""
+    name = "gather_scale_quant_dense_tokens"
+    dev, T, D, E, a = _gather_args(name, x, token_indices, expert_indices, scores, valid_token_count)
+    _require_cuda(name, x, scale_ub)
+    out = torch.empty((a, D), device=dev, dtype=FP8_DTYPE)
+    out_scale = torch.empty((a,), device=dev, dtype=torch.float32)
+    if a == 0 or D == 0:
+        return out, out_scale
+    ub = None
+    if scale_ub is not None:
+        ub = scale_ub if scale_ub.dtype == torch.float32 else scale_ub.to(torch.float32)
+    vtc = _valid_count(valid_token_count)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_gather_scale_quant_dense_tokens(
+            _ptr(x), _DTYPE_CODE[x.dtype], T, D, _ptr(token_indices), _index_bits(name, token_indices),
+            _ptr(expert_indices), _index_bits(name, expert_indices), _ptr(scores), _DTYPE_CODE[scores.dtype], E,
+            scores.stride(0), scores.stride(1), a, _ptr(ub), _ptr(vtc), _ptr(out), _ptr(out_scale), _stream(dev)), name)
+    return out, out_scale
+
+
+def scatter_add_dense_tokens(out_tokens, in_tokens, token_indices, valid_token_count=None) -> None:
+    """``out_tokens[token_indices[i]] += in_tokens[i]`` (atomic adds in the tensors' dtype)."""
+    name = "scatter_add_dense_tokens"
+    dev = _require_cuda(name, out_tokens, in_tokens, token_indices, valid_token_count)
+    assert in_tokens.is_contiguous()
+    assert token_indices.is_contiguous()
+    assert out_tokens.is_contiguous()
+    a, D = in_tokens.shape
+    if a == 0:
+        return
+    assert token_indices.shape == (a,)
+    assert out_tokens.ndim == 2 and out_tokens.shape[1] == D
+    if in_tokens.dtype != out_tokens.dtype or in_tokens.dtype not in _SCATTER_DTYPE_CODE:
+        raise RuntimeError(f"{name}: in/out tokens must share a dtype of float32, bfloat16, float16 or int32")
+    vtc = _valid_count(valid_token_count)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_scatter_add_dense_tokens(
+            _ptr(out_tokens), out_tokens.shape[0], _ptr(in_tokens), _SCATTER_DTYPE_CODE[in_tokens.dtype], a, D,
+            _ptr(token_indices), _index_bits(name, token_indices), _ptr(vtc), _stream(dev)), name)
+
+
+def scatter_add_padded_tokens(in_tokens, token_counts, token_indices, out_tokens) -> None:
+    """``out_tokens[token_indices[i]] += in_tokens[rank(i), i]`` over the rows counted by ``token_counts``."""
+    name = "scatter_add_padded_tokens"
+    dev = _require_cuda(name, in_tokens, token_counts, token_indices, out_tokens)
+    assert in_tokens.is_contiguous()
+    assert token_counts.is_contiguous()
+    assert token_indices.is_contiguous()
+    assert out_tokens.is_contiguous()
+    EP, T_K, D = in_tokens.shape
+    E = token_counts.shape[0]
+    assert tuple(token_indices.shape) == (T_K,)
+    assert T_K % out_tokens.shape[0] == 0 and out_tokens.shape[1] == D
+    if in_tokens.dtype != out_tokens.dtype or in_tokens.dtype not in _SCATTER_DTYPE_CODE:
+        raise RuntimeError(f"{name}: in/out tokens must share a dtype of float32, bfloat16, float16 or int32")
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_scatter_add_padded_tokens(
+            _ptr(in_tokens), _SCATTER_DTYPE_CODE[in_tokens.dtype], EP, T_K, D, _ptr(token_counts),
+            _index_bits(name, token_counts), E, _ptr(token_indices), _index_bits(name, token_indices),
+            _ptr(out_tokens), out_tokens.shape[0], _stream(dev)), name)

@@ -72,6 +72,12 @@ def lib() -> ctypes.CDLL:
         L.oracle_gemm_nvfp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
         L.oracle_gemm_nvfp4.restype = None
         L.oracle_check_fma_division.argtypes = [vp, vp, i64]
+        L.oracle_gather_scale_bf16.argtypes = [vp, i64, vp, i32, vp, i32, vp, i32, i64, i64, i64, i64, vp]
+        L.oracle_gather_scale_bf16.restype = None
+        L.oracle_gather_scale_quant_bf16.argtypes = [vp, i64, vp, i32, vp, i32, vp, i32, i64, i64, i64, i64, vp, vp, vp]
+        L.oracle_gather_scale_quant_bf16.restype = None
+        L.oracle_scatter_add.argtypes = [vp, vp, i32, i64, i64, vp, i32, i64, vp, i32, i64, i64]
+        L.oracle_scatter_add.restype = None
         L.oracle_silu_mul.argtypes = [vp, vp, i32, i64, i64, i64, i64, i64, vp]
         L.oracle_silu_mul.restype = None
         L.oracle_silu_mul_quant.argtypes = [vp, vp, i32, i64, i64, i64, i64, vp, i64, vp, vp]
@@ -355,3 +361,70 @@ def silu_mul_quant(x0: torch.Tensor, x1: torch.Tensor, scale_ub: Optional[torch.
         lib().oracle_silu_mul_quant(_p(x0), _p(x1), DTYPE_CODE[x0.dtype], T, D, x0.stride(0), x1.stride(0),
                                     _p(ub), valid, _p(q), _p(s))
     return q.view(torch.float8_e4m3fn), s
+
+
+# --------------------------------------------------------------------------
+# MoE token gather / scatter
+# --------------------------------------------------------------------------
+
+def _bits(t: torch.Tensor) -> int:
+    assert t.dtype in (torch.int32, torch.int64)
+    return 32 if t.dtype == torch.int32 else 64
+
+
+def gather_scale_dense_tokens(x, token_indices, expert_indices, scores, valid_token_count: Optional[int] = None):
+    """Exact statement of ``mslk/moe/gather_scatter.py:431-486`` for bf16 ``x``; rows past the count stay 0."""
+    x, token_indices, expert_indices, scores = _cpu(x), _cpu(token_indices), _cpu(expert_indices), _cpu(scores)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and scores.dtype in DTYPE_CODE
+    a, D = token_indices.shape[0], x.shape[1]
+    out = torch.zeros((a, D), dtype=torch.bfloat16)
+    valid = a if valid_token_count is None else int(valid_token_count)
+    if a and D:
+        lib().oracle_gather_scale_bf16(_p(x), D, _p(token_indices), _bits(token_indices), _p(expert_indices),
+                                       _bits(expert_indices), _p(scores), DTYPE_CODE[scores.dtype], scores.stride(0),
+                                       scores.stride(1), a, valid, _p(out))
+    return out
+
+
+def gather_scale_quant_dense_tokens(x, token_indices, expert_indices, scores, scale_ub=None,
+                                    valid_token_count: Optional[int] = None):
+    """``mslk/moe/gather_scatter.py:537-655`` with IEEE divisions; returns ``(fp8 [a, D], inverse scale [a])``."""
+    x, token_indices, expert_indices, scores = _cpu(x), _cpu(token_indices), _cpu(expert_indices), _cpu(scores)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and scores.dtype in DTYPE_CODE
+    a, D = token_indices.shape[0], x.shape[1]
+    q = torch.zeros((a, D), dtype=torch.uint8)
+    s = torch.zeros((a,), dtype=torch.float32)
+    ub = None if scale_ub is None else _cpu(scale_ub).to(torch.float32).contiguous()
+    valid = a if valid_token_count is None else int(valid_token_count)
+    if a and D:
+        lib().oracle_gather_scale_quant_bf16(_p(x), D, _p(token_indices), _bits(token_indices), _p(expert_indices),
+                                             _bits(expert_indices), _p(scores), DTYPE_CODE[scores.dtype],
+                                             scores.stride(0), scores.stride(1), a, valid, _p(ub), _p(q), _p(s))
+    return q.view(torch.float8_e4m3fn), s
+
+
+_SCATTER_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.int32: 3}
+
+
+def scatter_add_dense_tokens(out_tokens, in_tokens, token_indices, valid_token_count: Optional[int] = None):
+    """In place ``out_tokens[token_indices[i]] += in_tokens[i]`` in row order (``gather_scatter.py:489-526``)."""
+    out_tokens, in_tokens, token_indices = _cpu(out_tokens), _cpu(in_tokens), _cpu(token_indices)
+    assert out_tokens.is_contiguous() and in_tokens.is_contiguous() and in_tokens.dtype == out_tokens.dtype
+    a, D = in_tokens.shape
+    valid = a if valid_token_count is None else int(valid_token_count)
+    if a and D:
+        lib().oracle_scatter_add(_p(out_tokens), _p(in_tokens), _SCATTER_CODE[in_tokens.dtype], a, D, _p(token_indices),
+                                 _bits(token_indices), valid, None, 32, 1, 1)
+
+
+def scatter_add_padded_tokens(in_tokens, token_counts, token_indices, out_tokens):
+    """In place statement of ``gather_scatter.py:677-740`` for ``in_tokens [EP, T_K, D]``."""
+    in_tokens, token_counts, token_indices, out_tokens = (_cpu(in_tokens), _cpu(token_counts), _cpu(token_indices),
+                                                          _cpu(out_tokens))
+    assert out_tokens.is_contiguous() and in_tokens.is_contiguous() and in_tokens.dtype == out_tokens.dtype
+    EP, T_K, D = in_tokens.shape
+    E = token_counts.shape[0]
+    if T_K and D:
+        lib().oracle_scatter_add(_p(out_tokens), _p(in_tokens), _SCATTER_CODE[in_tokens.dtype], T_K, D,
+                                 _p(token_indices), _bits(token_indices), T_K, _p(token_counts), _bits(token_counts),
+                                 E, EP)

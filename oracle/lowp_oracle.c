@@ -450,3 +450,76 @@ ORACLE_API void oracle_silu_mul_quant(const void *x0, const void *x1, int dtype,
   }
   free(y);
 }
+
+/* ------------------------------------------------------------------------ */
+/* MoE token gather / scatter (mslk/moe/gather_scatter.py)                    */
+/* ------------------------------------------------------------------------ */
+
+static inline int64_t load_index(const void *p, int bits, int64_t i) {
+  return bits == 64 ? ((const int64_t *)p)[i] : (int64_t)((const int32_t *)p)[i];
+}
+
+/* :431-486  out[i] = bf16(f32(x[tok[i]]) * f32(scores[tok[i], exp[i]])); x and out are bf16.  Exact. */
+ORACLE_API void oracle_gather_scale_bf16(const uint16_t *x, int64_t D, const void *tok, int tok_bits, const void *exp_,
+                                         int exp_bits, const void *scores, int scores_dtype, int64_t stride_t,
+                                         int64_t stride_e, int64_t a, int64_t valid, uint16_t *out) {
+  for (int64_t i = 0; i < a && i < valid; ++i) {
+    int64_t ti = load_index(tok, tok_bits, i), ei = load_index(exp_, exp_bits, i);
+    float score = load_elem(scores, scores_dtype, ti * stride_t + ei * stride_e);
+    for (int64_t k = 0; k < D; ++k) out[i * D + k] = oracle_f32_to_bf16(bf16_to_f32(x[ti * D + k]) * score);
+  }
+}
+
+/* :537-655  the same product quantized per row: os = 448 / rmax, inv_scale = 1 / os, q = e4m3(v * os).
+ * The GPU kernels use an approximate division for the two quotients; IEEE division here, so the
+ * scale agrees to a few ulps and single bytes may differ by one code at rounding boundaries. */
+ORACLE_API void oracle_gather_scale_quant_bf16(const uint16_t *x, int64_t D, const void *tok, int tok_bits,
+                                               const void *exp_, int exp_bits, const void *scores, int scores_dtype,
+                                               int64_t stride_t, int64_t stride_e, int64_t a, int64_t valid,
+                                               const float *scale_ub, uint8_t *q, float *inv_scale) {
+  for (int64_t i = 0; i < a && i < valid; ++i) {
+    int64_t ti = load_index(tok, tok_bits, i), ei = load_index(exp_, exp_bits, i);
+    float score = load_elem(scores, scores_dtype, ti * stride_t + ei * stride_e);
+    float amax = 0.f;
+    for (int64_t k = 0; k < D; ++k) {
+      float v = fabsf(bf16_to_f32(x[ti * D + k]) * score);
+      if (v > amax) amax = v;
+    }
+    float rmax = amax > 1e-12f ? amax : 1e-12f;
+    if (scale_ub && rmax > *scale_ub) rmax = *scale_ub;
+    float os = 448.0f / rmax;
+    inv_scale[i] = 1.0f / os;
+    for (int64_t k = 0; k < D; ++k) q[i * D + k] = oracle_f32_to_e4m3((bf16_to_f32(x[ti * D + k]) * score) * os);
+  }
+}
+
+/* :489-526 / :677-740  out[tok[i]] += in[src_plane(i), i], one rounding per add, rows applied in order
+ * (one of the orders the reference's atomics may take).  dtype: 0 fp32, 1 bf16, 3 int32.
+ * counts == NULL: dense variant (plane 0, rows = min(a, valid)).  Otherwise the stacked row count is
+ * sum(counts) and the plane of row i is (expert owning i) / (E / EP). */
+ORACLE_API void oracle_scatter_add(void *out, const void *in, int dtype, int64_t rows, int64_t D, const void *tok,
+                                   int tok_bits, int64_t valid, const void *counts, int count_bits, int64_t E,
+                                   int64_t EP) {
+  int64_t n = rows < valid ? rows : valid;
+  int64_t total = 0;
+  if (counts) {
+    for (int64_t e = 0; e < E; ++e) total += load_index(counts, count_bits, e);
+    n = rows < total ? rows : total;
+  }
+  int64_t e = 0, end = counts ? load_index(counts, count_bits, 0) : 0;
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t plane = 0;
+    if (counts) {
+      while (i >= end) end += load_index(counts, count_bits, ++e);
+      plane = e / (E / EP);
+    }
+    int64_t to = load_index(tok, tok_bits, i);
+    for (int64_t k = 0; k < D; ++k) {
+      int64_t s = (plane * rows + i) * D + k, d = to * D + k;
+      if (dtype == 0) ((float *)out)[d] += ((const float *)in)[s];
+      else if (dtype == 1)
+        ((uint16_t *)out)[d] = oracle_f32_to_bf16(bf16_to_f32(((uint16_t *)out)[d]) + bf16_to_f32(((const uint16_t *)in)[s]));
+      else ((int32_t *)out)[d] += ((const int32_t *)in)[s];
+    }
+  }
+}

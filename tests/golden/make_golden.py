@@ -11,6 +11,9 @@ Two legs, both writing ``.npz`` files next to this script:
       reference's own test (``test/quantize/triton/fp4_quantize_test.py:259-296``),
       ``_to_blocked``, ``global_scale_nvfp4`` and ``dequantize_nvfp4``.
 ``--leg gpu_silu``  (needs a B200) runs the reference's fused ``silu_mul_quant`` (``mslk/moe/activation.py``).
+``--leg gpu_gather``  (needs a B200) runs the reference's ``gather_scale_quant_dense_tokens``
+    (``mslk/moe/gather_scatter.py``).  These two legs store outputs only; the tests regenerate the
+    seeded inputs with ``silu_inputs`` / ``gather_inputs`` (CPU generator, same torch build).
 ``--leg gpu``  (needs a B200) runs the reference's Triton kernels
     ``triton_quantize_fp8_row`` and ``triton_quantize_nvfp4`` on the same seeded
     inputs; these are the bit-level pins for the GPU arithmetic.
@@ -253,13 +256,58 @@ def leg_gpu_silu(ref_root: str):
     print("gpu silu leg written")
 
 
+# (name, T, D, E, scale_ub, valid rows, scores stored row-major)
+GATHER_CASES = [
+    ("g64x5120_e8", 64, 5120, 8, None, None, False),
+    ("g128x2048_e2_ub_partial", 128, 2048, 2, 1200.0, 64, True),
+    ("g32x1024_e4_ub_small", 32, 1024, 4, 0.05, None, False),
+]
+
+
+def gather_inputs(T, D, E, seed, rowmajor):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((T, D), generator=g, dtype=torch.float32).to(torch.bfloat16)
+    token_indices = torch.randperm(T, generator=g).to(torch.int32)
+    expert_indices = torch.randint(0, E, (T,), generator=g)
+    scores = torch.randn((E, T), generator=g, dtype=torch.float32).to(torch.bfloat16).transpose(0, 1)
+    if rowmajor:
+        scores = scores.contiguous()
+    return x, token_indices, expert_indices, scores
+
+
+def leg_gpu_gather(ref_root: str):
+    """gather_scale_quant_dense_tokens of the reference (Triton, mslk/moe/gather_scatter.py:96-169,537-655) on a B200."""
+    _import_reference(ref_root)
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_ref_gather_scatter",
+                                                  os.path.join(ref_root, "mslk", "moe", "gather_scatter.py"))
+    gs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gs)
+    out = {}
+    for i, (name, T, D, E, ub, valid, rowmajor) in enumerate(GATHER_CASES):
+        x, tok, ex, scores = gather_inputs(T, D, E, 500 + i, rowmajor)
+        scores_d = scores.cuda()          # a dense transposed view keeps its strides
+        assert scores_d.stride() == scores.stride()
+        ubt = None if ub is None else torch.tensor([ub], dtype=torch.float32, device="cuda")
+        vt = None if valid is None else torch.tensor([valid], dtype=torch.int32, device="cuda")
+        q, s = gs.gather_scale_quant_dense_tokens(x.cuda(), tok.cuda(), ex.cuda(), scores_d, ubt, vt)
+        torch.cuda.synchronize()
+        if valid is not None:
+            q.view(torch.uint8)[valid:] = 0
+            s[valid:] = 0
+        out[f"{name}.q"] = _raw(q)
+        out[f"{name}.s"] = _raw(s)
+    np.savez_compressed(os.path.join(HERE, "gather_scale_quant_triton_b200.npz"), **out)
+    print("gpu gather leg written")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu"], required=True)
+    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu", "gpu_gather"], required=True)
     ap.add_argument("--ref-root", required=True)
     ap.add_argument("--out-dir", default=None, help="write here instead of beside this script")
     args = ap.parse_args()
     if args.out_dir:
         HERE = args.out_dir
         os.makedirs(HERE, exist_ok=True)
-    {"cpu": leg_cpu, "gpu": leg_gpu, "gpu_silu": leg_gpu_silu}[args.leg](args.ref_root)
+    {"cpu": leg_cpu, "gpu": leg_gpu, "gpu_silu": leg_gpu_silu, "gpu_gather": leg_gpu_gather}[args.leg](args.ref_root)

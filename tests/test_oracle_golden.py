@@ -253,3 +253,56 @@ def test_silu_mul_quant_triton_fixture_close_to_oracle():
         ob = torch.where((b & 0x80) != 0, -(b & 0x7f), b & 0x7f)
         d = (oa - ob).abs()
         assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 2e-3, name
+
+
+def test_gather_scatter_oracles_against_torch_expressions():
+    # mslk/moe/gather_scatter.py:431-486, 489-526, 677-740 restated; test/moe/gather_scatter_test.py formulations
+    from golden.make_golden import gather_inputs
+    T, D, E = 48, 96, 4
+    x, tok, ex, scores = gather_inputs(T, D, E, 3, False)
+    o = oracle.gather_scale_dense_tokens(x, tok, ex, scores, 30)
+    ref = x[tok.long()] * scores[tok.long(), ex].view(-1, 1)
+    assert torch.equal(o[:30], ref[:30]) and bool((o[30:] == 0).all())
+    q, s = oracle.gather_scale_quant_dense_tokens(x, tok, ex, scores, torch.tensor([1200.0]))
+    torch.testing.assert_close(q.float() * s[:, None], ref.float(), atol=0.0625 * float(s.max()), rtol=0.125)
+    prod = x[tok.long()].float() * scores[tok.long(), ex].float().view(-1, 1)      # unrounded fp32 product
+    torch.testing.assert_close(s, prod.abs().amax(dim=1).clamp(min=1e-12) / 448.0, rtol=1e-6, atol=0)
+    g = torch.Generator().manual_seed(1)
+    for dtype in (torch.bfloat16, torch.int32, torch.float32):
+        inn = (torch.randn((24, D), generator=g) * 4).to(dtype)
+        out = (torch.randn((24, D), generator=g) * 4).to(dtype)
+        ti = torch.randperm(24, generator=g).to(torch.int32)
+        want = out.clone().scatter_add_(0, ti[:20].long().view(-1, 1).expand(-1, D), inn[:20])
+        oracle.scatter_add_dense_tokens(out, inn, ti, 20)
+        assert torch.equal(out, want)
+    EP, TK = 2, 40
+    inn = torch.randint(-9, 9, (EP, TK, D), generator=g, dtype=torch.int32)
+    counts = torch.tensor([7, 0, 20, 5])
+    ti = (torch.randperm(TK, generator=g) % 10).to(torch.int32)
+    out = torch.zeros((10, D), dtype=torch.int32)
+    oracle.scatter_add_padded_tokens(inn, counts, ti, out)
+    want = torch.zeros((10, D), dtype=torch.int32)
+    cs = [0, 7, 7, 27, 32]
+    for rank in range(EP):
+        s0, e0 = cs[2 * rank], cs[2 * rank + 2]
+        want.scatter_add_(0, ti[s0:e0].long().view(-1, 1).expand(-1, D), inn[rank, s0:e0])
+    assert torch.equal(out, want)
+
+
+def test_gather_scale_quant_triton_fixture_close_to_oracle():
+    gold = load_golden("gather_scale_quant_triton_b200.npz")
+    if gold is None:
+        pytest.skip("fixture captured from the reference's Triton kernel not present")
+    from golden.make_golden import GATHER_CASES, gather_inputs
+    for i, (name, T, D, E, ub, valid, rowmajor) in enumerate(GATHER_CASES):
+        x, tok, ex, scores = gather_inputs(T, D, E, 500 + i, rowmajor)
+        n = T if valid is None else valid
+        q, s = oracle.gather_scale_quant_dense_tokens(x, tok, ex, scores, None if ub is None else torch.tensor([ub]), valid)
+        s_g = torch.from_numpy(gold[f"{name}.s"]).reshape(T)
+        q_g = torch.from_numpy(gold[f"{name}.q"]).reshape(T, D)
+        torch.testing.assert_close(s[:n], s_g[:n], rtol=2e-6, atol=0)
+        a, b = q.view(torch.uint8)[:n].to(torch.int16), q_g[:n].to(torch.int16)
+        oa = torch.where((a & 0x80) != 0, -(a & 0x7f), a & 0x7f)
+        ob = torch.where((b & 0x80) != 0, -(b & 0x7f), b & 0x7f)
+        d = (oa - ob).abs()
+        assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 2e-3, name
