@@ -52,10 +52,10 @@ struct BlockIn {
   uint4 a, b;   // 16 bf16 = one scale block
 };
 
-template <bool kVec>
+template <int kVec>
 __device__ __forceinline__ BlockIn load_block(const __nv_bfloat16 *src) {
   BlockIn v;
-  if (kVec) {
+  if (kVec == 1) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(v.a.x), "=r"(v.a.y), "=r"(v.a.z), "=r"(v.a.w) : "l"(src));
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
@@ -78,7 +78,7 @@ __device__ __forceinline__ BlockIn load_block(const __nv_bfloat16 *src) {
 // and no barrier between warps.  Units are walked grid-stride with the next unit's block prefetched
 // into registers.  total = gs / float(s) comes from a 127-entry table of IEEE quotients built
 // once per CTA.
-template <bool kVec>
+template <int kVec>
 __global__ void __launch_bounds__(kThreads, 6)
     quant_nvfp4_kernel(const __nv_bfloat16 *__restrict__ x, int M, int nblk, int64_t row_stride,
                        const float *__restrict__ gs_ptr, uint8_t *__restrict__ q, uint8_t *__restrict__ scales,
@@ -172,12 +172,12 @@ MSLK_API int mslk_b200_quantize_nvfp4(const void *x, int64_t M, int64_t K, int64
   auto *xb = static_cast<const __nv_bfloat16 *>(x);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (vec_ok)
-    quant_nvfp4_kernel<true><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
+    quant_nvfp4_kernel<1><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
                                                           global_scale, static_cast<uint8_t *>(q),
                                                           static_cast<uint8_t *>(scales), static_cast<int>(n_col_tiles),
                                                           static_cast<int>(units));
   else
-    quant_nvfp4_kernel<false><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
+    quant_nvfp4_kernel<0><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
                                                            global_scale, static_cast<uint8_t *>(q),
                                                            static_cast<uint8_t *>(scales), static_cast<int>(n_col_tiles),
                                                            static_cast<int>(units));

@@ -173,9 +173,10 @@ def test_bad_index_is_reported_not_followed(ops):
     tok[3] = 99                         # outside [0, T): the row is skipped and the status word says so
     out = torch.zeros((16, 64), dtype=torch.bfloat16, device="cuda")
     from mslk_b200._lib import check, lib
+    xd, td, ed, sd = x.cuda(), tok.cuda(), ex.cuda(), scores.cuda()
     check(lib.mslk_b200_gather_scale_dense_tokens(
-        x.cuda().data_ptr(), 1, 16, 64, tok.cuda().data_ptr(), 32, ex.cuda().data_ptr(), 64, scores.cuda().data_ptr(), 1,
-        2, scores.stride(0), scores.stride(1), 16, None, out.data_ptr(), torch.cuda.current_stream().cuda_stream), "gather")
+        xd.data_ptr(), 1, 16, 64, td.data_ptr(), 32, ed.data_ptr(), 64, sd.data_ptr(), 1,
+        2, sd.stride(0), sd.stride(1), 16, None, out.data_ptr(), torch.cuda.current_stream().cuda_stream), "gather")
     assert _status() == 0x100
     assert float(out[3].float().abs().max()) == 0.0 and float(out[4].float().abs().max()) > 0.0
     assert _status() == 0
