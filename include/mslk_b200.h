@@ -201,6 +201,51 @@ int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale,
                        int64_t N, int64_t K, void *stream);
 
 /*
+ * Grouped (stacked) NVFP4 GEMM for mixture-of-experts layers: group g multiplies its m_g stacked rows
+ * of xq by its own weight block wq[g] and scales the result by global_scale[g].
+ * Replaces: csrc/gemm/cutlass/f4f4bf16_grouped.cu:321-374 (f4f4bf16_grouped_stacked, NVFP4 mode) with
+ *           f4f4bf16_grouped/f4f4bf16_grouped_common.cuh:57-148, and :376-475 (f4f4bf16_grouped_mm, 2D-3D
+ *           NVFP4 case) with include/mslk/gemm/cutlass/grouped_common.cuh:215-300.
+ * xq [total_M, K/2], wq [G, N, K/2] packed e2m1; x_scale: swizzled e4m3 atoms of the padded scale
+ * matrix in which every group starts on a 128-row boundary (what mslk_b200_quantize_nvfp4_stacked
+ * writes); w_scale: [G][roundup(N,128)][K/16] swizzled per group; global_scale fp32 [G]; y [total_M, N]
+ * bf16.  Group sizes come from the device: int64 M_sizes [G] (stacked form) or int32 END offsets [G]
+ * (grouped_mm form).  starting_row_after_padding (int64 [G+1], first scale row of every group, multiples
+ * of 128) may be NULL: the groups are then taken to follow each other, each padded to 128 rows.
+ * Rows past the sum of the sizes are left untouched.  K % 32 == 0, G <= 1024.
+ */
+int mslk_b200_f4f4bf16_grouped_stacked(const void *xq, const void *wq, const void *x_scale,
+                                       const void *w_scale, const int64_t *M_sizes,
+                                       const float *global_scale,
+                                       const int64_t *starting_row_after_padding, int64_t G,
+                                       int64_t total_M, int64_t N, int64_t K, void *y, void *stream);
+int mslk_b200_f4f4bf16_grouped_mm(const void *xq, const void *wq, const void *x_scale,
+                                  const void *w_scale, const int32_t *offsets,
+                                  const float *global_scale, int64_t G, int64_t total_M, int64_t N,
+                                  int64_t K, void *y, void *stream);
+
+/*
+ * NVFP4 quantization of stacked groups with one global scale per group.
+ * Replaces: mslk/quantize/triton/legacy/quantize_stacked.py:22-178,315-400 (nvfp4_quantize_stacked).
+ * x bf16 [M, K] (row stride in elements), m_sizes int64 [G] and global_scale fp32 [G] on the device.
+ * q [M, K/2]; scales: buffer of (M + 127*G) x roundup(K/16, 4) bytes holding the swizzled atoms of the
+ * padded scale matrix; the blocks of all groups present are written completely (padding = 0), the
+ * unused tail of the buffer is not touched.  Rows past sum(m_sizes) are not quantized.
+ */
+int mslk_b200_quantize_nvfp4_stacked(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                                     const int64_t *m_sizes, int64_t G, const float *global_scale,
+                                     void *q, void *scales, void *stream);
+
+/*
+ * Per-group NVFP4 global scale:  global_scale[g] = 2688 / max|x[rows of g]| (1e-8 for an all-zero group,
+ * FLT_MAX for a group without rows), tensor_idx[r] = group of row r (int64 [M], may be NULL).
+ * Replaces: mslk/quantize/triton/legacy/global_scale.py:40-230 (calculate_group_max).
+ */
+int mslk_b200_calculate_group_max(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                                  const int64_t *m_sizes, int64_t G, float *global_scale,
+                                  int64_t *tensor_idx, void *stream);
+
+/*
  * Fused SwiGLU + per-row FP8 quantization:  y = x0 * sigmoid(x0) * x1 (fp32),
  *     rmax = min(max(max_k |y|, 1e-12), *scale_ub)        (scale_ub may be NULL)
  *     q[r, k] = e4m3_rn_satfinite(y * (448 / rmax)),  inv_scale[r] = 1 / (448 / rmax).

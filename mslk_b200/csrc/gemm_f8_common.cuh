@@ -29,6 +29,9 @@ struct GemmParams {
   int G;
   int total_m;
   int group_m;  // rows of every group when m_sizes is null (batched GEMM); total_m for the dense case
+  // Alternative to m_sizes: int32 END offsets of the groups in the stacked rows (device, [G]);
+  // group g owns rows [end_offsets[g-1], end_offsets[g]).  Takes precedence when set.
+  const int32_t *end_offsets = nullptr;
   int N;
   int K;
   // Output placement: y (and y_extra[0..n_extra)) are row-major with a pitch of ldy elements; the
@@ -68,7 +71,10 @@ __device__ __forceinline__ void build_group_tables(const GemmParams &p, int n_ti
   for (int base = 0; base < p.G; base += 32) {
     const int g = base + lane;
     long long mg = 0;
-    if (g < p.G) mg = p.m_sizes ? p.m_sizes[g] : p.group_m;
+    if (g < p.G) {
+      if (p.end_offsets) mg = static_cast<long long>(p.end_offsets[g]) - (g > 0 ? p.end_offsets[g - 1] : 0);
+      else mg = p.m_sizes ? p.m_sizes[g] : p.group_m;
+    }
     if (mg < 0) mg = 0;
     if (mg > p.total_m) mg = p.total_m;
     int rows = static_cast<int>(mg);

@@ -20,12 +20,20 @@
 // tile); BN = 256 has room for one accumulator beside the scale columns.
 #include "../../include/mslk_b200.h"
 #include "common.cuh"
+#include "gemm_f8_common.cuh"   // group tables and the tile scheduler shared with the FP8 kernels
 #include "host.h"
 
 #include <cstdlib>
 
 namespace mslk_b200 {
 namespace {
+
+using gemm_f8::build_group_tables;
+using gemm_f8::GemmParams;
+using gemm_f8::kBandM;
+using gemm_f8::kMaxGroups;
+using gemm_f8::Scheduler;
+using gemm_f8::Tile;
 
 constexpr int kBM = 128;
 constexpr int kBKBytes = 128;        // bytes of packed K per stage row
@@ -35,13 +43,22 @@ constexpr int kAtomBytes = 512;      // 128 rows x 4 scales
 constexpr int kNumThreads = 192;
 
 struct Fp4Params {
-  const uint8_t *sfa;   // swizzled scales of A: [ceil(M/128)][ncb] atoms
-  const uint8_t *sfb;   // swizzled scales of B: [ceil(N/128)][ncb] atoms
-  const float *alpha;   // device scalar
+  const uint8_t *sfa;   // swizzled scales of A: [row blocks of 128][ncb] atoms
+  const uint8_t *sfb;   // swizzled scales of B: [G][ceil(N/128)][ncb] atoms
+  const float *alpha;   // device: one scalar (dense) or one per group
   __nv_bfloat16 *y;
   int *status;
-  int M, N, K;
+  int M, N, K;          // M = stacked rows of all groups
   int ncb;              // scale atoms per 128-row block = ceil(K / 64)
+  // Grouped (stacked) problems: G weight blocks of N rows, group g owning m_sizes[g] consecutive rows
+  // of X / Y.  The scale rows of every group start on a 128-row boundary of their own:
+  // sfa_row_start[g] (a multiple of 128) is the first row of group g in the padded scale matrix.
+  // Dense: G = 1, m_sizes = sfa_row_start = nullptr.
+  const int64_t *m_sizes;
+  const int32_t *end_offsets;      // alternative to m_sizes: int32 end offsets of the groups
+  const int64_t *sfa_row_start;    // may be null: groups then follow each other, each padded to 128 rows
+  int G;
+  int alpha_per_group;
 };
 
 template <int BN>
@@ -71,23 +88,13 @@ struct SmemTail {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int row_start[kMaxGroups + 1];    // first stacked row of every group
+  int tile_start[kMaxGroups + 1];   // first linear tile of every group
 };
 
 template <int BN>
 constexpr size_t smem_bytes() {
   return 1024 + static_cast<size_t>(Cfg<BN>::kStages) * Cfg<BN>::kStageBytes + sizeof(SmemTail<BN>);
-}
-
-// tile index -> (row block, column block), bands of 16 row blocks for L2 reuse
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &m_tile, int &n_tile) {
-  constexpr int kBand = 16;
-  const int per_band = kBand * n_tiles;
-  const int band = tile / per_band;
-  const int in_band = tile - band * per_band;
-  const int first_m = band * kBand;
-  const int band_m = min(m_tiles - first_m, kBand);
-  n_tile = in_band / band_m;
-  m_tile = first_m + (in_band - n_tile * band_m);
 }
 
 template <int BN>
@@ -101,9 +108,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
-  const int m_tiles = (p.M + kBM - 1) / kBM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int num_tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + kBKElems - 1) / kBKElems;
   const int n_row_blocks_b = (p.N + 127) / 128;
   volatile int *abort_flag = &S.abort_flag;
@@ -127,10 +132,21 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tmem_alloc(&S.tmem_base, C::kTmemCols);
     tmem_relinquish();
   }
+  if (warp == 2) {
+    GemmParams gp{};
+    gp.m_sizes = p.m_sizes;
+    gp.end_offsets = p.end_offsets;
+    gp.G = p.G;
+    gp.total_m = p.M;
+    gp.group_m = p.M;   // dense: one group of all rows (only read when m_sizes is null)
+    build_group_tables(gp, n_tiles, kBM, lane, S.row_start, S.tile_start);
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
+  const int num_tiles = S.tile_start[p.G];
+  Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, kBM, kBandM, 0};
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -138,9 +154,16 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        int m_tile, n_tile;
-        tile_coords(tile, m_tiles, n_tiles, m_tile, n_tile);
+      Tile t;
+      for (int tile = blockIdx.x; ok && sched.get(tile, t); tile += gridDim.x) {
+        const int g = sched.g;
+        const int n_tile = t.n0 / BN;
+        // 128-row block of this tile in the padded scale matrix of A, and of its columns in that of B
+        // (without an explicit table the padded blocks of the groups are consecutive, so the first block
+        // of group g is its first tile divided by the tiles per row block)
+        const int64_t sfa_block = (p.sfa_row_start ? p.sfa_row_start[g] / kBM : S.tile_start[g] / n_tiles) +
+                                  (t.row0 - S.row_start[g]) / kBM;
+        const int64_t sfb_block0 = static_cast<int64_t>(g) * n_row_blocks_b + n_tile * C::kNB;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
             ok = false;
@@ -155,13 +178,13 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           int nb_live = 0;  // 128-row blocks of B that exist for this tile
           for (int b = 0; b < C::kNB; ++b) nb_live += (n_tile * C::kNB + b) < n_row_blocks_b ? 1 : 0;
           mbar_arrive_expect_tx(&S.full[stage], C::kStageA + C::kStageB + sf_bytes * (1 + nb_live));
-          tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBKBytes, m_tile * kBM);
-          tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBKBytes, n_tile * BN);
-          bulk_load_1d(ssfa, p.sfa + (static_cast<size_t>(m_tile) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
+          tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBKBytes, t.row0);
+          tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBKBytes, t.wrow0);
+          bulk_load_1d(ssfa, p.sfa + (static_cast<size_t>(sfa_block) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
                        &S.full[stage]);
           for (int b = 0; b < nb_live; ++b)
             bulk_load_1d(ssfb + b * 4 * kAtomBytes,
-                         p.sfb + (static_cast<size_t>(n_tile * C::kNB + b) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
+                         p.sfb + (static_cast<size_t>(sfb_block0 + b) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
                          &S.full[stage]);
           if (++stage == C::kStages) {
             stage = 0;
@@ -260,15 +283,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
     const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
-    const float alpha = *p.alpha;
     int local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-      int m_tile, n_tile;
-      tile_coords(tile, m_tiles, n_tiles, m_tile, n_tile);
+    Tile t;
+    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x, ++local) {
+      const int n_tile = t.n0 / BN;
+      const float alpha = p.alpha[p.alpha_per_group ? sched.g : 0];
       const int acc = local % C::kAccStages;
       const uint32_t acc_phase = (local / C::kAccStages) & 1;
-      const int row = m_tile * kBM + row_in_tile;
-      const bool row_ok = row < p.M;
+      const int row = t.row0 + row_in_tile;
+      const bool row_ok = row_in_tile < t.rows;
       const bool got = mbar_wait(&S.tmem_full[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
@@ -341,20 +364,23 @@ int launch(const CUtensorMap &ta, const CUtensorMap &tb, const Fp4Params &p, int
 }  // namespace
 }  // namespace mslk_b200
 
-MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
-                                const float *global_scale, void *y, int64_t M, int64_t N, int64_t K, void *stream) {
-  using namespace mslk_b200;
-  clear_error();
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (M < 0 || N < 0 || K < 0) return fail(1, "f4f4bf16: bad shape");
+namespace mslk_b200 {
+namespace {
+
+int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+            const float *global_scale, void *y, const int64_t *m_sizes, const int32_t *end_offsets,
+            const int64_t *sfa_row_start, int64_t G, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+  const bool grouped = m_sizes || end_offsets;
+  if (M < 0 || N < 0 || K < 0 || G < 1) return fail(1, "%s: bad shape", name);
   if (M == 0 || N == 0) return 0;
-  if (!y) return fail(1, "f4f4bf16: null output pointer");
+  if (G > kMaxGroups) return fail(1, "%s: at most %d groups are supported (got %lld)", name, kMaxGroups, (long long)G);
+  if (!y) return fail(1, "%s: null output pointer", name);
   if (K == 0) return check_cuda(cudaMemsetAsync(y, 0, static_cast<size_t>(M) * N * 2, st), "memset");
-  if (!xq || !wq || !x_scale || !w_scale || !global_scale) return fail(1, "f4f4bf16: null pointer argument");
-  if (K % 32 != 0) return fail(1, "f4f4bf16: K (%lld) must be a multiple of 32 (16-byte rows of packed e2m1)", (long long)K);
-  if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(1, "f4f4bf16: dimension too large");
+  if (!xq || !wq || !x_scale || !w_scale || !global_scale) return fail(1, "%s: null pointer argument", name);
+  if (K % 32 != 0) return fail(1, "%s: K (%lld) must be a multiple of 32 (16-byte rows of packed e2m1)", name, (long long)K);
+  if (M > 0x7fffff00LL || G * N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(1, "%s: dimension too large", name);
   if ((reinterpret_cast<uintptr_t>(x_scale) | reinterpret_cast<uintptr_t>(w_scale)) & 15u)
-    return fail(1, "f4f4bf16: scale tensors must be 16-byte aligned");
+    return fail(1, "%s: scale tensors must be 16-byte aligned", name);
   int *status = device_status_ptr();
   if (!status) return 2;
 
@@ -368,17 +394,57 @@ MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_sc
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   p.ncb = static_cast<int>((K + 63) / 64);
+  p.m_sizes = m_sizes;
+  p.end_offsets = end_offsets;
+  p.sfa_row_start = sfa_row_start;
+  p.G = static_cast<int>(G);
+  p.alpha_per_group = grouped ? 1 : 0;
 
   const int sms = sm_count();
-  const int64_t m_tiles = (M + kBM - 1) / kBM;
+  const int64_t m_tiles = (M + kBM - 1) / kBM + (grouped ? G : 0);   // upper bound for ragged groups
   // 256-wide tiles halve the A traffic per flop but hold one accumulator only; use them when
   // there are enough tiles to fill the device, 128-wide (double-buffered) otherwise
   int bn = (m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
   if (const char *e = getenv("MSLK_B200_NVFP4_BN")) bn = atoi(e) == 128 ? 128 : 256;  // tuning aid
   CUtensorMap ta, tb;
   if (int rc = make_tmap_2d_bytes(&ta, xq, K / 2, M, K / 2, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  if (int rc = make_tmap_2d_bytes(&tb, wq, K / 2, N, K / 2, kBKBytes, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, K / 2, G * N, K / 2, kBKBytes, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   const int64_t tiles = m_tiles * ((N + bn - 1) / bn);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);
   return bn == 256 ? launch<256>(ta, tb, p, grid, st) : launch<128>(ta, tb, p, grid, st);
+}
+
+}  // namespace
+}  // namespace mslk_b200
+
+MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                const float *global_scale, void *y, int64_t M, int64_t N, int64_t K, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  return run_fp4("f4f4bf16", xq, wq, x_scale, w_scale, global_scale, y, nullptr, nullptr, nullptr, 1, M, N, K,
+                 static_cast<cudaStream_t>(stream));
+}
+
+MSLK_API int mslk_b200_f4f4bf16_grouped_stacked(const void *xq, const void *wq, const void *x_scale,
+                                                const void *w_scale, const int64_t *M_sizes,
+                                                const float *global_scale,
+                                                const int64_t *starting_row_after_padding, int64_t G,
+                                                int64_t total_M, int64_t N, int64_t K, void *y, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  const char *name = "f4f4bf16_grouped_stacked";
+  if (!M_sizes) return fail(1, "%s: M_sizes is null", name);
+  return run_fp4(name, xq, wq, x_scale, w_scale, global_scale, y, M_sizes, nullptr, starting_row_after_padding, G, total_M,
+                 N, K, static_cast<cudaStream_t>(stream));
+}
+
+MSLK_API int mslk_b200_f4f4bf16_grouped_mm(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                           const int32_t *offsets, const float *global_scale, int64_t G,
+                                           int64_t total_M, int64_t N, int64_t K, void *y, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  const char *name = "f4f4bf16_grouped_mm";
+  if (!offsets) return fail(1, "%s: offsets is null", name);
+  return run_fp4(name, xq, wq, x_scale, w_scale, global_scale, y, nullptr, offsets, nullptr, G, total_M, N, K,
+                 static_cast<cudaStream_t>(stream));
 }

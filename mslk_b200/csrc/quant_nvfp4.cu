@@ -147,6 +147,171 @@ __global__ void __launch_bounds__(kThreads, 6)
   }
 }
 
+
+// ---------------------------------------------------------------- stacked (grouped) variant
+// Rows of several groups stacked in one [M, K] tensor, group g owning m_sizes[g] consecutive rows and
+// its own global scale gs[g].  The scale rows of every group start on a 128-row boundary of the
+// padded scale matrix (group g at sum_{i<g} roundup(m_i, 128)), which is the layout the grouped
+// GEMM reads (mslk/quantize/triton/legacy/quantize_stacked.py:22-178,315-400).  A 128-row padded
+// tile therefore belongs to one group: the unit's group, source rows and scale are uniform per warp.
+constexpr int kMaxStackedGroups = 1024;
+
+// Inclusive prefix sums of the group sizes (rows) and of their 128-row blocks; one warp.
+__device__ __forceinline__ void build_stacked_tables(const int64_t *m_sizes, int G, int M, int lane, int *row_end,
+                                                     int *blk_end) {
+  int row_carry = 0, blk_carry = 0;
+  for (int base = 0; base < G; base += 32) {
+    const int g = base + lane;
+    long long mg = g < G ? m_sizes[g] : 0;
+    mg = mg < 0 ? 0 : (mg > M ? M : mg);
+    int rows = static_cast<int>(mg), blks = (rows + kTileRows - 1) / kTileRows;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, rows, o), b = __shfl_up_sync(0xffffffffu, blks, o);
+      if (lane >= o) {
+        rows += r;
+        blks += b;
+      }
+    }
+    if (g < G) {
+      row_end[g] = min(M, row_carry + rows);
+      blk_end[g] = blk_carry + blks;
+    }
+    row_carry = min(M, row_carry + __shfl_sync(0xffffffffu, rows, 31));
+    blk_carry += __shfl_sync(0xffffffffu, blks, 31);
+  }
+}
+
+template <int kVec>
+__global__ void __launch_bounds__(kThreads, 6)
+    quant_nvfp4_stacked_kernel(const __nv_bfloat16 *__restrict__ x, int M, int nblk, int64_t row_stride,
+                               const float *__restrict__ gs_ptr, const int64_t *__restrict__ m_sizes, int G,
+                               uint8_t *__restrict__ q, uint8_t *__restrict__ scales, int n_col_tiles) {
+  __shared__ int s_row_end[kMaxStackedGroups];
+  __shared__ int s_blk_end[kMaxStackedGroups];
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (tid < 32) build_stacked_tables(m_sizes, G, M, lane, s_row_end, s_blk_end);
+  __syncthreads();
+  const int c = lane & 3, row_in_tile = ((lane >> 2) & 3) * 32 + (lane >> 4);
+  const int64_t q_pitch = static_cast<int64_t>(nblk) * 8;
+  const int stride = gridDim.x * (kThreads / 32);
+  const int total_units = s_blk_end[G - 1] * n_col_tiles * kWarpsPerTile;
+
+  for (int unit = blockIdx.x * (kThreads / 32) + (tid >> 5); unit < total_units; unit += stride) {
+    const int tile = unit / kWarpsPerTile, w = unit - tile * kWarpsPerTile;
+    const int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
+    int lo = 0, hi = G - 1;   // group of padded row block tr: first g with blk_end[g] > tr
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (s_blk_end[mid] > tr) hi = mid; else lo = mid + 1;
+    }
+    const int g = lo;
+    const int blk0 = g ? s_blk_end[g - 1] : 0, row0 = g ? s_row_end[g - 1] : 0;
+    const int m = row0 + (tr - blk0) * kTileRows + row_in_tile + 2 * w;
+    const int j = tc * kTileBlocks + c;
+    const bool live = m < s_row_end[g] && j < nblk;
+    uint8_t s8 = 0;
+    if (live) {
+      const float gs = gs_ptr[g];
+      const BlockIn cur = load_block<kVec>(x + m * row_stride + j * 16);
+      const uint32_t wd[8] = {cur.a.x, cur.a.y, cur.a.z, cur.a.w, cur.b.x, cur.b.y, cur.b.z, cur.b.w};
+      __nv_bfloat162 mx = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&wd[0]));
+#pragma unroll
+      for (int i = 1; i < 8; ++i) mx = __hmax2(mx, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&wd[i])));
+      const float bamax = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
+      float s = __fmul_rn(__fdiv_rn(bamax, 6.0f), gs);
+      s = fminf(fmaxf(s, 0.001953125f), 448.0f);
+      s8 = f32_to_e4m3(s);
+      const float total = __fdiv_rn(gs, e4m3_to_f32(s8));
+      float lo8[8], hi8[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        lo8[2 * i] = __fmul_rn(__uint_as_float(wd[i] << 16), total);
+        lo8[2 * i + 1] = __fmul_rn(__uint_as_float(wd[i] & 0xffff0000u), total);
+        hi8[2 * i] = __fmul_rn(__uint_as_float(wd[4 + i] << 16), total);
+        hi8[2 * i + 1] = __fmul_rn(__uint_as_float(wd[4 + i] & 0xffff0000u), total);
+      }
+      *reinterpret_cast<uint2 *>(q + m * q_pitch + j * 8) = make_uint2(cvt_e2m1x8(lo8), cvt_e2m1x8(hi8));
+    }
+    scales[static_cast<int64_t>(unit) * 32 + lane] = s8;   // zero for the padding rows / columns of the group
+  }
+}
+
+// Per-group global scale 2688 / max|x| (mslk/quantize/triton/legacy/global_scale.py:40-152): phase 1
+// reduces |x| per group into an integer maximum (bf16 magnitudes order like their bit patterns).
+__global__ void __launch_bounds__(256) group_amax_kernel(const __nv_bfloat16 *__restrict__ x, int M, int K,
+                                                         int64_t row_stride, const int64_t *__restrict__ m_sizes, int G,
+                                                         unsigned int *__restrict__ amax_bits,
+                                                         int64_t *__restrict__ tensor_idx) {
+  __shared__ int s_row_end[kMaxStackedGroups];
+  __shared__ int s_blk_end[kMaxStackedGroups];
+  __shared__ unsigned int s_max[8];
+  if (threadIdx.x < 32) build_stacked_tables(m_sizes, G, M, threadIdx.x, s_row_end, s_blk_end);
+  __syncthreads();
+  const int total_rows = s_row_end[G - 1];
+  for (int row = blockIdx.x; row < total_rows; row += gridDim.x) {
+    int lo = 0, hi = G - 1;   // first g with row_end[g] > row
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (s_row_end[mid] > row) hi = mid; else lo = mid + 1;
+    }
+    const uint16_t *src = reinterpret_cast<const uint16_t *>(x + row * row_stride);
+    unsigned int mx = 0;
+    const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+    if (vec) {
+      for (int v = threadIdx.x; v < K / 8; v += blockDim.x) {
+        const uint4 d = *reinterpret_cast<const uint4 *>(src + v * 8);
+        const uint32_t wd[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const unsigned int a = wd[i] & 0x7fff7fffu;
+          const unsigned int l = a & 0xffffu, h = a >> 16;
+          // NaN patterns (> 0x7f80) are ignored, like max() does
+          if (l <= 0x7f80u) mx = max(mx, l);
+          if (h <= 0x7f80u) mx = max(mx, h);
+        }
+      }
+      for (int k = (K / 8) * 8 + threadIdx.x; k < K; k += blockDim.x) {
+        const unsigned int a = src[k] & 0x7fffu;
+        if (a <= 0x7f80u) mx = max(mx, a);
+      }
+    } else {
+      for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const unsigned int a = src[k] & 0x7fffu;
+        if (a <= 0x7f80u) mx = max(mx, a);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int m8 = 0;
+      for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) m8 = max(m8, s_max[i]);
+      atomicMax(amax_bits + lo, m8);
+      if (tensor_idx) tensor_idx[row] = lo;
+    }
+    __syncthreads();
+  }
+}
+
+// Phase 2: out[g] = 2688 / amax_g with the approximate division the reference's kernel lowers to
+// (div.full), 1e-8 standing in for an all-zero group; groups without rows keep FLT_MAX.
+__global__ void group_scale_finish_kernel(const unsigned int *__restrict__ amax_bits, const int64_t *__restrict__ m_sizes,
+                                          int G, float *__restrict__ out) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= G) return;
+  if (m_sizes[g] <= 0) {
+    out[g] = 3.4028234663852886e38f;
+    return;
+  }
+  const float amax = __uint_as_float(amax_bits[g] << 16);
+  float r;
+  const float d = amax == 0.f ? 1e-8f : amax;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(2688.0f), "f"(d));
+  out[g] = r;
+}
+
 }  // namespace
 }  // namespace mslk_b200
 
@@ -182,4 +347,65 @@ MSLK_API int mslk_b200_quantize_nvfp4(const void *x, int64_t M, int64_t K, int64
                                                            static_cast<uint8_t *>(scales), static_cast<int>(n_col_tiles),
                                                            static_cast<int>(units));
   return check_cuda(cudaGetLastError(), "quantize_nvfp4 launch");
+}
+
+MSLK_API int mslk_b200_quantize_nvfp4_stacked(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                                              const int64_t *m_sizes, int64_t G, const float *global_scale, void *q,
+                                              void *scales, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  const char *name = "quantize_nvfp4_stacked";
+  if (M < 0 || K < 0 || K % 16 != 0) return fail(1, "%s: K must be a non-negative multiple of 16", name);
+  if (G < 1 || G > kMaxStackedGroups) return fail(1, "%s: between 1 and %d groups are supported", name, kMaxStackedGroups);
+  if (M == 0 || K == 0) return 0;
+  if (!x || !q || !scales || !m_sizes || !global_scale) return fail(1, "%s: null pointer argument", name);
+  if (reinterpret_cast<uintptr_t>(q) & 7u) return fail(1, "%s: output must be 8-byte aligned", name);
+  if (M > 0x7fffff00LL || K > 0x7fffff00LL) return fail(1, "%s: dimension too large", name);
+  const int64_t n_col_tiles = (K / 16 + kTileBlocks - 1) / kTileBlocks;
+  const int64_t units_ub = ((M + kTileRows - 1) / kTileRows + G) * n_col_tiles * kWarpsPerTile;
+  if (units_ub > 0x7fff0000LL) return fail(1, "%s: tensor too large", name);
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && row_stride % 8 == 0;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 6;
+  const int64_t want = (units_ub + kThreads / 32 - 1) / (kThreads / 32);
+  const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+  auto *xb = static_cast<const __nv_bfloat16 *>(x);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (vec_ok)
+    quant_nvfp4_stacked_kernel<1><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
+                                                               global_scale, m_sizes, static_cast<int>(G),
+                                                               static_cast<uint8_t *>(q), static_cast<uint8_t *>(scales),
+                                                               static_cast<int>(n_col_tiles));
+  else
+    quant_nvfp4_stacked_kernel<0><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
+                                                               global_scale, m_sizes, static_cast<int>(G),
+                                                               static_cast<uint8_t *>(q), static_cast<uint8_t *>(scales),
+                                                               static_cast<int>(n_col_tiles));
+  return check_cuda(cudaGetLastError(), "quantize_nvfp4_stacked launch");
+}
+
+MSLK_API int mslk_b200_calculate_group_max(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                                           const int64_t *m_sizes, int64_t G, float *global_scale, int64_t *tensor_idx,
+                                           void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  const char *name = "calculate_group_max";
+  if (M < 0 || K < 0) return fail(1, "%s: bad shape", name);
+  if (G < 1 || G > kMaxStackedGroups) return fail(1, "%s: between 1 and %d groups are supported", name, kMaxStackedGroups);
+  if (!m_sizes || !global_scale) return fail(1, "%s: null pointer argument", name);
+  if (M > 0x7fffff00LL || K > 0x7fffff00LL) return fail(1, "%s: dimension too large", name);
+  if ((M > 0 && K > 0) && !x) return fail(1, "%s: null input", name);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the output doubles as the integer accumulator of phase 1 (bf16 magnitude bits), rewritten by phase 2
+  unsigned int *bits = reinterpret_cast<unsigned int *>(global_scale);
+  if (int rc = check_cuda(cudaMemsetAsync(bits, 0, sizeof(float) * static_cast<size_t>(G), st), "memset")) return rc;
+  if (M > 0 && K > 0) {
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    const unsigned blocks = static_cast<unsigned>(M < cap ? M : cap);
+    group_amax_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<int>(M), static_cast<int>(K),
+                                              row_stride, m_sizes, static_cast<int>(G), bits, tensor_idx);
+    if (int rc = check_cuda(cudaGetLastError(), "calculate_group_max launch")) return rc;
+  }
+  group_scale_finish_kernel<<<static_cast<unsigned>((G + 127) / 128), 128, 0, st>>>(bits, m_sizes, static_cast<int>(G),
+                                                                                   global_scale);
+  return check_cuda(cudaGetLastError(), "calculate_group_max launch");
 }

@@ -25,3 +25,5 @@ from .. import _lib  # noqa: F401,E402
 torch.ops.load_library(_OPS_LIB)
 
 from . import _meta  # noqa: F401,E402
+
+from . import _grouped_fp4  # noqa: F401,E402  mslk::f4f4bf16_grouped_stacked / mslk::f4f4bf16_grouped_mm

@@ -4,6 +4,7 @@
     python -m mslk_b200.microbench f8f8bf16_rowwise --shape 8192,8192,8192
     python -m mslk_b200.microbench batched --shape 8,2048,4096,4096          # B,M,N,K
     python -m mslk_b200.microbench grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
+    python -m mslk_b200.microbench f4f4bf16_grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
     python -m mslk_b200.microbench f4f4bf16 --shape 8192,8192,8192
     python -m mslk_b200.microbench quantize_nvfp4 --shape 8192,8192
     python -m mslk_b200.microbench silu_mul_quant --shape 16384,14336      # T,D; also times the unfused pair
@@ -134,6 +135,29 @@ def bench_grouped(ops, E, tokens, N, K, args):
             "counts": counts.tolist(), "us": sec * 1e6, "TFLOPs": flops / sec / 1e12}
 
 
+def bench_f4f4bf16_grouped(ops, E, tokens, N, K, args):
+    counts = zipf_counts(E, tokens)
+    ms = counts.to(torch.int64).cuda()
+    x = _randn((tokens, K))
+    w = _randn((E * N, K), args.w_std)
+    w_ms = torch.full((E,), N, dtype=torch.int64, device="cuda")
+    x_gs, _ = ops.calculate_group_max(x, ms)
+    w_gs, _ = ops.calculate_group_max(w, w_ms)
+    sec_q = _time(lambda i: ops.nvfp4_quantize_stacked(ms, x, x_gs), 1, args.iters, args.warmup, args.graph)
+    xq, xs = ops.nvfp4_quantize_stacked(ms, x, x_gs)
+    wq, ws2 = ops.nvfp4_quantize_stacked(w_ms, w, w_gs)
+    padded_n = (N + 127) // 128 * 128
+    ws = ws2[: E * padded_n].view(E, padded_n, -1)
+    alpha = torch.reciprocal(x_gs * w_gs)
+    wq3 = wq.view(E, N, K // 2)
+    sec = _time(lambda i: ops.f4f4bf16_grouped_stacked(xq, wq3, xs, ws, ms, alpha, None, use_mx=False), 1, args.iters,
+                args.warmup, args.graph)
+    flops = 2.0 * tokens * N * K
+    return {"op": "f4f4bf16_grouped_stacked", "E": E, "tokens": tokens, "N": N, "K": K, "us": sec * 1e6,
+            "TFLOPs": flops / sec / 1e12, "quantize_stacked_us": sec_q * 1e6,
+            "quantize_stacked_GBps": tokens * K * 2.5625 / sec_q / 1e9, "counts": counts.tolist()}
+
+
 def bench_quantize_nvfp4(ops, M, K, args):
     nv = _variants(M * K * 2, args.rotate_mb)
     xs = [_randn((M, K)) for _ in range(nv)]
@@ -165,7 +189,7 @@ def bench_f4f4bf16(ops, M, N, K, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "batched", "grouped", "f4f4bf16", "quantize_nvfp4", "silu_mul_quant",
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "quantize_nvfp4", "silu_mul_quant",
                                    "sweep"])
     ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
     ap.add_argument("--experts", type=int, default=16)
@@ -190,6 +214,8 @@ def main():
         out.append(bench_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
     elif args.op == "quantize_nvfp4":
         out.append(bench_quantize_nvfp4(ops, *(shape or [8192, 8192]), args))
+    elif args.op == "f4f4bf16_grouped":
+        out.append(bench_f4f4bf16_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
     elif args.op == "silu_mul_quant":
         out.append(bench_silu_mul_quant(ops, *(shape or [16384, 14336]), args))
     elif args.op == "f4f4bf16":

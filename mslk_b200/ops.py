@@ -11,6 +11,9 @@ operators they stand for:
 * ``f8f8bf16_rowwise_grouped_stacked`` -- ``csrc/gemm/cutlass/f8f8bf16_rowwise_grouped.cu:342-368``
 * ``quantize_nvfp4``         -- ``mslk/quantize/triton/quantize_kernels/nvfp4.py:62-149``
 * ``f4f4bf16``               -- ``csrc/gemm/cutlass/f4f4bf16.cu:6413-6473``
+* ``f4f4bf16_grouped_stacked`` / ``f4f4bf16_grouped_mm`` -- ``csrc/gemm/cutlass/f4f4bf16_grouped.cu:321-475``
+* ``calculate_group_max`` / ``nvfp4_quantize_stacked`` -- ``mslk/quantize/triton/legacy/global_scale.py:156-230``,
+  ``legacy/quantize_stacked.py:315-400``
 * ``silu_mul`` / ``silu_mul_quant`` -- ``mslk/moe/activation.py:25-69,72-133``
 * ``gather_scale_dense_tokens``, ``gather_scale_quant_dense_tokens``, ``scatter_add_dense_tokens``,
   ``scatter_add_padded_tokens`` -- ``mslk/moe/gather_scatter.py:18-282``
@@ -333,6 +336,137 @@ def reduce_slots(stage: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
         out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev)
     with torch.cuda.device(dev):
         check(lib.mslk_b200_reduce_slots_bf16(_ptr(stage), slots, rows, cols, _ptr(out), _stream(dev)), "reduce_slots")
+    return out
+
+
+# --------------------------------------------------------------------------- NVFP4, stacked groups (MoE)
+
+def calculate_group_max(input: torch.Tensor, m_sizes: torch.Tensor):
+    """Per-group NVFP4 global scale ``2688 / max|x|`` and the group index of every row:
+    ``(global_scale fp32 [G], tensor_idx int64 [M])``."""
+    name = "calculate_group_max"
+    dev = _require_cuda(name, input, m_sizes)
+    assert input.ndim >= 1, f"input.ndim needs to be >= 1, but got {input.ndim}."
+    x2 = input.reshape(1 if input.ndim == 1 else -1, input.shape[-1])
+    if x2.dtype != torch.bfloat16:
+        raise RuntimeError(f"{name}: input must be bfloat16, got {x2.dtype}")
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    if m_sizes.dtype != torch.int64:
+        m_sizes = m_sizes.to(torch.int64)
+    M, K = x2.shape
+    G = m_sizes.numel()
+    out = torch.empty((G,), dtype=torch.float32, device=dev)
+    tensor_idx = torch.empty((M,), dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_calculate_group_max(_ptr(x2), M, K, x2.stride(0), _ptr(m_sizes.contiguous()), G, _ptr(out),
+                                                _ptr(tensor_idx), _stream(dev)), name)
+    return out, tensor_idx
+
+
+def nvfp4_quantize_stacked(m_sizes: torch.Tensor, input: torch.Tensor, global_scale: torch.Tensor):
+    """NVFP4 quantization of stacked groups: ``(xq [M, K/2] packed, scale [(M + 127 G), roundup(K/16, 4)] swizzled)``;
+    every group's scale rows start on a 128-row boundary."""
+    name = "nvfp4_quantize_stacked"
+    dev = _require_cuda(name, input, m_sizes, global_scale)
+    assert input.ndim >= 1, f"input.ndim needs to be >= 1, but got {input.ndim}."
+    x2 = input.reshape(-1, input.shape[-1])
+    M, K = x2.shape
+    assert K % 16 == 0, f"K must be divisible by 16, but got {K}."
+    if x2.dtype != torch.bfloat16:
+        raise RuntimeError(f"{name}: input must be bfloat16, got {x2.dtype}")
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    if m_sizes.dtype != torch.int64:
+        m_sizes = m_sizes.to(torch.int64)
+    G = m_sizes.shape[0]
+    padded_cols = (K // 16 + 3) // 4 * 4
+    xq = torch.empty((M, K // 2), device=dev, dtype=torch.uint8)
+    scale = torch.empty((M + G * 127, padded_cols), device=dev, dtype=torch.uint8)
+    gs = global_scale.reshape(-1).to(torch.float32)
+    if gs.numel() != G:
+        raise RuntimeError(f"{name}: global_scale must hold one value per group")
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_quantize_nvfp4_stacked(_ptr(x2), M, K, x2.stride(0), _ptr(m_sizes.contiguous()), G, _ptr(gs),
+                                                   _ptr(xq), _ptr(scale), _stream(dev)), name)
+    fp4 = getattr(torch, "float4_e2m1fn_x2", None)
+    return (xq.view(fp4) if fp4 is not None else xq), scale.view(FP8_DTYPE)
+
+
+def _as_bytes(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.uint8 else t.view(torch.uint8)
+
+
+def f4f4bf16_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes, global_scale=None, starting_row_after_padding=None,
+                             use_mx: bool = True) -> torch.Tensor:
+    """Grouped NVFP4 GEMM over stacked rows: ``XQ [total_M, K/2]``, ``WQ [G, N, K/2]``, fp32 ``global_scale [G]``."""
+    name = "f4f4bf16_grouped_stacked"
+    dev = _require_cuda(name, XQ, WQ, x_scale, w_scale, M_sizes, global_scale, starting_row_after_padding)
+    if global_scale is None or use_mx:
+        raise RuntimeError(f"{name}: only the NVFP4 mode (global_scale given, use_mx=False) is implemented")
+    if M_sizes.dtype != torch.int64:
+        raise RuntimeError("M_sizes must be int64.")
+    if WQ.dim() != 3 or WQ.shape[0] != M_sizes.shape[0]:
+        raise RuntimeError("Weights should be shape [G, N, K].")
+    if not (XQ.is_contiguous() and WQ.is_contiguous() and x_scale.is_contiguous() and w_scale.is_contiguous()):
+        raise RuntimeError(f"{name}: XQ, WQ, x_scale and w_scale must be contiguous")
+    total_M = XQ.shape[0]
+    G, N, K = WQ.shape[0], WQ.shape[1], WQ.shape[2] * 2
+    srp = None
+    if starting_row_after_padding is not None:
+        if starting_row_after_padding.numel() % (G + 1) != 0 or starting_row_after_padding.dtype != torch.int64:
+            raise RuntimeError(f"{name}: starting_row_after_padding must be int64 with a multiple of G+1 entries")
+        srp = starting_row_after_padding.contiguous()
+    gs = global_scale.reshape(-1).to(torch.float32)
+    if gs.numel() != G:
+        raise RuntimeError(f"{name}: global_scale must hold one value per group")
+    Y = torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
+    if total_M == 0:
+        return Y
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f4f4bf16_grouped_stacked(
+            _ptr(_as_bytes(XQ)), _ptr(_as_bytes(WQ)), _ptr(x_scale), _ptr(w_scale), _ptr(M_sizes.contiguous()), _ptr(gs),
+            _ptr(srp), G, total_M, N, K, _ptr(Y), _stream(dev)), name)
+    return Y
+
+
+def f4f4bf16_grouped_mm(XQ, WQ, x_scale, w_scale, offsets, output=None, global_scale=None) -> torch.Tensor:
+    """``torch._scaled_grouped_mm``-style 2D-3D grouped NVFP4 GEMM: ``XQ [total_M, K/2]``, ``WQ [G, K/2, N]`` given as
+    the transposed view of a contiguous ``[G, N, K/2]`` tensor, int32 END ``offsets [G]``."""
+    name = "f4f4bf16_grouped_mm"
+    dev = _require_cuda(name, XQ, WQ, x_scale, w_scale, offsets, global_scale, output)
+    if offsets.dtype != torch.int32:
+        raise RuntimeError("offsets must be int32.")
+    if offsets.dim() != 1:
+        raise RuntimeError("offsets must be 1D tensor.")
+    if not XQ.is_contiguous():
+        raise RuntimeError("XQ must be row major.")
+    if not WQ.transpose(-2, -1).is_contiguous():
+        raise RuntimeError("WQ must be column major.")
+    if not (x_scale.is_contiguous() and w_scale.is_contiguous()):
+        raise RuntimeError("x_scale and w_scale must be contiguous.")
+    if global_scale is None or x_scale.dtype != FP8_DTYPE:
+        raise RuntimeError(f"{name}: only NVFP4 (float8_e4m3fn scales with a global_scale) is implemented")
+    if XQ.dim() != 2 or WQ.dim() != 3:
+        raise RuntimeError(f"{name}: only the 2D-3D form (XQ [total_M, K], WQ [G, K, N]) is implemented")
+    G = offsets.shape[0]
+    total_M = XQ.shape[0]
+    N, K = WQ.shape[-1], WQ.shape[-2] * 2
+    if XQ.shape[1] * 2 != K or WQ.shape[0] != G:
+        raise RuntimeError("for 2d-3d grouped GEMM, XQ shape must be (total_M, K) and WQ shape must be (G, K, N).")
+    out = output if output is not None else torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
+    if out.dim() != 2 or out.shape[0] != total_M or out.shape[1] != N or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise RuntimeError("for 2d-3d grouped GEMM, output shape must be (total_M, N).")
+    if out.numel() == 0:
+        return out
+    gs = global_scale.reshape(-1).to(torch.float32)
+    if gs.numel() != G:
+        raise RuntimeError(f"{name}: global_scale must hold one value per group")
+    wq = WQ.transpose(-2, -1)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f4f4bf16_grouped_mm(
+            _ptr(_as_bytes(XQ)), _ptr(_as_bytes(wq)), _ptr(x_scale), _ptr(w_scale), _ptr(offsets.contiguous()), _ptr(gs),
+            G, total_M, N, K, _ptr(out), _stream(dev)), name)
     return out
 
 

@@ -25,3 +25,22 @@ def triton_quantize_nvfp4(
     if hasattr(torch, "float4_e2m1fn_x2"):
         xq = xq.view(torch.float4_e2m1fn_x2)
     return xq, scales
+
+
+def calculate_group_max(input: torch.Tensor, m_sizes: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-group NVFP4 global scales for stacked MoE activations
+    (``mslk/quantize/triton/legacy/global_scale.py:156-230``): ``(global_scale [G] fp32, group of each row [M] int64)``."""
+    from ... import ops as _ops
+    return _ops.calculate_group_max(input, m_sizes)
+
+
+def nvfp4_quantize_stacked(
+    m_sizes: torch.Tensor,
+    input: torch.Tensor,
+    global_scale: torch.Tensor,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Quantize concatenated MoE activations to NVFP4 with per-expert global scales
+    (``mslk/quantize/triton/legacy/quantize_stacked.py:315-400``).  Returns the packed data ``[M, K // 2]`` and the
+    padded + swizzled scale buffer in which every group starts on a 128-row boundary."""
+    from ... import ops as _ops
+    return _ops.nvfp4_quantize_stacked(m_sizes, input, global_scale)

@@ -428,3 +428,68 @@ def scatter_add_padded_tokens(in_tokens, token_counts, token_indices, out_tokens
         lib().oracle_scatter_add(_p(out_tokens), _p(in_tokens), _SCATTER_CODE[in_tokens.dtype], T_K, D,
                                  _p(token_indices), _bits(token_indices), T_K, _p(token_counts), _bits(token_counts),
                                  E, EP)
+
+
+# --------------------------------------------------------------------------
+# NVFP4 for stacked groups (MoE)
+# --------------------------------------------------------------------------
+
+def calculate_group_max(x: torch.Tensor, m_sizes: Sequence[int]):
+    """``mslk/quantize/triton/legacy/global_scale.py:40-230``: per group ``2688 / max|x|`` (IEEE division here;
+    the GPU kernels use an approximate one, so agreement is to a couple of ulps), ``1e-8`` replacing a zero
+    maximum, ``FLT_MAX`` for groups without rows; plus the group index of every row."""
+    x = _cpu(x)
+    out = torch.full((len(m_sizes),), torch.finfo(torch.float32).max, dtype=torch.float32)
+    idx = torch.zeros((x.shape[0],), dtype=torch.int64)
+    r = 0
+    for g, m in enumerate(m_sizes):
+        if m > 0:
+            amax = x[r:r + m].abs().max().float()
+            out[g] = torch.tensor(2688.0) / torch.where(amax == 0, torch.tensor(1e-8), amax)
+            idx[r:r + m] = g
+        r += m
+    return out, idx
+
+
+def nvfp4_quantize_stacked(m_sizes: Sequence[int], x: torch.Tensor, global_scale: torch.Tensor):
+    """``mslk/quantize/triton/legacy/quantize_stacked.py:22-178``: every group quantized with its own global scale
+    (bit-exact block arithmetic of :func:`quantize_nvfp4`), its scale rows padded to a multiple of 128.  Returns
+    ``(packed uint8 [M, K/2], scale bytes [sum of padded rows, cols_pad] swizzled per group, padded row starts)``."""
+    x = _cpu(x)
+    M, K = x.shape
+    q = torch.zeros((M, K // 2), dtype=torch.uint8)
+    scales, starts = [], [0]
+    r = 0
+    for g, m in enumerate(m_sizes):
+        if m > 0:
+            qg, sg = quantize_nvfp4(x[r:r + m].contiguous(), global_scale[g:g + 1])
+            q[r:r + m] = qg
+            scales.append(sg.view(torch.uint8).reshape(-1, sg.shape[-1]))
+        starts.append(starts[-1] + (m + 127) // 128 * 128)
+        r += m
+    pc = (K // 16 + 3) // 4 * 4
+    s = torch.cat(scales, dim=0) if scales else torch.zeros((0, pc), dtype=torch.uint8)
+    return q, s.view(torch.float8_e4m3fn), starts
+
+
+def gemm_nvfp4_grouped_stacked(xq, wq, x_scale, w_scale, m_sizes: Sequence[int], global_scale, starts=None):
+    """Per group :func:`gemm_nvfp4_torch` on its rows, weights, scale blocks and global scale
+    (``csrc/gemm/cutlass/f4f4bf16_grouped/f4f4bf16_grouped_common.cuh:57-148`` pointer arithmetic)."""
+    xq, wq = _cpu(xq), _cpu(wq)
+    G, N = wq.shape[0], wq.shape[1]
+    K = wq.shape[2] * 2
+    pc = (K // 16 + 3) // 4 * 4
+    xs = _cpu(x_scale).view(torch.uint8).reshape(-1, pc)
+    ws = _cpu(w_scale).view(torch.uint8).reshape(G, -1, pc)
+    y = torch.zeros((xq.shape[0], N), dtype=torch.bfloat16)
+    r, pr = 0, 0
+    for g, m in enumerate(m_sizes):
+        if starts is not None:
+            pr = int(starts[g])
+        mp = (m + 127) // 128 * 128
+        if m > 0:
+            y[r:r + m] = gemm_nvfp4_torch(xq[r:r + m], wq[g], xs[pr:pr + mp].view(torch.float8_e4m3fn),
+                                          ws[g].view(torch.float8_e4m3fn), global_scale[g:g + 1])
+        r += m
+        pr += mp
+    return y

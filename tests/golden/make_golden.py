@@ -11,6 +11,9 @@ Two legs, both writing ``.npz`` files next to this script:
       reference's own test (``test/quantize/triton/fp4_quantize_test.py:259-296``),
       ``_to_blocked``, ``global_scale_nvfp4`` and ``dequantize_nvfp4``.
 ``--leg gpu_silu``  (needs a B200) runs the reference's fused ``silu_mul_quant`` (``mslk/moe/activation.py``).
+``--leg gpu_fp4_stacked``  (needs a B200) runs ``calculate_group_max`` and ``nvfp4_quantize_stacked``
+    (``mslk/quantize/triton/legacy``); the scale bytes of the real rows are stored un-swizzled, the padding
+    rows (which the reference leaves uninitialised) are not.
 ``--leg gpu_gather``  (needs a B200) runs the reference's ``gather_scale_quant_dense_tokens``
     (``mslk/moe/gather_scatter.py``).  These two legs store outputs only; the tests regenerate the
     seeded inputs with ``silu_inputs`` / ``gather_inputs`` (CPU generator, same torch build).
@@ -301,13 +304,65 @@ def leg_gpu_gather(ref_root: str):
     print("gpu gather leg written")
 
 
+# (name, rows per group, K): stacked NVFP4 quantization with one global scale per group
+STACKED_CASES = [
+    ("st_4g", [64, 232, 0, 600], 1024),
+    ("st_1g", [300], 512),
+    ("st_16g", [0, 129, 1, 128, 127, 0, 0, 256, 300, 5, 64, 0, 96, 33, 512, 7], 256),
+]
+
+
+def stacked_inputs(m_sizes, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    parts = [torch.randn((m, K), generator=g, dtype=torch.float32) * (0.05 * (1 + 3 * i)) for i, m in enumerate(m_sizes)]
+    if len(parts) > 2 and m_sizes[-1] > 0:
+        parts[-1] = parts[-1] * 0.0          # an all-zero group: the 1e-8 stand-in of the global scale
+    return torch.cat(parts, dim=0).to(torch.bfloat16)
+
+
+def unswizzle_stacked_scales(scale_flat, m_sizes, K):
+    """[sum m, K/16] scale bytes of the real rows, from the padded + swizzled buffer."""
+    pc = (K // 16 + 3) // 4 * 4
+    buf = scale_flat.reshape(-1).view(torch.uint8).cpu()
+    rows, pr = [], 0
+    for m in m_sizes:
+        mp = (m + 127) // 128 * 128
+        if m > 0:
+            blk = buf[pr * pc:(pr + mp) * pc].reshape(mp // 128, pc // 4, 32, 4, 4)   # [rb, cb, r%32, r//32, c]
+            un = blk.permute(0, 3, 2, 1, 4).reshape(mp, pc)                           # row = rb*128 + (r//32)*32 + r%32
+            rows.append(un[:m, : K // 16])
+        pr += mp
+    return torch.cat(rows, dim=0) if rows else torch.zeros((0, K // 16), dtype=torch.uint8)
+
+
+def leg_gpu_fp4_stacked(ref_root: str):
+    """calculate_group_max + nvfp4_quantize_stacked of the reference (Triton) on a B200."""
+    _import_reference(ref_root)
+    from mslk.quantize.triton.legacy.global_scale import calculate_group_max
+    from mslk.quantize.triton.legacy.quantize_stacked import nvfp4_quantize_stacked
+    out = {}
+    for i, (name, m_sizes, K) in enumerate(STACKED_CASES):
+        x = stacked_inputs(m_sizes, K, 600 + i).cuda()
+        ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+        gs, idx = calculate_group_max(x, ms)
+        q, s = nvfp4_quantize_stacked(ms, x, gs)
+        torch.cuda.synchronize()
+        out[f"{name}.gs"] = _raw(gs)
+        out[f"{name}.idx"] = _raw(idx)
+        out[f"{name}.q"] = _raw(q.view(torch.uint8))
+        out[f"{name}.s_rows"] = _raw(unswizzle_stacked_scales(s, m_sizes, K))
+    np.savez_compressed(os.path.join(HERE, "nvfp4_stacked_triton_b200.npz"), **out)
+    print("gpu fp4 stacked leg written")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu", "gpu_gather"], required=True)
+    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu", "gpu_gather", "gpu_fp4_stacked"], required=True)
     ap.add_argument("--ref-root", required=True)
     ap.add_argument("--out-dir", default=None, help="write here instead of beside this script")
     args = ap.parse_args()
     if args.out_dir:
         HERE = args.out_dir
         os.makedirs(HERE, exist_ok=True)
-    {"cpu": leg_cpu, "gpu": leg_gpu, "gpu_silu": leg_gpu_silu, "gpu_gather": leg_gpu_gather}[args.leg](args.ref_root)
+    {"cpu": leg_cpu, "gpu": leg_gpu, "gpu_silu": leg_gpu_silu, "gpu_gather": leg_gpu_gather,
+     "gpu_fp4_stacked": leg_gpu_fp4_stacked}[args.leg](args.ref_root)

@@ -1,0 +1,167 @@
+"""GPU parity tests of the stacked (MoE) NVFP4 path through the C ABI: per-group global scales,
+stacked quantization, grouped GEMM in its stacked (M_sizes) and grouped_mm (end offsets) forms.
+
+Quantizer: bit for bit against the oracle (packed data and the scale bytes of the real rows), and against
+outputs captured from the reference's Triton kernels on a B200.  GEMM: the fp32 dequantize-matmul formula
+per group (rtol 1.6e-2 / atol 1e-2 scaled with the output spread) and the reference test's tolerance against
+the bf16 grouped product (test/gemm/gemm_test.py:2398-2443: atol 5e-2, rtol 6e-2)."""
+import pytest
+import torch
+
+import oracle
+from helpers import load_golden
+from golden.make_golden import STACKED_CASES, stacked_inputs, unswizzle_stacked_scales
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mslk_b200 import ops as _ops
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return _ops
+
+
+def _status():
+    from mslk_b200._lib import device_status
+    return device_status()
+
+
+def test_group_max_and_stacked_quantize_vs_oracle(ops):
+    for i, (name, m_sizes, K) in enumerate(STACKED_CASES):
+        x = stacked_inputs(m_sizes, K, 600 + i)
+        ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+        gs, idx = ops.calculate_group_max(x.cuda(), ms)
+        gs_ref, idx_ref = oracle.calculate_group_max(x, m_sizes)
+        torch.testing.assert_close(gs.cpu(), gs_ref, rtol=5e-7, atol=0)   # approximate vs IEEE division
+        assert torch.equal(idx.cpu()[: sum(m_sizes)], idx_ref[: sum(m_sizes)])
+        # quantize with the GPU's own global scales so that the block arithmetic can be compared bit for bit
+        q, s = ops.nvfp4_quantize_stacked(ms, x.cuda(), gs)
+        q_ref, s_ref, starts = oracle.nvfp4_quantize_stacked(m_sizes, x, gs.cpu())
+        assert s.shape == (sum(m_sizes) + 127 * len(m_sizes), (K // 16 + 3) // 4 * 4)
+        assert torch.equal(q.view(torch.uint8).cpu(), q_ref), name
+        n_bytes = s_ref.numel()
+        assert torch.equal(s.view(torch.uint8).cpu().reshape(-1)[:n_bytes], s_ref.view(torch.uint8).reshape(-1)), name
+    assert _status() == 0
+
+
+def test_triton_fixture_bit_exact(ops):
+    gold = load_golden("nvfp4_stacked_triton_b200.npz")
+    if gold is None:
+        pytest.skip("fixture captured from the reference's Triton kernels not present")
+    for i, (name, m_sizes, K) in enumerate(STACKED_CASES):
+        x = stacked_inputs(m_sizes, K, 600 + i).cuda()
+        ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+        gs, idx = ops.calculate_group_max(x, ms)
+        assert torch.equal(gs.cpu().view(torch.int32), torch.from_numpy(gold[f"{name}.gs"]).view(torch.int32)), name
+        assert torch.equal(idx.cpu(), torch.from_numpy(gold[f"{name}.idx"])), name
+        q, s = ops.nvfp4_quantize_stacked(ms, x, gs)
+        assert torch.equal(q.view(torch.uint8).cpu(), torch.from_numpy(gold[f"{name}.q"])), name
+        assert torch.equal(unswizzle_stacked_scales(s, m_sizes, K), torch.from_numpy(gold[f"{name}.s_rows"])), name
+    assert _status() == 0
+
+
+def _grouped_problem(ops, m_sizes, N, K, seed):
+    G = len(m_sizes)
+    g = torch.Generator().manual_seed(seed)
+    X = (torch.randn((sum(m_sizes), K), generator=g) * 0.1).to(torch.bfloat16).cuda()
+    W = (torch.randn((G, N, K), generator=g) * 0.01).to(torch.bfloat16).cuda()
+    ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+    w_ms = torch.full((G,), N, dtype=torch.int64, device="cuda")
+    x_gs, _ = ops.calculate_group_max(X, ms)
+    w_gs, _ = ops.calculate_group_max(W.reshape(G * N, K), w_ms)
+    xq, x_scale = ops.nvfp4_quantize_stacked(ms, X, x_gs)
+    wq, w_scale_2d = ops.nvfp4_quantize_stacked(w_ms, W.reshape(G * N, K), w_gs)
+    wq = wq.view(G, N, K // 2)
+    padded_N = (N + 127) // 128 * 128
+    w_scale = w_scale_2d[: G * padded_N].view(G, padded_N, -1)
+    # groups without rows have a FLT_MAX scale; their alpha is never used
+    alpha = torch.reciprocal(x_gs * w_gs)
+    return X, W, ms, xq, wq, x_scale, w_scale, alpha
+
+
+def _check_grouped(y, X, W, m_sizes, xq, wq, x_scale, w_scale, alpha, tag):
+    total = sum(m_sizes)
+    y_or = oracle.gemm_nvfp4_grouped_stacked(xq.view(torch.uint8).cpu(), wq.view(torch.uint8).cpu(), x_scale.cpu(),
+                                             w_scale.cpu(), m_sizes, alpha.cpu())
+    scale = max(1.0, float(y_or.float().std()))
+    torch.testing.assert_close(y.cpu()[:total].float(), y_or[:total].float(), rtol=1.6e-2, atol=1e-2 * scale,
+                               msg=lambda m: f"{tag}: {m}")
+    r = 0
+    for g, m in enumerate(m_sizes):       # the reference test's check against the unquantized product
+        if m:
+            ref = X[r:r + m].float() @ W[g].float().T
+            torch.testing.assert_close(y[r:r + m].float(), ref, atol=5.0e-2, rtol=6.0e-2, msg=lambda s: f"{tag} g{g}: {s}")
+        r += m
+
+
+@pytest.mark.parametrize("m_sizes,N,K", [
+    ([256], 256, 2048),                      # the reference's cases (reduced G * M for the CPU oracle)
+    ([500, 500, 500, 500], 1024, 2048),
+    ([64, 232, 600], 512, 1024),             # ragged
+    ([0, 129, 1, 128, 0, 300], 384, 512),    # empty groups, N not a multiple of the tile
+    ([3, 0, 5, 1], 72, 64),
+    ([1000, 24], 2048, 256),
+])
+def test_grouped_stacked_gemm(ops, m_sizes, N, K):
+    X, W, ms, xq, wq, x_scale, w_scale, alpha = _grouped_problem(ops, m_sizes, N, K, seed=sum(m_sizes) + N)
+    starts = torch.tensor([0] + [(m + 127) // 128 * 128 for m in m_sizes], dtype=torch.int64).cumsum(0).cuda()
+    y = ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, starts, use_mx=False)
+    assert y.shape == (sum(m_sizes), N) and y.dtype == torch.bfloat16
+    _check_grouped(y, X, W, m_sizes, xq, wq, x_scale, w_scale, alpha, "stacked")
+    # without the padded-start table (derived from the sizes) and through the end-offset form: same bits
+    y2 = ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, None, use_mx=False)
+    assert torch.equal(y, y2)
+    offsets = ms.cumsum(0).to(torch.int32)
+    y3 = ops.f4f4bf16_grouped_mm(xq, wq.transpose(-2, -1), x_scale, w_scale, offsets, None, alpha)
+    assert torch.equal(y, y3)
+    assert _status() == 0
+
+
+def test_grouped_equals_dense_per_group(ops):
+    # every group through the dense operator with its own scale blocks
+    m_sizes, N, K = [200, 56, 128], 256, 512
+    X, W, ms, xq, wq, x_scale, w_scale, alpha = _grouped_problem(ops, m_sizes, N, K, seed=5)
+    y = ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, None, use_mx=False)
+    pc = x_scale.shape[1]
+    r = pr = 0
+    for g, m in enumerate(m_sizes):
+        mp = (m + 127) // 128 * 128
+        y_g = ops.f4f4bf16(xq.view(torch.uint8)[r:r + m].contiguous(), wq.view(torch.uint8)[g].contiguous(),
+                           x_scale[pr:pr + mp].contiguous(), w_scale[g].contiguous(), global_scale=alpha[g:g + 1])
+        assert torch.equal(y[r:r + m], y_g), f"group {g}"
+        r += m
+        pr += mp
+    assert pc == K // 16
+    assert _status() == 0
+
+
+def test_rows_past_the_sum_untouched_and_errors(ops):
+    m_sizes, N, K = [10, 20], 128, 256
+    X, W, ms, xq, wq, x_scale, w_scale, alpha = _grouped_problem(ops, m_sizes + [0], N, K, seed=9)
+    import mslk_b200.gemm  # noqa: F401
+    y = torch.ops.mslk.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, None, False)
+    assert y.shape == (30, N)
+    with pytest.raises(RuntimeError, match="NVFP4"):
+        ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, None, None)
+    with pytest.raises(RuntimeError, match="int64"):
+        ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms.int(), alpha, None, use_mx=False)
+    with pytest.raises(RuntimeError, match="int32"):
+        ops.f4f4bf16_grouped_mm(xq, wq.transpose(-2, -1), x_scale, w_scale, ms.cumsum(0), None, alpha)
+    assert _status() == 0
+
+
+def test_moe_shape_zipf(ops):
+    # 16 experts, Zipf counts with empty experts, hidden 2048 -> 1024 (reduced from the FP8 MoE configuration)
+    from mslk_b200.microbench import zipf_counts
+    m_sizes = zipf_counts(16, 4096).tolist()
+    X, W, ms, xq, wq, x_scale, w_scale, alpha = _grouped_problem(ops, m_sizes, 1024, 2048, seed=3)
+    y = ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, None, use_mx=False)
+    r = 0
+    for g, m in enumerate(m_sizes):
+        if m:
+            ref = X[r:r + m].float() @ W[g].float().T
+            err = (y[r:r + m].float() - ref).norm() / ref.norm()
+            assert float(err) < 0.2, f"group {g}: relative error {float(err)}"
+        r += m
+    assert _status() == 0

@@ -306,3 +306,39 @@ def test_gather_scale_quant_triton_fixture_close_to_oracle():
         ob = torch.where((b & 0x80) != 0, -(b & 0x7f), b & 0x7f)
         d = (oa - ob).abs()
         assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 2e-3, name
+
+
+def test_stacked_nvfp4_oracles_consistent_with_dense_oracle():
+    # quantize_stacked.py:22-178 / global_scale.py:40-230 restated on top of the pinned dense NVFP4 oracle
+    from golden.make_golden import STACKED_CASES, stacked_inputs, unswizzle_stacked_scales
+    for i, (name, m_sizes, K) in enumerate(STACKED_CASES):
+        x = stacked_inputs(m_sizes, K, 600 + i)
+        gs, idx = oracle.calculate_group_max(x, m_sizes)
+        q, s, starts = oracle.nvfp4_quantize_stacked(m_sizes, x, gs)
+        assert starts[-1] == sum((m + 127) // 128 * 128 for m in m_sizes) and s.shape[0] == starts[-1]
+        r = 0
+        for g, m in enumerate(m_sizes):
+            if m:
+                amax = float(x[r:r + m].abs().max())
+                assert float(gs[g]) == pytest.approx(2688.0 / (amax if amax else 1e-8), rel=1e-6)
+                assert bool((idx[r:r + m] == g).all())
+                qd, sd = oracle.quantize_nvfp4(x[r:r + m].contiguous(), gs[g:g + 1])
+                assert torch.equal(q[r:r + m], qd)
+                assert torch.equal(unswizzle_stacked_scales(s, m_sizes, K)[r:r + m],
+                                   oracle.from_blocked(sd.view(torch.uint8).reshape(-1), m, K // 16))
+            else:
+                assert float(gs[g]) == torch.finfo(torch.float32).max
+            r += m
+    # grouped GEMM oracle = dense oracle per group
+    m_sizes, N, K = [5, 0, 130], 48, 64
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn((135, K), generator=g).to(torch.bfloat16)
+    w = (torch.randn((3 * N, K), generator=g) * 0.1).to(torch.bfloat16)
+    xgs, _ = oracle.calculate_group_max(x, m_sizes)
+    wgs, _ = oracle.calculate_group_max(w, [N] * 3)
+    xq, xs, starts = oracle.nvfp4_quantize_stacked(m_sizes, x, xgs)
+    wq, ws, _ = oracle.nvfp4_quantize_stacked([N] * 3, w, wgs)
+    alpha = 1.0 / (xgs * wgs)
+    y = oracle.gemm_nvfp4_grouped_stacked(xq, wq.view(3, N, K // 2), xs, ws, m_sizes, alpha, starts)
+    ref = torch.cat([x[:5].float() @ w[:N].float().T, x[5:].float() @ w[2 * N:].float().T])
+    assert float((y.float() - ref).norm() / ref.norm()) < 0.2

@@ -23,6 +23,12 @@ def test_schemas_match_reference_strings(mslk):
     }
     for name, schema in want.items():
         assert str(getattr(mslk, name).default._schema) == schema
+    assert str(mslk.f4f4bf16_grouped_stacked.default._schema) == (
+        "mslk::f4f4bf16_grouped_stacked(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor M_sizes, "
+        "Tensor? global_scale=None, Tensor? starting_row_after_padding=None, bool use_mx=True) -> Tensor")
+    assert str(mslk.f4f4bf16_grouped_mm.default._schema) == (
+        "mslk::f4f4bf16_grouped_mm(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor offsets, "
+        "Tensor(a!)? output=None, Tensor(a!)? global_scale=None) -> Tensor")
     import importlib
     importlib.import_module("mslk.moe.activation")   # mslk/moe/activation.py:137-176 defines these from Python
     assert str(mslk.silu_mul.default._schema) == "mslk::silu_mul(Tensor x0, Tensor x1, Tensor? valid_token_count=None) -> Tensor"
