@@ -179,6 +179,20 @@ int mslk_b200_f8f8bf16_rowwise_batched(const void *xq, const void *wq, const flo
                                        void *stream);
 
 /*
+ * The grouped GEMM with the MoE combine fused into its epilogue: stacked row r of the product is ADDED
+ * atomically to row scatter_indices[r] of y (bf16 [y_rows, N], which the caller has initialised) instead
+ * of being stored at row r.  Replaces: mslk/gemm/triton/grouped_gemm.py:1112-1137
+ * (grouped_gemm_fp8_rowwise with _output_tensor / _scatter_add_indices; epilogue :386-402).
+ * Indices are int32 or int64 on the device (`index_bits`).  With several rows landing on one output row
+ * the sum depends on the order of the atomics, as in the reference.  An index outside [0, y_rows) skips
+ * the row and sets bit 0x200 of the device status word.
+ */
+int mslk_b200_f8f8bf16_rowwise_grouped_stacked_scatter_add(
+    const void *xq, const void *wq, const float *x_scale, const float *w_scale, const int64_t *M_sizes,
+    int64_t G, int64_t total_M, int64_t N, int64_t K, const void *scatter_indices, int index_bits,
+    void *y, int64_t y_rows, void *stream);
+
+/*
  * NVFP4 quantization (e2m1 data, one e4m3 scale per 16 elements in the 128x4
  * swizzled layout, optional fp32 per-tensor global scale read from the device).
  * Replaces: mslk/quantize/triton/quantize_kernels/nvfp4.py:62-296.

@@ -51,6 +51,9 @@ lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i6
 lib.mslk_b200_f4f4bf16.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_batched.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f8f8bf16_rowwise_batched.restype = _int
+lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked_scatter_add.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp,
+                                                                       _int, _vp, _i64, _vp]
+lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked_scatter_add.restype = _int
 lib.mslk_b200_f4f4bf16_grouped_stacked.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]
 lib.mslk_b200_f4f4bf16_grouped_stacked.restype = _int
 lib.mslk_b200_f4f4bf16_grouped_mm.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]

@@ -13,6 +13,8 @@ import sys
 _ALIASES = {
     "mslk": "mslk_b200",
     "mslk.gemm": "mslk_b200.gemm",
+    "mslk.gemm.triton": "mslk_b200.gemm.triton",
+    "mslk.gemm.triton.grouped_gemm": "mslk_b200.gemm.triton.grouped_gemm",
     "mslk.quantize": "mslk_b200.quantize",
     "mslk.quantize.triton": "mslk_b200.quantize.triton",
     "mslk.quantize.triton.fp8_quantize": "mslk_b200.quantize.triton.fp8_quantize",

@@ -18,6 +18,9 @@ enum : int {
   kStatusMmaTimeout = 2,        // MMA issuer waited too long for operands / accumulator
   kStatusEpilogueTimeout = 3,   // epilogue waited too long for an accumulator
   kStatusDrainTimeout = 4,      // teardown waited too long for copies in flight
+  // bits OR-ed in by kernels that met an index outside its tensor (the row is skipped, not followed)
+  kStatusBadGatherIndex = 0x100,
+  kStatusBadScatterIndex = 0x200,
 };
 
 // Upper bound for any single pipeline wait.  Generous against the longest legal

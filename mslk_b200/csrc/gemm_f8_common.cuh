@@ -32,6 +32,12 @@ struct GemmParams {
   // Alternative to m_sizes: int32 END offsets of the groups in the stacked rows (device, [G]);
   // group g owns rows [end_offsets[g-1], end_offsets[g]).  Takes precedence when set.
   const int32_t *end_offsets = nullptr;
+  // Scatter-add epilogue (MoE combine fused into the grouped GEMM): when set, stacked row r of the
+  // product is ADDED atomically (bf16 vector reductions) to row scatter_idx[r] of y, which then has
+  // scatter_rows rows; indices are 32- or 64-bit integers on the device.
+  const void *scatter_idx = nullptr;
+  int scatter_bits = 32;
+  int scatter_rows = 0;
   int N;
   int K;
   // Output placement: y (and y_extra[0..n_extra)) are row-major with a pitch of ldy elements; the
@@ -179,6 +185,22 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&acc)[32], float 
   uint32_t packed[16];
   epilogue_pack<BIAS>(acc, xs, ws, bs, packed);
   if (!row_ok) return;
+  if (p.scatter_idx) {   // elem_off already addresses the destination row
+    __nv_bfloat16 *dst = p.y + elem_off;
+    if (vec_ok && cols_left >= 32) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        asm volatile("red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst + 8 * j),
+                     "r"(packed[4 * j]), "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                     : "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < cols_left)
+          atomicAdd(dst + j, __ushort_as_bfloat16(static_cast<unsigned short>(packed[j / 2] >> ((j & 1) * 16))));
+    }
+    return;
+  }
   for (int dsti = -1; dsti < p.n_extra; ++dsti) {
     __nv_bfloat16 *dst = (dsti < 0 ? p.y : p.y_extra[dsti]) + elem_off;
     if (vec_ok && cols_left >= 32) {

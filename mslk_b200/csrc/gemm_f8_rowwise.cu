@@ -226,8 +226,17 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         bs_s[c] = b;
       }
       __syncwarp();
-      const bool row_ok = row_in_tile < t.rows;
+      bool row_ok = row_in_tile < t.rows;
       const float xs = row_ok ? p.x_scale[t.row0 + row_in_tile] : 0.f;
+      long long out_row = t.row0 + row_in_tile;
+      if (p.scatter_idx && row_ok) {
+        out_row = p.scatter_bits == 64 ? static_cast<const long long *>(p.scatter_idx)[t.row0 + row_in_tile]
+                                       : static_cast<long long>(static_cast<const int *>(p.scatter_idx)[t.row0 + row_in_tile]);
+        if (out_row < 0 || out_row >= p.scatter_rows) {   // reported, not followed
+          atomicOr(p.status, kStatusBadScatterIndex);
+          row_ok = false;
+        }
+      }
       // warp-uniform decision: either every lane saw the accumulator complete or the warp leaves
       const bool got = mbar_wait(&S.tmem_full[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       if (!__all_sync(0xffffffffu, got)) {
@@ -236,7 +245,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(quad * 32) << 16);
-      const size_t yoff = static_cast<size_t>(t.row0 + row_in_tile) * p.ldy + p.col0 + t.n0;
+      const size_t yoff = static_cast<size_t>(out_row) * p.ldy + p.col0 + t.n0;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int cols_left = p.N - (t.n0 + c * 32);
@@ -335,6 +344,9 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
     for (int i = 0; i < 7; ++i) p.y_extra[i] = placement->y_extra[i];
     p.rs_rows = placement->rs_rows;
     p.rs_slot = placement->rs_slot;
+    p.scatter_idx = placement->scatter_idx;
+    p.scatter_bits = placement->scatter_bits;
+    p.scatter_rows = placement->scatter_rows;
   }
 
   // few tokens AND scratch given: weight-streaming kernel with the K dimension split.  Opt-in: on
@@ -352,7 +364,8 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
                              ((N + 255) / 256);
   // grouped problems: pairs pay off only when the average group is several 256-row tiles tall
   const bool groups_tall = !m_sizes || total_m / G >= 512;
-  const bool want_pair = force == 2 || p.rs_rows > 0 || (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2);
+  const bool want_pair = !p.scatter_idx &&   // the scatter-add epilogue lives in the one-CTA kernel
+                         (force == 2 || p.rs_rows > 0 || (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2));
   if (want_pair) {
     const int rc = launch_pair_kernel(xq, wq, p, st);
     if (rc >= 0) return rc;  // -1: pairs unavailable on this device, fall through to one CTA per tile
@@ -482,4 +495,28 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_batched(const void *xq, const void *wq, 
   // B equal groups of M stacked rows, group b multiplying its own weight block wq[b]
   return run(xq, wq, x_scale, w_scale, bias, bias_kind, y, nullptr, B, B * M, N, K, nullptr, 0,
              static_cast<cudaStream_t>(stream), "f8f8bf16_rowwise_batched");
+}
+
+MSLK_API int mslk_b200_f8f8bf16_rowwise_grouped_stacked_scatter_add(const void *xq, const void *wq, const float *x_scale,
+                                                                    const float *w_scale, const int64_t *M_sizes,
+                                                                    int64_t G, int64_t total_M, int64_t N, int64_t K,
+                                                                    const void *scatter_indices, int index_bits,
+                                                                    void *y, int64_t y_rows, void *stream) {
+  using namespace mslk_b200;
+  using namespace mslk_b200::gemm_f8;
+  clear_error();
+  const char *name = "f8f8bf16_rowwise_grouped_stacked_scatter_add";
+  if (!M_sizes) return fail(1, "%s: M_sizes is null", name);
+  if (!scatter_indices) return fail(1, "%s: scatter_indices is null", name);
+  if (index_bits != 32 && index_bits != 64) return fail(1, "%s: indices must be int32 or int64", name);
+  if (y_rows < 0 || y_rows > 0x7fffffffLL) return fail(1, "%s: bad output row count", name);
+  if (K == 0) return 0;   // an empty reduction adds nothing
+  GemmParams placement;
+  placement.N = static_cast<int>(N);
+  default_placement(placement);
+  placement.scatter_idx = scatter_indices;
+  placement.scatter_bits = index_bits;
+  placement.scatter_rows = static_cast<int>(y_rows);
+  return run(xq, wq, x_scale, w_scale, nullptr, MSLK_B200_BIAS_NONE, y, M_sizes, G, total_M, N, K, nullptr, 0,
+             static_cast<cudaStream_t>(stream), name, &placement);
 }

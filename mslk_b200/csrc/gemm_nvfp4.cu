@@ -97,6 +97,20 @@ constexpr size_t smem_bytes() {
   return 1024 + static_cast<size_t>(Cfg<BN>::kStages) * Cfg<BN>::kStageBytes + sizeof(SmemTail<BN>);
 }
 
+// Tile lookup of the epilogue warps as a real call: the scheduler's temporaries then do not share the
+// register budget of the accumulator drain (128 packed registers for BN = 256).
+__device__ __noinline__ bool epilogue_tile(const int *tile_start, const int *row_start, int G, int N, int n_tiles, int bn,
+                                           int tile, int &g, int &row0, int &rows, int &n0) {
+  Scheduler sched{tile_start, row_start, G, N, n_tiles, bn, kBM, kBandM, g};
+  Tile t;
+  if (!sched.get(tile, t)) return false;
+  g = sched.g;
+  row0 = t.row0;
+  rows = t.rows;
+  n0 = t.n0;
+  return true;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kNumThreads, 1)
     gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -284,14 +298,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int row_in_tile = quad * 32 + lane;
     const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
     int local = 0;
-    Tile t;
-    for (int tile = blockIdx.x; sched.get(tile, t); tile += gridDim.x, ++local) {
-      const int n_tile = t.n0 / BN;
-      const float alpha = p.alpha[p.alpha_per_group ? sched.g : 0];
+    int g = 0, row0, rows, n0;
+    for (int tile = blockIdx.x; epilogue_tile(S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, tile, g, row0, rows, n0);
+         tile += gridDim.x, ++local) {
+      const int n_tile = n0 / BN;
+      const float alpha = p.alpha[p.alpha_per_group ? g : 0];
       const int acc = local % C::kAccStages;
       const uint32_t acc_phase = (local / C::kAccStages) & 1;
-      const int row = t.row0 + row_in_tile;
-      const bool row_ok = row_in_tile < t.rows;
+      const int row = row0 + row_in_tile;
+      const bool row_ok = row_in_tile < rows;
       const bool got = mbar_wait(&S.tmem_full[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();

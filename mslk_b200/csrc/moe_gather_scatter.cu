@@ -99,7 +99,7 @@ __device__ __forceinline__ bool locate_row(const GatherParams &p, int64_t row, i
   ti = load_index(p.token_indices, p.token_bits, row);
   const int64_t ei = load_index(p.expert_indices, p.expert_bits, row);
   if (ti < 0 || ti >= p.T || ei < 0 || ei >= p.E) {
-    if (threadIdx.x == 0) atomicOr(p.status, 0x100);
+    if (threadIdx.x == 0) atomicOr(p.status, kStatusBadGatherIndex);
     return false;
   }
   score = load_as_f32(p.scores, p.scores_dtype, ti * p.stride_t + ei * p.stride_e);
@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(256) scatter_add_kernel(const ScatterParams p)
     const int64_t row = i / per_row, v = i - row * per_row;
     const int64_t to = load_index(p.token_indices, p.token_bits, row);
     if (to < 0 || to >= p.T) {
-      atomicOr(p.status, 0x200);
+      atomicOr(p.status, kStatusBadScatterIndex);
       continue;
     }
     int64_t src_row = row;

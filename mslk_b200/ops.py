@@ -221,6 +221,35 @@ def f8f8bf16_rowwise_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes) -> torch
     return y
 
 
+def f8f8bf16_rowwise_grouped_stacked_scatter_add(XQ, WQ, x_scale, w_scale, M_sizes, output, scatter_add_indices) -> torch.Tensor:
+    """The stacked grouped GEMM with the combine fused in: ``output[scatter_add_indices[r]] += product[r]`` (atomic, bf16)."""
+    name = "f8f8bf16_rowwise_grouped_stacked_scatter_add"
+    dev = _check_rowwise_args(name, XQ, WQ, x_scale, w_scale)
+    _require_cuda(name, XQ, M_sizes, output, scatter_add_indices)
+    if M_sizes.dtype != torch.int64:
+        raise RuntimeError(f"{name}: M_sizes must be int64.")
+    if WQ.dim() != 3 or WQ.shape[0] != M_sizes.numel():
+        raise RuntimeError(f"{name}: WQ must be [G,N,K] with G == M_sizes.numel()")
+    if XQ.dim() != 2 or XQ.shape[1] != WQ.shape[2]:
+        raise RuntimeError(f"{name}: XQ must be [total_M,K] with the K of WQ")
+    G, N, K = WQ.shape
+    total_M = XQ.shape[0]
+    if x_scale.numel() != total_M or w_scale.numel() != G * N:
+        raise RuntimeError(f"{name}: scale sizes must match total_M and G*N")
+    assert scatter_add_indices.is_contiguous()
+    assert scatter_add_indices.shape == (total_M,)
+    if output.dtype != torch.bfloat16 or output.dim() != 2 or output.shape[1] != N or not output.is_contiguous():
+        raise RuntimeError(f"{name}: output must be a contiguous bfloat16 [rows, N] tensor")
+    if total_M == 0 or N == 0:
+        return output
+    xs, ws, ms = x_scale.contiguous(), w_scale.contiguous(), M_sizes.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked_scatter_add(
+            _ptr(XQ), _ptr(WQ), _ptr(xs), _ptr(ws), _ptr(ms), G, total_M, N, K, _ptr(scatter_add_indices),
+            _index_bits(name, scatter_add_indices), _ptr(output), output.shape[0], _stream(dev)), name)
+    return output
+
+
 # --------------------------------------------------------------------------- NVFP4
 
 def nvfp4_scale_shape(rows: int, K: int):

@@ -333,3 +333,53 @@ def test_batched_output_argument_empty_dims_and_errors(ops):
     with pytest.raises(RuntimeError, match="float32"):
         ops.f8f8bf16_rowwise_batched(xq, wq, xs, ws, torch.zeros((2, 128), dtype=torch.bfloat16, device="cuda"))
     assert _status() == 0
+
+
+# ------------------------------------------------------------------ grouped GEMM + fused scatter-add (MoE combine)
+
+@pytest.mark.parametrize("G,m_sizes,N,K,topk", [
+    (4, [128, 256, 0, 64], 512, 512, 1),
+    (16, [0, 300, 0, 17, 129, 0, 1, 640, 128, 127, 0, 0, 255, 256, 257, 1000], 768, 640, 1),
+    (8, [64] * 8, 256, 1024, 2),
+    (4, [3, 0, 5, 1], 72, 128, 1),           # narrow, element-wise atomics for the ragged column tail
+    (16, [256] * 16, 1024, 512, 4),
+])
+def test_grouped_scatter_add_epilogue(ops, G, m_sizes, N, K, topk):
+    # mslk/gemm/triton/grouped_gemm.py:386-402: product row r is added to output[indices[r]]
+    xq, wq, xs, ws, ms, y_plain = _grouped_case(ops, G, m_sizes, N, K, seed=G + N + topk)
+    total = sum(m_sizes)
+    T = max(total // topk, 1)
+    g = torch.Generator().manual_seed(total)
+    idx = (torch.randperm(total, generator=g) % T).to(torch.int32).cuda()
+    out0 = (torch.randn((T, N), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    out = out0.clone()
+    ret = ops.f8f8bf16_rowwise_grouped_stacked_scatter_add(xq, wq, xs, ws.view(-1), ms, out, idx)
+    assert ret.data_ptr() == out.data_ptr()
+    if topk == 1:
+        # every output row receives at most one product row: one bf16 addition, exactly reproducible
+        want = out0.clone()
+        want[idx.long()] = (out0[idx.long()].float() + y_plain[:total].float()).to(torch.bfloat16)
+        assert torch.equal(out, want)
+    else:
+        want = out0.float().index_add_(0, idx.long(), y_plain[:total].float())
+        scale = max(1.0, float(want.std()))
+        torch.testing.assert_close(out.float(), want, rtol=1.6e-2, atol=2e-2 * scale)
+    # the reference's Python entry point, int64 indices
+    import mslk_b200.gemm.triton.grouped_gemm as gg
+    out2 = out0.clone()
+    gg.grouped_gemm_fp8_rowwise(xq, wq.view(G * N, K), ms.int(), xs, ws.view(-1), _output_tensor=out2,
+                                _scatter_add_indices=idx.long())
+    if topk == 1:
+        assert torch.equal(out2, out)
+    assert torch.equal(gg.grouped_gemm_fp8_rowwise(xq, wq.view(G * N, K), ms.int(), xs, ws.view(-1))[:total], y_plain[:total])
+    assert _status() == 0
+
+
+def test_scatter_add_bad_index_reported(ops):
+    xq, wq, xs, ws, ms, _ = _grouped_case(ops, 2, [16, 16], 128, 128, seed=1)
+    idx = torch.arange(32, dtype=torch.int32, device="cuda")
+    idx[5] = 1000
+    out = torch.zeros((32, 128), dtype=torch.bfloat16, device="cuda")
+    ops.f8f8bf16_rowwise_grouped_stacked_scatter_add(xq, wq, xs, ws.view(-1), ms, out, idx)
+    assert _status() == 0x200
+    assert float(out[5].float().abs().max()) == 0.0 and float(out[6].float().abs().max()) > 0.0
