@@ -197,38 +197,23 @@ __global__ void __launch_bounds__(kThreads, 6)
   const int stride = gridDim.x * (kThreads / 32);
   const int total_units = s_blk_end[G - 1] * n_col_tiles * kWarpsPerTile;
 
-  auto locate = [&](int u, int &mm, int &jj, int &gg) {
-    const int tile = u / kWarpsPerTile, w = u - tile * kWarpsPerTile;
+  for (int unit = blockIdx.x * (kThreads / 32) + (tid >> 5); unit < total_units; unit += stride) {
+    const int tile = unit / kWarpsPerTile, w = unit - tile * kWarpsPerTile;
     const int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
     int lo = 0, hi = G - 1;   // group of padded row block tr: first g with blk_end[g] > tr
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
       if (s_blk_end[mid] > tr) hi = mid; else lo = mid + 1;
     }
-    gg = lo;
-    const int blk0 = lo ? s_blk_end[lo - 1] : 0, row0 = lo ? s_row_end[lo - 1] : 0;
-    mm = row0 + (tr - blk0) * kTileRows + row_in_tile + 2 * w;
-    jj = tc * kTileBlocks + c;
-    return mm < s_row_end[lo] && jj < nblk;
-  };
-  int unit = blockIdx.x * (kThreads / 32) + (tid >> 5);
-  if (unit >= total_units) return;
-  int m, j, g;
-  bool live = locate(unit, m, j, g);
-  BlockIn cur{};
-  if (live) cur = load_block<kVec>(x + m * row_stride + j * 16);
-  while (unit < total_units) {
-    const int nunit = unit + stride;   // prefetch the next unit's block
-    int nm = 0, nj = 0, ng = 0;
-    bool nlive = false;
-    BlockIn nxt{};
-    if (nunit < total_units) {
-      nlive = locate(nunit, nm, nj, ng);
-      if (nlive) nxt = load_block<kVec>(x + nm * row_stride + nj * 16);
-    }
+    const int g = lo;
+    const int blk0 = g ? s_blk_end[g - 1] : 0, row0 = g ? s_row_end[g - 1] : 0;
+    const int m = row0 + (tr - blk0) * kTileRows + row_in_tile + 2 * w;
+    const int j = tc * kTileBlocks + c;
+    const bool live = m < s_row_end[g] && j < nblk;
     uint8_t s8 = 0;
     if (live) {
       const float gs = gs_ptr[g];
+      const BlockIn cur = load_block<kVec>(x + m * row_stride + j * 16);
       const uint32_t wd[8] = {cur.a.x, cur.a.y, cur.a.z, cur.a.w, cur.b.x, cur.b.y, cur.b.z, cur.b.w};
       __nv_bfloat162 mx = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&wd[0]));
 #pragma unroll
@@ -249,12 +234,6 @@ __global__ void __launch_bounds__(kThreads, 6)
       *reinterpret_cast<uint2 *>(q + m * q_pitch + j * 8) = make_uint2(cvt_e2m1x8(lo8), cvt_e2m1x8(hi8));
     }
     scales[static_cast<int64_t>(unit) * 32 + lane] = s8;   // zero for the padding rows / columns of the group
-    unit = nunit;
-    m = nm;
-    j = nj;
-    g = ng;
-    live = nlive;
-    cur = nxt;
   }
 }
 

@@ -7,6 +7,7 @@
     python -m mslk_b200.microbench f4f4bf16_grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
     python -m mslk_b200.microbench f4f4bf16 --shape 8192,8192,8192
     python -m mslk_b200.microbench quantize_nvfp4 --shape 8192,8192
+    python -m mslk_b200.microbench moe_gather_scatter --tokens 16384 --shape 5120,16,2      # D,E,top-k
     python -m mslk_b200.microbench silu_mul_quant --shape 16384,14336      # T,D; also times the unfused pair
     python -m mslk_b200.microbench sweep          # the Llama-3-8B sweep: M x (N,K), quantize + GEMM
 
@@ -80,6 +81,29 @@ def bench_f8f8bf16_rowwise(ops, M, N, K, args):
     byts = M * K + N * K + 2.0 * M * N + 4.0 * (M + N)
     return {"op": "f8f8bf16_rowwise", "M": M, "N": N, "K": K, "us": sec * 1e6, "TFLOPs": flops / sec / 1e12,
             "GBps": byts / sec / 1e9}
+
+
+def bench_moe_gather_scatter(ops, T, D, E, topk, args):
+    """Dispatch / combine around the grouped GEMM: a = T * topk rows gathered from T tokens, and added back."""
+    a = T * topk
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = _randn((T, D))
+    scores = torch.rand((T, E), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    tok = (torch.randperm(a, generator=g, device="cuda") % T).to(torch.int32)
+    ex = torch.randint(0, E, (a,), generator=g, device="cuda")
+    out = []
+    sec = _time(lambda i: ops.gather_scale_dense_tokens(x, tok, ex, scores), 1, args.iters, args.warmup, args.graph)
+    out.append({"op": "gather_scale_dense_tokens", "T": T, "D": D, "a": a, "us": sec * 1e6, "GBps": 4.0 * a * D / sec / 1e9})
+    sec = _time(lambda i: ops.gather_scale_quant_dense_tokens(x, tok, ex, scores), 1, args.iters, args.warmup, args.graph)
+    out.append({"op": "gather_scale_quant_dense_tokens", "T": T, "D": D, "a": a, "us": sec * 1e6,
+                "GBps": 3.0 * a * D / sec / 1e9})
+    y = _randn((a, D))
+    acc = torch.zeros((T, D), dtype=torch.bfloat16, device="cuda")
+    sec = _time(lambda i: ops.scatter_add_dense_tokens(acc, y, tok), 1, args.iters, args.warmup, args.graph)
+    # bytes: the rows read plus a read-modify-write of the destination rows
+    out.append({"op": "scatter_add_dense_tokens", "T": T, "D": D, "a": a, "us": sec * 1e6,
+                "GBps": (2.0 * a * D + 4.0 * a * D) / sec / 1e9})
+    return out
 
 
 def bench_silu_mul_quant(ops, T, D, args):
@@ -189,7 +213,7 @@ def bench_f4f4bf16(ops, M, N, K, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "quantize_nvfp4", "silu_mul_quant",
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "moe_gather_scatter", "quantize_nvfp4", "silu_mul_quant",
                                    "sweep"])
     ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
     ap.add_argument("--experts", type=int, default=16)
@@ -216,6 +240,8 @@ def main():
         out.append(bench_quantize_nvfp4(ops, *(shape or [8192, 8192]), args))
     elif args.op == "f4f4bf16_grouped":
         out.append(bench_f4f4bf16_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
+    elif args.op == "moe_gather_scatter":
+        out.extend(bench_moe_gather_scatter(ops, args.tokens, *(shape or [5120, 16, 2]), args))
     elif args.op == "silu_mul_quant":
         out.append(bench_silu_mul_quant(ops, *(shape or [16384, 14336]), args))
     elif args.op == "f4f4bf16":
