@@ -276,6 +276,24 @@ __device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc
       : "memory");
 }
 
+// Pair-wide block-scaled NVFP4 MMA (M = 256 over both CTAs): like mma_f8f6f4_pair, with the scale
+// factors read from the same tensor-memory columns of each CTA (A scales of its own 128 rows, B scales
+// of all N columns).
+__device__ __forceinline__ void mma_nvfp4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Pair-wide smem -> TMEM copy: each CTA copies from its own shared memory (same offset) into its own
+// tensor memory (same column).
+__device__ __forceinline__ void tc_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t s_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(s_desc) : "memory");
+}
+
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of
 // 128 bytes with the 128-byte swizzle (what a TMA box {128 B, rows} with
 // CU_TENSOR_MAP_SWIZZLE_128B writes): 8-row groups are 1024 bytes apart.

@@ -21,6 +21,7 @@
 #include "../../include/mslk_b200.h"
 #include "common.cuh"
 #include "gemm_f8_common.cuh"   // group tables and the tile scheduler shared with the FP8 kernels
+#include "gemm_nvfp4_pair.h"
 #include "host.h"
 
 #include <cstdlib>
@@ -416,6 +417,19 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   p.alpha_per_group = grouped ? 1 : 0;
 
   const int sms = sm_count();
+  // CTA pairs (256 x 256 tiles, a third less shared-memory traffic per flop) for dense problems with
+  // enough such tiles to occupy every pair of SMs
+  static const int force = [] {
+    const char *e = getenv("MSLK_B200_NVFP4_KERNEL");  // "1cta" | "2cta": tuning aid, default = heuristic
+    return !e ? 0 : (e[0] == '2' ? 2 : 1);
+  }();
+  const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  if (!grouped && (force == 2 || (force == 0 && pair_tiles >= sms / 2))) {
+    nvfp4_pair::PairParams pp{global_scale, static_cast<__nv_bfloat16 *>(y), status, static_cast<int>(M),
+                              static_cast<int>(N), static_cast<int>(K), static_cast<int>((K + 63) / 64)};
+    const int rc = nvfp4_pair::launch_pair_kernel(xq, wq, x_scale, w_scale, pp, st);
+    if (rc >= 0) return rc;   // -1: pairs unavailable, fall through to one CTA per tile
+  }
   const int64_t m_tiles = (M + kBM - 1) / kBM + (grouped ? G : 0);   // upper bound for ragged groups
   // 256-wide tiles halve the A traffic per flop but hold one accumulator only; use them when
   // there are enough tiles to fill the device, 128-wide (double-buffered) otherwise

@@ -111,6 +111,12 @@ int make_tmap_2d_bytes(CUtensorMap *out, const void *base, uint64_t cols_bytes, 
                 swizzle);
 }
 
+int make_tmap_2d_u32(CUtensorMap *out, const void *base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
+                     uint32_t box_cols, uint32_t box_rows) {
+  return encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, base, cols, rows, pitch_bytes, box_cols, box_rows,
+                CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 int make_tmap_2d_bf16(CUtensorMap *out, const void *base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
                       uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
   return encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, cols, rows, pitch_bytes, box_cols, box_rows, swizzle);

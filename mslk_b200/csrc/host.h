@@ -31,6 +31,9 @@ int make_tmap_2d_bytes(CUtensorMap *out, const void *base, uint64_t cols_bytes, 
                        CUtensorMapSwizzle swizzle);
 
 // Same for 2-byte (bf16) elements: cols / box_cols are element counts.
+// 2-D map over 32-bit words, no swizzle (rows wider than 256 bytes, e.g. 512-byte scale atoms)
+int make_tmap_2d_u32(CUtensorMap *out, const void *base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
+                     uint32_t box_cols, uint32_t box_rows);
 int make_tmap_2d_bf16(CUtensorMap *out, const void *base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes,
                       uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle);
 
