@@ -13,29 +13,15 @@
 #include "../../include/mslk_b200.h"
 #include "common.cuh"
 #include "host.h"
+#include "rowwise_elem.cuh"
 
 #include <algorithm>
 
 namespace mslk_b200 {
 namespace {
 
-__device__ __forceinline__ float div_full(float a, float b) {
-  float r;
-  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-__device__ __forceinline__ uint4 ld_nc_v4(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
+using namespace rowwise;
+
 __device__ __forceinline__ int64_t load_index(const void *p, int bits, int64_t i) {
   return bits == 64 ? static_cast<const int64_t *>(p)[i] : static_cast<int64_t>(static_cast<const int32_t *>(p)[i]);
 }
@@ -44,41 +30,6 @@ __device__ __forceinline__ float load_as_f32(const void *p, int dtype, int64_t i
   if (dtype == MSLK_B200_F16) return __half2float(static_cast<const __half *>(p)[i]);
   return static_cast<const float *>(p)[i];
 }
-
-template <typename T>
-struct Elem;
-template <>
-struct Elem<__nv_bfloat16> {
-  static __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      f[2 * i] = __uint_as_float(w[i] << 16);
-      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
-  }
-  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) { return pack_bf16x2(lo, hi); }
-  static __device__ __forceinline__ float load(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
-  static __device__ __forceinline__ __nv_bfloat16 make(float v) { return __float2bfloat16_rn(v); }
-};
-template <>
-struct Elem<__half> {
-  static __device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]) {
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 p = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-      f[2 * i] = p.x;
-      f[2 * i + 1] = p.y;
-    }
-  }
-  static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    const __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t *>(&h);
-  }
-  static __device__ __forceinline__ float load(const __half *p) { return __half2float(*p); }
-  static __device__ __forceinline__ __half make(float v) { return __float2half_rn(v); }
-};
 
 struct GatherParams {
   const void *x;
@@ -120,7 +71,7 @@ __global__ void __launch_bounds__(1024) gather_scale_kernel(const GatherParams p
     const int nvec = static_cast<int>(p.D / 8);
     for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
       float f[8];
-      Elem<T>::unpack8(ld_nc_v4(src + static_cast<int64_t>(v) * 8), f);
+      Elem<T>::unpack8(ld_stream_v4(src + static_cast<int64_t>(v) * 8), f);
       uint4 o;
       o.x = Elem<T>::pack2(__fmul_rn(f[0], score), __fmul_rn(f[1], score));
       o.y = Elem<T>::pack2(__fmul_rn(f[2], score), __fmul_rn(f[3], score));
@@ -134,18 +85,6 @@ __global__ void __launch_bounds__(1024) gather_scale_kernel(const GatherParams p
 }
 
 // ---------------------------------------------------------------- gather + scale + per-row FP8 quantize
-__device__ __forceinline__ float block_max(float v, float *s_part) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x / 32] = v;
-  __syncthreads();
-  const int warps = blockDim.x / 32;
-  float m = (threadIdx.x & 31) < warps ? s_part[threadIdx.x & 31] : 0.f;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  return m;
-}
-
 // One CTA per output row, the scaled row kept in registers (kVecs vectors of 8 per thread), so the
 // source row is read once (the reference reads it twice, the second time from L2).
 template <typename T, int kVecs, int kMaxThreads>
@@ -163,7 +102,7 @@ __global__ void __launch_bounds__(kMaxThreads) gather_scale_quant_vec_kernel(con
 #pragma unroll
   for (int i = 0; i < kVecs; ++i) {
     const int v = threadIdx.x + i * nthreads;
-    raw[i] = v < nvec ? ld_nc_v4(src + static_cast<int64_t>(v) * 8) : make_uint4(0, 0, 0, 0);
+    raw[i] = v < nvec ? ld_stream_v4(src + static_cast<int64_t>(v) * 8) : make_uint4(0, 0, 0, 0);
   }
   float y[kVecs][8];
   float amax = 0.f;
@@ -182,21 +121,7 @@ __global__ void __launch_bounds__(kMaxThreads) gather_scale_quant_vec_kernel(con
   if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
   const float out_scale = div_full(448.0f, rmax);
   if (threadIdx.x == 0) p.inv_scale[row] = div_full(1.0f, out_scale);
-  uint8_t *qr = static_cast<uint8_t *>(p.out) + row * p.D;
-#pragma unroll
-  for (int i = 0; i < kVecs; ++i) {
-    const int v = threadIdx.x + i * nthreads;
-    if (v < nvec) {
-      uint32_t o[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t lo = cvt_e4m3x2(__fmul_rn(y[i][4 * h], out_scale), __fmul_rn(y[i][4 * h + 1], out_scale));
-        const uint32_t hi = cvt_e4m3x2(__fmul_rn(y[i][4 * h + 2], out_scale), __fmul_rn(y[i][4 * h + 3], out_scale));
-        o[h] = lo | (hi << 16);
-      }
-      *reinterpret_cast<uint2 *>(qr + static_cast<int64_t>(v) * 8) = make_uint2(o[0], o[1]);
-    }
-  }
+  store_row_e4m3<kVecs>(y, out_scale, static_cast<uint8_t *>(p.out) + row * p.D, nvec, nthreads);
 }
 
 // Any D / alignment: two passes over the source row.
@@ -331,7 +256,7 @@ __global__ void __launch_bounds__(256) scatter_add_kernel(const ScatterParams p)
     if (kVec) {
       const char *src = static_cast<const char *>(p.in) + (src_row * p.D) * elem_bytes<kDtype>() + v * 16;
       char *dst = static_cast<char *>(p.out) + (to * p.D) * elem_bytes<kDtype>() + v * 16;
-      red_add_16B<kDtype>(dst, ld_nc_v4(src));
+      red_add_16B<kDtype>(dst, ld_stream_v4(src));
     } else {
       red_add_elem<kDtype>(p.out, p.in, to * p.D + v, src_row * p.D + v);
     }

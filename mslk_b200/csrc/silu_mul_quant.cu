@@ -18,11 +18,14 @@
 #include "../../include/mslk_b200.h"
 #include "common.cuh"
 #include "host.h"
+#include "rowwise_elem.cuh"
 
 #include <algorithm>
 
 namespace mslk_b200 {
 namespace {
+
+using namespace rowwise;
 
 __device__ __forceinline__ float ex2_approx_ftz(float x) {
   float r;
@@ -32,11 +35,6 @@ __device__ __forceinline__ float ex2_approx_ftz(float x) {
 __device__ __forceinline__ float rcp_approx_ftz(float x) {
   float r;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
-  return r;
-}
-__device__ __forceinline__ float div_full(float a, float b) {
-  float r;
-  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
   return r;
 }
 // The reference's kernel lowers sigmoid(x) to  div.full(1, 1 + ex2.approx(-x * log2(e))).  Two
@@ -68,41 +66,6 @@ __device__ __forceinline__ void silu_mul8(const float (&f0)[8], const float (&f1
     for (int j = 0; j < 8; ++j) y[j] = silu_mul<false>(f0[j], f1[j]);
   }
 }
-__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
-  uint16_t r;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-
-template <typename T>
-__device__ __forceinline__ void unpack8(const uint4 &v, float (&f)[8]);
-template <>
-__device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4 &v, float (&f)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-template <>
-__device__ __forceinline__ void unpack8<__half>(const uint4 &v, float (&f)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 p = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-    f[2 * i] = p.x;
-    f[2 * i + 1] = p.y;
-  }
-}
-
-__device__ __forceinline__ uint4 ld_stream_v4(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
 
 struct SiluParams {
   const void *x0;
@@ -113,19 +76,6 @@ struct SiluParams {
   const int *valid_token_count;
   int64_t T, D, stride0, stride1;
 };
-
-// Maximum over the block (blockDim.x a multiple of 32, at most 1024); s_part holds 32 floats.
-__device__ __forceinline__ float block_max(float v, float *s_part) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x / 32] = v;
-  __syncthreads();
-  const int warps = blockDim.x / 32;
-  float m = (threadIdx.x & 31) < warps ? s_part[threadIdx.x & 31] : 0.f;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  return m;
-}
 
 // Vector path: D % 8 == 0, 16-byte aligned rows; kVecs 8-element vectors per thread, the block size
 // chosen by the host so that kVecs * blockDim.x covers the row with less than one warp of slack.
@@ -155,9 +105,8 @@ __global__ void __launch_bounds__(kMaxThreads) silu_mul_quant_vec_kernel(const S
 #pragma unroll
   for (int i = 0; i < kVecs; ++i) {
     float f0[8], f1[8];
-    unpack8<T>(a[i], f0);
-    unpack8<T>(b[i], f1);
-#pragma unroll
+    Elem<T>::unpack8(a[i], f0);
+    Elem<T>::unpack8(b[i], f1);
     silu_mul8(f0, f1, y[i]);
 #pragma unroll
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(y[i][j]));
@@ -167,32 +116,7 @@ __global__ void __launch_bounds__(kMaxThreads) silu_mul_quant_vec_kernel(const S
   if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
   const float y_scale = div_full(448.0f, rmax);
   if (threadIdx.x == 0) p.inv_scale[row] = div_full(1.0f, y_scale);
-  uint8_t *qr = p.q + row * p.D;
-#pragma unroll
-  for (int i = 0; i < kVecs; ++i) {
-    const int v = threadIdx.x + i * kBlock;
-    if (v < nvec) {
-      uint32_t o[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t lo = cvt_e4m3x2(__fmul_rn(y[i][4 * h], y_scale), __fmul_rn(y[i][4 * h + 1], y_scale));
-        const uint32_t hi = cvt_e4m3x2(__fmul_rn(y[i][4 * h + 2], y_scale), __fmul_rn(y[i][4 * h + 3], y_scale));
-        o[h] = lo | (hi << 16);
-      }
-      *reinterpret_cast<uint2 *>(qr + static_cast<int64_t>(v) * 8) = make_uint2(o[0], o[1]);
-    }
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ float to_f32(const T *p);
-template <>
-__device__ __forceinline__ float to_f32<__nv_bfloat16>(const __nv_bfloat16 *p) {
-  return __bfloat162float(*p);
-}
-template <>
-__device__ __forceinline__ float to_f32<__half>(const __half *p) {
-  return __half2float(*p);
+  store_row_e4m3<kVecs>(y, y_scale, p.q + row * p.D, nvec, kBlock);
 }
 
 // General path (any D / alignment): two passes, y recomputed in the second.
@@ -204,7 +128,7 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_generic_kernel(const Si
   const T *r0 = static_cast<const T *>(p.x0) + row * p.stride0;
   const T *r1 = static_cast<const T *>(p.x1) + row * p.stride1;
   float amax = 0.f;
-  for (int64_t k = threadIdx.x; k < p.D; k += kBlock) amax = fmaxf(amax, fabsf(silu_mul<false>(to_f32<T>(r0 + k), to_f32<T>(r1 + k))));
+  for (int64_t k = threadIdx.x; k < p.D; k += kBlock) amax = fmaxf(amax, fabsf(silu_mul<false>(Elem<T>::load(r0 + k), Elem<T>::load(r1 + k))));
   amax = block_max(amax, s_part);
   float rmax = fmaxf(amax, 1e-12f);
   if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
@@ -212,7 +136,7 @@ __global__ void __launch_bounds__(kBlock) silu_mul_quant_generic_kernel(const Si
   if (threadIdx.x == 0) p.inv_scale[row] = div_full(1.0f, y_scale);
   uint8_t *qr = p.q + row * p.D;
   for (int64_t k = threadIdx.x; k < p.D; k += kBlock) {
-    const float y = silu_mul<false>(to_f32<T>(r0 + k), to_f32<T>(r1 + k));
+    const float y = silu_mul<false>(Elem<T>::load(r0 + k), Elem<T>::load(r1 + k));
     qr[k] = static_cast<uint8_t>(cvt_e4m3x2(__fmul_rn(y, y_scale), 0.f) & 0xffu);
   }
 }
@@ -240,28 +164,6 @@ int launch_typed(const SiluParams &p, bool vec_ok, cudaStream_t st) {
   return check_cuda(cudaGetLastError(), "silu_mul_quant launch");
 }
 
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi);
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
-  return pack_bf16x2(lo, hi);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
-  const __half2 h = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<const uint32_t *>(&h);
-}
-template <typename T>
-__device__ __forceinline__ T from_f32(float v);
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
-  return __float2bfloat16_rn(v);
-}
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) {
-  return __float2half_rn(v);
-}
-
 // y = x0 * sigmoid(x0) * x1 without quantization (the reference's _mslk_silu_mul,
 // mslk/moe/activation.py:181-217): elementwise, output in the input dtype, contiguous [T, D].
 template <typename T, bool kVec>
@@ -275,22 +177,22 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const SiluParams p, T *__
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
       const int64_t row = i / per_row, v = i - row * per_row;
       float f0[8], f1[8];
-      unpack8<T>(ld_stream_v4(x0 + row * p.stride0 + v * 8), f0);
-      unpack8<T>(ld_stream_v4(x1 + row * p.stride1 + v * 8), f1);
+      Elem<T>::unpack8(ld_stream_v4(x0 + row * p.stride0 + v * 8), f0);
+      Elem<T>::unpack8(ld_stream_v4(x1 + row * p.stride1 + v * 8), f1);
       float r[8];
       silu_mul8(f0, f1, r);
       uint4 o;
-      o.x = pack2<T>(r[0], r[1]);
-      o.y = pack2<T>(r[2], r[3]);
-      o.z = pack2<T>(r[4], r[5]);
-      o.w = pack2<T>(r[6], r[7]);
+      o.x = Elem<T>::pack2(r[0], r[1]);
+      o.y = Elem<T>::pack2(r[2], r[3]);
+      o.z = Elem<T>::pack2(r[4], r[5]);
+      o.w = Elem<T>::pack2(r[6], r[7]);
       *reinterpret_cast<uint4 *>(y + row * p.D + v * 8) = o;
     }
   } else {
     const int64_t total = valid * p.D;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += step) {
       const int64_t row = i / p.D, k = i - row * p.D;
-      y[i] = from_f32<T>(silu_mul<false>(to_f32<T>(x0 + row * p.stride0 + k), to_f32<T>(x1 + row * p.stride1 + k)));
+      y[i] = Elem<T>::make(silu_mul<false>(Elem<T>::load(x0 + row * p.stride0 + k), Elem<T>::load(x1 + row * p.stride1 + k)));
     }
   }
 }
