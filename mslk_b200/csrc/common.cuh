@@ -307,6 +307,18 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// The same for rows of 64 bytes with the 64-byte swizzle (TMA box {64 B, rows},
+// CU_TENSOR_MAP_SWIZZLE_64B): 8-row groups are 512 bytes apart; tiles must start on a 512-byte boundary.
+__device__ __forceinline__ uint64_t make_kmajor_sw64_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;                          // SWIZZLE_64B
+  return d;
+}
+
 // Shared-memory descriptor of one 512-byte scale-factor atom (32 rows of 16 bytes, no
 // swizzle: 8-row groups are 128 bytes apart) for tcgen05.cp.
 __device__ __forceinline__ uint64_t make_sf_atom_desc(uint32_t smem_addr) {

@@ -8,7 +8,7 @@
 // kernel ran only 20 % faster.  Scale factors: each
 // CTA needs, in its own tensor memory, the A scales of its own 128 rows and the B scales of ALL 256
 // columns; both CTAs therefore fetch both B scale blocks themselves (4 KB per K block; no load is
-// multicast).  Scale atoms travel as TMA boxes of {512 bytes, 4 atoms} over a 2-D view of the scale
+// multicast).  Scale atoms travel as TMA boxes of {512 bytes, atoms of one stage} over a 2-D view of the scale
 // buffer, so that, like the operand tiles, they can signal the leader's barrier from either CTA.
 //
 //   CTA rank 0 ("leader")                              CTA rank 1
@@ -25,6 +25,8 @@
 
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace mslk_b200 {
 namespace nvfp4_pair {
 namespace {
@@ -32,39 +34,52 @@ namespace {
 constexpr int kBM = 128;                 // rows per CTA
 constexpr int kPairRows = 256;           // rows of the pair tile
 constexpr int kPairBN = 256;             // columns of the pair tile
-constexpr int kBKBytes = 128;            // bytes of packed K per stage row (256 elements)
-constexpr int kBKElems = 256;
 constexpr int kMmaKBytes = 32;           // 64 K-elements per instruction
-constexpr int kAtomBytes = 512;          // 128 rows x 4 scales
+constexpr int kAtomBytes = 512;          // 128 rows x 4 scales = the scales of one instruction
 constexpr int kNumThreads = 192;
-constexpr int kStageA = kBM * kBKBytes;                 // 16 KB
-constexpr int kStageB = (kPairBN / 2) * kBKBytes;       // 16 KB
-constexpr int kStageSFA = 4 * kAtomBytes;               // 2 KB
-constexpr int kStageSFB = 2 * 4 * kAtomBytes;           // 4 KB: both 128-column blocks
-constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
-static_assert(kStageBytes % 1024 == 0, "stages keep the 1024-byte alignment of the swizzled tiles");
-constexpr int kStages = 5;
 constexpr int kAccCols = kPairBN;        // one accumulator
-constexpr int kSfCols = 16 + 32;         // one set of scale columns: A (4 per instruction) + B (8 per instruction)
 constexpr int kSfBase = kAccCols;
-static_assert(kSfBase + 2 * kSfCols <= 512, "tensor memory budget");
 constexpr int kTmemCols = 512;
 constexpr int kBand = 8;                 // 8 x 256 rows per scheduling band
 // block-scaled instruction descriptor: e2m1 x e2m1, ue4m3 scales, K-major, N = 256, M = 256 over the pair
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPairBN >> 3) << 17) | (0u << 23) |
                             (static_cast<uint32_t>(kPairRows >> 4) << 24);
 
+// K extent of a pipeline stage: BK bytes of packed K per row.  Operand arrival from L2 bounds this
+// kernel, so eleven small stages (64-byte rows = 128 elements of K, 64-byte swizzle, two instructions)
+// were tried against five large ones (128-byte rows, four instructions): on 8192^3 the small stages
+// took 387 us against 282 us -- 64-byte row segments use the L2-to-SM path badly -- so 128 is the default.
+template <int BK>
+struct PCfg {
+  static_assert(BK == 64 || BK == 128, "stage rows are 64 or 128 bytes");
+  static constexpr int kBKBytes = BK;
+  static constexpr int kBKElems = 2 * BK;
+  static constexpr int kMmasPerStage = BK / kMmaKBytes;
+  static constexpr int kStageA = kBM * BK;
+  static constexpr int kStageB = (kPairBN / 2) * BK;
+  static constexpr int kStageSFA = kMmasPerStage * kAtomBytes;
+  static constexpr int kStageSFB = 2 * kMmasPerStage * kAtomBytes;   // both 128-column blocks
+  static constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
+  static_assert(kStageBytes % (BK * 8) == 0, "stages keep the alignment of the swizzled tiles");
+  static constexpr int kStages = BK == 128 ? 5 : 11;
+  static constexpr int kSfCols = 12 * kMmasPerStage;   // one set of scale columns: A (4 per instruction) + B (8)
+  static_assert(kSfBase + 2 * kSfCols <= 512, "tensor memory budget");
+};
+
+template <int BK>
 struct SmemTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[PCfg<BK>::kStages];
+  uint64_t empty[PCfg<BK>::kStages];
   uint64_t tmem_full;
   uint64_t tmem_empty;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + sizeof(SmemTail);
-static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+template <int BK>
+constexpr size_t smem_bytes() {
+  return 1024 + static_cast<size_t>(PCfg<BK>::kStages) * PCfg<BK>::kStageBytes + sizeof(SmemTail<BK>);
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &m_tile, int &n_tile) {
   const int per_band = kBand * n_tiles;
@@ -76,13 +91,18 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   m_tile = first_m + (in_band - n_tile * band_m);
 }
 
+template <int BK>
 __global__ void __launch_bounds__(kNumThreads, 1)
     gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                            const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                            const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SmemTail &S = *reinterpret_cast<SmemTail *>(ring + static_cast<size_t>(kStages) * kStageBytes);
+  using C = PCfg<BK>;
+  constexpr int kStages = C::kStages, kStageBytes = C::kStageBytes, kStageA = C::kStageA, kStageB = C::kStageB;
+  constexpr int kStageSFA = C::kStageSFA, kMmasPerStage = C::kMmasPerStage, kSfCols = C::kSfCols;
+  constexpr int kBKBytes = C::kBKBytes, kBKElems = C::kBKElems;
+  SmemTail<BK> &S = *reinterpret_cast<SmemTail<BK> *>(ring + static_cast<size_t>(kStages) * kStageBytes);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -146,9 +166,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * kStageBytes);
           tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBKBytes, a_block * kBM);
           tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBKBytes, n_tile * kPairBN + static_cast<int>(rank) * kBM);
-          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, a_block * p.ncb + 4 * kb);
-          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, (n_tile * 2) * p.ncb + 4 * kb);
-          tma_load_2d_pair(ssfb + 4 * kAtomBytes, &tmap_sfb, leader_full, 0, (n_tile * 2 + 1) * p.ncb + 4 * kb);
+          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, a_block * p.ncb + kMmasPerStage * kb);
+          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, (n_tile * 2) * p.ncb + kMmasPerStage * kb);
+          tma_load_2d_pair(ssfb + kMmasPerStage * kAtomBytes, &tmap_sfb, leader_full, 0,
+                           (n_tile * 2 + 1) * p.ncb + kMmasPerStage * kb);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -182,12 +203,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         const uint32_t ssfa = sa + kStageA + kStageB;
         const uint32_t ssfb = ssfa + kStageSFA;
         const uint32_t sfa_t = tmem_base + kSfBase + buf * kSfCols;
-        const uint32_t sfb_t = sfa_t + 16;
-        const int atoms = min(4, p.ncb - 4 * q.kb);
+        const uint32_t sfb_t = sfa_t + 4 * kMmasPerStage;
+        const int atoms = min(kMmasPerStage, p.ncb - kMmasPerStage * q.kb);
         for (int k = 0; k < atoms; ++k) {
           tc_cp_32x128b_warpx4_pair(sfa_t + 4 * k, make_sf_atom_desc(ssfa + k * kAtomBytes));
           tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k, make_sf_atom_desc(ssfb + k * kAtomBytes));
-          tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k + 4, make_sf_atom_desc(ssfb + (4 + k) * kAtomBytes));
+          tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k + 4, make_sf_atom_desc(ssfb + (kMmasPerStage + k) * kAtomBytes));
         }
       };
       Pos pos{pair_id, 0, 0, 0, 0u};
@@ -219,11 +240,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           tc_fence_after();
         }
         const uint32_t sa = smem_u32(ring + static_cast<size_t>(pos.stage) * kStageBytes);
-        const uint64_t da = make_kmajor_sw128_desc(sa);
-        const uint64_t db = make_kmajor_sw128_desc(sa + kStageA);
+        const uint64_t da = kBKBytes == 128 ? make_kmajor_sw128_desc(sa) : make_kmajor_sw64_desc(sa);
+        const uint64_t db = kBKBytes == 128 ? make_kmajor_sw128_desc(sa + kStageA) : make_kmajor_sw64_desc(sa + kStageA);
         const uint32_t sfa_t = tmem_base + kSfBase + (n & 1) * kSfCols;
-        const uint32_t sfb_t = sfa_t + 16;
-        const int atoms = min(4, p.ncb - 4 * pos.kb);
+        const uint32_t sfb_t = sfa_t + 4 * kMmasPerStage;
+        const int atoms = min(kMmasPerStage, p.ncb - kMmasPerStage * pos.kb);
         for (int k = 0; k < atoms; ++k)
           mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
                          db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), kIdesc, sfa_t + 4 * k, sfb_t + 8 * k,
@@ -304,10 +325,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   }
 }
 
-}  // namespace
-
-int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
-                       cudaStream_t st) {
+template <int BK>
+int launch_bk(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
+              cudaStream_t st) {
+  using C = PCfg<BK>;
+  constexpr size_t kSmemBytes = smem_bytes<BK>();
+  static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
   static int max_pairs[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -326,13 +349,13 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   cfg.numAttrs = 1;
 
   if (max_pairs[dev] == 0) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_pair_kernel<BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(kSmemBytes)),
                             "cudaFuncSetAttribute(gemm_nvfp4_pair)"))
       return rc;
     cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
     int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_nvfp4_pair_kernel, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_nvfp4_pair_kernel<BK>, &cfg);
     if (e != cudaSuccess || n <= 0) {
       cudaGetLastError();
       max_pairs[dev] = -1;
@@ -350,14 +373,28 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   const int64_t kbytes = p.K / 2;
   const uint64_t a_blocks = (static_cast<uint64_t>(p.M) + kBM - 1) / kBM, b_blocks = (static_cast<uint64_t>(p.N) + kBM - 1) / kBM;
   CUtensorMap ta, tb, tsa, tsb;
-  if (int rc = make_tmap_2d_bytes(&ta, xq, kbytes, p.M, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, p.N, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  // scale buffers as [atoms, 128 words]: a box of 4 atoms is the 2 KB of one K block of one 128-row block
-  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, 4)) return rc;
-  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, 4)) return rc;
+  const CUtensorMapSwizzle swz = BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  if (int rc = make_tmap_2d_bytes(&ta, xq, kbytes, p.M, kbytes, BK, kBM, swz)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, p.N, kbytes, BK, kBM, swz)) return rc;
+  // scale buffers as [atoms, 128 words]: a box holds the atoms of one K block of one 128-row block
+  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, C::kMmasPerStage))
+    return rc;
+  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, C::kMmasPerStage))
+    return rc;
 
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel, ta, tb, tsa, tsb, p), "f4f4bf16 pair launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel<BK>, ta, tb, tsa, tsb, p), "f4f4bf16 pair launch");
+}
+
+}  // namespace
+
+int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
+                       cudaStream_t st) {
+  static const int bk = [] {
+    const char *e = getenv("MSLK_B200_NVFP4_PAIR_BK");   // "64" | "128": tuning aid, default 128 (measured faster)
+    return e && atoi(e) == 64 ? 64 : 128;
+  }();
+  return bk == 128 ? launch_bk<128>(xq, wq, x_scale, w_scale, p, st) : launch_bk<64>(xq, wq, x_scale, w_scale, p, st);
 }
 
 }  // namespace nvfp4_pair
