@@ -362,8 +362,9 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   }();
   const int64_t pair_tiles = (m_sizes ? (total_m + 2 * kBM - 1) / (2 * kBM) : G * ((group_m + 2 * kBM - 1) / (2 * kBM))) *
                              ((N + 255) / 256);
-  // grouped problems: pairs pay off only when the average group is several 256-row tiles tall
-  const bool groups_tall = !m_sizes || total_m / G >= 512;
+  // grouped problems run on pairs with swapped operand roles (tokens as the N operand, padded to 16
+  // only), which pays off unless the groups are tiny
+  const bool groups_tall = !m_sizes || total_m / G >= 128;
   const bool want_pair = !p.scatter_idx &&   // the scatter-add epilogue lives in the one-CTA kernel
                          (force == 2 || p.rs_rows > 0 || (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2));
   if (want_pair) {

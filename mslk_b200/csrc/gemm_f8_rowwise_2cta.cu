@@ -22,6 +22,7 @@
 // control path of both CTAs reaches them.
 #include "gemm_f8_common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace mslk_b200 {
@@ -39,8 +40,18 @@ constexpr int kOutSlabBytes = 32 * kOutCols * 2;   // 32 rows x 64 bf16
 constexpr int kOutStageBytes = 4 * 2 * kOutSlabBytes;  // four epilogue warps, double-buffered
 constexpr int kTmemCols = 512;          // two 256-column accumulators
 constexpr int kPairBandM = 8;           // 8 x 256 rows per band, matching 16 x 128 of the 1-CTA kernel
-constexpr uint32_t kIdesc = (1u << 4) | (static_cast<uint32_t>(kPairBN >> 3) << 17) |
-                            (static_cast<uint32_t>(kPairRows >> 4) << 24);
+// instruction descriptor: fp32 accumulate, e4m3 x e4m3, K-major, M = 256 over the pair, N = n
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kPairRows >> 4) << 24);
+}
+constexpr uint32_t kIdesc = make_idesc(kPairBN);
+
+// Swapped operand roles (kSwap), used for grouped problems: the WEIGHT rows are the 256-row M operand
+// of the pair-wide instruction and the tokens of a group are its N operand, whose extent may be any
+// multiple of 16 up to 256.  A ragged group then wastes at most 15 token columns of tensor work
+// instead of up to 255 rows.  The accumulator holds the transposed tile (lane = weight row, column =
+// token), which the epilogue writes back with 2-byte stores that are contiguous across a warp.
+__device__ __forceinline__ int swap_cols(int rows) { return max(32, (rows + 15) / 16 * 16); }
 
 // Tensor maps of the output buffers (own + up to 7 further destinations), box {64 columns, 32 rows}.
 struct OutMaps {
@@ -63,8 +74,10 @@ struct SmemTail {
 constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + kOutStageBytes + sizeof(SmemTail);
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 
+template <bool kSwap>
 __global__ void __launch_bounds__(kNumThreads, 1)
     gemm_f8_rowwise_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                const __grid_constant__ CUtensorMap tmap_a32, const __grid_constant__ CUtensorMap tmap_a64,
                                 const __grid_constant__ OutMaps ymaps, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -85,6 +98,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    if (kSwap) {
+      prefetch_tensormap(&tmap_a32);
+      prefetch_tensormap(&tmap_a64);
+    }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&S.full[s], 1);
       mbar_init(&S.empty[s], 1);
@@ -126,9 +143,21 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           uint8_t *sa = ring + static_cast<size_t>(stage) * kStageBytes;
           uint8_t *sb = sa + kStageA;
           const uint32_t leader_full = mapa_u32(smem_u32(&S.full[stage]), 0);
-          if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * kStageBytes);
-          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBK, t.row0 + static_cast<int>(rank) * kBM);
-          tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBK, t.wrow0 + static_cast<int>(rank) * (kPairBN / 2));
+          if (kSwap) {
+            // weights -> M operand (this CTA's 128 of the tile's 256 weight rows); tokens -> N operand
+            // (this CTA's half of the tile's token columns, fetched with the smallest box of 32 / 64 / 128
+            // rows that holds it: a short tile is bound by its loads, not by its instructions)
+            const int half = swap_cols(t.rows) / 2;
+            const int box = half <= 32 ? 32 : (half <= 64 ? 64 : 128);
+            const CUtensorMap *tok = half <= 32 ? &tmap_a32 : (half <= 64 ? &tmap_a64 : &tmap_a);
+            if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * (kStageA + box * kBK));
+            tma_load_2d_pair(sa, &tmap_b, leader_full, kb * kBK, t.wrow0 + static_cast<int>(rank) * kBM);
+            tma_load_2d_pair(sb, tok, leader_full, kb * kBK, t.row0 + static_cast<int>(rank) * half);
+          } else {
+            if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * kStageBytes);
+            tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBK, t.row0 + static_cast<int>(rank) * kBM);
+            tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBK, t.wrow0 + static_cast<int>(rank) * (kPairBN / 2));
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -154,6 +183,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairBN);
+        const uint32_t idesc = kSwap ? make_idesc(swap_cols(t.rows)) : kIdesc;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
             ok = false;
@@ -166,7 +196,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             mma_f8f6f4_pair(d_tmem, da + static_cast<uint64_t>(k * (kUmmaK >> 4)),
-                            db + static_cast<uint64_t>(k * (kUmmaK >> 4)), kIdesc, (kb | k) != 0 ? 1u : 0u);
+                            db + static_cast<uint64_t>(k * (kUmmaK >> 4)), idesc, (kb | k) != 0 ? 1u : 0u);
           }
           // free the stage in both CTAs once these MMAs have read it
           const uint32_t e = smem_u32(&S.empty[stage]);
@@ -197,6 +227,58 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     for (int tile = pair_id; sched.get(tile, t); tile += num_pairs, ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      if (kSwap) {
+        // transposed tile: lane = weight row, columns = the tile's tokens
+        const int nt = swap_cols(t.rows);
+        const int n_local = static_cast<int>(rank) * kBM + row_in_cta;
+        const bool n_ok = t.n0 + n_local < p.N;
+        const float wsc = n_ok ? p.w_scale[t.ws0 + n_local] : 0.f;
+        float *xs_s = S.w_scale[warp - 2];   // this warp's buffer: the row scales of the tile's tokens
+        for (int c = lane; c < nt; c += 32) xs_s[c] = c < t.rows ? p.x_scale[t.row0 + c] : 0.f;
+        __syncwarp();
+        const bool got = mbar_wait(&S.tmem_full[acc], acc_phase, abort_flag, p.status, kStatusEpilogueTimeout);
+        if (!__all_sync(0xffffffffu, got)) break;
+        tc_fence_after();
+        const uint32_t taddr =
+            tmem_base + static_cast<uint32_t>(acc * kPairBN) + (static_cast<uint32_t>(quad * 32) << 16);
+        __nv_bfloat16 *ycol = p.y + static_cast<size_t>(t.row0) * p.ldy + p.col0 + t.n0 + n_local;
+        const int warp_n0 = t.n0 + static_cast<int>(rank) * kBM + quad * 32;   // first weight row of this warp
+        uint8_t *bufs = out_stage + (warp - 2) * 2 * kOutSlabBytes;
+#pragma unroll 1
+        for (int c = 0; c * 32 < t.rows; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (p.tma_store && c * 32 + 32 <= t.rows && warp_n0 + 32 <= p.N) {
+            // whole 32-token x 32-column block: transpose through shared memory (row = token, 64 bytes),
+            // one TMA store of 2 KB
+            uint8_t *buf = bufs + (slab_seq++ & 1) * kOutSlabBytes;
+            if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done with it
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              *reinterpret_cast<__nv_bfloat16 *>(buf + j * 64 + lane * 2) =
+                  __float2bfloat16_rn((__uint_as_float(r[j]) * xs_s[c * 32 + j]) * wsc);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&ymaps.m[1], buf, p.col0 + warp_n0, t.row0 + c * 32);
+              tma_store_commit();
+            }
+          } else if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int token = c * 32 + j;
+              if (token < t.rows)
+                ycol[static_cast<size_t>(token) * p.ldy] = __float2bfloat16_rn((__uint_as_float(r[j]) * xs_s[token]) * wsc);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty[acc]), 0));
+        continue;
+      }
       float *ws_s = S.w_scale[warp - 2];
       float *bs_s = S.bias[warp - 2];
       for (int c = lane; c < kPairBN; c += 32) {
@@ -312,15 +394,16 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
   cfg.numAttrs = 1;
 
   if (max_pairs[dev] == 0) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_f8_rowwise_pair_kernel,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 static_cast<int>(kSmemBytes)),
-                            "cudaFuncSetAttribute(gemm_f8_rowwise_pair)"))
-      return rc;
+    for (const void *fn : {reinterpret_cast<const void *>(gemm_f8_rowwise_pair_kernel<false>),
+                           reinterpret_cast<const void *>(gemm_f8_rowwise_pair_kernel<true>)})
+      if (int rc = check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   static_cast<int>(kSmemBytes)),
+                              "cudaFuncSetAttribute(gemm_f8_rowwise_pair)"))
+        return rc;
     // how many CTA pairs the device can hold at once: a persistent kernel must not launch more
     cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
     int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_f8_rowwise_pair_kernel, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_f8_rowwise_pair_kernel<false>, &cfg);
     if (e != cudaSuccess || n <= 0) {
       cudaGetLastError();
       max_pairs[dev] = -1;
@@ -336,8 +419,10 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
                            ((p.N + kPairBN - 1) / kPairBN);
   const int pairs = static_cast<int>(tiles_ub < max_pairs[dev] ? tiles_ub : max_pairs[dev]);
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, ta32, ta64;
   if (int rc = make_tmap_2d_bytes(&ta, xq, p.K, p.total_m, p.K, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&ta32, xq, p.K, p.total_m, p.K, kBK, 32, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&ta64, xq, p.K, p.total_m, p.K, kBK, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d_bytes(&tb, wq, p.K, static_cast<uint64_t>(p.G) * p.N, p.K, kBK, kPairBN / 2,
                                   CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
@@ -366,7 +451,27 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
     return fail(1, "row-scatter GEMM needs 16-byte aligned buffers, N %% 64 == 0 and rows per rank %% 32 == 0");
 
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel, ta, tb, ymaps, q),
+  // grouped problems (ragged token counts) run with swapped operand roles
+  static const int swap_env = [] {
+    const char *e = getenv("MSLK_B200_GROUPED_SWAP");   // "0" | "1": tuning aid, default = heuristic
+    return !e ? -1 : (e[0] == '1' ? 1 : 0);
+  }();
+  // measured on E = 8 ... 128 experts: a gain of 16-19 % at a mean of 256 tokens per group, break-even near 1024,
+  // a loss of 7 % at 4096 (the transposed epilogue costs more than the padding it saves)
+  bool swap = q.m_sizes != nullptr && q.bias_kind == MSLK_B200_BIAS_NONE && q.n_extra == 0 && q.rs_rows == 0;
+  if (swap) swap = swap_env >= 0 ? swap_env == 1 : q.total_m / q.G < 2048;
+  if (swap) {
+    // its epilogue stores 32-token x 32-column blocks: box {32 columns = 64 bytes, 32 rows}, no swizzle, in map slot 1
+    q.tma_store = (q.ldy % 8 == 0) && (q.col0 % 8 == 0) && (reinterpret_cast<uintptr_t>(q.y) & 15u) == 0;
+    if (q.tma_store)
+      if (int rc = make_tmap_2d_bf16(&ymaps.m[1], q.y, q.ldy, q.total_m, static_cast<uint64_t>(q.ldy) * 2, 32, 32,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE))
+        return rc;
+  }
+  if (swap)
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel<true>, ta, tb, ta32, ta64, ymaps, q),
+                      "f8f8bf16_rowwise pair launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel<false>, ta, tb, ta32, ta64, ymaps, q),
                     "f8f8bf16_rowwise pair launch");
 }
 
