@@ -110,7 +110,7 @@ def test_empty_dims_and_errors(ops):
 
 
 def test_linearity_in_scales_full_size(ops):
-    # size-independent property at a BASELINE size: doubling x_scale doubles y exactly (power of two),
+    # size-independent property at a full benchmark size: doubling x_scale doubles y exactly (power of two),
     # and the result matches the fp32 formula on a sampled set of rows
     M, N, K = 8192, 8192, 8192
     xq, wq, xs, ws = _quant(ops, M, N, K, seed=4)

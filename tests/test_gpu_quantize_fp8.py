@@ -123,7 +123,7 @@ def test_empty_and_errors(ops):
 
 
 def test_full_size_properties(ops):
-    # size-independent properties at a BASELINE size: round trip within the reference's own
+    # size-independent properties at a full benchmark size: round trip within the reference's own
     # tolerance (test/quantize/fp8_quantize_correctness_test.py:119-124), every row hits +-448
     a = randn_bf16((8192, 8192), 13).cuda()
     q, s = ops.quantize_fp8_row(a)
