@@ -365,7 +365,8 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   // grouped problems run on pairs with swapped operand roles (tokens as the N operand, padded to 16
   // only), which pays off unless the groups are tiny
   const bool groups_tall = !m_sizes || total_m / G >= 128;
-  const bool want_pair = !p.scatter_idx &&   // the scatter-add epilogue lives in the one-CTA kernel
+  // scatter-add epilogue: in the pair kernel for grouped problems with swapped roles, else in this file's kernel
+  const bool want_pair = (!p.scatter_idx || (m_sizes && total_m / G < 2048)) &&
                          (force == 2 || p.rs_rows > 0 || (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2));
   if (want_pair) {
     const int rc = launch_pair_kernel(xq, wq, p, st);

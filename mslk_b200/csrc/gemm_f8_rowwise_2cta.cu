@@ -249,7 +249,40 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           uint32_t r[32];
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
-          if (p.tma_store && c * 32 + 32 <= t.rows && warp_n0 + 32 <= p.N) {
+          if (p.scatter_idx) {
+            // fused combine: the block is transposed through shared memory, then lane l owns token
+            // c*32 + l and ADDS its 32 columns (64 bytes) to row scatter_idx[token] of y
+            uint8_t *buf = bufs + (slab_seq++ & 1) * kOutSlabBytes;
+            __syncwarp();   // the lanes are done reading the block staged two chunks ago
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              *reinterpret_cast<__nv_bfloat16 *>(buf + j * 64 + lane * 2) =
+                  __float2bfloat16_rn((__uint_as_float(r[j]) * xs_s[c * 32 + j]) * wsc);
+            __syncwarp();
+            const int token = c * 32 + lane;
+            if (token < t.rows) {
+              const long long dst = p.scatter_bits == 64
+                                        ? static_cast<const long long *>(p.scatter_idx)[t.row0 + token]
+                                        : static_cast<long long>(static_cast<const int *>(p.scatter_idx)[t.row0 + token]);
+              if (dst < 0 || dst >= p.scatter_rows) {
+                atomicOr(p.status, kStatusBadScatterIndex);   // reported, not followed
+              } else {
+                __nv_bfloat16 *yrow = p.y + static_cast<size_t>(dst) * p.ldy + p.col0 + warp_n0;
+                if (p.tma_store && warp_n0 + 32 <= p.N) {   // 16-byte aligned destination, whole block in range
+#pragma unroll
+                  for (int q4 = 0; q4 < 4; ++q4) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(buf + lane * 64 + q4 * 16);
+                    asm volatile("red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(yrow + 8 * q4),
+                                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                                 : "memory");
+                  }
+                } else {
+                  for (int j = 0; j < 32 && warp_n0 + j < p.N; ++j)
+                    atomicAdd(yrow + j, *reinterpret_cast<const __nv_bfloat16 *>(buf + lane * 64 + j * 2));
+                }
+              }
+            }
+          } else if (p.tma_store && c * 32 + 32 <= t.rows && warp_n0 + 32 <= p.N) {
             // whole 32-token x 32-column block: transpose through shared memory (row = token, 64 bytes),
             // one TMA store of 2 KB
             uint8_t *buf = bufs + (slab_seq++ & 1) * kOutSlabBytes;
@@ -459,7 +492,11 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
   // measured on E = 8 ... 128 experts: a gain of 16-19 % at a mean of 256 tokens per group, break-even near 1024,
   // a loss of 7 % at 4096 (the transposed epilogue costs more than the padding it saves)
   bool swap = q.m_sizes != nullptr && q.bias_kind == MSLK_B200_BIAS_NONE && q.n_extra == 0 && q.rs_rows == 0;
-  if (swap) swap = swap_env >= 0 ? swap_env == 1 : q.total_m / q.G < 2048;
+  if (q.scatter_idx) {
+    if (!swap) return -1;   // the scatter-add epilogue of this kernel exists for swapped roles only
+  } else if (swap) {
+    swap = swap_env >= 0 ? swap_env == 1 : q.total_m / q.G < 2048;
+  }
   if (swap) {
     // its epilogue stores 32-token x 32-column blocks: box {32 columns = 64 bytes, 32 rows}, no swizzle, in map slot 1
     q.tma_store = (q.ldy % 8 == 0) && (q.col0 % 8 == 0) && (reinterpret_cast<uintptr_t>(q.y) & 15u) == 0;

@@ -154,9 +154,16 @@ def bench_grouped(ops, E, tokens, N, K, args):
     ms = counts.to(torch.int64).cuda()
     sec = _time(lambda i: ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws.view(-1), ms), 1, args.iters,
                 args.warmup, args.graph)
+    # the same product with the combine fused in: rows added to a top-2 style destination
+    g = torch.Generator(device="cuda").manual_seed(1)
+    idx = (torch.randperm(tokens, generator=g, device="cuda") % max(tokens // 2, 1)).to(torch.int32)
+    acc = torch.zeros((max(tokens // 2, 1), N), dtype=torch.bfloat16, device="cuda")
+    sec_sc = _time(lambda i: ops.f8f8bf16_rowwise_grouped_stacked_scatter_add(xq, wq, xs, ws.view(-1), ms, acc, idx), 1,
+                   args.iters, args.warmup, args.graph)
     flops = 2.0 * tokens * N * K
     return {"op": "f8f8bf16_rowwise_grouped_stacked", "E": E, "tokens": tokens, "N": N, "K": K,
-            "counts": counts.tolist(), "us": sec * 1e6, "TFLOPs": flops / sec / 1e12}
+            "counts": counts.tolist(), "us": sec * 1e6, "TFLOPs": flops / sec / 1e12,
+            "with_scatter_add_us": sec_sc * 1e6, "with_scatter_add_TFLOPs": flops / sec_sc / 1e12}
 
 
 def bench_f4f4bf16_grouped(ops, E, tokens, N, K, args):

@@ -343,6 +343,8 @@ def test_batched_output_argument_empty_dims_and_errors(ops):
     (8, [64] * 8, 256, 1024, 2),
     (4, [3, 0, 5, 1], 72, 128, 1),           # narrow, element-wise atomics for the ragged column tail
     (16, [256] * 16, 1024, 512, 4),
+    (16, [512] * 16, 2048, 512, 1),          # enough 256 x 256 tiles for CTA pairs (swapped roles, vector reductions)
+    (12, [300, 700, 0, 256, 1, 511, 512, 513, 40, 1000, 64, 900], 2304, 256, 2),
 ])
 def test_grouped_scatter_add_epilogue(ops, G, m_sizes, N, K, topk):
     # mslk/gemm/triton/grouped_gemm.py:386-402: product row r is added to output[indices[r]]
