@@ -338,8 +338,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             uint4 *d4 = reinterpret_cast<uint4 *>(dst);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              d4[j] = make_uint4(packed[c * 16 + 4 * j], packed[c * 16 + 4 * j + 1], packed[c * 16 + 4 * j + 2],
-                                 packed[c * 16 + 4 * j + 3]);
+              __stcs(d4 + j, make_uint4(packed[c * 16 + 4 * j], packed[c * 16 + 4 * j + 1], packed[c * 16 + 4 * j + 2],
+                                        packed[c * 16 + 4 * j + 3]));   // streaming: the output must not evict the operands from L2
           } else if (cols_left > 0) {
             uint16_t *d = reinterpret_cast<uint16_t *>(dst);
 #pragma unroll
@@ -424,7 +424,8 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
     return !e ? 0 : (e[0] == '2' ? 2 : 1);
   }();
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  if (!grouped && (force == 2 || (force == 0 && pair_tiles >= sms / 2))) {
+  // (few-token shapes stay on one CTA per tile: a 256-row pair tile would be mostly padding)
+  if (!grouped && (force == 2 || (force == 0 && M > 128 && pair_tiles >= sms / 2))) {
     nvfp4_pair::PairParams pp{global_scale, static_cast<__nv_bfloat16 *>(y), status, static_cast<int>(M),
                               static_cast<int>(N), static_cast<int>(K), static_cast<int>((K + 63) / 64)};
     const int rc = nvfp4_pair::launch_pair_kernel(xq, wq, x_scale, w_scale, pp, st);

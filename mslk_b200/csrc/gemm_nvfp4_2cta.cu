@@ -302,8 +302,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             uint4 *d4 = reinterpret_cast<uint4 *>(dst);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              d4[j] = make_uint4(packed[c * 16 + 4 * j], packed[c * 16 + 4 * j + 1], packed[c * 16 + 4 * j + 2],
-                                 packed[c * 16 + 4 * j + 3]);
+              __stcs(d4 + j, make_uint4(packed[c * 16 + 4 * j], packed[c * 16 + 4 * j + 1], packed[c * 16 + 4 * j + 2],
+                                        packed[c * 16 + 4 * j + 3]));   // streaming: the output must not evict the operands from L2
           } else if (cols_left > 0) {
             uint16_t *d = reinterpret_cast<uint16_t *>(dst);
 #pragma unroll
