@@ -104,24 +104,35 @@ __global__ void __launch_bounds__(kMaxThreads) gather_scale_quant_vec_kernel(con
     const int v = threadIdx.x + i * nthreads;
     raw[i] = v < nvec ? ld_stream_v4(src + static_cast<int64_t>(v) * 8) : make_uint4(0, 0, 0, 0);
   }
-  float y[kVecs][8];
-  float amax = 0.f;
+  // Row maximum of |x * score|: rounding is monotone, so it is |fl(max|x| * score)|; the packed inputs
+  // stay in registers (16 instead of 32 per thread) and the products are formed again when they are stored.
+  float xmax = 0.f;
 #pragma unroll
-  for (int i = 0; i < kVecs; ++i) {
-    float f[8];
-    Elem<T>::unpack8(raw[i], f);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      y[i][j] = __fmul_rn(f[j], score);
-      amax = fmaxf(amax, fabsf(y[i][j]));
-    }
-  }
-  amax = block_max(amax, s_part);
+  for (int i = 0; i < kVecs; ++i) xmax = fmaxf(xmax, Elem<T>::absmax8(raw[i]));
+  const float amax = block_max(fabsf(__fmul_rn(xmax, score)), s_part);
   float rmax = fmaxf(amax, 1e-12f);
   if (p.scale_ub) rmax = fminf(rmax, *p.scale_ub);
   const float out_scale = div_full(448.0f, rmax);
   if (threadIdx.x == 0) p.inv_scale[row] = div_full(1.0f, out_scale);
-  store_row_e4m3<kVecs>(y, out_scale, static_cast<uint8_t *>(p.out) + row * p.D, nvec, nthreads);
+  uint8_t *qr = static_cast<uint8_t *>(p.out) + row * p.D;
+#pragma unroll
+  for (int i = 0; i < kVecs; ++i) {
+    const int v = threadIdx.x + i * nthreads;
+    if (v < nvec) {
+      float f[8];
+      Elem<T>::unpack8(raw[i], f);
+      uint32_t o[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = cvt_e4m3x2(__fmul_rn(__fmul_rn(f[4 * h], score), out_scale),
+                                       __fmul_rn(__fmul_rn(f[4 * h + 1], score), out_scale));
+        const uint32_t hi = cvt_e4m3x2(__fmul_rn(__fmul_rn(f[4 * h + 2], score), out_scale),
+                                       __fmul_rn(__fmul_rn(f[4 * h + 3], score), out_scale));
+        o[h] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint2 *>(qr + static_cast<int64_t>(v) * 8) = make_uint2(o[0], o[1]);
+    }
+  }
 }
 
 // Any D / alignment: two passes over the source row.

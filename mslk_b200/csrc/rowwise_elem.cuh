@@ -43,6 +43,14 @@ struct Elem<__nv_bfloat16> {
       f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
     }
   }
+  // max |element| of the 8 packed values (exact: abs and max do not round)
+  static __device__ __forceinline__ float absmax8(const uint4 &v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    __nv_bfloat162 m = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
+#pragma unroll
+    for (int i = 1; i < 4; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+    return fmaxf(__bfloat162float(m.x), __bfloat162float(m.y));
+  }
   static __device__ __forceinline__ uint32_t pack2(float lo, float hi) { return pack_bf16x2(lo, hi); }
   static __device__ __forceinline__ float load(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
   static __device__ __forceinline__ __nv_bfloat16 make(float v) { return __float2bfloat16_rn(v); }
@@ -57,6 +65,13 @@ struct Elem<__half> {
       f[2 * i] = p.x;
       f[2 * i + 1] = p.y;
     }
+  }
+  static __device__ __forceinline__ float absmax8(const uint4 &v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    __half2 m = __habs2(*reinterpret_cast<const __half2 *>(&w[0]));
+#pragma unroll
+    for (int i = 1; i < 4; ++i) m = __hmax2(m, __habs2(*reinterpret_cast<const __half2 *>(&w[i])));
+    return fmaxf(__low2float(m), __high2float(m));
   }
   static __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
