@@ -119,17 +119,47 @@ def make_inputs(device, seed):
     return layers
 
 
-def run_step(ops, layers, outs, ev=None):
-    """One pass of the hot path.  With `ev`, CUDA events bracket every kernel launch."""
+def run_step(ops, layers, outs, ev=None, side=None, prev_done=None):
+    """One pass of the hot path.  With `ev`, CUDA events bracket every kernel launch.
+
+    With `side` (a second CUDA stream) the HBM-bound quantize kernels run there and the tensor-bound
+    GEMMs on the current stream, each GEMM waiting for its own input only: a quantize CTA fits on an SM
+    beside the persistent GEMM CTA, so the quantization of projection i+1 overlaps the GEMM of
+    projection i.  `prev_done` (events of the previous step's GEMMs) keeps the side stream at most one
+    step ahead.  Returns the GEMM-done events of this step."""
+    main = torch.cuda.current_stream()
+    done = []
     for i, L in enumerate(layers):
-        if ev is not None:
-            ev[i][0].record()
-        xq, xs = ops.quantize_fp8_row(L["x"])
-        if ev is not None:
-            ev[i][1].record()
-        ops.f8f8bf16_rowwise_out(xq, L["wq"], xs, L["ws"], outs[i])
+        if side is None:
+            if ev is not None:
+                ev[i][0].record()
+            xq, xs = ops.quantize_fp8_row(L["x"])
+            if ev is not None:
+                ev[i][1].record()
+        else:
+            with torch.cuda.stream(side):
+                if prev_done is not None:
+                    side.wait_event(prev_done[i])
+                if ev is not None:
+                    ev[i][0].record(side)
+                xq, xs = ops.quantize_fp8_row(L["x"])
+                if ev is not None:
+                    ev[i][1].record(side)
+                ready = torch.cuda.Event()
+                ready.record(side)
+            xq.record_stream(main)
+            xs.record_stream(main)
+            main.wait_event(ready)
         if ev is not None:
             ev[i][2].record()
+        ops.f8f8bf16_rowwise_out(xq, L["wq"], xs, L["ws"], outs[i])
+        if ev is not None:
+            ev[i][3].record()
+        if side is not None:
+            d = torch.cuda.Event()
+            d.record()
+            done.append(d)
+    return done
 
 
 def cpu_reference_step(sample):
@@ -176,6 +206,8 @@ def base_line(args, world):
         "config": {"workload": "llama3-8b layer projections, M=8192 tokens per GPU: quantize_fp8_row + "
                                "f8f8bf16_rowwise for (N,K) in (6144,4096),(4096,4096),(28672,4096),(4096,14336)",
                    "tokens_per_gpu": M_TOKENS, "parallelism": f"replicas x{world} (no collective)",
+                   "streams": ("2: quantize kernels on a side stream overlap the previous projection's GEMM"
+                               if getattr(args, "streams", 1) == 2 else "1"),
                    "l2": "per-step working set (0.44 GB activations + 0.22 GB weights + 0.7 GB outputs) exceeds the 126 MB L2"},
     }
 
@@ -222,18 +254,23 @@ def run_ours(args, rank, world, local_rank):
 
     sampler = ClockSampler(local_rank)
     sampler.start()          # before the warm-up: nvidia-smi needs a moment to deliver its first sample
+    side = torch.cuda.Stream(device=device) if args.streams == 2 else None
+    prev = None
     for _ in range(max(args.warmup, 3)):
-        run_step(ops, layers, outs)
+        prev = run_step(ops, layers, outs, None, side, prev)
     barrier()
 
     # ---- timed region: K steps, CUDA events on the launching stream, events around every launch
-    ev = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in layers] for _ in range(args.steps)]
+    ev = [[[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in layers] for _ in range(args.steps)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record()
+    prev = None
+    if side is not None:
+        side.wait_event(start)
     for s in range(args.steps):
-        run_step(ops, layers, outs, ev[s])
-    stop.record()
+        prev = run_step(ops, layers, outs, ev[s], side, prev)
+    stop.record()      # the last GEMM waited for every quantize kernel, so this closes both streams
     barrier()
     clocks = sampler.stop()
     ms = start.elapsed_time(stop)
@@ -245,7 +282,7 @@ def run_ours(args, rank, world, local_rank):
         raise RuntimeError("a kernel reported a pipeline timeout during the timed region")
 
     q_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) / args.steps for i in range(len(layers))]
-    g_ms = [sum(ev[s][i][1].elapsed_time(ev[s][i][2]) for s in range(args.steps)) / args.steps for i in range(len(layers))]
+    g_ms = [sum(ev[s][i][2].elapsed_time(ev[s][i][3]) for s in range(args.steps)) / args.steps for i in range(len(layers))]
 
     # ---- end to end through the public API with host buffers (pinned), copies inside the timed region
     e2e = None
@@ -366,6 +403,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--streams", type=int, choices=[1, 2], default=1,
+                    help="2: quantize kernels on a side stream, overlapping the previous projection's GEMM "
+                         "(+2 %% throughput measured; the per-kernel GEMM intervals then include the shared time)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
