@@ -32,6 +32,10 @@ struct GemmParams {
   // Alternative to m_sizes: int32 END offsets of the groups in the stacked rows (device, [G]);
   // group g owns rows [end_offsets[g-1], end_offsets[g]).  Takes precedence when set.
   const int32_t *end_offsets = nullptr;
+  // Rows of the A (token) box of the one-CTA kernel's tensor map: 128, or fewer for a dense problem with
+  // fewer rows, so that TMA neither fetches nor zero-fills rows that do not exist (the instruction still
+  // reads 128 rows of shared memory; what the extra rows hold only reaches masked output rows).
+  int a_box_rows = 128;
   // Scatter-add epilogue (MoE combine fused into the grouped GEMM): when set, stacked row r of the
   // product is ADDED atomically (bf16 vector reductions) to row scatter_idx[r] of y, which then has
   // scatter_rows rows; indices are 32- or 64-bit integers on the device.

@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           }
           uint8_t *sa = ring + static_cast<size_t>(stage) * Cfg::kStageBytes;
           uint8_t *sb = sa + Cfg::kStageA;
-          mbar_arrive_expect_tx(&S.full[stage], Cfg::kStageBytes);
+          mbar_arrive_expect_tx(&S.full[stage], p.a_box_rows * kBK + Cfg::kStageB);
           tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBK, t.row0);
           tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBK, t.wrow0);
           ++issued;
@@ -375,7 +375,8 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   }
 
   CUtensorMap ta, tb;
-  if (int rc = make_tmap_2d_bytes(&ta, xq, K, total_m, K, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (!m_sizes && G == 1 && total_m < kBM) p.a_box_rows = static_cast<int>((total_m + 7) / 8 * 8);
+  if (int rc = make_tmap_2d_bytes(&ta, xq, K, total_m, K, kBK, p.a_box_rows, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d_bytes(&tb, wq, K, G * N, K, kBK, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
 
   const int64_t tiles_ub = m_tiles_ub * ((N + bn - 1) / bn);

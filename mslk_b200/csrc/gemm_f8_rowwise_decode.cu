@@ -21,6 +21,8 @@
 // (thread = weight row).  All pipeline waits are bounded (common.cuh).
 #include "gemm_f8_common.cuh"
 
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 namespace mslk_b200 {
@@ -262,16 +264,30 @@ int launch_decode(const CUtensorMap &tw, const CUtensorMap &tx, const DecodePara
 
 int decode_token_tile(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128; }
 
-// Number of K splits for a decode-shaped problem: enough CTAs for about two per SM, each
-// split keeping at least four K blocks.
+// Number of K splits for a decode-shaped problem.  Two CTAs fit on an SM; the launch costs
+// waves(s) * (K blocks per split + a fixed per-CTA overhead of about three K blocks), waves(s) =
+// ceil(tiles * s / (2 * SMs)): a split count that leaves a mostly empty last wave (e.g. 224 tiles
+// x 2 splits on 296 slots) is worse than none.  Each split keeps at least two K blocks.
 int decode_splits(int64_t N, int64_t K, int sms) {
+  static const int forced = [] {
+    const char *e = getenv("MSLK_B200_DECODE_SPLITS");   // tuning aid
+    return e ? atoi(e) : 0;
+  }();
   const int64_t n_tiles = (N + kWRows - 1) / kWRows;
   const int64_t k_blocks = (K + kBK - 1) / kBK;
-  int64_t s = (2 * sms + n_tiles - 1) / n_tiles;
-  if (s > k_blocks / 4) s = k_blocks / 4;
-  if (s > 32) s = 32;
-  if (s < 1) s = 1;
-  return static_cast<int>(s);
+  const int64_t slots = 2 * static_cast<int64_t>(sms);
+  const int64_t s_max = std::max<int64_t>(1, std::min<int64_t>(32, k_blocks / 2));
+  if (forced > 0) return static_cast<int>(std::min<int64_t>(forced, s_max));
+  int64_t best = 1, best_cost = -1;
+  for (int64_t s = 1; s <= s_max; ++s) {
+    const int64_t waves = (n_tiles * s + slots - 1) / slots;
+    const int64_t cost = waves * ((k_blocks + s - 1) / s + 3);
+    if (best_cost < 0 || cost < best_cost) {
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return static_cast<int>(best);
 }
 
 size_t decode_scratch_bytes(int64_t M, int64_t N, int64_t K, int sms) {

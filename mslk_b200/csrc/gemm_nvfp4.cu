@@ -60,6 +60,7 @@ struct Fp4Params {
   const int64_t *sfa_row_start;    // may be null: groups then follow each other, each padded to 128 rows
   int G;
   int alpha_per_group;
+  int a_box_rows;       // rows of the A box: 128, or fewer for a dense problem with fewer rows (no out-of-range fill)
 };
 
 template <int BN>
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
           int nb_live = 0;  // 128-row blocks of B that exist for this tile
           for (int b = 0; b < C::kNB; ++b) nb_live += (n_tile * C::kNB + b) < n_row_blocks_b ? 1 : 0;
-          mbar_arrive_expect_tx(&S.full[stage], C::kStageA + C::kStageB + sf_bytes * (1 + nb_live));
+          mbar_arrive_expect_tx(&S.full[stage], p.a_box_rows * kBKBytes + C::kStageB + sf_bytes * (1 + nb_live));
           tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBKBytes, t.row0);
           tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBKBytes, t.wrow0);
           bulk_load_1d(ssfa, p.sfa + (static_cast<size_t>(sfa_block) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
@@ -415,6 +416,7 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   p.sfa_row_start = sfa_row_start;
   p.G = static_cast<int>(G);
   p.alpha_per_group = grouped ? 1 : 0;
+  p.a_box_rows = (!grouped && M < kBM) ? static_cast<int>((M + 7) / 8 * 8) : kBM;
 
   const int sms = sm_count();
   // CTA pairs (256 x 256 tiles, a third less shared-memory traffic per flop) for dense problems with
@@ -437,7 +439,7 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   int bn = (m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
   if (const char *e = getenv("MSLK_B200_NVFP4_BN")) bn = atoi(e) == 128 ? 128 : 256;  // tuning aid
   CUtensorMap ta, tb;
-  if (int rc = make_tmap_2d_bytes(&ta, xq, K / 2, M, K / 2, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&ta, xq, K / 2, M, K / 2, kBKBytes, p.a_box_rows, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d_bytes(&tb, wq, K / 2, G * N, K / 2, kBKBytes, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   const int64_t tiles = m_tiles * ((N + bn - 1) / bn);
   const int grid = static_cast<int>(tiles < sms ? tiles : sms);

@@ -2,6 +2,7 @@
 
     python -m mslk_b200.microbench quantize_fp8_row --shape 8192,4096
     python -m mslk_b200.microbench f8f8bf16_rowwise --shape 8192,8192,8192
+    python -m mslk_b200.microbench decode --graph                            # M = 1, 16, 32: general vs split-K kernel
     python -m mslk_b200.microbench batched --shape 8,2048,4096,4096          # B,M,N,K
     python -m mslk_b200.microbench grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
     python -m mslk_b200.microbench f4f4bf16_grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
@@ -135,6 +136,29 @@ def bench_batched(ops, B, M, N, K, args):
             "loop_over_dense_TFLOPs": flops / sec_loop / 1e12}
 
 
+def bench_decode(ops, M, N, K, args):
+    """Few-token GEMM: the general kernel against the split-K weight-streaming kernel (caller-provided workspace)."""
+    from ._lib import check, lib
+    nv = _variants(N * K, args.rotate_mb)
+    xq, xs = ops.quantize_fp8_row(_randn((M, K)))
+    ws = [ops.quantize_fp8_row(_randn((N, K), args.w_std)) for _ in range(nv)]
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    sec = _time(lambda i: ops.f8f8bf16_rowwise_out(xq, ws[i][0], xs, ws[i][1], y), nv, args.iters, args.warmup, args.graph)
+    nbytes = lib.mslk_b200_f8f8bf16_rowwise_workspace_bytes(M, N, K)
+    work = torch.zeros((max(nbytes, 16),), dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream
+
+    def split(i):
+        check(lib.mslk_b200_f8f8bf16_rowwise_ws(xq.data_ptr(), ws[i][0].data_ptr(), xs.data_ptr(), ws[i][1].data_ptr(), None,
+                                                0, y.data_ptr(), M, N, K, work.data_ptr(), nbytes, stream().cuda_stream),
+              "f8f8bf16_rowwise_ws")
+    sec_ws = _time(split, nv, args.iters, args.warmup, args.graph)
+    byts = N * K + M * K + 2.0 * M * N
+    return {"op": "f8f8bf16_rowwise few tokens", "M": M, "N": N, "K": K, "general_us": sec * 1e6,
+            "general_GBps": byts / sec / 1e9, "split_k_us": sec_ws * 1e6, "split_k_GBps": byts / sec_ws / 1e9,
+            "workspace_bytes": nbytes}
+
+
 def zipf_counts(experts, tokens, seed=0, s=1.2, n_empty=2):
     """Per-expert token counts: top-1 routing with Zipf(s) expert popularity, the `n_empty` least popular
     experts forced to zero tokens (their tokens go to the most popular one)."""
@@ -220,7 +244,7 @@ def bench_f4f4bf16(ops, M, N, K, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "moe_gather_scatter", "quantize_nvfp4", "silu_mul_quant",
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "decode", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "moe_gather_scatter", "quantize_nvfp4", "silu_mul_quant",
                                    "sweep"])
     ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
     ap.add_argument("--experts", type=int, default=16)
@@ -239,6 +263,10 @@ def main():
         out.append(bench_quantize_fp8_row(ops, *(shape or [8192, 4096]), args))
     elif args.op == "f8f8bf16_rowwise":
         out.append(bench_f8f8bf16_rowwise(ops, *(shape or [8192, 8192, 8192]), args))
+    elif args.op == "decode":
+        for M in ((shape[0],) if shape else (1, 16, 32)):
+            for N, K in (((shape[1], shape[2]),) if shape else ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336))):
+                out.append(bench_decode(ops, M, N, K, args))
     elif args.op == "batched":
         out.append(bench_batched(ops, *(shape or [8, 2048, 4096, 4096]), args))
     elif args.op == "grouped":
