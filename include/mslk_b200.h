@@ -215,6 +215,19 @@ int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale,
                        int64_t N, int64_t K, void *stream);
 
 /*
+ * Same GEMM with caller-provided scratch memory.  With 1 <= M <= 128 tokens the weight-streaming
+ * kernel may split K over several CTAs per 128 weight rows; the fp32 partial tiles and completion
+ * counters then live in `workspace` (mslk_b200_f4f4bf16_workspace_bytes(M, N, K) bytes, 0 when the
+ * shape needs none; 16-byte aligned, contents irrelevant on entry, not shared by calls that may run
+ * at the same time).  Without workspace (null or too small) the same kernel runs unsplit.
+ */
+size_t mslk_b200_f4f4bf16_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int mslk_b200_f4f4bf16_ws(const void *xq, const void *wq, const void *x_scale,
+                          const void *w_scale, const float *global_scale, void *y, int64_t M,
+                          int64_t N, int64_t K, void *workspace, size_t workspace_bytes,
+                          void *stream);
+
+/*
  * Grouped (stacked) NVFP4 GEMM for mixture-of-experts layers: group g multiplies its m_g stacked rows
  * of xq by its own weight block wq[g] and scales the result by global_scale[g].
  * Replaces: csrc/gemm/cutlass/f4f4bf16_grouped.cu:321-374 (f4f4bf16_grouped_stacked, NVFP4 mode) with

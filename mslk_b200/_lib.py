@@ -49,6 +49,10 @@ lib.mslk_b200_quantize_nvfp4.argtypes = [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _
 lib.mslk_b200_quantize_nvfp4.restype = _int
 lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f4f4bf16.restype = _int
+lib.mslk_b200_f4f4bf16_workspace_bytes.argtypes = [_i64, _i64, _i64]
+lib.mslk_b200_f4f4bf16_workspace_bytes.restype = ctypes.c_size_t
+lib.mslk_b200_f4f4bf16_ws.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.c_size_t, _vp]
+lib.mslk_b200_f4f4bf16_ws.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_batched.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f8f8bf16_rowwise_batched.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked_scatter_add.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp,

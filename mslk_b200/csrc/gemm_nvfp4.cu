@@ -21,6 +21,7 @@
 #include "../../include/mslk_b200.h"
 #include "common.cuh"
 #include "gemm_f8_common.cuh"   // group tables and the tile scheduler shared with the FP8 kernels
+#include "gemm_nvfp4_decode.h"
 #include "gemm_nvfp4_pair.h"
 #include "host.h"
 
@@ -386,7 +387,8 @@ namespace {
 
 int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scale, const void *w_scale,
             const float *global_scale, void *y, const int64_t *m_sizes, const int32_t *end_offsets,
-            const int64_t *sfa_row_start, int64_t G, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+            const int64_t *sfa_row_start, int64_t G, int64_t M, int64_t N, int64_t K, cudaStream_t st,
+            void *scratch = nullptr, size_t scratch_size = 0) {
   const bool grouped = m_sizes || end_offsets;
   if (M < 0 || N < 0 || K < 0 || G < 1) return fail(1, "%s: bad shape", name);
   if (M == 0 || N == 0) return 0;
@@ -425,6 +427,11 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
     const char *e = getenv("MSLK_B200_NVFP4_KERNEL");  // "1cta" | "2cta": tuning aid, default = heuristic
     return !e ? 0 : (e[0] == '2' ? 2 : 1);
   }();
+  // few tokens: weight-streaming kernel (weights on the 128 accumulator rows, two CTAs per SM, K split
+  // over CTAs when the caller passed scratch memory)
+  if (!grouped && force == 0 && M <= nvfp4_decode::kMaxTokens && N >= 128)
+    return nvfp4_decode::launch_decode_kernel(xq, wq, x_scale, w_scale, global_scale, y, status, M, N, K, scratch,
+                                              scratch_size, st);
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   // (few-token shapes stay on one CTA per tile: a 256-row pair tile would be mostly padding)
   if (!grouped && (force == 2 || (force == 0 && M > 128 && pair_tiles >= sms / 2))) {
@@ -455,6 +462,21 @@ MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_sc
   clear_error();
   return run_fp4("f4f4bf16", xq, wq, x_scale, w_scale, global_scale, y, nullptr, nullptr, nullptr, 1, M, N, K,
                  static_cast<cudaStream_t>(stream));
+}
+
+MSLK_API size_t mslk_b200_f4f4bf16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  using namespace mslk_b200;
+  if (M < 1 || N < 128 || K < 32) return 0;
+  return nvfp4_decode::scratch_bytes(M, N, K, sm_count());
+}
+
+MSLK_API int mslk_b200_f4f4bf16_ws(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                   const float *global_scale, void *y, int64_t M, int64_t N, int64_t K,
+                                   void *workspace, size_t workspace_bytes, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  return run_fp4("f4f4bf16", xq, wq, x_scale, w_scale, global_scale, y, nullptr, nullptr, nullptr, 1, M, N, K,
+                 static_cast<cudaStream_t>(stream), workspace, workspace_bytes);
 }
 
 MSLK_API int mslk_b200_f4f4bf16_grouped_stacked(const void *xq, const void *wq, const void *x_scale,

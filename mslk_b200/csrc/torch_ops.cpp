@@ -181,8 +181,13 @@ at::Tensor f4f4bf16(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor
   if (M == 0 || N == 0 || K == 0) return Y.zero_();
   c10::cuda::CUDAGuard guard(XQ.device());
   const at::Tensor gs = global_scale->reshape({-1}).to(at::kFloat);
-  check_rc(mslk_b200_f4f4bf16(XQ.data_ptr(), WQ.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
-                              gs.data_ptr<float>(), Y.data_ptr(), M, N, K, stream_of(XQ)),
+  // few-token shapes may split K over CTAs: scratch for the partial tiles comes from the caching allocator
+  const size_t wsz = mslk_b200_f4f4bf16_workspace_bytes(M, N, K);
+  at::Tensor ws;
+  if (wsz) ws = at::empty({static_cast<int64_t>(wsz)}, XQ.options().dtype(at::kByte));
+  check_rc(mslk_b200_f4f4bf16_ws(XQ.data_ptr(), WQ.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(),
+                                 gs.data_ptr<float>(), Y.data_ptr(), M, N, K, wsz ? ws.data_ptr() : nullptr, wsz,
+                                 stream_of(XQ)),
            "f4f4bf16");
   return Y;
 }

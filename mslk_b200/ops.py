@@ -302,8 +302,10 @@ def f4f4bf16(XQ, WQ, x_scale, w_scale, output=None, global_scale=None, mxfp4_blo
         return output.zero_()
     gs = global_scale.reshape(-1).to(torch.float32)
     with torch.cuda.device(dev):
-        check(lib.mslk_b200_f4f4bf16(_ptr(XQ), _ptr(WQ), _ptr(x_scale), _ptr(w_scale), _ptr(gs), _ptr(output),
-                                     M, N, K, _stream(dev)), name)
+        wsz = lib.mslk_b200_f4f4bf16_workspace_bytes(M, N, K)   # few tokens: scratch for K splitting
+        ws = torch.empty(wsz, dtype=torch.uint8, device=dev) if wsz else None
+        check(lib.mslk_b200_f4f4bf16_ws(_ptr(XQ), _ptr(WQ), _ptr(x_scale), _ptr(w_scale), _ptr(gs), _ptr(output),
+                                        M, N, K, _ptr(ws) if wsz else None, wsz, _stream(dev)), name)
     return output
 
 

@@ -101,3 +101,50 @@ def _rows_of_scales(s_blocked, rows, K):
     plain = oracle.from_blocked(u8(s_blocked.cpu()).reshape(-1), M, K // 16)
     sub = plain[rows.cpu()]
     return oracle.to_blocked(sub).view(torch.float8_e4m3fn).cuda()
+
+
+# ---------------------------------------------------------------------------
+# Few tokens (1 <= M <= 128): the weight-streaming kernel (weights on the accumulator rows, tokens on
+# the columns, K optionally split over CTAs).  Shapes: every token tile (16/32/64/128) with a ragged
+# token count, N not a multiple of 128, K with a partial last scale atom (K % 64 != 0) and a partial
+# last K block (K % 256 != 0), K long enough to be split.
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (7, 144, 96), (16, 4096, 2048), (17, 384, 320), (33, 1024, 4096),
+                                   (64, 272, 1056), (65, 256, 16384), (100, 4096, 2048), (128, 400, 16384),
+                                   (3, 256, 32768), (1, 28672, 8192)])
+def test_few_token_gemm_vs_fp32_dequant_formula(ops, M, N, K):
+    x, w, xq, wq, sx, sw, alpha, y = _gemm_case(ops, M, N, K, seed=11)
+    y_ref = oracle.gemm_nvfp4_torch(xq, wq, sx, sw, alpha)
+    scale = max(1.0, float(y_ref.float().std()))
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=1.6e-2, atol=1e-2 * scale)
+    assert _status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 256, 16384), (40, 384, 32768)])
+def test_few_token_gemm_split_and_unsplit_agree(ops, M, N, K):
+    """The C entry point without workspace runs unsplit, the one with workspace splits K (these shapes
+    ask for scratch); both follow the same arithmetic up to the fp32 summation order."""
+    from mslk_b200._lib import lib
+    x, w, xq, wq, sx, sw, alpha, y_split = _gemm_case(ops, M, N, K, seed=13)
+    assert lib.mslk_b200_f4f4bf16_workspace_bytes(M, N, K) > 0
+    y_plain = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.mslk_b200_f4f4bf16(xq.data_ptr(), wq.data_ptr(), sx.data_ptr(), sw.data_ptr(), alpha.data_ptr(),
+                                y_plain.data_ptr(), M, N, K, stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    scale = max(1.0, float(y_plain.float().std()))
+    torch.testing.assert_close(y_split.float(), y_plain.float(), rtol=8e-3, atol=4e-3 * scale)
+    # repeated calls give identical bits (the partial tiles are summed in split order)
+    y_again = ops.f4f4bf16(xq, wq, sx, sw, global_scale=alpha)
+    assert torch.equal(y_again, y_split)
+    assert _status() == 0
+
+
+def test_few_token_gemm_workspace_size_contract():
+    from mslk_b200._lib import lib
+    assert lib.mslk_b200_f4f4bf16_workspace_bytes(1, 28672, 8192) == 0      # short K: unsplit
+    assert lib.mslk_b200_f4f4bf16_workspace_bytes(256, 256, 32768) == 0     # more than 128 tokens: other kernels
+    assert lib.mslk_b200_f4f4bf16_workspace_bytes(0, 256, 32768) == 0
+    need = lib.mslk_b200_f4f4bf16_workspace_bytes(5, 256, 32768)
+    assert need > 0 and need % 16 == 0
