@@ -354,6 +354,14 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   // kernel below finish sooner than split + partial sums + tickets, so no scratch = general kernel.
   if (!m_sizes && G == 1 && !placement && scratch && total_m <= kDecodeMaxTokens && N >= 128)
     return launch_decode_kernel(xq, wq, p, scratch, scratch_bytes, false, st);
+  // Without scratch the same kernel runs unsplit, one CTA per 128 weight rows at two CTAs per SM.  It is
+  // taken when the 32-column tiles of the general kernel would need more than one wave (N > 32 x SMs):
+  // M = 1 / 16, (N, K) = (6144, 4096): 10.9 / 11.1 us against 13.8; (28672, 4096): 21.3 / 21.8 against
+  // 24.0 / 24.5; with N = 4096 the general kernel's single wave of 128 tiles is faster (8.8 against 10.4 us),
+  // and so it is with more than 32 tokens (M = 128, (8192, 8192): 23.9 against 32.9 us).
+  if (!m_sizes && G == 1 && !placement && !scratch && total_m <= kDecodeMaxTokens && N > 32 * sm_count() &&
+      !getenv("MSLK_B200_NO_DECODE"))
+    return launch_decode_kernel(xq, wq, p, nullptr, 0, false, st);
 
   // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs
   static const int force = [] {

@@ -69,6 +69,7 @@ struct DecodeParams {
   int M, N, K;
   int splits;
   int kb_per_split;        // K blocks (of 128) per split
+  int x_box_rows;          // rows of the token box (M rounded up to 8): absent rows are not zero-filled
 };
 
 template <int BT>
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(kNumThreads, 2)
         if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) break;
         uint8_t *sw = ring + static_cast<size_t>(stage) * C::kStageBytes;
         uint8_t *sx = sw + C::kStageW;
-        mbar_arrive_expect_tx(&S.full[stage], C::kStageBytes);
+        mbar_arrive_expect_tx(&S.full[stage], C::kStageW + p.x_box_rows * kBK);
         tma_load_2d(sw, &tmap_w, &S.full[stage], kb * kBK, n_tile * kWRows);
         tma_load_2d(sx, &tmap_x, &S.full[stage], kb * kBK, 0);
         if (++stage == C::kStages) {
@@ -321,6 +322,7 @@ int launch_decode_kernel(const void *xq, const void *wq, const GemmParams &gp, v
   p.K = gp.K;
   p.splits = splits;
   p.kb_per_split = (k_blocks + splits - 1) / splits;
+  p.x_box_rows = std::min<int>(bt, (gp.total_m + 7) / 8 * 8);
   p.partials = nullptr;
   p.tickets = nullptr;
   if (splits > 1) {
@@ -332,7 +334,7 @@ int launch_decode_kernel(const void *xq, const void *wq, const GemmParams &gp, v
 
   CUtensorMap tw, tx;
   if (int rc = make_tmap_2d_bytes(&tw, wq, gp.K, gp.N, gp.K, kBK, kWRows, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  if (int rc = make_tmap_2d_bytes(&tx, xq, gp.K, gp.total_m, gp.K, kBK, bt, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tx, xq, gp.K, gp.total_m, gp.K, kBK, p.x_box_rows, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   switch (bt) {
     case 16: return launch_decode<16>(tw, tx, p, static_cast<int>(n_tiles), st);
     case 32: return launch_decode<32>(tw, tx, p, static_cast<int>(n_tiles), st);

@@ -429,7 +429,10 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   }();
   // few tokens: weight-streaming kernel (weights on the 128 accumulator rows, two CTAs per SM, K split
   // over CTAs when the caller passed scratch memory)
-  if (!grouped && force == 0 && M <= nvfp4_decode::kMaxTokens && N >= 128)
+  // (65..128 tokens: only when the general kernel's 128-column tiles need more than one wave --
+  // M = 128, N = 28672: 30.7 against 36.4 us, but N = 8192: 21.0 against 19.7 us)
+  if (!grouped && force == 0 && N >= 128 &&
+      (M <= 64 || (M <= nvfp4_decode::kMaxTokens && (N + 127) / 128 > sms)))
     return nvfp4_decode::launch_decode_kernel(xq, wq, x_scale, w_scale, global_scale, y, status, M, N, K, scratch,
                                               scratch_size, st);
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
