@@ -349,17 +349,17 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
     p.scatter_rows = placement->scatter_rows;
   }
 
-  // few tokens AND scratch given: weight-streaming kernel with the K dimension split.  Opt-in: on
-  // the shapes measured (Llama-3-8B projections, M = 1..32) the 32-column tiles of the general
-  // kernel below finish sooner than split + partial sums + tickets, so no scratch = general kernel.
+  // few tokens AND scratch given: weight-streaming kernel with the K dimension split over independent
+  // CTAs (partial tiles and completion tickets in the caller's scratch memory).
   if (!m_sizes && G == 1 && !placement && scratch && total_m <= kDecodeMaxTokens && N >= 128)
     return launch_decode_kernel(xq, wq, p, scratch, scratch_bytes, false, st);
-  // Without scratch the same kernel runs unsplit, one CTA per 128 weight rows at two CTAs per SM.  It is
-  // taken when the 32-column tiles of the general kernel would need more than one wave (N > 32 x SMs):
-  // M = 1 / 16, (N, K) = (6144, 4096): 10.9 / 11.1 us against 13.8; (28672, 4096): 21.3 / 21.8 against
-  // 24.0 / 24.5; with N = 4096 the general kernel's single wave of 128 tiles is faster (8.8 against 10.4 us),
-  // and so it is with more than 32 tokens (M = 128, (8192, 8192): 23.9 against 32.9 us).
-  if (!m_sizes && G == 1 && !placement && !scratch && total_m <= kDecodeMaxTokens && N > 32 * sm_count() &&
+  // Without scratch the same kernel splits K inside thread-block clusters (partial tiles meet in shared
+  // memory) or runs unsplit, one CTA per 128 weight rows at two CTAs per SM.  M = 1 / 16 / 32 against the
+  // general kernel's 32-column tiles: (4096, 4096) 7.0 / 7.9 / 9.4 us against 8.8 / 8.8 / 9.0; (6144, 4096)
+  // 8.2 / 9.6 / 10.9 against 13.8; (4096, 14336) 12.9 / 13.7 / 14.6 against 20.5; (8192, 8192) 14.6 / 15.8 /
+  // 16.9 against 23.3; (28672, 4096) 21.3 / 21.8 / 22.8 against 24.1 / 24.6 / 25.0.  Above 32 tokens the
+  // general kernel is faster (M = 128, (8192, 8192): 23.9 against 32.9 us).
+  if (!m_sizes && G == 1 && !placement && !scratch && total_m <= kDecodeMaxTokens && N >= 2048 &&
       !getenv("MSLK_B200_NO_DECODE"))
     return launch_decode_kernel(xq, wq, p, nullptr, 0, false, st);
 

@@ -84,6 +84,7 @@ struct KParams {
   int x_box_rows;          // rows of the token box (M rounded up to 8): no out-of-range fill
   int splits;
   int kb_per_split;        // K blocks (of 256 elements) per split
+  int cluster_reduce;      // 1: the `splits` CTAs of a tile form one thread-block cluster and meet in shared memory
 };
 
 template <int BT>
@@ -125,6 +126,13 @@ __global__ void __launch_bounds__(kNumThreads, 2)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
+
+  // state of the epilogue threads (warps 2..5), kept across the cluster barrier below
+  const int quad = warp & 3;
+  const int n = n_tile * kWRows + quad * 32 + lane;
+  const bool n_ok = n < p.N;
+  float acc[BT];
+  bool do_epilogue = false;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -191,10 +199,6 @@ __global__ void __launch_bounds__(kNumThreads, 2)
     __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue: thread = weight row
-    const int quad = warp & 3;
-    const int n = n_tile * kWRows + quad * 32 + lane;
-    const bool n_ok = n < p.N;
-    float acc[BT];
     bool have = false;
     if (my_kb > 0) {
       const bool got = mbar_wait(&S.acc_full, 0, abort_flag, p.status, kStatusEpilogueTimeout);
@@ -225,8 +229,15 @@ __global__ void __launch_bounds__(kNumThreads, 2)
     }
     const bool aborted = (my_kb > 0) && !have;
 
-    bool do_epilogue = !aborted;
-    if (p.splits > 1 && !aborted) {
+    do_epilogue = !aborted;
+    if (p.cluster_reduce) {
+      // Partial tile into this CTA's own shared memory ([token][weight row] fp32 over the ring, whose
+      // stages have all been consumed once the accumulator is complete); collected after the barrier below.
+      float *red = reinterpret_cast<float *>(ring);
+#pragma unroll
+      for (int m = 0; m < BT; ++m)
+        if (m < p.M) red[m * kWRows + quad * 32 + lane] = acc[m];
+    } else if (p.splits > 1 && !aborted) {
       float *mine = p.partials + ((static_cast<size_t>(n_tile) * p.splits + split) * BT) * kWRows + quad * 32 + lane;
 #pragma unroll
       for (int m = 0; m < BT; ++m)
@@ -250,12 +261,38 @@ __global__ void __launch_bounds__(kNumThreads, 2)
         }
       }
     }
-    if (do_epilogue && n_ok) {
+  }
+
+  if (p.cluster_reduce) {
+    // Split K inside a thread-block cluster: every CTA of the cluster (all threads, all roles) meets at
+    // the hardware barrier; then CTA r finishes the tokens m = r, r + splits, ...: it adds the partial
+    // sums of all CTAs, read from their shared memory in rank order (deterministic), and stores the
+    // result.  The second barrier keeps every CTA resident until its peers have read it.  No scratch
+    // memory, no tickets, no extra launch.
+    cluster_sync_all();
+    if (warp >= 2 && do_epilogue && n_ok) {
       const float alpha = *p.alpha;
+      const uint32_t mine = smem_u32(ring) + static_cast<uint32_t>(quad * 32 + lane) * 4u;
+      uint32_t peer[8];
 #pragma unroll
-      for (int m = 0; m < BT; ++m)
-        if (m < p.M) p.y[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(acc[m] * alpha);
+      for (int s = 0; s < 8; ++s) peer[s] = mapa_u32(mine, static_cast<uint32_t>(s < p.splits ? s : 0));
+      for (int m = split; m < p.M; m += p.splits) {
+        float part[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          part[s] = s < p.splits ? ld_shared_cluster_f32(peer[s] + static_cast<uint32_t>(m * kWRows) * 4u) : 0.f;
+        float a = part[0];
+#pragma unroll
+        for (int s = 1; s < 8; ++s) a += part[s];
+        p.y[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(a * alpha);
+      }
     }
+    cluster_sync_all();
+  } else if (warp >= 2 && do_epilogue && n_ok) {
+    const float alpha = *p.alpha;
+#pragma unroll
+    for (int m = 0; m < BT; ++m)
+      if (m < p.M) p.y[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(acc[m] * alpha);
   }
 
   tc_fence_before();
@@ -279,6 +316,23 @@ int launch_decode(const CUtensorMap &tw, const CUtensorMap &tx, const KParams &p
                             "cudaFuncSetAttribute(gemm_nvfp4_decode)"))
       return rc;
     attr_set[dev] = true;
+  }
+  if (p.cluster_reduce) {
+    // the splits of one tile (grid y) form a thread-block cluster
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_tiles, p.splits, 1);
+    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = static_cast<unsigned>(p.splits);
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_decode_kernel<BT>, tw, tx, p),
+                      "f4f4bf16 decode launch (cluster)");
   }
   gemm_nvfp4_decode_kernel<BT><<<dim3(n_tiles, p.splits, 1), kNumThreads, smem, st>>>(tw, tx, p);
   return check_cuda(cudaGetLastError(), "f4f4bf16 decode launch");
@@ -306,6 +360,23 @@ int choose_splits(int64_t N, int64_t K, int sms) {
   return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(s, s_max)));
 }
 
+// Cluster size (2, 4 or 8 CTAs along K) for the split that needs no scratch: K is split only when the
+// unsplit launch would leave more than half of the SMs without a CTA; then the largest size that still
+// fits all CTAs on the device at once (two per SM) and leaves every CTA at least eight K blocks.
+int cluster_splits(int64_t N, int64_t K, int sms) {
+  static const int forced = [] {
+    const char *e = getenv("MSLK_B200_NVFP4_DECODE_CLUSTER");   // tuning aid: 1, 2, 4 or 8
+    return e ? atoi(e) : 0;
+  }();
+  const int64_t n_tiles = (N + kWRows - 1) / kWRows;
+  const int64_t k_blocks = (K / 2 + kBKBytes - 1) / kBKBytes;
+  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return k_blocks >= forced ? forced : 1;
+  if (2 * n_tiles > sms) return 1;
+  int s = 1;
+  while (s < 8 && n_tiles * (2 * s) <= 2 * static_cast<int64_t>(sms) && k_blocks / (2 * s) >= 8) s *= 2;
+  return s;
+}
+
 }  // namespace
 
 size_t scratch_bytes(int64_t M, int64_t N, int64_t K, int sms) {
@@ -327,7 +398,14 @@ int launch_decode_kernel(const void *xq, const void *wq, const void *x_scale, co
   const int bt = token_tile(M);
   const size_t partial_bytes = static_cast<size_t>(n_tiles) * splits * bt * kWRows * sizeof(float);
   const size_t ticket_bytes = static_cast<size_t>(n_tiles) * 4 * sizeof(unsigned int);
-  if (splits > 1 && (!scratch || scratch_size < partial_bytes + ticket_bytes)) splits = 1;  // no scratch: one CTA per tile
+  // K split inside thread-block clusters (partial tiles meet in shared memory) whenever that applies;
+  // the scratch form only for what clusters do not cover (more than eight splits are never chosen).
+  bool cluster_reduce = false;
+  const int cs = cluster_splits(N, K, sms);
+  if (cs > 1 || !scratch || scratch_size < partial_bytes + ticket_bytes) {
+    splits = cs;
+    cluster_reduce = cs > 1;
+  }
 
   KParams p;
   p.sfx = static_cast<const uint8_t *>(x_scale);
@@ -342,9 +420,10 @@ int launch_decode_kernel(const void *xq, const void *wq, const void *x_scale, co
   p.x_box_rows = std::min<int>(bt, static_cast<int>((M + 7) / 8 * 8));
   p.splits = splits;
   p.kb_per_split = (k_blocks + splits - 1) / splits;
+  p.cluster_reduce = cluster_reduce ? 1 : 0;
   p.partials = nullptr;
   p.tickets = nullptr;
-  if (splits > 1) {
+  if (splits > 1 && !cluster_reduce) {
     p.partials = static_cast<float *>(scratch);
     p.tickets = reinterpret_cast<unsigned int *>(static_cast<uint8_t *>(scratch) + partial_bytes);
     if (int rc = check_cuda(cudaMemsetAsync(p.tickets, 0, ticket_bytes, st), "zero split-K tickets")) return rc;

@@ -121,10 +121,12 @@ def test_few_token_gemm_vs_fp32_dequant_formula(ops, M, N, K):
     assert _status() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(5, 256, 16384), (40, 384, 32768)])
+@pytest.mark.parametrize("M,N,K", [(5, 256, 16384), (40, 384, 32768), (5, 9600, 16384), (40, 9728, 16384)])
 def test_few_token_gemm_split_and_unsplit_agree(ops, M, N, K):
-    """The C entry point without workspace runs unsplit, the one with workspace splits K (these shapes
-    ask for scratch); both follow the same arithmetic up to the fp32 summation order."""
+    """With few 128-row weight blocks K is split inside thread-block clusters with or without workspace
+    (first two shapes); with more than half as many blocks as SMs the entry point without workspace runs
+    unsplit and the one with workspace splits K over independent CTAs.  All follow the same arithmetic up
+    to the fp32 summation order."""
     from mslk_b200._lib import lib
     x, w, xq, wq, sx, sw, alpha, y_split = _gemm_case(ops, M, N, K, seed=13)
     assert lib.mslk_b200_f4f4bf16_workspace_bytes(M, N, K) > 0
