@@ -78,7 +78,7 @@ def test_case_list_against_oracle(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("D", [8, 100, 2049, 4096, 6152, 16384, 32768, 40000])
+@pytest.mark.parametrize("D", [8, 100, 2049, 4096, 6152, 16384, 16392, 16408, 28672, 32768, 40000])
 def test_widths_and_dtypes(ops, dtype, D):
     # every dispatch bucket of the vector kernel, the general kernel (odd D) and very wide rows
     g = torch.Generator().manual_seed(D)
