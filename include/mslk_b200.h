@@ -139,10 +139,12 @@ int mslk_b200_f8f8bf16_rowwise_ws(const void *xq, const void *wq, const float *x
  * allocates and frees nothing.  Serves 1 <= M <= 128, N >= 128, K % 16 == 0 as long as the
  * split-K scratch of the shape fits the 8 MiB (always true for M <= 32; for more tokens only
  * small N*K do); a shape that needs more is rejected with a message, never truncated.  The first call on a
- * device looks up the array's device address: make that call outside stream capture.  All calls
- * on a GPU share the array -- the tickets in it are cleared on the stream before each launch,
- * the partial sums are overwritten -- so calls that could overlap on one GPU must be ordered
- * by the caller.  Same arithmetic and arguments as mslk_b200_f8f8bf16_rowwise.
+ * device looks up the array's device address: make that call outside stream capture.  Up to 32
+ * tokens the kernel splits K inside thread-block clusters and does not touch the array, so such
+ * calls may overlap freely.  With more tokens all calls on a GPU share the array -- the tickets in
+ * it are cleared on the stream before each launch, the partial sums are overwritten -- so calls
+ * that could overlap on one GPU must be ordered by the caller.  Same arithmetic and arguments as
+ * mslk_b200_f8f8bf16_rowwise.
  * This entry point has no counterpart in the reference (its op always allocates its workspace).
  */
 int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, const float *x_scale,

@@ -525,7 +525,10 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, 
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   default_placement(p);
-  // scratch_is_clean = false: the tickets are zeroed on the stream before the launch
+  // Up to 32 tokens K is split inside thread-block clusters, which need no scratch at all (and are faster);
+  // above, the built-in array holds the partial tiles and the tickets are zeroed on the stream before the launch.
+  if (M <= kDecodeMaxTokens)
+    return launch_decode_kernel(xq, wq, p, nullptr, 0, false, static_cast<cudaStream_t>(stream));
   return launch_decode_kernel(xq, wq, p, scratch, kBuiltinScratchBytes, false, static_cast<cudaStream_t>(stream));
 }
 
