@@ -429,10 +429,13 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   }();
   // few tokens: weight-streaming kernel (weights on the 128 accumulator rows, two CTAs per SM, K split
   // over CTAs when the caller passed scratch memory)
-  // (65..128 tokens: only when the general kernel's 128-column tiles need more than one wave --
-  // M = 128, N = 28672: 30.7 against 36.4 us, but N = 8192: 21.0 against 19.7 us)
+  // (65..128 tokens: when the general kernel's 128-column tiles need more than one wave -- M = 128,
+  // N = 28672: 30.7 against 36.4 us -- or when K is long and is split inside clusters -- M = 128, (N, K) =
+  // (4096, 14336): 18.1 against 29.7 us, M = 100, (8192, 28672): 32.1 against 54.0, (8192, 8192): 18.5 against
+  // 19.9; with K = 4096 the general kernel wins, (4096, 4096): 12.5 against 19.2 us)
+  const int64_t w_blocks = (N + 127) / 128;
   if (!grouped && force == 0 && N >= 128 &&
-      (M <= 64 || (M <= nvfp4_decode::kMaxTokens && (N + 127) / 128 > sms)))
+      (M <= 64 || (M <= nvfp4_decode::kMaxTokens && (w_blocks > sms || (2 * w_blocks <= sms && K >= 8192)))))
     return nvfp4_decode::launch_decode_kernel(xq, wq, x_scale, w_scale, global_scale, y, status, M, N, K, scratch,
                                               scratch_size, st);
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);

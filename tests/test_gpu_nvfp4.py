@@ -108,11 +108,13 @@ def _rows_of_scales(s_blocked, rows, K):
 # the columns, K optionally split over CTAs).  Shapes: every token tile (16/32/64/128) with a ragged
 # token count, N not a multiple of 128, K with a partial last scale atom (K % 64 != 0) and a partial
 # last K block (K % 256 != 0), K long enough to be split; 65..128 tokens take this kernel only with more
-# than one wave of 128-row weight blocks (N > 128 x SMs), otherwise the general kernel.
+# than one wave of 128-row weight blocks (N > 128 x SMs) or with long K split in clusters, otherwise the
+# general kernel.
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (7, 144, 96), (16, 4096, 2048), (17, 384, 320), (33, 1024, 4096),
                                    (64, 272, 1056), (65, 256, 16384), (100, 4096, 2048), (128, 400, 16384),
-                                   (3, 256, 32768), (1, 28672, 8192), (100, 19072, 320), (128, 28672, 512)])
+                                   (3, 256, 32768), (1, 28672, 8192), (100, 19072, 320), (128, 28672, 512), (128, 512, 8192),
+                                   (97, 2048, 16384)])
 def test_few_token_gemm_vs_fp32_dequant_formula(ops, M, N, K):
     x, w, xq, wq, sx, sw, alpha, y = _gemm_case(ops, M, N, K, seed=11)
     y_ref = oracle.gemm_nvfp4_torch(xq, wq, sx, sw, alpha)
