@@ -359,8 +359,13 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   // 8.2 / 9.6 / 10.9 against 13.8; (4096, 14336) 12.9 / 13.7 / 14.6 against 20.5; (8192, 8192) 14.6 / 15.8 /
   // 16.9 against 23.3; (28672, 4096) 21.3 / 21.8 / 22.8 against 24.1 / 24.6 / 25.0.  Above 32 tokens the
   // general kernel is faster (M = 128, (8192, 8192): 23.9 against 32.9 us).
-  if (!m_sizes && G == 1 && !placement && !scratch && total_m <= kDecodeMaxTokens && N >= 2048 &&
-      !getenv("MSLK_B200_NO_DECODE"))
+  // 33..128 tokens: only with long K and few weight blocks, i.e. when the cluster split applies -- M = 64:
+  // (4096, 14336) 16.3 against 20.7 us, (8192, 8192) 20.5 against 23.5, (8192, 28672) 45.1 against 69.0;
+  // M = 128: (8192, 28672) 50.9 against 69.8, but (8192, 8192) 24.4 against 24.1.
+  const bool few_blocks = 2 * ((static_cast<int64_t>(N) + 127) / 128) <= sm_count();
+  const bool more_tokens_ok = few_blocks && ((total_m <= 64 && K >= 8192) || (total_m <= 128 && K >= 16384));
+  if (!m_sizes && G == 1 && !placement && !scratch && N >= 2048 && !getenv("MSLK_B200_NO_DECODE") &&
+      (total_m <= kDecodeMaxTokens || more_tokens_ok))
     return launch_decode_kernel(xq, wq, p, nullptr, 0, false, st);
 
   // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs

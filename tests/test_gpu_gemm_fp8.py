@@ -188,7 +188,8 @@ def test_grouped_moe_shape_zipf(ops):
 @pytest.mark.parametrize("M", [1, 3, 16, 17, 32, 64, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 128), (1000, 512), (4096, 4096), (6144, 1024)])
 def test_few_token_shapes_split_and_unsplit(ops, M, N, K):
-    # with scratch, M <= 32 takes the weight-streaming split-K kernel; without, the general kernel
+    # with scratch, M <= 32 takes the weight-streaming kernel with K split over independent CTAs (tickets);
+    # without, the same kernel with the cluster split (N >= 2048) or the general kernel
     from mslk_b200._lib import lib, check
     xq, wq, xs, ws = _quant(ops, M, N, K, seed=M + N, w_std=1.0)
     bias = torch.randn(N, device="cuda") if (M + N) % 2 else None
@@ -213,6 +214,23 @@ def test_few_token_shapes_split_and_unsplit(ops, M, N, K):
     _close(y2, y_ref, f"decode unsplit {M}x{N}x{K}")
     # the split result does not depend on CTA finishing order: repeated calls are bit-identical
     assert torch.equal(split_call(), y)
+    assert _status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,bias_dtype", [
+    (1, 2048, 16384, None), (20, 4096, 8576, torch.float32), (32, 2304, 4224, torch.bfloat16),
+    (64, 4096, 8192, torch.bfloat16), (128, 2048, 16384, torch.float32), (5, 8192, 1024, None),
+    (33, 6144, 8192, None), (16, 28672, 512, torch.float32)])
+def test_few_token_shapes_cluster_split(ops, M, N, K, bias_dtype):
+    """Without scratch the weight-streaming kernel splits K inside thread-block clusters (2, 4 or 8 CTAs whose
+    partial tiles meet in distributed shared memory), also with a ragged last split, or runs unsplit (many
+    weight blocks, short K); up to 128 tokens with long K.  Deterministic: repeated calls are bit-identical."""
+    xq, wq, xs, ws = _quant(ops, M, N, K, seed=M + K, w_std=1.0)
+    bias = None if bias_dtype is None else torch.randn(N, device="cuda").to(bias_dtype)
+    y_ref = oracle.gemm_f8_rowwise_torch(xq, wq, xs, ws, bias)
+    y = ops.f8f8bf16_rowwise(xq, wq, xs, ws, bias=bias)
+    _close(y, y_ref, f"cluster split {M}x{N}x{K}")
+    assert torch.equal(ops.f8f8bf16_rowwise(xq, wq, xs, ws, bias=bias), y)
     assert _status() == 0
 
 
