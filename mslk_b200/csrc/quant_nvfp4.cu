@@ -52,6 +52,20 @@ struct BlockIn {
   uint4 a, b;   // 16 bf16 = one scale block
 };
 
+// a / b rounded to nearest, from b and its correctly rounded reciprocal rb: q0 = a * rb is within one
+// unit of the quotient, the remainder a - b * q0 is exact in an fma, and one more fma lands on the
+// correctly rounded quotient (Markstein) -- as long as nothing is subnormal on the way, which the
+// magnitude guard ensures; outside it, and for a zero numerator, the IEEE division itself runs.
+__device__ __forceinline__ float div_rn_via_rcp(float a, float b, float rb) {
+  const float aa = fabsf(a);
+  if (aa > 0x1p-80f && aa < 0x1p80f) {   // b in [2^-9, 448] or 6: quotient and remainder stay normal
+    const float q0 = __fmul_rn(a, rb);
+    const float rem = __fmaf_rn(-b, q0, a);
+    return __fmaf_rn(rem, rb, q0);
+  }
+  return __fdiv_rn(a, b);
+}
+
 template <int kVec>
 __device__ __forceinline__ BlockIn load_block(const __nv_bfloat16 *src) {
   BlockIn v;
@@ -124,7 +138,7 @@ __global__ void __launch_bounds__(kThreads, 6)
 #pragma unroll
       for (int i = 1; i < 8; ++i) mx = __hmax2(mx, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
       const float bamax = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
-      float s = __fmul_rn(__fdiv_rn(bamax, 6.0f), gs);
+      float s = __fmul_rn(div_rn_via_rcp(bamax, 6.0f, 0x1.555556p-3f), gs);
       s = fminf(fmaxf(s, 0.001953125f), 448.0f);
       s8 = f32_to_e4m3(s);
       const float total = s_total[s8 & 127];
@@ -189,15 +203,26 @@ __global__ void __launch_bounds__(kThreads, 6)
                                uint8_t *__restrict__ q, uint8_t *__restrict__ scales, int n_col_tiles) {
   __shared__ int s_row_end[kMaxStackedGroups];
   __shared__ int s_blk_end[kMaxStackedGroups];
+  __shared__ float2 s_e4m3[128];   // value of every positive e4m3 code and its correctly rounded reciprocal
   const int tid = threadIdx.x, lane = tid & 31;
   if (tid < 32) build_stacked_tables(m_sizes, G, M, lane, s_row_end, s_blk_end);
+  if (tid >= 128) {
+    const float v = e4m3_to_f32(static_cast<uint8_t>(tid - 128));
+    s_e4m3[tid - 128] = make_float2(v, __frcp_rn(v));
+  }
   __syncthreads();
   const int c = lane & 3, row_in_tile = ((lane >> 2) & 3) * 32 + (lane >> 4);
   const int64_t q_pitch = static_cast<int64_t>(nblk) * 8;
   const int stride = gridDim.x * (kThreads / 32);
   const int total_units = s_blk_end[G - 1] * n_col_tiles * kWarpsPerTile;
 
-  for (int unit = blockIdx.x * (kThreads / 32) + (tid >> 5); unit < total_units; unit += stride) {
+  // Two units per iteration: both group lookups and both loads are issued before either block is
+  // converted, so the lookup of one unit hides behind the load of the other.
+  struct Loc {
+    int m, j, g;
+    bool live;
+  };
+  auto locate = [&](int unit) {
     const int tile = unit / kWarpsPerTile, w = unit - tile * kWarpsPerTile;
     const int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
     int lo = 0, hi = G - 1;   // group of padded row block tr: first g with blk_end[g] > tr
@@ -205,24 +230,27 @@ __global__ void __launch_bounds__(kThreads, 6)
       const int mid = (lo + hi) >> 1;
       if (s_blk_end[mid] > tr) hi = mid; else lo = mid + 1;
     }
-    const int g = lo;
-    const int blk0 = g ? s_blk_end[g - 1] : 0, row0 = g ? s_row_end[g - 1] : 0;
-    const int m = row0 + (tr - blk0) * kTileRows + row_in_tile + 2 * w;
-    const int j = tc * kTileBlocks + c;
-    const bool live = m < s_row_end[g] && j < nblk;
+    const int blk0 = lo ? s_blk_end[lo - 1] : 0, row0 = lo ? s_row_end[lo - 1] : 0;
+    Loc l;
+    l.g = lo;
+    l.m = row0 + (tr - blk0) * kTileRows + row_in_tile + 2 * w;
+    l.j = tc * kTileBlocks + c;
+    l.live = l.m < s_row_end[lo] && l.j < nblk;
+    return l;
+  };
+  auto emit = [&](int unit, const Loc &l, const BlockIn &cur, float gs) {
     uint8_t s8 = 0;
-    if (live) {
-      const float gs = gs_ptr[g];
-      const BlockIn cur = load_block<kVec>(x + m * row_stride + j * 16);
+    if (l.live) {
       const uint32_t wd[8] = {cur.a.x, cur.a.y, cur.a.z, cur.a.w, cur.b.x, cur.b.y, cur.b.z, cur.b.w};
       __nv_bfloat162 mx = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&wd[0]));
 #pragma unroll
       for (int i = 1; i < 8; ++i) mx = __hmax2(mx, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&wd[i])));
       const float bamax = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
-      float s = __fmul_rn(__fdiv_rn(bamax, 6.0f), gs);
-      s = fminf(fmaxf(s, 0.001953125f), 448.0f);
-      s8 = f32_to_e4m3(s);
-      const float total = __fdiv_rn(gs, e4m3_to_f32(s8));
+      float sc = __fmul_rn(div_rn_via_rcp(bamax, 6.0f, 0x1.555556p-3f), gs);
+      sc = fminf(fmaxf(sc, 0.001953125f), 448.0f);
+      s8 = f32_to_e4m3(sc);
+      const float2 vr = s_e4m3[s8 & 127];   // s8 is a code in [2^-9, 448]: never zero, never NaN
+      const float total = div_rn_via_rcp(gs, vr.x, vr.y);
       float lo8[8], hi8[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -231,9 +259,28 @@ __global__ void __launch_bounds__(kThreads, 6)
         hi8[2 * i] = __fmul_rn(__uint_as_float(wd[4 + i] << 16), total);
         hi8[2 * i + 1] = __fmul_rn(__uint_as_float(wd[4 + i] & 0xffff0000u), total);
       }
-      *reinterpret_cast<uint2 *>(q + m * q_pitch + j * 8) = make_uint2(cvt_e2m1x8(lo8), cvt_e2m1x8(hi8));
+      *reinterpret_cast<uint2 *>(q + l.m * q_pitch + l.j * 8) = make_uint2(cvt_e2m1x8(lo8), cvt_e2m1x8(hi8));
     }
     scales[static_cast<int64_t>(unit) * 32 + lane] = s8;   // zero for the padding rows / columns of the group
+  };
+  for (int unit = blockIdx.x * (kThreads / 32) + (tid >> 5); unit < total_units; unit += 2 * stride) {
+    const int unit2 = unit + stride;
+    const bool have2 = unit2 < total_units;
+    const Loc l1 = locate(unit);
+    Loc l2 = l1;
+    if (have2) l2 = locate(unit2);
+    BlockIn b1 = {}, b2 = {};
+    float gs1 = 0.f, gs2 = 0.f;
+    if (l1.live) {
+      b1 = load_block<kVec>(x + l1.m * row_stride + l1.j * 16);
+      gs1 = gs_ptr[l1.g];
+    }
+    if (have2 && l2.live) {
+      b2 = load_block<kVec>(x + l2.m * row_stride + l2.j * 16);
+      gs2 = gs_ptr[l2.g];
+    }
+    emit(unit, l1, b1, gs1);
+    if (have2) emit(unit2, l2, b2, gs2);
   }
 }
 
