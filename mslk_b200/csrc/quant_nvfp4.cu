@@ -216,27 +216,12 @@ __global__ void __launch_bounds__(kThreads, 6)
   const int stride = gridDim.x * (kThreads / 32);
   const int total_units = s_blk_end[G - 1] * n_col_tiles * kWarpsPerTile;
 
-  // Two units per iteration: both group lookups and both loads are issued before either block is
-  // converted, so the lookup of one unit hides behind the load of the other.
+  // The kernel is bound by instruction issue (ncu: issue slots 71 % busy, ~240 warp instructions per
+  // unit), so the unit -> (row block, column tile, warp slot) split is carried along incrementally
+  // instead of by two divisions per unit, and the group is a running index (row blocks only grow).
   struct Loc {
     int m, j, g;
     bool live;
-  };
-  auto locate = [&](int unit) {
-    const int tile = unit / kWarpsPerTile, w = unit - tile * kWarpsPerTile;
-    const int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
-    int lo = 0, hi = G - 1;   // group of padded row block tr: first g with blk_end[g] > tr
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (s_blk_end[mid] > tr) hi = mid; else lo = mid + 1;
-    }
-    const int blk0 = lo ? s_blk_end[lo - 1] : 0, row0 = lo ? s_row_end[lo - 1] : 0;
-    Loc l;
-    l.g = lo;
-    l.m = row0 + (tr - blk0) * kTileRows + row_in_tile + 2 * w;
-    l.j = tc * kTileBlocks + c;
-    l.live = l.m < s_row_end[lo] && l.j < nblk;
-    return l;
   };
   auto emit = [&](int unit, const Loc &l, const BlockIn &cur, float gs) {
     uint8_t s8 = 0;
@@ -263,24 +248,37 @@ __global__ void __launch_bounds__(kThreads, 6)
     }
     scales[static_cast<int64_t>(unit) * 32 + lane] = s8;   // zero for the padding rows / columns of the group
   };
-  for (int unit = blockIdx.x * (kThreads / 32) + (tid >> 5); unit < total_units; unit += 2 * stride) {
-    const int unit2 = unit + stride;
-    const bool have2 = unit2 < total_units;
-    const Loc l1 = locate(unit);
-    Loc l2 = l1;
-    if (have2) l2 = locate(unit2);
-    BlockIn b1 = {}, b2 = {};
-    float gs1 = 0.f, gs2 = 0.f;
-    if (l1.live) {
-      b1 = load_block<kVec>(x + l1.m * row_stride + l1.j * 16);
-      gs1 = gs_ptr[l1.g];
+  int unit = blockIdx.x * (kThreads / 32) + (tid >> 5);
+  int tile = unit / kWarpsPerTile, w = unit - tile * kWarpsPerTile;
+  int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
+  const int d_tile = stride / kWarpsPerTile, d_w = stride - d_tile * kWarpsPerTile;
+  const int d_tr = d_tile / n_col_tiles, d_tc = d_tile - d_tr * n_col_tiles;
+  int g = 0;
+  for (; unit < total_units; unit += stride) {
+    while (g < G - 1 && s_blk_end[g] <= tr) ++g;   // group of padded row block tr: first g with blk_end[g] > tr
+    const int blk0 = g ? s_blk_end[g - 1] : 0, row0 = g ? s_row_end[g - 1] : 0;
+    Loc l;
+    l.g = g;
+    l.m = row0 + (tr - blk0) * kTileRows + row_in_tile + 2 * w;
+    l.j = tc * kTileBlocks + c;
+    l.live = l.m < s_row_end[g] && l.j < nblk;
+    BlockIn blk = {};
+    float gs = 0.f;
+    if (l.live) {
+      blk = load_block<kVec>(x + l.m * row_stride + l.j * 16);
+      gs = gs_ptr[g];
     }
-    if (have2 && l2.live) {
-      b2 = load_block<kVec>(x + l2.m * row_stride + l2.j * 16);
-      gs2 = gs_ptr[l2.g];
+    emit(unit, l, blk, gs);
+    // next unit of this warp: unit + stride, digit by digit
+    w += d_w;
+    const int carry = w >= kWarpsPerTile ? 1 : 0;
+    w -= carry * kWarpsPerTile;
+    tc += d_tc + carry;
+    tr += d_tr;
+    if (tc >= n_col_tiles) {
+      tc -= n_col_tiles;
+      ++tr;
     }
-    emit(unit, l1, b1, gs1);
-    if (have2) emit(unit2, l2, b2, gs2);
   }
 }
 
