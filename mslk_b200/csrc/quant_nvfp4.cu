@@ -109,15 +109,30 @@ __global__ void __launch_bounds__(kThreads, 6)
 
   int unit = blockIdx.x * (kThreads / 32) + (tid >> 5);
   if (unit >= total_units) return;
+  // unit -> (row block tr, column tile tc, warp slot w), carried along digit by digit: the kernel is
+  // close to its instruction-issue limit and two divisions per unit were a fifth of its instructions
+  int tile = unit / kWarpsPerTile, w = unit - tile * kWarpsPerTile;
+  int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
+  const int d_tile = stride / kWarpsPerTile, d_w = stride - d_tile * kWarpsPerTile;
+  const int d_tr = d_tile / n_col_tiles, d_tc = d_tile - d_tr * n_col_tiles;
   int m, j;
-  auto locate = [&](int u, int &mm, int &jj) {
-    const int tile = u / kWarpsPerTile, w = u - tile * kWarpsPerTile;
-    const int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
+  auto locate_here = [&](int &mm, int &jj) {
     mm = tr * kTileRows + row_in_tile + 2 * w;
     jj = tc * kTileBlocks + c;
     return mm < M && jj < nblk;
   };
-  bool live = locate(unit, m, j);
+  auto advance = [&]() {
+    w += d_w;
+    const int carry = w >= kWarpsPerTile ? 1 : 0;
+    w -= carry * kWarpsPerTile;
+    tc += d_tc + carry;
+    tr += d_tr;
+    if (tc >= n_col_tiles) {
+      tc -= n_col_tiles;
+      ++tr;
+    }
+  };
+  bool live = locate_here(m, j);
   BlockIn cur{};
   if (live) cur = load_block<kVec>(x + m * row_stride + j * 16);
   while (unit < total_units) {
@@ -127,7 +142,8 @@ __global__ void __launch_bounds__(kThreads, 6)
     bool nlive = false;
     BlockIn nxt{};
     if (nunit < total_units) {
-      nlive = locate(nunit, nm, nj);
+      advance();
+      nlive = locate_here(nm, nj);
       if (nlive) nxt = load_block<kVec>(x + nm * row_stride + nj * 16);
     }
     uint8_t s8 = 0;
