@@ -1,0 +1,191 @@
+"""Races this library's kernels against the reference's own sm_100 kernels on one B200.
+
+    python baseline/race_ref_gpu.py [--quick] [--out gpurun_out/race_ref_gpu.jsonl]
+
+Needs baseline/_ref/libmslk_ref_gpu.so (built by baseline/build_ref_gpu.py from the reference's sources at
+stock CUTLASS) and, for the quantizer, baseline/_ref/pyref (the reference's Python package, `--python`).
+For every case both sides get the same device tensors, are timed the same way (CUDA events around `iters`
+back-to-back launches after warm-up, weights rotated through more than the L2 holds) and their outputs are
+compared element by element in bf16 units in the last place.  One JSON line per case:
+    {"case": ..., "ours_us": ..., "ref_us": ..., "ours_over_ref_speed": ref_us / ours_us,
+     "max_ulp": ..., "frac_within_1ulp": ..., "frac_equal": ...}
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+sys.path.insert(0, ROOT)
+
+
+def bf16_ulp_diff(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """|a - b| counted in bf16 steps (both tensors bf16): bit patterns mapped to a monotone integer line."""
+    def key(t):
+        i = t.contiguous().view(torch.int16).to(torch.int32)
+        return torch.where(i < 0, -(i & 0x7fff), i)
+    return (key(a) - key(b)).abs()
+
+
+def compare(y, y_ref):
+    d = bf16_ulp_diff(y, y_ref)
+    n = d.numel()
+    return {"max_ulp": int(d.max()), "frac_within_1ulp": float((d <= 1).sum()) / n, "frac_equal": float((d == 0).sum()) / n}
+
+
+def time_us(fn, n_variants, iters, warmup):
+    for i in range(warmup):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i % n_variants)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def randn(shape, std=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+def variants(bytes_per_variant, rotate_mb=400.0):
+    return max(1, min(8, math.ceil(rotate_mb * 1e6 / max(1, bytes_per_variant))))
+
+
+def race_dense(ops, ref, M, N, K, iters, warmup, w_std=0.02):
+    nv = variants(N * K)
+    xq, xs = ops.quantize_fp8_row(randn((M, K), seed=1))
+    ws = [ops.quantize_fp8_row(randn((N, K), w_std, seed=10 + i)) for i in range(nv)]
+    y, y_ref = (torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    # the instance the reference's heuristic picks on sm_100 (csrc/gemm/cutlass/f8f8bf16_rowwise.cu:24-50)
+    ref_fn = ref.f8f8bf16_rowwise_small if M <= 128 else ref.f8f8bf16_rowwise_large
+    ours = time_us(lambda i: ops.f8f8bf16_rowwise_out(xq, ws[i][0], xs, ws[i][1], y), nv, iters, warmup)
+    theirs = time_us(lambda i: ref_fn(xq, ws[i][0], xs, ws[i][1], y_ref), nv, iters, warmup)
+    ops.f8f8bf16_rowwise_out(xq, ws[0][0], xs, ws[0][1], y)
+    ref_fn(xq, ws[0][0], xs, ws[0][1], y_ref)
+    torch.cuda.synchronize()
+    flops = 2.0 * M * N * K
+    return {"case": f"f8f8bf16_rowwise M={M} N={N} K={K}", "ours_us": ours, "ref_us": theirs,
+            "ours_tflops": flops / ours / 1e6, "ref_tflops": flops / theirs / 1e6, "ours_over_ref_speed": theirs / ours,
+            "ref_instance": "128_64_128_1_1_1" if M <= 128 else "128_256_128_2_1_1", **compare(y, y_ref)}
+
+
+def race_grouped(ops, ref, E, tokens, N, K, iters, warmup):
+    from mslk_b200.microbench import zipf_counts
+    counts = zipf_counts(E, tokens)
+    ms = counts.to(torch.int64).cuda()
+    xq, xs = ops.quantize_fp8_row(randn((tokens, K), seed=2))
+    wq, ws = ops.quantize_fp8_row(randn((E, N, K), 0.02, seed=3))
+    y_ref = torch.empty((tokens * N,), dtype=torch.bfloat16, device="cuda")
+    ours = time_us(lambda i: ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws.view(-1), ms), 1, iters, warmup)
+    theirs = time_us(lambda i: ref.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms, y_ref), 1, iters, warmup)
+    y = ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws.view(-1), ms)
+    yr = ref.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms, y_ref)
+    torch.cuda.synchronize()
+    flops = 2.0 * tokens * N * K
+    return {"case": f"f8f8bf16_rowwise_grouped_stacked E={E} tokens={tokens} N={N} K={K} (Zipf 1.2, two empty experts)",
+            "ours_us": ours, "ref_us": theirs, "ours_tflops": flops / ours / 1e6, "ref_tflops": flops / theirs / 1e6,
+            "ours_over_ref_speed": theirs / ours, "ref_instance": "grouped_256_256_128_2_1_1", **compare(y, yr)}
+
+
+def race_nvfp4(ops, ref, M, N, K, iters, warmup):
+    nv = variants(N * K // 2)
+    x = randn((M, K), seed=4)
+    gx = (448.0 * 6.0) / x.abs().amax().float()
+    xq, sx = ops.quantize_nvfp4(x, gx)
+    ws = []
+    for i in range(nv):
+        w = randn((N, K), seed=20 + i)
+        gw = (448.0 * 6.0) / w.abs().amax().float()
+        wq, sw = ops.quantize_nvfp4(w, gw)
+        ws.append((wq, sw, (1.0 / (gx * gw)).reshape(1)))
+    y, y_ref = (torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    # csrc/gemm/cutlass/f4f4bf16.cu:44-1266: 256_256_2_1_1 for 8192^3, 256_128_4_1_1 for M <= 64 at (28672, 8192)
+    ref_fn = ref.f4f4bf16_small if M <= 128 else ref.f4f4bf16_large
+    ours = time_us(lambda i: ops.f4f4bf16(xq, ws[i][0], sx, ws[i][1], output=y, global_scale=ws[i][2]), nv, iters, warmup)
+    theirs = time_us(lambda i: ref_fn(xq, ws[i][0], sx, ws[i][1], y_ref, ws[i][2]), nv, iters, warmup)
+    ops.f4f4bf16(xq, ws[0][0], sx, ws[0][1], output=y, global_scale=ws[0][2])
+    ref_fn(xq, ws[0][0], sx, ws[0][1], y_ref, ws[0][2])
+    torch.cuda.synchronize()
+    flops = 2.0 * M * N * K
+    return {"case": f"f4f4bf16 (NVFP4) M={M} N={N} K={K}", "ours_us": ours, "ref_us": theirs,
+            "ours_tflops": flops / ours / 1e6, "ref_tflops": flops / theirs / 1e6, "ours_over_ref_speed": theirs / ours,
+            "ref_instance": "256_128_4_1_1" if M <= 128 else "256_256_2_1_1", **compare(y, y_ref)}
+
+
+def race_quantize(ops, ref_quant, M, K, iters, warmup):
+    nv = variants(M * K * 2)
+    xs = [randn((M, K), seed=30 + i) for i in range(nv)]
+    ours = time_us(lambda i: ops.quantize_fp8_row(xs[i]), nv, iters, warmup)
+    theirs = time_us(lambda i: ref_quant(xs[i]), nv, iters, warmup)
+    q, s = ops.quantize_fp8_row(xs[0])
+    qr, sr = ref_quant(xs[0])
+    byts = 3.0 * M * K + 4.0 * M
+    return {"case": f"quantize_fp8_row M={M} K={K} bf16", "ours_us": ours, "ref_us": theirs, "ours_gbs": byts / ours / 1e3,
+            "ref_gbs": byts / theirs / 1e3, "ours_over_ref_speed": theirs / ours,
+            "bytes_equal": bool(torch.equal(q.view(torch.uint8), qr.view(torch.uint8))), "scales_equal": bool(torch.equal(s, sr)),
+            "ref_kernel": "triton_quantize_fp8_row (mslk/quantize/triton/fp8_quantize.py:210-316)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true", help="headline shapes only")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    lib = os.path.join(HERE, "_ref", "libmslk_ref_gpu.so")
+    if not os.path.exists(lib):
+        print(json.dumps({"unavailable": f"{lib} is missing: run baseline/build_ref_gpu.py"}))
+        return
+    from mslk_b200 import ops
+    torch.ops.load_library(lib)
+    ref = torch.ops.mslk_ref
+    lines = []
+
+    def emit(r):
+        lines.append(r)
+        print(json.dumps(r), flush=True)
+
+    llama = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
+    emit(race_dense(ops, ref, 8192, 8192, 8192, args.iters, args.warmup))
+    for M in ((8192,) if args.quick else (8192, 2048, 128, 16, 1)):
+        for N, K in llama:
+            emit(race_dense(ops, ref, M, N, K, args.iters if M >= 2048 else 4 * args.iters, args.warmup))
+    if not args.quick:
+        emit(race_dense(ops, ref, 4096, 4096, 4096, args.iters, args.warmup))
+        for N, K in ((57344 // 8, 8192), (8192, 28672 // 8)):
+            emit(race_dense(ops, ref, 8192, N, K, args.iters, args.warmup, w_std=0.01))
+    for N, K in ((16384, 5120), (5120, 8192)):
+        emit(race_grouped(ops, ref, 16, 16384, N, K, args.iters, args.warmup))
+    emit(race_nvfp4(ops, ref, 8192, 8192, 8192, args.iters, args.warmup))
+    for M in (1, 32):
+        emit(race_nvfp4(ops, ref, M, 28672, 8192, 4 * args.iters, args.warmup))
+    pyref = os.path.join(HERE, "_ref", "pyref")
+    if os.path.isdir(pyref):
+        os.environ["MSLK_PYTHON_ONLY"] = "1"
+        sys.path.insert(0, pyref)
+        for name in [m for m in sys.modules if m == "mslk" or m.startswith("mslk.")]:
+            del sys.modules[name]
+        from mslk.quantize.triton.fp8_quantize import triton_quantize_fp8_row
+        for M, K in ((8192, 4096), (8192, 14336), (8192, 8192), (8192, 28672), (16384, 5120)):
+            emit(race_quantize(ops, triton_quantize_fp8_row, M, K, args.iters, args.warmup))
+    if args.out:
+        os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
+        with open(args.out, "w") as f:
+            for r in lines:
+                f.write(json.dumps(r) + "\n")
+
+
+if __name__ == "__main__":
+    main()

@@ -47,6 +47,16 @@ const char *mslk_b200_last_error(void);
 int mslk_b200_device_status(int *status_out);
 
 /*
+ * Self-test of the bounded waits every pipeline kernel of this library uses: launches one tiny CTA that
+ * waits on an mbarrier nothing ever arrives on, with `limit_ns` (<= 100 ms) as the limit instead of the
+ * kernels' 2 s.  The wait gives up by itself: the kernel stores the epilogue-timeout code (3) in the device
+ * status word, writes 1 to *returned_flag (device int, may be NULL) and returns normally -- the context stays
+ * usable.  The reference's nearest analogue is the launch-error check of
+ * include/mslk/utils/kernel_launcher.cuh:420-448; it has no device-side wait bound.
+ */
+int mslk_b200_selftest_wait_timeout(uint64_t limit_ns, int *returned_flag, void *stream);
+
+/*
  * Per-row FP8 (e4m3fn) quantization.
  * Replaces: mslk/quantize/triton/fp8_quantize.py:36-207 (_kernel_quantize_fp8_row)
  *           as launched by triton_quantize_fp8_row (:210-316).

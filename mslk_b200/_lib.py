@@ -26,6 +26,8 @@ lib.mslk_b200_abi_version.restype = _int
 lib.mslk_b200_last_error.restype = ctypes.c_char_p
 lib.mslk_b200_device_status.argtypes = [ctypes.POINTER(_int)]
 lib.mslk_b200_device_status.restype = _int
+lib.mslk_b200_selftest_wait_timeout.argtypes = [ctypes.c_uint64, _vp, _vp]
+lib.mslk_b200_selftest_wait_timeout.restype = _int
 lib.mslk_b200_quantize_fp8_row.argtypes = [_vp, _int] + [_i64] * 9 + [_vp, _vp, _f32, _vp, _vp, _vp]
 lib.mslk_b200_quantize_fp8_row.restype = _int
 lib.mslk_b200_f8f8bf16_rowwise.argtypes = [_vp, _vp, _vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]

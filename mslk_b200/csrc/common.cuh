@@ -78,17 +78,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 
 // Bounded wait.  Returns false (after recording `code` in *status and raising the
-// CTA-wide abort flag) when the barrier phase does not complete within
-// kWaitTimeoutNs, or as soon as another role of this CTA has raised the flag.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status, int code) {
+// CTA-wide abort flag) when the barrier phase does not complete within `limit_ns`,
+// or as soon as another role of this CTA has raised the flag.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status,
+                                                int code, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xffu) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -96,6 +96,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
   }
   return true;
+}
+// The pipeline waits of the kernels: bounded by kWaitTimeoutNs.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int *status, int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, status, code, kWaitTimeoutNs);
 }
 
 // ---------------------------------------------------------------- TMA

@@ -28,6 +28,7 @@
 // status code, drains, frees its tensor memory and returns.
 #include "gemm_f8_common.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace mslk_b200 {
@@ -279,9 +280,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
 template <int BN>
 int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, int grid, cudaStream_t st) {
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; two first calls may both set the (idempotent) attribute
   int dev = 0;
-  cudaGetDevice(&dev);
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
   constexpr size_t smem = smem_bytes<BN>();
   static_assert(smem <= 232448, "shared memory budget exceeded");
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

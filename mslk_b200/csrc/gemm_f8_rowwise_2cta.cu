@@ -22,6 +22,7 @@
 // control path of both CTAs reaches them.
 #include "gemm_f8_common.cuh"
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -409,9 +410,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 }  // namespace
 
 int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cudaStream_t st) {
-  static int max_pairs[64] = {};
+  static std::atomic<int> max_pairs[64];   // zero-initialised; a racing first call computes the same value
   int dev = 0;
-  cudaGetDevice(&dev);
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
   if (dev < 0 || dev >= 64) return -1;
 
   cudaLaunchConfig_t cfg = {};
@@ -450,7 +451,8 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
                                           : static_cast<int64_t>(p.G) * ((p.group_m + kPairRows - 1) / kPairRows);
   const int64_t tiles_ub = row_blocks_ub *
                            ((p.N + kPairBN - 1) / kPairBN);
-  const int pairs = static_cast<int>(tiles_ub < max_pairs[dev] ? tiles_ub : max_pairs[dev]);
+  const int64_t mp = max_pairs[dev].load();
+  const int pairs = static_cast<int>(tiles_ub < mp ? tiles_ub : mp);
 
   CUtensorMap ta, tb, ta32, ta64;
   if (int rc = make_tmap_2d_bytes(&ta, xq, p.K, p.total_m, p.K, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;

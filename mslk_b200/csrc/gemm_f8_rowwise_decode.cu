@@ -21,6 +21,7 @@
 // (thread = weight row).  All pipeline waits are bounded (common.cuh).
 #include "gemm_f8_common.cuh"
 
+#include <atomic>
 #include <algorithm>
 #include <cstdlib>
 #include <mutex>
@@ -286,9 +287,9 @@ __global__ void __launch_bounds__(kNumThreads, 2)
 
 template <int BT>
 int launch_decode(const CUtensorMap &tw, const CUtensorMap &tx, const DecodeParams &p, int n_tiles, cudaStream_t st) {
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; two first calls may both set the (idempotent) attribute
   int dev = 0;
-  cudaGetDevice(&dev);
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
   constexpr size_t smem = decode_smem_bytes<BT>();
   static_assert(smem <= 113 * 1024, "two CTAs per SM need at most ~113 KB each");
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -458,7 +459,7 @@ namespace mslk_b200 {
 namespace gemm_f8 {
 namespace {
 
-constexpr size_t kBuiltinScratchBytes = 8u << 20;  // 8 MiB: every shape with M <= 32, smaller ones up to M = 128
+constexpr size_t kBuiltinScratchBytes = 8u << 20;  // 8 MiB: bounds the shapes with 33..128 tokens (fewer tokens use no scratch)
 constexpr int kNoAllocMaxTokens = 128;             // what the weight-streaming kernel itself can take
 static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
 
@@ -503,12 +504,16 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, 
     return fail(1, "%s: K (%lld) must be a positive multiple of 16", name, (long long)K);
   if (!xq || !wq || !x_scale || !w_scale || !y) return fail(1, "%s: null pointer argument", name);
   if (bias_kind != MSLK_B200_BIAS_NONE && !bias) return fail(1, "%s: bias_kind set but bias is null", name);
-  const size_t need = decode_scratch_bytes(M, N, K, sm_count());
-  if (need > kBuiltinScratchBytes)
-    return fail(1, "%s: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in buffer holds %zu", name,
-                (long long)M, (long long)N, (long long)K, need, kBuiltinScratchBytes);
+  // Up to 32 tokens K is split inside thread-block clusters: no scratch, no size limit, no address look-up.
+  // Above, the split-K partial tiles live in the built-in array, whose size bounds the shapes served.
   void *scratch = nullptr;
-  if (int rc = builtin_scratch_ptr(&scratch)) return rc;
+  if (M > kDecodeMaxTokens) {
+    const size_t need = decode_scratch_bytes(M, N, K, sm_count());
+    if (need > kBuiltinScratchBytes)
+      return fail(1, "%s: M=%lld N=%lld K=%lld needs %zu bytes of scratch, the built-in buffer holds %zu", name,
+                  (long long)M, (long long)N, (long long)K, need, kBuiltinScratchBytes);
+    if (int rc = builtin_scratch_ptr(&scratch)) return rc;
+  }
   int *status = device_status_ptr();
   if (!status) return 2;
   GemmParams p;
@@ -525,8 +530,7 @@ MSLK_API int mslk_b200_f8f8bf16_rowwise_noalloc(const void *xq, const void *wq, 
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
   default_placement(p);
-  // Up to 32 tokens K is split inside thread-block clusters, which need no scratch at all (and are faster);
-  // above, the built-in array holds the partial tiles and the tickets are zeroed on the stream before the launch.
+  // The tickets in the built-in array are zeroed on the stream before the launch.
   if (M <= kDecodeMaxTokens)
     return launch_decode_kernel(xq, wq, p, nullptr, 0, false, static_cast<cudaStream_t>(stream));
   return launch_decode_kernel(xq, wq, p, scratch, kBuiltinScratchBytes, false, static_cast<cudaStream_t>(stream));

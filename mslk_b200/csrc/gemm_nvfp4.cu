@@ -25,6 +25,7 @@
 #include "gemm_nvfp4_pair.h"
 #include "host.h"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace mslk_b200 {
@@ -363,9 +364,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 
 template <int BN>
 int launch(const CUtensorMap &ta, const CUtensorMap &tb, const Fp4Params &p, int grid, cudaStream_t st) {
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; two first calls may both set the (idempotent) attribute
   int dev = 0;
-  cudaGetDevice(&dev);
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
   constexpr size_t smem = smem_bytes<BN>();
   static_assert(smem <= 232448, "shared memory budget exceeded");
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

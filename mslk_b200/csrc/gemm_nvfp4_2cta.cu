@@ -25,6 +25,7 @@
 
 #include "common.cuh"
 
+#include <atomic>
 #include <cstdlib>
 
 namespace mslk_b200 {
@@ -331,9 +332,9 @@ int launch_bk(const void *xq, const void *wq, const void *x_scale, const void *w
   using C = PCfg<BK>;
   constexpr size_t kSmemBytes = smem_bytes<BK>();
   static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
-  static int max_pairs[64] = {};
+  static std::atomic<int> max_pairs[64];   // zero-initialised; a racing first call computes the same value
   int dev = 0;
-  cudaGetDevice(&dev);
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
   if (dev < 0 || dev >= 64) return -1;
 
   cudaLaunchConfig_t cfg = {};
@@ -368,7 +369,8 @@ int launch_bk(const void *xq, const void *wq, const void *x_scale, const void *w
   const int64_t m_tiles = (static_cast<int64_t>(p.M) + kPairRows - 1) / kPairRows;
   const int64_t n_tiles = (static_cast<int64_t>(p.N) + kPairBN - 1) / kPairBN;
   const int64_t tiles = m_tiles * n_tiles;
-  const int pairs = static_cast<int>(tiles < max_pairs[dev] ? tiles : max_pairs[dev]);
+  const int64_t mp = max_pairs[dev].load();
+  const int pairs = static_cast<int>(tiles < mp ? tiles : mp);
 
   const int64_t kbytes = p.K / 2;
   const uint64_t a_blocks = (static_cast<uint64_t>(p.M) + kBM - 1) / kBM, b_blocks = (static_cast<uint64_t>(p.N) + kBM - 1) / kBM;

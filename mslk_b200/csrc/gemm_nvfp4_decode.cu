@@ -27,6 +27,7 @@
 
 #include "common.cuh"
 
+#include <atomic>
 #include <algorithm>
 #include <cstdlib>
 
@@ -305,9 +306,9 @@ __global__ void __launch_bounds__(kNumThreads, 2)
 
 template <int BT>
 int launch_decode(const CUtensorMap &tw, const CUtensorMap &tx, const KParams &p, int n_tiles, cudaStream_t st) {
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];   // zero-initialised; two first calls may both set the (idempotent) attribute
   int dev = 0;
-  cudaGetDevice(&dev);
+  if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
   constexpr size_t smem = decode_smem_bytes<BT>();
   static_assert(smem <= 113 * 1024, "two CTAs per SM need at most ~113 KB each");
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "../../include/mslk_b200.h"
+#include "common.cuh"
 
 namespace mslk_b200 {
 
@@ -123,6 +124,38 @@ int make_tmap_2d_bf16(CUtensorMap *out, const void *base, uint64_t cols, uint64_
 }
 
 }  // namespace mslk_b200
+
+namespace mslk_b200 {
+namespace {
+// One CTA waits on an mbarrier that nothing ever arrives on, with the caller's (short) limit: the bounded
+// wait must give up, leave its code in the status word and let the kernel return normally.
+__global__ void selftest_wait_timeout_kernel(unsigned long long limit_ns, int *status, int *returned) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait_limit(&bar, 0, &abort_flag, status, kStatusEpilogueTimeout, limit_ns);
+  __syncthreads();
+  // the other threads see the abort flag, as the other roles of a GEMM CTA do
+  if (threadIdx.x == 32 && returned) *returned = abort_flag ? 1 : (ok ? 0 : 1);
+}
+}  // namespace
+}  // namespace mslk_b200
+
+MSLK_API int mslk_b200_selftest_wait_timeout(uint64_t limit_ns, int *returned_flag, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  if (limit_ns == 0 || limit_ns > 100000000ull) return fail(1, "selftest_wait_timeout: limit must be 1 ns .. 100 ms");
+  int *status = device_status_ptr();
+  if (!status) return 2;
+  selftest_wait_timeout_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, status, returned_flag);
+  return check_cuda(cudaGetLastError(), "selftest_wait_timeout launch");
+}
 
 MSLK_API int mslk_b200_abi_version(void) { return MSLK_B200_ABI_VERSION; }
 

@@ -29,6 +29,16 @@ void check_rc(int rc, const char *what) {
 
 void *stream_of(const at::Tensor &t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
 
+// Every tensor whose raw pointer reaches a kernel must live on the device the kernel runs on: a CPU
+// tensor or one on another GPU would make the kernel dereference a host or foreign address.
+void same_device(const at::Tensor &t, const at::Tensor &ref, const char *op, const char *arg) {
+  TORCH_CHECK(t.is_cuda(), op, ": ", arg, " must be a CUDA tensor (this library has no CPU path)");
+  TORCH_CHECK(t.device() == ref.device(), op, ": ", arg, " must be on the same device as XQ (", t.device(), " vs ",
+              ref.device(), ")");
+}
+
+int64_t round_up(int64_t v, int64_t to) { return (v + to - 1) / to * to; }
+
 int64_t prod_leading(const at::Tensor &t) {
   int64_t p = 1;
   for (int64_t i = 0; i + 1 < t.dim(); ++i) p *= t.size(i);
@@ -44,7 +54,10 @@ void rowwise_impl(const at::Tensor &XQ, const at::Tensor &WQ, const at::Tensor &
               "f8f8bf16_rowwise: XQ and WQ must be float8_e4m3fn");
   TORCH_CHECK(x_scale.dtype() == at::kFloat && w_scale.dtype() == at::kFloat,
               "f8f8bf16_rowwise: x_scale and w_scale must be float32");
-  TORCH_CHECK(x_scale.is_cuda() && w_scale.is_cuda(), "f8f8bf16_rowwise: scales must be CUDA tensors");
+  same_device(WQ, XQ, "f8f8bf16_rowwise", "WQ");
+  same_device(x_scale, XQ, "f8f8bf16_rowwise", "x_scale");
+  same_device(w_scale, XQ, "f8f8bf16_rowwise", "w_scale");
+  same_device(out, XQ, "f8f8bf16_rowwise", "output");
   TORCH_CHECK(XQ.dim() >= 1 && WQ.dim() >= 1, "f8f8bf16_rowwise: XQ and WQ need at least one dimension");
   const int64_t K = XQ.size(-1);
   const int64_t M = prod_leading(XQ);
@@ -57,7 +70,8 @@ void rowwise_impl(const at::Tensor &XQ, const at::Tensor &WQ, const at::Tensor &
   at::Tensor b;
   if (bias.has_value()) {
     b = bias->contiguous();
-    TORCH_CHECK(b.is_cuda() && b.numel() == N, "f8f8bf16_rowwise: bias must be a CUDA tensor of N elements");
+    same_device(b, XQ, "f8f8bf16_rowwise", "bias");
+    TORCH_CHECK(b.numel() == N, "f8f8bf16_rowwise: bias must have N elements");
     TORCH_CHECK(b.dtype() == at::kFloat || b.dtype() == at::kBFloat16,
                 "f8f8bf16_rowwise: bias must be float32 or bfloat16");
     kind = b.dtype() == at::kFloat ? MSLK_B200_BIAS_F32 : MSLK_B200_BIAS_BF16;
@@ -97,6 +111,9 @@ at::Tensor f8f8bf16_rowwise_grouped_stacked(at::Tensor XQ, at::Tensor WQ, at::Te
   TORCH_CHECK(WQ.dim() == 3 && WQ.size(0) == M_sizes.numel(), n, ": WQ must be [G,N,K] with G == M_sizes.numel()");
   TORCH_CHECK(XQ.dim() == 2 && XQ.size(1) == WQ.size(2), n, ": XQ must be [total_M,K] with the K of WQ");
   TORCH_CHECK(x_scale.dtype() == at::kFloat && w_scale.dtype() == at::kFloat, n, ": scales must be float32");
+  same_device(WQ, XQ, n, "WQ");
+  same_device(x_scale, XQ, n, "x_scale");
+  same_device(w_scale, XQ, n, "w_scale");
   const int64_t G = WQ.size(0), N = WQ.size(1), K = WQ.size(2), total_M = XQ.size(0);
   TORCH_CHECK(x_scale.numel() == total_M && w_scale.numel() == G * N, n, ": scale sizes must equal total_M and G*N");
   at::Tensor Y = at::empty({total_M, N}, XQ.options().dtype(at::kBFloat16));
@@ -127,22 +144,25 @@ at::Tensor f8f8bf16_rowwise_batched(at::Tensor XQ, at::Tensor WQ, at::Tensor x_s
   TORCH_CHECK(WQ.size(0) == B, n, ": XQ and WQ disagree on the batch count");
   if (M == 0 || N == 0 || K == 0) return at::zeros({B, M, N}, XQ.options().dtype(at::kBFloat16));
   TORCH_CHECK(XQ.size(2) == K, n, ": XQ and WQ disagree on K");
-  TORCH_CHECK(x_scale.is_cuda() && w_scale.is_cuda() && x_scale.numel() == B * M && w_scale.numel() == B * N, n,
-              ": scales must be CUDA tensors of B*M and B*N elements");
+  same_device(WQ, XQ, n, "WQ");
+  same_device(x_scale, XQ, n, "x_scale");
+  same_device(w_scale, XQ, n, "w_scale");
+  TORCH_CHECK(x_scale.numel() == B * M && w_scale.numel() == B * N, n, ": scales must have B*M and B*N elements");
   at::Tensor b;
   int kind = MSLK_B200_BIAS_NONE;
   if (bias.has_value()) {
     b = bias->contiguous();
     TORCH_CHECK(b.dtype() == at::kFloat, "Bias type must be float32 if provided.");
-    TORCH_CHECK(b.is_cuda() && b.numel() == B * N, n, ": bias must be a CUDA tensor of B*N elements");
+    same_device(b, XQ, n, "bias");
+    TORCH_CHECK(b.numel() == B * N, n, ": bias must have B*N elements");
     kind = MSLK_B200_BIAS_F32;
   }
   at::Tensor Y;
   if (output.has_value()) {
     Y = *output;
     TORCH_CHECK(Y.dtype() == at::kBFloat16);
-    TORCH_CHECK(Y.is_cuda() && Y.is_contiguous() && Y.numel() == B * M * N, n,
-                ": output must be a contiguous CUDA tensor of B*M*N elements");
+    same_device(Y, XQ, n, "output");
+    TORCH_CHECK(Y.is_contiguous() && Y.numel() == B * M * N, n, ": output must be a contiguous tensor of B*M*N elements");
   } else {
     Y = at::empty({B, M, N}, XQ.options().dtype(at::kBFloat16));
   }
@@ -170,9 +190,22 @@ at::Tensor f4f4bf16(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor
   const int64_t M = XQ.size(0), K = XQ.size(1) * 2, N = WQ.size(0);
   TORCH_CHECK(WQ.size(1) * 2 == K, "f4f4bf16: XQ and WQ disagree on K");
   TORCH_CHECK(N % 16 == 0 && K % 16 == 0, "f4f4bf16: N and K must be multiples of 16");
+  same_device(WQ, XQ, "f4f4bf16", "WQ");
+  same_device(x_scale, XQ, "f4f4bf16", "x_scale");
+  same_device(w_scale, XQ, "f4f4bf16", "w_scale");
+  same_device(*global_scale, XQ, "f4f4bf16", "global_scale");
+  // the kernels copy whole 512-byte scale atoms of the swizzled layout padded to [roundup(rows,128), roundup(K/16,4)]
+  TORCH_CHECK(x_scale.element_size() == 1 && w_scale.element_size() == 1, "f4f4bf16: scales must be 1-byte (e4m3) tensors");
+  TORCH_CHECK(x_scale.numel() >= round_up(M, 128) * round_up(K / 16, 4),
+              "f4f4bf16: x_scale holds ", x_scale.numel(), " scales, the padded swizzled layout of [", M, ", ", K / 16,
+              "] needs ", round_up(M, 128) * round_up(K / 16, 4));
+  TORCH_CHECK(w_scale.numel() >= round_up(N, 128) * round_up(K / 16, 4),
+              "f4f4bf16: w_scale holds ", w_scale.numel(), " scales, the padded swizzled layout of [", N, ", ", K / 16,
+              "] needs ", round_up(N, 128) * round_up(K / 16, 4));
   at::Tensor Y;
   if (output.has_value()) {
     Y = *output;
+    same_device(Y, XQ, "f4f4bf16", "output");
     TORCH_CHECK(Y.dtype() == at::kBFloat16 && Y.is_contiguous() && Y.dim() == 2 && Y.size(0) == M && Y.size(1) == N,
                 "f4f4bf16: output must be a contiguous bfloat16 [M,N] tensor");
   } else {
@@ -247,7 +280,11 @@ std::tuple<at::Tensor, at::Tensor> quantize_nvfp4(at::Tensor x, std::optional<at
   at::Tensor q = at::empty({M, K / 2}, x.options().dtype(at::kByte));
   at::Tensor s = at::empty({pr, pc}, x.options().dtype(at::kFloat8_e4m3fn));
   at::Tensor gs;
-  if (global_scale.has_value()) gs = global_scale->reshape({-1}).to(at::kFloat);
+  if (global_scale.has_value()) {
+    TORCH_CHECK(global_scale->is_cuda() && global_scale->device() == x.device(),
+                "quantize_nvfp4: global_scale must be on the same device as x");
+    gs = global_scale->reshape({-1}).to(at::kFloat);
+  }
   c10::cuda::CUDAGuard guard(x.device());
   check_rc(mslk_b200_quantize_nvfp4(x2.data_ptr(), M, K, x2.stride(0), gs.defined() ? gs.data_ptr<float>() : nullptr,
                                     q.data_ptr(), s.data_ptr(), stream_of(x)),
@@ -260,9 +297,18 @@ std::tuple<at::Tensor, at::Tensor> quantize_nvfp4(at::Tensor x, std::optional<at
   return {q.view(qshape), s.view(sshape)};
 }
 
+// Status word of the current device: 0, or the code left by a kernel whose bounded pipeline wait expired /
+// that skipped an out-of-range index.  Synchronises the device and clears the word; not for use under capture.
+int64_t device_status() {
+  int st = 0;
+  check_rc(mslk_b200_device_status(&st), "device_status");
+  return st;
+}
+
 }  // namespace
 
 TORCH_LIBRARY_FRAGMENT(mslk, m) {
+  m.def("device_status() -> int", device_status);
   m.def(
       "f8f8bf16_rowwise(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor? bias=None, bool "
       "use_fast_accum=True) -> Tensor");

@@ -119,6 +119,7 @@ def f8f8bf16_rowwise_out(XQ, WQ, x_scale, w_scale, output, bias=None, use_fast_a
     ``use_fast_accum`` is accepted for signature parity and has no effect (as on the
     reference's sm_100 path)."""
     dev = _check_rowwise_args("f8f8bf16_rowwise", XQ, WQ, x_scale, w_scale)
+    _require_cuda("f8f8bf16_rowwise", XQ, output)
     K = XQ.shape[-1]
     M = math.prod(XQ.shape[:-1])
     N = math.prod(WQ.shape[:-1])
@@ -184,6 +185,7 @@ def f8f8bf16_rowwise_batched(XQ, WQ, x_scale, w_scale, bias=None, use_fast_accum
             raise RuntimeError(f"{name}: bias must have B*N elements")
         bias = bias.contiguous()
         kind = 1
+    _require_cuda(name, XQ, output)
     if output is None:
         output = torch.empty((B, M, N), dtype=torch.bfloat16, device=dev)
     elif output.dtype != torch.bfloat16 or output.numel() != B * M * N or not output.is_contiguous():
@@ -256,6 +258,17 @@ def nvfp4_scale_shape(rows: int, K: int):
     return ((rows + 127) // 128 * 128, (K // 16 + 3) // 4 * 4)
 
 
+def _check_nvfp4_scale_extent(name: str, arg: str, scale: torch.Tensor, rows: int, K: int, groups: int = 1) -> None:
+    """The kernels bulk-copy whole 512-byte atoms of the swizzled scale layout, padded to
+    ``[roundup(rows, 128), roundup(K/16, 4)]`` per group: a shorter tensor would be read past its end."""
+    if scale.element_size() != 1:
+        raise RuntimeError(f"{name}: {arg} must be a 1-byte (e4m3) tensor, got {scale.dtype}")
+    pr, pc = nvfp4_scale_shape(rows, K)
+    need = groups * pr * pc
+    if scale.numel() < need:
+        raise RuntimeError(f"{name}: {arg} holds {scale.numel()} scales; the padded swizzled layout needs {need}")
+
+
 def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
     """Returns ``(xq uint8 [..., K/2], scales float8_e4m3fn [rows_pad, cols_pad] swizzled)``."""
     dev = _require_cuda("quantize_nvfp4", x, global_scale)
@@ -294,6 +307,8 @@ def f4f4bf16(XQ, WQ, x_scale, w_scale, output=None, global_scale=None, mxfp4_blo
         raise RuntimeError(f"{name}: K mismatch")
     if N % 16 != 0 or K % 16 != 0:
         raise RuntimeError(f"{name}: N and K must be multiples of 16")
+    _check_nvfp4_scale_extent(name, "x_scale", x_scale, M, K)
+    _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K)
     if output is None:
         output = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     elif output.dtype != torch.bfloat16 or tuple(output.shape) != (M, N) or not output.is_contiguous():
@@ -319,6 +334,7 @@ def f8f8bf16_rowwise_allgather(XQ, WQ_shard, x_scale, w_scale_shard, out_ptrs, r
     Ranks must synchronise afterwards before reading columns written by peers."""
     import ctypes
     dev = _check_rowwise_args("f8f8bf16_rowwise_allgather", XQ, WQ_shard, x_scale, w_scale_shard)
+    _require_cuda("f8f8bf16_rowwise_allgather", XQ, out_local, bias_shard)
     M, K = XQ.shape
     n_local = WQ_shard.shape[0]
     world = len(out_ptrs)
@@ -359,7 +375,7 @@ def f8f8bf16_rowwise_scatter(XQ_kshard, WQ_kshard, x_scale, w_scale, stage_ptrs,
 
 def reduce_slots(stage: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[rows, N] = sum_s stage[s]`` for a contiguous bf16 ``[slots, rows, N]`` tensor (fp32 accumulation)."""
-    dev = _require_cuda("reduce_slots", stage)
+    dev = _require_cuda("reduce_slots", stage, out)
     slots, rows, cols = stage.shape
     if stage.dtype != torch.bfloat16 or not stage.is_contiguous():
         raise RuntimeError("reduce_slots: stage must be a contiguous bfloat16 [slots, rows, N] tensor")
@@ -451,6 +467,10 @@ def f4f4bf16_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes, global_scale=Non
     gs = global_scale.reshape(-1).to(torch.float32)
     if gs.numel() != G:
         raise RuntimeError(f"{name}: global_scale must hold one value per group")
+    if total_M:
+        _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, groups=G)
+        # the group sizes live on the device: the host can only check the smallest layout any split of total_M needs
+        _check_nvfp4_scale_extent(name, "x_scale", x_scale, total_M, K)
     Y = torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
     if total_M == 0:
         return Y
@@ -485,6 +505,9 @@ def f4f4bf16_grouped_mm(XQ, WQ, x_scale, w_scale, offsets, output=None, global_s
     N, K = WQ.shape[-1], WQ.shape[-2] * 2
     if XQ.shape[1] * 2 != K or WQ.shape[0] != G:
         raise RuntimeError("for 2d-3d grouped GEMM, XQ shape must be (total_M, K) and WQ shape must be (G, K, N).")
+    if total_M and N:
+        _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, groups=G)
+        _check_nvfp4_scale_extent(name, "x_scale", x_scale, total_M, K)
     out = output if output is not None else torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
     if out.dim() != 2 or out.shape[0] != total_M or out.shape[1] != N or out.dtype != torch.bfloat16 or not out.is_contiguous():
         raise RuntimeError("for 2d-3d grouped GEMM, output shape must be (total_M, N).")

@@ -118,3 +118,61 @@ def test_torch_compile_uses_fake_kernels(mslk):
     x = torch.randn(64, 512, device="cuda").bfloat16()
     y = torch.compile(f, backend="eager", fullgraph=True)(x)
     torch.testing.assert_close(y, f(x))
+
+
+def test_export_strict_and_run(mslk):
+    """The reference's export case (test/gemm/gemm_test.py:259-289): export with strict=True, then run the
+    exported program on the GPU and compare with the eager call."""
+    from mslk.quantize.triton.fp8_quantize import quantize_fp8_row
+
+    class Mod(torch.nn.Module):
+        def forward(self, xq, wq, xs, ws):
+            return torch.ops.mslk.f8f8bf16_rowwise(xq, wq, xs, ws)
+
+    x = (torch.randn(256, 256, device="cuda") * 0.1).bfloat16()
+    w = (torch.randn(256, 256, device="cuda") * 0.01).bfloat16()
+    xq, xs = quantize_fp8_row(x)
+    wq, ws = quantize_fp8_row(w)
+    ep = torch.export.export(Mod().cuda(), (xq, wq, xs, ws), strict=True)
+    y = ep.module()(xq, wq, xs, ws)
+    assert torch.equal(y, mslk.f8f8bf16_rowwise(xq, wq, xs, ws))
+
+
+def test_operators_reject_a_cpu_tensor_in_every_pointer_argument(mslk):
+    """A host tensor in a slot whose raw pointer reaches a kernel must raise through TORCH_CHECK, not launch."""
+    from mslk.quantize.triton.fp8_quantize import quantize_fp8_row
+    x = (torch.randn(64, 256, device="cuda") * 0.1).bfloat16()
+    w = (torch.randn(128, 256, device="cuda") * 0.01).bfloat16()
+    xq, xs = quantize_fp8_row(x)
+    wq, ws = quantize_fp8_row(w)
+    out = torch.empty((64, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="output must be a CUDA tensor"):
+        mslk.f8f8bf16_rowwise_out(xq, wq, xs, ws, out.cpu())
+    with pytest.raises(RuntimeError, match="x_scale must be a CUDA tensor"):
+        mslk.f8f8bf16_rowwise(xq, wq, xs.cpu(), ws)
+    with pytest.raises(RuntimeError, match="bias must be a CUDA tensor"):
+        mslk.f8f8bf16_rowwise(xq, wq, xs, ws, bias=torch.zeros(128))
+    ms = torch.tensor([64], dtype=torch.int64, device="cuda")
+    with pytest.raises(RuntimeError, match="w_scale must be a CUDA tensor"):
+        mslk.f8f8bf16_rowwise_grouped_stacked(xq, wq[None], xs, ws.cpu(), ms)
+    with pytest.raises(RuntimeError, match="x_scale must be a CUDA tensor"):
+        mslk.f8f8bf16_rowwise_grouped_stacked(xq, wq[None], xs.cpu(), ws, ms)
+    # NVFP4: output, global_scale, short scale tensors
+    from mslk.quantize.triton.fp4_quantize import triton_quantize_nvfp4
+    from mslk.quantize.triton.fp4_utils import global_scale_nvfp4
+    gx, gw = global_scale_nvfp4(x), global_scale_nvfp4(w)
+    q4, sx = triton_quantize_nvfp4(x, gx)
+    w4, sw = triton_quantize_nvfp4(w, gw)
+    gs = 1 / (gx * gw)
+    with pytest.raises(RuntimeError, match="output must be a CUDA tensor"):
+        mslk.f4f4bf16(q4, w4, sx, sw, output=out.cpu(), global_scale=gs)
+    with pytest.raises(RuntimeError, match="global_scale must be a CUDA tensor"):
+        mslk.f4f4bf16(q4, w4, sx, sw, global_scale=gs.cpu())
+    with pytest.raises(RuntimeError, match="x_scale holds"):
+        mslk.f4f4bf16(q4, w4, sx.reshape(-1)[: 64 * 16], sw, global_scale=gs)
+    torch.testing.assert_close(mslk.f4f4bf16(q4, w4, sx, sw, global_scale=gs), (x @ w.T).to(torch.bfloat16), atol=5e-2, rtol=5e-2)
+
+
+def test_device_status_operator(mslk):
+    """torch.ops.mslk.device_status() reads (and clears) the device status word without ctypes."""
+    assert mslk.device_status() == 0

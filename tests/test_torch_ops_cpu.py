@@ -86,3 +86,91 @@ def test_nvfp4_layout_helpers_roundtrip():
     assert torch.equal(_from_blocked(b, (150, 9)), x)
     import oracle
     assert torch.equal(b, oracle.to_blocked(x))
+
+
+def _fake_cuda(make):
+    """Tensors that report device cuda:0 without a GPU (fake tensors): enough for the host-side argument
+    checks of mslk_b200.ops, which inspect devices / dtypes / shapes before any kernel is launched."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode(allow_non_fake_inputs=True):
+        return make()
+
+
+def test_ops_reject_a_cpu_tensor_in_every_pointer_argument():
+    """A CPU tensor in ANY slot whose raw pointer reaches a kernel must raise in Python, never launch."""
+    from mslk_b200 import ops
+    f8 = torch.float8_e4m3fn
+    xq, wq, xs, ws, out, bias = _fake_cuda(lambda: (
+        torch.empty((4, 64), dtype=f8, device="cuda"), torch.empty((128, 64), dtype=f8, device="cuda"),
+        torch.empty((4,), device="cuda"), torch.empty((128,), device="cuda"),
+        torch.empty((4, 128), dtype=torch.bfloat16, device="cuda"), torch.empty((128,), device="cuda")))
+    cpu = {"xq": torch.empty((4, 64)).to(f8), "wq": torch.empty((128, 64)).to(f8), "xs": torch.empty(4),
+           "ws": torch.empty(128), "out": torch.empty((4, 128), dtype=torch.bfloat16), "bias": torch.empty(128)}
+    for slot in ("xq", "wq", "xs", "ws", "out", "bias"):
+        args = {"xq": xq, "wq": wq, "xs": xs, "ws": ws, "out": out, "bias": bias}
+        args[slot] = cpu[slot]
+        with pytest.raises(RuntimeError, match="CUDA"):
+            ops.f8f8bf16_rowwise_out(args["xq"], args["wq"], args["xs"], args["ws"], args["out"], args["bias"])
+    # batched: user-provided output
+    xq3, wq3, xs3, ws3 = _fake_cuda(lambda: (
+        torch.empty((2, 4, 64), dtype=f8, device="cuda"), torch.empty((2, 128, 64), dtype=f8, device="cuda"),
+        torch.empty((2, 4), device="cuda"), torch.empty((2, 128), device="cuda")))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.f8f8bf16_rowwise_batched(xq3, wq3, xs3, ws3, output=torch.empty((2, 4, 128), dtype=torch.bfloat16))
+    # NVFP4: output and global_scale
+    q, wq4, sx, sw, gs = _fake_cuda(lambda: (
+        torch.empty((4, 32), dtype=torch.uint8, device="cuda"), torch.empty((128, 32), dtype=torch.uint8, device="cuda"),
+        torch.empty((128, 4), dtype=f8, device="cuda"), torch.empty((128, 4), dtype=f8, device="cuda"),
+        torch.empty((1,), device="cuda")))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.f4f4bf16(q, wq4, sx, sw, output=torch.empty((4, 128), dtype=torch.bfloat16), global_scale=gs)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.f4f4bf16(q, wq4, sx, sw, global_scale=torch.ones(1))
+
+
+def test_ops_reject_scale_tensors_shorter_than_the_padded_swizzled_layout():
+    """The NVFP4 kernels copy whole 512-byte scale atoms: an unpadded scale tensor would be read past its end."""
+    from mslk_b200 import ops
+    f8 = torch.float8_e4m3fn
+    M, N, K = 4, 144, 64                      # padded layouts: x [128, 4], w [256, 4]
+    q, wq, gs = _fake_cuda(lambda: (torch.empty((M, K // 2), dtype=torch.uint8, device="cuda"),
+                                    torch.empty((N, K // 2), dtype=torch.uint8, device="cuda"),
+                                    torch.empty((1,), device="cuda")))
+    ok_x, ok_w, short_x, short_w = _fake_cuda(lambda: (
+        torch.empty((128, 4), dtype=f8, device="cuda"), torch.empty((256, 4), dtype=f8, device="cuda"),
+        torch.empty((M, 4), dtype=f8, device="cuda"), torch.empty((N, 4), dtype=f8, device="cuda")))
+    with pytest.raises(RuntimeError, match="x_scale holds"):
+        ops.f4f4bf16(q, wq, short_x, ok_w, global_scale=gs)
+    with pytest.raises(RuntimeError, match="w_scale holds"):
+        ops.f4f4bf16(q, wq, ok_x, short_w, global_scale=gs)
+    # grouped: the weight scales of every group are padded separately
+    wg, ms = _fake_cuda(lambda: (torch.empty((2, N, K // 2), dtype=torch.uint8, device="cuda"),
+                                 torch.empty((2,), dtype=torch.int64, device="cuda")))
+    gs2 = _fake_cuda(lambda: torch.empty((2,), device="cuda"))
+    with pytest.raises(RuntimeError, match="w_scale holds"):
+        ops.f4f4bf16_grouped_stacked(q, wg, ok_x, ok_w, ms, gs2, use_mx=False)
+
+
+def test_export_strict_traces_through_the_fake_kernels(mslk):
+    """torch.export(strict=True) of a module that quantizes and multiplies, as the reference's
+    ExportCompileTests.test_f8f8bf16_export does (test/gemm/gemm_test.py:236-289); meta tensors need no GPU."""
+    from mslk.quantize.triton.fp8_quantize import quantize_fp8_row
+
+    class Mod(torch.nn.Module):
+        def forward(self, x, wq, ws, wg, wgs, m_sizes):
+            xq, xs = quantize_fp8_row(x)
+            y = torch.ops.mslk.f8f8bf16_rowwise(xq, wq, xs, ws)
+            z = torch.ops.mslk.f8f8bf16_rowwise_grouped_stacked(xq, wg, xs, wgs, m_sizes)
+            return y, z
+
+    f8 = torch.float8_e4m3fn
+    args = (torch.empty((64, 512), dtype=torch.bfloat16, device="meta"),
+            torch.empty((256, 512), dtype=f8, device="meta"), torch.empty((256,), device="meta"),
+            torch.empty((4, 128, 512), dtype=f8, device="meta"), torch.empty((512,), device="meta"),
+            torch.empty((4,), dtype=torch.int64, device="meta"))
+    ep = torch.export.export(Mod(), args, strict=True)
+    targets = [str(n.target) for n in ep.graph.nodes if n.op == "call_function"]
+    assert "triton.quantize_fp8_row.default" in targets
+    assert "mslk.f8f8bf16_rowwise.default" in targets and "mslk.f8f8bf16_rowwise_grouped_stacked.default" in targets
+    y, z = [n for n in ep.graph.nodes if n.op == "output"][0].args[0]
+    assert tuple(y.meta["val"].shape) == (64, 256) and tuple(z.meta["val"].shape) == (64, 128)
