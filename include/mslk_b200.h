@@ -240,6 +240,15 @@ int mslk_b200_f4f4bf16_ws(const void *xq, const void *wq, const void *x_scale,
                           void *stream);
 
 /*
+ * Diagnostics of the CTA-pair NVFP4 kernel's pipeline.  `dev_counters` is a device array of four 64-bit
+ * counters (zeroed by the caller) or NULL to switch the measurement off; while set, every launch of the pair
+ * kernel adds SM clock cycles summed over its CTA pairs: [0] the MMA-issuing lane waiting for operand stages
+ * to arrive, [1] the same lane waiting for the epilogue to hand back the accumulator, [2] that lane's whole
+ * loop, [3] the leader's TMA-issuing lane waiting for free stages.  No counterpart in the reference.
+ */
+int mslk_b200_debug_nvfp4_pair_timers(unsigned long long *dev_counters);
+
+/*
  * Grouped (stacked) NVFP4 GEMM for mixture-of-experts layers: group g multiplies its m_g stacked rows
  * of xq by its own weight block wq[g] and scales the result by global_scale[g].
  * Replaces: csrc/gemm/cutlass/f4f4bf16_grouped.cu:321-374 (f4f4bf16_grouped_stacked, NVFP4 mode) with

@@ -51,6 +51,8 @@ lib.mslk_b200_quantize_nvfp4.argtypes = [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _
 lib.mslk_b200_quantize_nvfp4.restype = _int
 lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f4f4bf16.restype = _int
+lib.mslk_b200_debug_nvfp4_pair_timers.argtypes = [_vp]
+lib.mslk_b200_debug_nvfp4_pair_timers.restype = _int
 lib.mslk_b200_f4f4bf16_workspace_bytes.argtypes = [_i64, _i64, _i64]
 lib.mslk_b200_f4f4bf16_workspace_bytes.restype = ctypes.c_size_t
 lib.mslk_b200_f4f4bf16_ws.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, ctypes.c_size_t, _vp]

@@ -87,7 +87,10 @@ def build_torch_ops(force: bool = False, verbose: bool = False) -> str:
     inc.append(f"-I{sysconfig.get_paths()['include']}")
     torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
     cmd = [
-        os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+        # the system g++: its libstdc++.so is the one libtorch uses.  ($CXX may point at a toolchain that links
+        # libstdc++ statically; a second copy of the stream/locale state inside this library crashes on the first
+        # formatted TORCH_CHECK message.)
+        os.environ.get("MSLK_B200_CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
         f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", "-DTORCH_EXTENSION_NAME=_torch_ops",
         *inc, src, "-o", TORCH_LIB,
         f"-L{PKG}", "-lmslk_b200", f"-L{torch_lib}", "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda", "-ltorch_cuda",

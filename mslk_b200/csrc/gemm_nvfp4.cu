@@ -214,85 +214,76 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    // The K blocks of all tiles of this CTA form one stream.  The scale atoms of block i+1 are
-    // copied to tensor memory (into the other of two column sets) BEFORE the instructions of
-    // block i are issued, so the copies run behind those instructions instead of in front of
-    // the ones that need them.
+    // Per stage: the stage's scale atoms are copied to tensor memory (alternating between two sets of scale
+    // columns, so a copy never lands on scales an earlier instruction still reads), then its instructions
+    // are issued; copies and instructions execute in issue order.  The descriptors of a stage differ from
+    // those of stage 0 only in the address field (16-byte units), so they are formed by one addition.
     if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
-      struct Pos {
-        int tile, kb, stage, local;
-        uint32_t phase;
-      };
-      auto advance = [&](Pos &q) {
-        if (++q.kb == k_blocks) {
-          q.kb = 0;
-          q.tile += gridDim.x;
-          ++q.local;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      uint32_t n = 0;
+      bool ok = true;
+      const uint32_t ring0 = smem_u32(ring);
+      const uint64_t da0 = make_kmajor_sw128_desc(ring0);
+      const uint64_t db0 = make_kmajor_sw128_desc(ring0 + C::kStageA);
+      const uint64_t dsfa0 = make_sf_atom_desc(ring0 + C::kStageA + C::kStageB);
+      const uint64_t dsfb0 = make_sf_atom_desc(ring0 + C::kStageA + C::kStageB + C::kStageSFA);
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+        const int acc = local % C::kAccStages;
+        const uint32_t acc_phase = (local / C::kAccStages) & 1;
+        if (!mbar_wait(&S.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+          ok = false;
+          break;
         }
-        if (++q.stage == C::kStages) {
-          q.stage = 0;
-          q.phase ^= 1;
-        }
-      };
-      auto copy_scales = [&](const Pos &q, int buf) {
-        const uint32_t sa = smem_u32(ring + static_cast<size_t>(q.stage) * C::kStageBytes);
-        const uint32_t ssfa = sa + C::kStageA + C::kStageB;
-        const uint32_t ssfb = ssfa + C::kStageSFA;
-        const uint32_t sfa_t = tmem_base + C::kSfaCol + buf * C::kSfCols;
-        const uint32_t sfb_t = sfa_t + 16;
-        const int atoms = min(4, p.ncb - 4 * q.kb);
-        for (int k = 0; k < atoms; ++k) {
-          tc_cp_32x128b_warpx4(sfa_t + 4 * k, make_sf_atom_desc(ssfa + k * kAtomBytes));
-#pragma unroll
-          for (int b = 0; b < C::kNB; ++b)
-            tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * k + 4 * b, make_sf_atom_desc(ssfb + (b * 4 + k) * kAtomBytes));
-        }
-      };
-      Pos pos{static_cast<int>(blockIdx.x), 0, 0, 0, 0u};
-      bool ok = pos.tile < num_tiles;
-      if (ok) {
-        ok = mbar_wait(&S.full[pos.stage], pos.phase, abort_flag, p.status, kStatusMmaTimeout);
-        if (ok) {
-          tc_fence_after();
-          copy_scales(pos, 0);
-        }
-      }
-      int n = 0;
-      while (ok && pos.tile < num_tiles) {
-        Pos nxt = pos;
-        advance(nxt);
-        if (nxt.tile < num_tiles) {
-          if (!mbar_wait(&S.full[nxt.stage], nxt.phase, abort_flag, p.status, kStatusMmaTimeout)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          copy_scales(nxt, (n + 1) & 1);
-        }
-        const int acc = pos.local % C::kAccStages;
-        if (pos.kb == 0) {
-          const uint32_t acc_phase = (pos.local / C::kAccStages) & 1;
-          if (!mbar_wait(&S.tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-        }
+        tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        const uint32_t sa = smem_u32(ring + static_cast<size_t>(pos.stage) * C::kStageBytes);
-        const uint64_t da = make_kmajor_sw128_desc(sa);
-        const uint64_t db = make_kmajor_sw128_desc(sa + C::kStageA);
-        const uint32_t sfa_t = tmem_base + C::kSfaCol + (n & 1) * C::kSfCols;
-        const uint32_t sfb_t = sfa_t + 16;
-        const int atoms = min(4, p.ncb - 4 * pos.kb);
-        for (int k = 0; k < atoms; ++k)
-          mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                    db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t + 4 * k,
-                    sfb_t + 4 * C::kNB * k, (pos.kb | k) != 0 ? 1u : 0u);
-        tc_commit(&S.empty[pos.stage]);
-        if (pos.kb == k_blocks - 1) tc_commit(&S.tmem_full[acc]);
-        pos = nxt;
-        ++n;
+        for (int kb = 0; kb < k_blocks; ++kb, ++n) {
+          if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t soff = static_cast<uint64_t>((static_cast<uint32_t>(stage) * C::kStageBytes) >> 4);
+          const uint64_t da = da0 + soff, db = db0 + soff, dsfa = dsfa0 + soff, dsfb = dsfb0 + soff;
+          const uint32_t sfa_t = tmem_base + C::kSfaCol + (n & 1u) * C::kSfCols;
+          const uint32_t sfb_t = sfa_t + 16;
+          const int atoms = min(4, p.ncb - 4 * kb);
+          if (atoms == 4) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              tc_cp_32x128b_warpx4(sfa_t + 4 * k, dsfa + static_cast<uint64_t>(k * (kAtomBytes >> 4)));
+#pragma unroll
+              for (int b = 0; b < C::kNB; ++b)
+                tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * k + 4 * b,
+                                     dsfb + static_cast<uint64_t>((b * 4 + k) * (kAtomBytes >> 4)));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                        db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t + 4 * k,
+                        sfb_t + 4 * C::kNB * k, (kb | k) != 0 ? 1u : 0u);
+          } else {
+            for (int k = 0; k < atoms; ++k) {
+              tc_cp_32x128b_warpx4(sfa_t + 4 * k, dsfa + static_cast<uint64_t>(k * (kAtomBytes >> 4)));
+#pragma unroll
+              for (int b = 0; b < C::kNB; ++b)
+                tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * k + 4 * b,
+                                     dsfb + static_cast<uint64_t>((b * 4 + k) * (kAtomBytes >> 4)));
+            }
+            for (int k = 0; k < atoms; ++k)
+              mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                        db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t + 4 * k,
+                        sfb_t + 4 * C::kNB * k, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&S.empty[stage]);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&S.tmem_full[acc]);
       }
     }
     __syncwarp();
@@ -469,6 +460,11 @@ MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_sc
   clear_error();
   return run_fp4("f4f4bf16", xq, wq, x_scale, w_scale, global_scale, y, nullptr, nullptr, nullptr, 1, M, N, K,
                  static_cast<cudaStream_t>(stream));
+}
+
+MSLK_API int mslk_b200_debug_nvfp4_pair_timers(unsigned long long *dev_counters) {
+  mslk_b200::nvfp4_pair::set_pipe_timers(dev_counters);
+  return 0;
 }
 
 MSLK_API size_t mslk_b200_f4f4bf16_workspace_bytes(int64_t M, int64_t N, int64_t K) {

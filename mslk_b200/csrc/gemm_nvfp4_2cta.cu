@@ -2,22 +2,24 @@
 //
 // Two CTAs on neighbouring SMs compute one 256 x 256 output tile with 256 x 256 x 64 instructions.
 // Each CTA loads its own 128 rows of A and its own 128 of the 256 rows of B: 38 KB per SM and K block
-// (256 elements of K) instead of the 54 KB of the one-CTA kernel with 256-column tiles.  That matters
-// because this GEMM is bound by how fast operands arrive from L2 (bytes in flight per SM / latency),
-// not by the tensor pipe: with three of four instructions and all scale copies removed the one-CTA
-// kernel ran only 20 % faster.  Scale factors: each
-// CTA needs, in its own tensor memory, the A scales of its own 128 rows and the B scales of ALL 256
+// (256 elements of K) instead of the 54 KB of the one-CTA kernel with 256-column tiles.  Scale factors:
+// each CTA needs, in its own tensor memory, the A scales of its own 128 rows and the B scales of ALL 256
 // columns; both CTAs therefore fetch both B scale blocks themselves (4 KB per K block; no load is
 // multicast).  Scale atoms travel as TMA boxes of {512 bytes, atoms of one stage} over a 2-D view of the scale
 // buffer, so that, like the operand tiles, they can signal the leader's barrier from either CTA.
 //
 //   CTA rank 0 ("leader")                              CTA rank 1
 //   warp 0  producer: own empty[s] -> 5 TMA loads into own smem, bytes counted on the LEADER's full[s]
-//   warp 1  MMA issuer: tcgen05.cp (pair-wide: every CTA copies its own atoms into its own tensor
-//           memory) one K block ahead, then the pair-wide MMAs; commits to both CTAs' barriers
+//           (L2 prefetches of the boxes 2..16 K blocks ahead were tried: 247 us against 219 us on 8192^3)
+//   warp 1  MMA issuer: per stage, tcgen05.cp of the stage's scale atoms (pair-wide: every CTA copies its
+//           own atoms into its own tensor memory; two alternating sets of scale columns, so the copies of
+//           stage i+1 never overwrite scales the instructions of stage i still read), then the four
+//           pair-wide MMAs; commits to both CTAs' barriers
 //                                                       (idle; takes part in TMEM alloc)
-//   warps 2..5 epilogue on the CTA's own 128 accumulator rows; all eight warps arrive on the
-//           leader's tmem_empty barrier
+//   warps 2..9 epilogue on the CTA's own 128 accumulator rows: two warps per 32-lane quadrant, each draining
+//           128 of the 256 columns into registers (the next load in flight while a chunk is packed), handing
+//           the accumulator back, then staging 32 x 64 bf16 slabs in swizzled shared memory for TMA stores
+//           (128-byte row segments); all sixteen warps of the pair arrive on the leader's tmem_empty barrier
 //
 // Waits are bounded as everywhere else (common.cuh); cluster-wide hardware barriers only at start-up
 // and teardown, reached on every path.
@@ -25,6 +27,7 @@
 
 #include "common.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 
@@ -37,73 +40,69 @@ constexpr int kPairRows = 256;           // rows of the pair tile
 constexpr int kPairBN = 256;             // columns of the pair tile
 constexpr int kMmaKBytes = 32;           // 64 K-elements per instruction
 constexpr int kAtomBytes = 512;          // 128 rows x 4 scales = the scales of one instruction
-constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueWarps = 8;
+constexpr int kNumThreads = 64 + 32 * kNumEpilogueWarps;
 constexpr int kAccCols = kPairBN;        // one accumulator
 constexpr int kSfBase = kAccCols;
 constexpr int kTmemCols = 512;
-constexpr int kBand = 8;                 // 8 x 256 rows per scheduling band
 // block-scaled instruction descriptor: e2m1 x e2m1, ue4m3 scales, K-major, N = 256, M = 256 over the pair
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPairBN >> 3) << 17) | (0u << 23) |
                             (static_cast<uint32_t>(kPairRows >> 4) << 24);
 
-// K extent of a pipeline stage: BK bytes of packed K per row.  Operand arrival from L2 bounds this
-// kernel, so eleven small stages (64-byte rows = 128 elements of K, 64-byte swizzle, two instructions)
-// were tried against five large ones (128-byte rows, four instructions): on 8192^3 the small stages
-// took 387 us against 282 us -- 64-byte row segments use the L2-to-SM path badly -- so 128 is the default.
-template <int BK>
-struct PCfg {
-  static_assert(BK == 64 || BK == 128, "stage rows are 64 or 128 bytes");
-  static constexpr int kBKBytes = BK;
-  static constexpr int kBKElems = 2 * BK;
-  static constexpr int kMmasPerStage = BK / kMmaKBytes;
-  static constexpr int kStageA = kBM * BK;
-  static constexpr int kStageB = (kPairBN / 2) * BK;
-  static constexpr int kStageSFA = kMmasPerStage * kAtomBytes;
-  static constexpr int kStageSFB = 2 * kMmasPerStage * kAtomBytes;   // both 128-column blocks
-  static constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
-  static_assert(kStageBytes % (BK * 8) == 0, "stages keep the alignment of the swizzled tiles");
-  static constexpr int kStages = BK == 128 ? 5 : 11;
-  static constexpr int kSfCols = 12 * kMmasPerStage;   // one set of scale columns: A (4 per instruction) + B (8)
-  static_assert(kSfBase + 2 * kSfCols <= 512, "tensor memory budget");
-};
+// A pipeline stage holds 128 bytes of packed K per row (256 elements, four instructions).  Stages of 64-byte
+// rows (64-byte swizzle, eleven of them) were measured slower: 387 us against 282 us on 8192^3.
+constexpr int kBKBytes = 128;
+constexpr int kBKElems = 256;
+constexpr int kMmasPerStage = kBKBytes / kMmaKBytes;
+constexpr int kStageA = kBM * kBKBytes;
+constexpr int kStageB = (kPairBN / 2) * kBKBytes;
+constexpr int kStageSFA = kMmasPerStage * kAtomBytes;
+constexpr int kStageSFB = 2 * kMmasPerStage * kAtomBytes;   // both 128-column blocks
+constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
+static_assert(kStageBytes % 1024 == 0, "stages keep the alignment of the swizzled tiles");
+constexpr int kStages = 5;
+constexpr int kSfCols = 12 * kMmasPerStage;   // one set of scale columns: A (4 per instruction) + B (8)
+static_assert(kSfBase + 2 * kSfCols <= 512, "tensor memory budget");
 
-template <int BK>
 struct SmemTail {
-  uint64_t full[PCfg<BK>::kStages];
-  uint64_t empty[PCfg<BK>::kStages];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
   uint64_t tmem_full;
   uint64_t tmem_empty;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-template <int BK>
-constexpr size_t smem_bytes() {
-  return 1024 + static_cast<size_t>(PCfg<BK>::kStages) * PCfg<BK>::kStageBytes + sizeof(SmemTail<BK>);
-}
+constexpr int kOutCols = 64;                        // columns of one staged output slab (128-byte rows)
+constexpr int kOutSlabBytes = 32 * kOutCols * 2;    // 32 rows x 64 bf16
+constexpr int kOutStageBytes = kNumEpilogueWarps * kOutSlabBytes;
+constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + kOutStageBytes + sizeof(SmemTail);
+static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &m_tile, int &n_tile) {
-  const int per_band = kBand * n_tiles;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int band_rows, int &m_tile, int &n_tile) {
+  const int per_band = band_rows * n_tiles;
   const int band = tile / per_band;
   const int in_band = tile - band * per_band;
-  const int first_m = band * kBand;
-  const int band_m = min(m_tiles - first_m, kBand);
+  const int first_m = band * band_rows;
+  const int band_m = min(m_tiles - first_m, band_rows);
   n_tile = in_band / band_m;
   m_tile = first_m + (in_band - n_tile * band_m);
 }
 
-template <int BK>
+__device__ __forceinline__ long long clock_now() {
+  long long t;
+  asm volatile("mov.u64 %0, %clock64;" : "=l"(t));
+  return t;
+}
+
 __global__ void __launch_bounds__(kNumThreads, 1)
     gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                            const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                           const PairParams p) {
+                           const __grid_constant__ CUtensorMap tmap_y, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *ring = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  using C = PCfg<BK>;
-  constexpr int kStages = C::kStages, kStageBytes = C::kStageBytes, kStageA = C::kStageA, kStageB = C::kStageB;
-  constexpr int kStageSFA = C::kStageSFA, kMmasPerStage = C::kMmasPerStage, kSfCols = C::kSfCols;
-  constexpr int kBKBytes = C::kBKBytes, kBKElems = C::kBKElems;
-  SmemTail<BK> &S = *reinterpret_cast<SmemTail<BK> *>(ring + static_cast<size_t>(kStages) * kStageBytes);
+  uint8_t *out_stage = ring + static_cast<size_t>(kStages) * kStageBytes;   // 1024-byte aligned slabs
+  SmemTail &S = *reinterpret_cast<SmemTail *>(out_stage + kOutStageBytes);
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -116,18 +115,20 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const int num_tiles = m_tiles * n_tiles;
   const int k_blocks = (p.K + kBKElems - 1) / kBKElems;
   volatile int *abort_flag = &S.abort_flag;
+  const bool timed = p.timers != nullptr;
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
     prefetch_tensormap(&tmap_sfa);
     prefetch_tensormap(&tmap_sfb);
+    prefetch_tensormap(&tmap_y);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&S.full[s], 1);
       mbar_init(&S.empty[s], 1);
     }
     mbar_init(&S.tmem_full, 1);
-    mbar_init(&S.tmem_empty, 8);   // four epilogue warps in each CTA
+    mbar_init(&S.tmem_empty, 2 * kNumEpilogueWarps);   // the epilogue warps of both CTAs
     S.abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -148,15 +149,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long t_empty = 0;
       for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
         int m_tile, n_tile;
-        tile_coords(tile, m_tiles, n_tiles, m_tile, n_tile);
+        tile_coords(tile, m_tiles, n_tiles, p.band, m_tile, n_tile);
         const int a_block = m_tile * 2 + static_cast<int>(rank);   // 128-row block of this CTA's A rows
         for (int kb = 0; kb < k_blocks; ++kb) {
+          const long long t0 = timed ? clock_now() : 0;
           if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
             ok = false;
             break;
           }
+          if (timed) t_empty += clock_now() - t0;
           uint8_t *sa = ring + static_cast<size_t>(stage) * kStageBytes;
           uint8_t *sb = sa + kStageA;
           uint8_t *ssfa = sb + kStageB;
@@ -177,143 +181,169 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           }
         }
       }
+      if (timed && leader) atomicAdd(p.timers + 3, static_cast<unsigned long long>(t_empty));
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader only)
-    // The K blocks of all tiles of this pair form one stream; the scale atoms of block i+1 are copied
-    // to tensor memory (into the other of two column sets) before the instructions of block i issue.
     if (leader && elect_one()) {
-      struct Pos {
-        int tile, kb, stage, local;
-        uint32_t phase;
-      };
-      auto advance = [&](Pos &q) {
-        if (++q.kb == k_blocks) {
-          q.kb = 0;
-          q.tile += num_pairs;
-          ++q.local;
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      uint32_t n = 0;     // K blocks issued so far: selects the set of scale columns
+      bool ok = true;
+      long long t_full = 0, t_acc = 0;
+      const long long t_begin = timed ? clock_now() : 0;
+      // the descriptors of a stage differ from those of stage 0 only in the address field (bits 0..13, in
+      // 16-byte units); shared memory is smaller than 2^18 bytes, so adding to the low word never carries out
+      const uint32_t ring0 = smem_u32(ring);
+      const uint64_t da0 = make_kmajor_sw128_desc(ring0);
+      const uint64_t db0 = make_kmajor_sw128_desc(ring0 + kStageA);
+      const uint64_t dsfa0 = make_sf_atom_desc(ring0 + kStageA + kStageB);
+      const uint64_t dsfb0 = make_sf_atom_desc(ring0 + kStageA + kStageB + kStageSFA);
+      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs, ++local) {
+        {
+          const long long t0 = timed ? clock_now() : 0;
+          if (!mbar_wait(&S.tmem_empty, (local & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          if (timed) t_acc += clock_now() - t0;
         }
-        if (++q.stage == kStages) {
-          q.stage = 0;
-          q.phase ^= 1;
-        }
-      };
-      auto copy_scales = [&](const Pos &q, int buf) {
-        const uint32_t sa = smem_u32(ring + static_cast<size_t>(q.stage) * kStageBytes);
-        const uint32_t ssfa = sa + kStageA + kStageB;
-        const uint32_t ssfb = ssfa + kStageSFA;
-        const uint32_t sfa_t = tmem_base + kSfBase + buf * kSfCols;
-        const uint32_t sfb_t = sfa_t + 4 * kMmasPerStage;
-        const int atoms = min(kMmasPerStage, p.ncb - kMmasPerStage * q.kb);
-        for (int k = 0; k < atoms; ++k) {
-          tc_cp_32x128b_warpx4_pair(sfa_t + 4 * k, make_sf_atom_desc(ssfa + k * kAtomBytes));
-          tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k, make_sf_atom_desc(ssfb + k * kAtomBytes));
-          tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k + 4, make_sf_atom_desc(ssfb + (kMmasPerStage + k) * kAtomBytes));
-        }
-      };
-      Pos pos{pair_id, 0, 0, 0, 0u};
-      bool ok = pos.tile < num_tiles;
-      if (ok) {
-        ok = mbar_wait(&S.full[pos.stage], pos.phase, abort_flag, p.status, kStatusMmaTimeout);
-        if (ok) {
+        tc_fence_after();
+        for (int kb = 0; kb < k_blocks; ++kb, ++n) {
+          const long long t0 = timed ? clock_now() : 0;
+          if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
+            ok = false;
+            break;
+          }
+          if (timed) t_full += clock_now() - t0;
           tc_fence_after();
-          copy_scales(pos, 0);
+          const uint64_t soff = static_cast<uint64_t>((static_cast<uint32_t>(stage) * kStageBytes) >> 4);
+          const uint64_t da = da0 + soff, db = db0 + soff, dsfa = dsfa0 + soff, dsfb = dsfb0 + soff;
+          const uint32_t sfa_t = tmem_base + kSfBase + (n & 1u) * kSfCols;
+          const uint32_t sfb_t = sfa_t + 4 * kMmasPerStage;
+          const int atoms = min(kMmasPerStage, p.ncb - kMmasPerStage * kb);
+          if (atoms == kMmasPerStage) {
+#pragma unroll
+            for (int k = 0; k < kMmasPerStage; ++k) {
+              tc_cp_32x128b_warpx4_pair(sfa_t + 4 * k, dsfa + static_cast<uint64_t>(k * (kAtomBytes >> 4)));
+              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k, dsfb + static_cast<uint64_t>(k * (kAtomBytes >> 4)));
+              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k + 4,
+                                        dsfb + static_cast<uint64_t>((kMmasPerStage + k) * (kAtomBytes >> 4)));
+            }
+#pragma unroll
+            for (int k = 0; k < kMmasPerStage; ++k)
+              mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                             db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), kIdesc, sfa_t + 4 * k, sfb_t + 8 * k,
+                             (kb | k) != 0 ? 1u : 0u);
+          } else {
+            for (int k = 0; k < atoms; ++k) {
+              tc_cp_32x128b_warpx4_pair(sfa_t + 4 * k, dsfa + static_cast<uint64_t>(k * (kAtomBytes >> 4)));
+              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k, dsfb + static_cast<uint64_t>(k * (kAtomBytes >> 4)));
+              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * k + 4,
+                                        dsfb + static_cast<uint64_t>((kMmasPerStage + k) * (kAtomBytes >> 4)));
+            }
+            for (int k = 0; k < atoms; ++k)
+              mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                             db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), kIdesc, sfa_t + 4 * k, sfb_t + 8 * k,
+                             (kb | k) != 0 ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&S.empty[stage]);
+          tc_commit_pair(mapa_u32(e, 0));
+          tc_commit_pair(mapa_u32(e, 1));
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
         }
+        if (!ok) break;
+        const uint32_t f = smem_u32(&S.tmem_full);
+        tc_commit_pair(mapa_u32(f, 0));
+        tc_commit_pair(mapa_u32(f, 1));
       }
-      int n = 0;
-      while (ok && pos.tile < num_tiles) {
-        Pos nxt = pos;
-        advance(nxt);
-        if (nxt.tile < num_tiles) {
-          if (!mbar_wait(&S.full[nxt.stage], nxt.phase, abort_flag, p.status, kStatusMmaTimeout)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          copy_scales(nxt, (n + 1) & 1);
-        }
-        if (pos.kb == 0) {
-          if (!mbar_wait(&S.tmem_empty, (pos.local & 1) ^ 1, abort_flag, p.status, kStatusMmaTimeout)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-        }
-        const uint32_t sa = smem_u32(ring + static_cast<size_t>(pos.stage) * kStageBytes);
-        const uint64_t da = kBKBytes == 128 ? make_kmajor_sw128_desc(sa) : make_kmajor_sw64_desc(sa);
-        const uint64_t db = kBKBytes == 128 ? make_kmajor_sw128_desc(sa + kStageA) : make_kmajor_sw64_desc(sa + kStageA);
-        const uint32_t sfa_t = tmem_base + kSfBase + (n & 1) * kSfCols;
-        const uint32_t sfb_t = sfa_t + 4 * kMmasPerStage;
-        const int atoms = min(kMmasPerStage, p.ncb - kMmasPerStage * pos.kb);
-        for (int k = 0; k < atoms; ++k)
-          mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                         db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), kIdesc, sfa_t + 4 * k, sfb_t + 8 * k,
-                         (pos.kb | k) != 0 ? 1u : 0u);
-        const uint32_t e = smem_u32(&S.empty[pos.stage]);
-        tc_commit_pair(mapa_u32(e, 0));
-        tc_commit_pair(mapa_u32(e, 1));
-        if (pos.kb == k_blocks - 1) {
-          const uint32_t f = smem_u32(&S.tmem_full);
-          tc_commit_pair(mapa_u32(f, 0));
-          tc_commit_pair(mapa_u32(f, 1));
-        }
-        pos = nxt;
-        ++n;
+      if (timed) {
+        atomicAdd(p.timers + 0, static_cast<unsigned long long>(t_full));
+        atomicAdd(p.timers + 1, static_cast<unsigned long long>(t_acc));
+        atomicAdd(p.timers + 2, static_cast<unsigned long long>(clock_now() - t_begin));
       }
     }
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
-    const int quad = warp & 3;
+    const int quad = warp & 3;                 // tensor-memory lanes this warp may read: 32 * (warp % 4) ...
+    const int half = (warp - 2) >> 2;          // which 128 of the tile's 256 columns
     const int row_in_cta = quad * 32 + lane;
-    const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
     const float alpha = *p.alpha;
+    uint8_t *buf = out_stage + (warp - 2) * kOutSlabBytes;
     int local = 0;
     for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++local) {
       int m_tile, n_tile;
-      tile_coords(tile, m_tiles, n_tiles, m_tile, n_tile);
-      const int row = m_tile * kPairRows + static_cast<int>(rank) * kBM + row_in_cta;
-      const bool row_ok = row < p.M;
+      tile_coords(tile, m_tiles, n_tiles, p.band, m_tile, n_tile);
+      const int row0 = m_tile * kPairRows + static_cast<int>(rank) * kBM + quad * 32;   // first row of this warp's slab
+      const int col0 = n_tile * kPairBN + half * 128;
       const bool got = mbar_wait(&S.tmem_full, local & 1, abort_flag, p.status, kStatusEpilogueTimeout);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-      __nv_bfloat16 *yrow = p.y + static_cast<size_t>(row) * p.N + n_tile * kPairBN;
-      // drain the whole accumulator (scaled, packed to bf16) and hand it back before the stores
-      uint32_t packed[kPairBN / 2];
-#pragma unroll
-      for (int c = 0; c < kPairBN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * 128);
+      // drain this warp's 128 columns (scaled, packed to bf16) with the next load in flight while a chunk is
+      // packed, and hand the accumulator back before anything is stored
+      uint32_t packed[64];
+      uint32_t ra[32], rb[32];
+      auto pack = [&](const uint32_t (&r)[32], int c) {
 #pragma unroll
         for (int j = 0; j < 32; j += 2)
           packed[c * 16 + j / 2] = pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
-      }
+      };
+      tmem_ld_32x32(taddr, ra);
+      tmem_ld_wait();
+      tmem_ld_32x32(taddr + 32, rb);
+      pack(ra, 0);
+      tmem_ld_wait();
+      tmem_ld_32x32(taddr + 64, ra);
+      pack(rb, 1);
+      tmem_ld_wait();
+      tmem_ld_32x32(taddr + 96, rb);
+      pack(ra, 2);
+      tmem_ld_wait();
+      pack(rb, 3);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty), 0));
-      if (row_ok) {
+      if (p.tma_store) {
 #pragma unroll
-        for (int c = 0; c < kPairBN / 32; ++c) {
-          const int cols_left = p.N - (n_tile * kPairBN + c * 32);
-          __nv_bfloat16 *dst = yrow + c * 32;
-          if (y_vec_ok && cols_left >= 32) {
-            uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+        for (int s2 = 0; s2 < 2; ++s2) {
+          if (col0 + s2 * kOutCols >= p.N || row0 >= p.M) break;     // slab entirely outside the matrix (warp-uniform)
+          if (lane == 0) tma_store_wait_read<0>();   // the store that last read this buffer is done with it
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              __stcs(d4 + j, make_uint4(packed[c * 16 + 4 * j], packed[c * 16 + 4 * j + 1], packed[c * 16 + 4 * j + 2],
-                                        packed[c * 16 + 4 * j + 3]));   // streaming: the output must not evict the operands from L2
-          } else if (cols_left > 0) {
-            uint16_t *d = reinterpret_cast<uint16_t *>(dst);
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < cols_left) d[j] = static_cast<uint16_t>(packed[c * 16 + j / 2] >> ((j & 1) * 16));
+          for (int q = 0; q < 8; ++q) {
+            const int chunk = q ^ (lane & 7);          // 128-byte swizzle: 16-byte chunk index xor row
+            *reinterpret_cast<uint4 *>(buf + lane * 128 + chunk * 16) =
+                make_uint4(packed[s2 * 32 + 4 * q], packed[s2 * 32 + 4 * q + 1], packed[s2 * 32 + 4 * q + 2],
+                           packed[s2 * 32 + 4 * q + 3]);
           }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_y, buf, col0 + s2 * kOutCols, row0);   // rows / columns past the matrix are clipped
+            tma_store_commit();
+          }
+        }
+      } else if (row0 + lane < p.M) {
+        __nv_bfloat16 *yrow = p.y + static_cast<size_t>(row0 + lane) * p.N + col0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int cols_left = p.N - (col0 + c * 32);
+          uint16_t *d = reinterpret_cast<uint16_t *>(yrow + c * 32);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < cols_left) d[j] = static_cast<uint16_t>(packed[c * 16 + j / 2] >> ((j & 1) * 16));
         }
       }
     }
+    if (lane == 0) tma_store_wait<0>();   // every staged slab has been written out before the CTA leaves
+    __syncwarp();
   }
 
   // ------------------------------------------------------------------ teardown
@@ -326,12 +356,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   }
 }
 
-template <int BK>
-int launch_bk(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
-              cudaStream_t st) {
-  using C = PCfg<BK>;
-  constexpr size_t kSmemBytes = smem_bytes<BK>();
-  static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+std::atomic<unsigned long long *> g_timers{nullptr};
+
+}  // namespace
+
+void set_pipe_timers(unsigned long long *dev_counters) { g_timers.store(dev_counters); }
+
+int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
+                       cudaStream_t st) {
   static std::atomic<int> max_pairs[64];   // zero-initialised; a racing first call computes the same value
   int dev = 0;
   if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
@@ -350,13 +382,13 @@ int launch_bk(const void *xq, const void *wq, const void *x_scale, const void *w
   cfg.numAttrs = 1;
 
   if (max_pairs[dev] == 0) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_pair_kernel<BK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(kSmemBytes)),
                             "cudaFuncSetAttribute(gemm_nvfp4_pair)"))
       return rc;
     cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
     int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_nvfp4_pair_kernel<BK>, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_nvfp4_pair_kernel, &cfg);
     if (e != cudaSuccess || n <= 0) {
       cudaGetLastError();
       max_pairs[dev] = -1;
@@ -375,28 +407,33 @@ int launch_bk(const void *xq, const void *wq, const void *x_scale, const void *w
   const int64_t kbytes = p.K / 2;
   const uint64_t a_blocks = (static_cast<uint64_t>(p.M) + kBM - 1) / kBM, b_blocks = (static_cast<uint64_t>(p.N) + kBM - 1) / kBM;
   CUtensorMap ta, tb, tsa, tsb;
-  const CUtensorMapSwizzle swz = BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  if (int rc = make_tmap_2d_bytes(&ta, xq, kbytes, p.M, kbytes, BK, kBM, swz)) return rc;
-  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, p.N, kbytes, BK, kBM, swz)) return rc;
+  if (int rc = make_tmap_2d_bytes(&ta, xq, kbytes, p.M, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, p.N, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   // scale buffers as [atoms, 128 words]: a box holds the atoms of one K block of one 128-row block
-  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, C::kMmasPerStage))
+  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, kMmasPerStage))
     return rc;
-  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, C::kMmasPerStage))
+  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, kMmasPerStage))
     return rc;
 
+  PairParams q = p;
+  // TMA stores need a 16-byte aligned base and row pitch; otherwise the epilogue stores element by element
+  CUtensorMap ty;
+  q.tma_store = ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0 && p.N % 8 == 0) ? 1 : 0;
+  if (q.tma_store) {
+    if (int rc = make_tmap_2d_bf16(&ty, p.y, p.N, p.M, static_cast<uint64_t>(p.N) * 2, kOutCols, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  } else {
+    ty = ta;   // never dereferenced
+  }
+  // Tiles of a band of `band` 256-row blocks run column by column, so the band's rows of A stay in L2 while B
+  // streams through once per band: as tall a band as keeps its A rows (packed data + scales) within ~40 MB.
+  const int64_t a_bytes_per_block = static_cast<int64_t>(kPairRows) * (kbytes + kbytes / 8);
+  q.band = static_cast<int>(std::max<int64_t>(4, std::min<int64_t>(m_tiles, (40ll << 20) / std::max<int64_t>(1, a_bytes_per_block))));
+  static const int env_band = [] { const char *e = getenv("MSLK_B200_NVFP4_BAND"); return e ? atoi(e) : 0; }();        // tuning aid
+  if (env_band > 0) q.band = env_band;
+  q.timers = g_timers.load();
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel<BK>, ta, tb, tsa, tsb, p), "f4f4bf16 pair launch");
-}
-
-}  // namespace
-
-int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
-                       cudaStream_t st) {
-  static const int bk = [] {
-    const char *e = getenv("MSLK_B200_NVFP4_PAIR_BK");   // "64" | "128": tuning aid, default 128 (measured faster)
-    return e && atoi(e) == 64 ? 64 : 128;
-  }();
-  return bk == 128 ? launch_bk<128>(xq, wq, x_scale, w_scale, p, st) : launch_bk<64>(xq, wq, x_scale, w_scale, p, st);
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel, ta, tb, tsa, tsb, ty, q), "f4f4bf16 pair launch");
 }
 
 }  // namespace nvfp4_pair

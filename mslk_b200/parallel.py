@@ -15,6 +15,9 @@ in the CPU tests):
   with a reduce-scatter over the token dimension.
 * :func:`expert_slice` -- contiguous expert ranges per rank for the grouped (MoE) GEMM; tokens are
   bucketed per rank, no collective.
+* :func:`balanced_expert_assignment` -- token-count-aware placement of the experts (greedy, largest
+  first): with skewed routing the slowest rank of a contiguous split holds several popular experts, while
+  the bound of any placement is max(largest expert, total / ranks) tokens on one rank.
 
 The GEMM itself is passed in as ``gemm_fn(xq, wq, x_scale, w_scale) -> bf16 [M, N]`` so that the
 sharding logic can be exercised on CPU ranks with the oracle's formula; on GPUs it is
@@ -51,6 +54,31 @@ def expert_token_range(m_sizes: Sequence[int], rank: int, world: int) -> Tuple[i
     row0 = int(sum(int(v) for v in m_sizes[:e0]))
     row1 = row0 + int(sum(int(v) for v in m_sizes[e0:e1]))
     return row0, row1, (e0, e1)
+
+
+def balanced_expert_assignment(m_sizes: Sequence[int], world: int):
+    """Greedy longest-processing-time placement: experts sorted by token count, each given to the rank with
+    the fewest tokens so far (ties: fewest experts, then lowest rank).  Returns ``(experts_of_rank, load_of_rank)``
+    with the expert ids of every rank in ascending order.  The weights of a rank are gathered ONCE with that
+    index list (``wq[experts_of_rank[r]]``); per step only the tokens are bucketed by it."""
+    counts = [int(v) for v in m_sizes]
+    order = sorted(range(len(counts)), key=lambda e: (-counts[e], e))
+    experts = [[] for _ in range(world)]
+    load = [0] * world
+    for e in order:
+        r = min(range(world), key=lambda i: (load[i], len(experts[i]), i))
+        experts[r].append(e)
+        load[r] += counts[e]
+    return [sorted(x) for x in experts], load
+
+
+def expert_rows(m_sizes: Sequence[int], experts: Sequence[int]):
+    """Half-open row ranges, in the stacked token tensor, of the given experts (for bucketing tokens by a
+    non-contiguous expert placement)."""
+    starts = [0]
+    for v in m_sizes:
+        starts.append(starts[-1] + int(v))
+    return [(starts[e], starts[e + 1]) for e in experts]
 
 
 class ColumnParallelLinear:
