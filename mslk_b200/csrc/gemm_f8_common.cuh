@@ -59,6 +59,12 @@ struct GemmParams {
   // [world * rs_rows, N] staging buffer; the owner sums the slots afterwards.
   int rs_rows;
   int rs_slot;
+  // Tile order of the CTA-pair kernel (set by its launcher).  band_m > 0: bands of band_m row blocks, inside a
+  // band the tiles run column by column, so the band's rows of X stay in L2 while W streams through once per
+  // band.  band_n > 0 (dense problems only, takes precedence): bands of band_n column blocks, inside a band row
+  // by row, so the band's rows of W stay and X streams.
+  int band_m = 0;
+  int band_n = 0;
 };
 
 inline void default_placement(GemmParams &p) {
@@ -132,6 +138,7 @@ struct Scheduler {
   int tile_rows;  // rows of one scheduled tile: 128 (single CTA) or 256 (CTA pair)
   int band_m;     // row blocks per band
   int g;
+  int band_n = 0; // > 0 (one group only): bands of band_n column blocks, rows fastest-varying outside
 
   __device__ __forceinline__ bool get(int tile, Tile &t) {
     if (tile >= tile_start[G]) return false;
@@ -139,13 +146,24 @@ struct Scheduler {
     const int local = tile - tile_start[g];
     const int mg = row_start[g + 1] - row_start[g];
     const int m_tiles = (mg + tile_rows - 1) / tile_rows;
-    const int per_band = band_m * n_tiles;
-    const int band = local / per_band;
-    const int in_band = local - band * per_band;
-    const int first_m = band * band_m;
-    const int this_band_m = min(m_tiles - first_m, band_m);
-    const int n_tile = in_band / this_band_m;
-    const int m_tile = first_m + (in_band - n_tile * this_band_m);
+    int n_tile, m_tile;
+    if (band_n > 0) {
+      const int per_band = band_n * m_tiles;
+      const int band = local / per_band;
+      const int in_band = local - band * per_band;
+      const int first_n = band * band_n;
+      const int this_band_n = min(n_tiles - first_n, band_n);
+      m_tile = in_band / this_band_n;
+      n_tile = first_n + (in_band - m_tile * this_band_n);
+    } else {
+      const int per_band = band_m * n_tiles;
+      const int band = local / per_band;
+      const int in_band = local - band * per_band;
+      const int first_m = band * band_m;
+      const int this_band_m = min(m_tiles - first_m, band_m);
+      n_tile = in_band / this_band_m;
+      m_tile = first_m + (in_band - n_tile * this_band_m);
+    }
     t.row0 = row_start[g] + m_tile * tile_rows;
     t.rows = min(tile_rows, mg - m_tile * tile_rows);
     t.n0 = n_tile * bn;

@@ -104,6 +104,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tmem_alloc(&S.tmem_base, Cfg::kTmemCols);
     tmem_relinquish();
   }
+  // everything above touched shared and tensor memory only: it may run under the tail of the previous kernel
+  // of the stream; from here on global memory is read (group sizes, operands, scales) and written
+  griddep_wait();
+  griddep_launch_dependents();
   if (warp == 2) build_group_tables(p, n_tiles, kBM, lane, S.row_start, S.tile_start);
   tc_fence_before();
   __syncthreads();
@@ -292,8 +296,15 @@ int launch(const CUtensorMap &ta, const CUtensorMap &tb, const GemmParams &p, in
       return rc;
     attr_set[dev] = true;
   }
-  gemm_f8_rowwise_kernel<BN><<<grid, kNumThreads, smem, st>>>(ta, tb, p);
-  return check_cuda(cudaGetLastError(), "f8f8bf16_rowwise launch");
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_attribute(&attr[0]);   // the prologue may overlap the tail of the previous kernel of the stream
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_kernel<BN>, ta, tb, p), "f8f8bf16_rowwise launch");
 }
 
 int run(const void *xq, const void *wq, const float *xs, const float *ws, const void *bias, int bias_kind, void *y,

@@ -22,6 +22,7 @@
 // control path of both CTAs reaches them.
 #include "gemm_f8_common.cuh"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -40,7 +41,7 @@ constexpr int kOutCols = 64;                       // columns of one staged outp
 constexpr int kOutSlabBytes = 32 * kOutCols * 2;   // 32 rows x 64 bf16
 constexpr int kOutStageBytes = 4 * 2 * kOutSlabBytes;  // four epilogue warps, double-buffered
 constexpr int kTmemCols = 512;          // two 256-column accumulators
-constexpr int kPairBandM = 8;           // 8 x 256 rows per band, matching 16 x 128 of the 1-CTA kernel
+constexpr int kPairBandM = 8;           // default band: 8 x 256 rows (grouped problems)
 // instruction descriptor: fp32 accumulate, e4m3 x e4m3, K-major, M = 256 over the pair, N = n
 __host__ __device__ constexpr uint32_t make_idesc(int n) {
   return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kPairRows >> 4) << 24);
@@ -119,6 +120,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tmem_alloc_pair(&S.tmem_base, kTmemCols);
     tmem_relinquish_pair();
   }
+  // everything above touched shared and tensor memory only: it may run under the tail of the previous kernel
+  // of the stream; from here on global memory is read (group sizes, operands, scales) and written
+  griddep_wait();
+  griddep_launch_dependents();
   if (warp == 2) build_group_tables(p, n_tiles, kPairRows, lane, S.row_start, S.tile_start);
   tc_fence_before();
   __syncthreads();
@@ -126,7 +131,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
 
-  Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, kPairBN, kPairRows, kPairBandM, 0};
+  Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, kPairBN, kPairRows, p.band_m > 0 ? p.band_m : kPairBandM, 0,
+                  p.G == 1 ? p.band_n : 0};
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (both CTAs)
@@ -416,7 +422,7 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
   if (dev < 0 || dev >= 64) return -1;
 
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
@@ -425,7 +431,7 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = st;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 1;   // the occupancy query below takes the cluster shape only
 
   if (max_pairs[dev] == 0) {
     for (const void *fn : {reinterpret_cast<const void *>(gemm_f8_rowwise_pair_kernel<false>),
@@ -485,6 +491,37 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
   if (q.rs_rows > 0 && (!tma_ok || q.rs_rows % 32 != 0 || q.total_m % 32 != 0))
     return fail(1, "row-scatter GEMM needs 16-byte aligned buffers, N %% 64 == 0 and rows per rank %% 32 == 0");
 
+  // Tile order of dense problems.  All pairs advance through K together, so one wave of P pairs working on b
+  // blocks of one dimension and P / b of the other touches (b + P / b) 256-row slabs of K bytes each.  When that
+  // working set fits the part of L2 a kernel can count on (about 45 MB measured: 8192^3 ran 368 us with bands of
+  // 16, 402 us with bands of 32), the band's operand stays resident between waves and the other operand is read
+  // once per band: take the tallest such band, along whichever dimension then moves fewer bytes.  When it cannot
+  // fit (long K) nothing survives between waves anyway and the squarest wave (bands of 8) reads least.
+  // (L2 eviction hints on the TMA copies were measured too: evict_last on the resident operand changed nothing,
+  // evict_first on the streamed operand and the stores raised the DRAM reads by 15-20 %: lines were dropped before
+  // every pair of the wave had fetched them.)
+  if (q.G == 1 && !q.m_sizes && !q.end_offsets) {
+    static const int env_band = [] { const char *e = getenv("MSLK_B200_F8_BAND"); return e ? atoi(e) : 0; }();   // tuning aid: >0 row bands, <0 column bands
+    const int64_t m_tiles = (static_cast<int64_t>(q.total_m) + kPairRows - 1) / kPairRows;
+    const int64_t n_tiles = (static_cast<int64_t>(q.N) + kPairBN - 1) / kPairBN;
+    const double slab = static_cast<double>(kPairRows) * q.K, budget = 45.0 * (1 << 20), P = static_cast<double>(pairs);
+    auto tallest = [&](int64_t tiles) {
+      int64_t best = 0;
+      for (int64_t b = 8; b <= tiles; ++b)
+        if ((b + P / b) * slab <= budget) best = b;
+      return best;
+    };
+    const int64_t bm = tallest(m_tiles), bn = tallest(n_tiles);
+    const double a_bytes = static_cast<double>(q.total_m) * q.K, b_bytes = static_cast<double>(q.N) * q.K;
+    const double traffic_m = bm ? a_bytes + b_bytes * ((m_tiles + bm - 1) / bm) : 1e30;
+    const double traffic_n = bn ? b_bytes + a_bytes * ((n_tiles + bn - 1) / bn) : 1e30;
+    q.band_m = kPairBandM;
+    if (bm && traffic_m <= traffic_n) q.band_m = static_cast<int>(bm);
+    else if (bn) q.band_n = static_cast<int>(bn);
+    if (env_band > 0) { q.band_m = env_band; q.band_n = 0; }
+    if (env_band < 0) { q.band_n = -env_band; q.band_m = 0; }
+  }
+
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   // grouped problems (ragged token counts) run with swapped operand roles
   static const int swap_env = [] {
@@ -507,6 +544,7 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
                                      CU_TENSOR_MAP_SWIZZLE_NONE))
         return rc;
   }
+  cfg.numAttrs = 1 + pdl_attribute(&attr[1]);   // the prologue may overlap the tail of the previous kernel of the stream
   if (swap)
     return check_cuda(cudaLaunchKernelEx(&cfg, gemm_f8_rowwise_pair_kernel<true>, ta, tb, ta32, ta64, ymaps, q),
                       "f8f8bf16_rowwise pair launch");

@@ -425,10 +425,17 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   } else {
     ty = ta;   // never dereferenced
   }
-  // Tiles of a band of `band` 256-row blocks run column by column, so the band's rows of A stay in L2 while B
-  // streams through once per band: as tall a band as keeps its A rows (packed data + scales) within ~40 MB.
-  const int64_t a_bytes_per_block = static_cast<int64_t>(kPairRows) * (kbytes + kbytes / 8);
-  q.band = static_cast<int>(std::max<int64_t>(4, std::min<int64_t>(m_tiles, (40ll << 20) / std::max<int64_t>(1, a_bytes_per_block))));
+  // Tiles of a band of `band` 256-row blocks run column by column.  All pairs advance through K together, so a wave
+  // of P pairs touches (band + P / band) slabs of 256 rows (packed data + scales); while that fits the ~45 MB of L2
+  // a kernel can count on, the band's rows of A stay resident between waves and B is read once per band: take the
+  // tallest such band, else the squarest wave (8).
+  {
+    const double slab = static_cast<double>(kPairRows) * (kbytes + kbytes / 8), budget = 45.0 * (1 << 20), P = static_cast<double>(pairs);
+    int64_t best = 0;
+    for (int64_t b2 = 8; b2 <= m_tiles; ++b2)
+      if ((b2 + P / b2) * slab <= budget) best = b2;
+    q.band = static_cast<int>(best ? best : std::min<int64_t>(8, m_tiles));
+  }
   static const int env_band = [] { const char *e = getenv("MSLK_B200_NVFP4_BAND"); return e ? atoi(e) : 0; }();        // tuning aid
   if (env_band > 0) q.band = env_band;
   q.timers = g_timers.load();

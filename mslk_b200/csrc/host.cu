@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -66,6 +67,17 @@ int sm_count() {
     g_sm_count[dev] = n;
   }
   return g_sm_count[dev];
+}
+
+int pdl_attribute(cudaLaunchAttribute *attr) {
+  static const bool enabled = [] {
+    const char *e = getenv("MSLK_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  if (!enabled) return 0;
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = 1;
+  return 1;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,

@@ -23,6 +23,10 @@ int *device_status_ptr();
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Programmatic dependent launch: fills `attr` with the stream-serialization attribute and returns 1 when the
+// launchers should use it (default), 0 when the environment variable MSLK_B200_PDL=0 switched it off (read once).
+int pdl_attribute(cudaLaunchAttribute *attr);
+
 // Encodes a 2-D row-major tensor map: `rows` x `cols_bytes` bytes-per-row view of
 // `base` with row pitch `pitch_bytes`, box {box_cols_bytes, box_rows}, 1-byte
 // elements, the given swizzle, zero fill out of bounds.  Returns 0 or records an error.

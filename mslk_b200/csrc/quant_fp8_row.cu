@@ -233,6 +233,8 @@ __global__ void __launch_bounds__(kBlock) quant_fp8_row_vec_kernel(const QuantPa
   constexpr int kRowsPerBlock = kBlock / kThreadsPerRow;
   constexpr int kWarpsPerRow = kThreadsPerRow / 32;
   __shared__ float s_part[kBlock / 32];
+  griddep_launch_dependents();   // the next kernel of the stream may start its prologue
+  griddep_wait();                // ... and this one touches memory only after the previous kernel has finished
 
   const int tid = threadIdx.x;
   const int t_in_row = tid % kThreadsPerRow;
@@ -351,8 +353,15 @@ int launch_vec(const QuantParams &p, cudaStream_t st) {
   constexpr int kRowsPerBlock = kBlock / kThreadsPerRow;
   const int64_t blocks = (p.rows + kRowsPerBlock - 1) / kRowsPerBlock;
   if (blocks > 0x7fffffffLL) return fail(1, "quantize_fp8_row: too many rows (%lld)", (long long)p.rows);
-  quant_fp8_row_vec_kernel<T, kVecs, kThreadsPerRow, kBlock><<<static_cast<unsigned>(blocks), kBlock, 0, st>>>(p);
-  return check_cuda(cudaGetLastError(), "quantize_fp8_row launch");
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+  cfg.blockDim = dim3(kBlock, 1, 1);
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_attribute(&attr[0]);
+  return check_cuda(cudaLaunchKernelEx(&cfg, quant_fp8_row_vec_kernel<T, kVecs, kThreadsPerRow, kBlock>, p),
+                    "quantize_fp8_row launch");
 }
 
 template <typename T>

@@ -134,19 +134,25 @@ def test_ffn70b_fused_collective_placements_emulated(ops, P):
         ops.f8f8bf16_rowwise_scatter(xq[:, r * kl:(r + 1) * kl].contiguous(), wq[:, r * kl:(r + 1) * kl].contiguous(),
                                      xs, ws, sptrs, r)
     y = torch.cat([ops.reduce_slots(s) for s in stages], dim=0)
+    # The P partial products are rounded to bf16 before the owner sums them in fp32 in rank order (NCCL's bf16
+    # reduce-scatter rounds as often): against the unsharded fp32 formula an element may be off by one bf16 step
+    # of its LARGEST partial product, which near a cancellation is more than the 1e-2 absolute bound, so that
+    # bound is doubled here ...
     scale = max(1.0, float(y_ref.float().std()))
-    torch.testing.assert_close(y.float(), y_ref.float(), rtol=RTOL, atol=ATOL * scale)
-    # The P partial products are rounded to bf16 before the owner sums them in fp32 in rank order.  Emulate exactly
-    # that from the formula's own partial products: the result must agree to the last bit wherever the partials do,
-    # and a partial that differs by one bf16 step moves the sum by one step OF THAT PARTIAL (the absolute floor).
-    parts = [fp8_rowwise_formula_chunked(xq[:, r * kl:(r + 1) * kl].contiguous(), wq[:, r * kl:(r + 1) * kl].contiguous(), xs, ws)
-             for r in range(P)]
-    emul = torch.zeros((M, N), dtype=torch.float32, device="cuda")
-    for part in parts:
-        emul += part.float()
-    part_rms = float(parts[0].float().pow(2).mean().sqrt())
-    assert_sharp_bf16(y, emul.to(torch.bfloat16), f"fused reduce-scatter P={P} vs fp32 sum of bf16 partials",
-                      within_1ulp=0.995, max_ulp=2, floor_abs=part_rms * 2.0 ** -7)
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=RTOL, atol=2 * ATOL * scale)
+    # ... and the sharp statement is made against exactly that arithmetic, emulated from the formula's own partial
+    # products: |y - sum_r bf16(partial_r)| <= one bf16 step of the largest partial + one of the sum.
+    parts = torch.stack([fp8_rowwise_formula_chunked(xq[:, r * kl:(r + 1) * kl].contiguous(),
+                                                     wq[:, r * kl:(r + 1) * kl].contiguous(), xs, ws) for r in range(P)])
+    emul = parts.float().sum(0)
+    tol = (parts.float().abs().amax(0) + emul.abs()) * 2.0 ** -7
+    err = (y.float() - emul).abs()
+    worst = float((err - tol).max())
+    frac_equal = float((y == emul.to(torch.bfloat16)).float().mean())
+    print({"case": f"fused reduce-scatter P={P} vs fp32 sum of bf16 partials", "frac_equal": frac_equal,
+           "max_err_over_bound": float((err / tol.clamp_min(1e-30)).max())})
+    assert worst <= 0, f"an element is {worst} beyond one bf16 step of its largest partial product"
+    assert frac_equal > 0.995
     assert _status() == 0
 
 
