@@ -6,7 +6,7 @@ Needs baseline/_ref/libmslk_ref_gpu.so (built by baseline/build_ref_gpu.py from 
 stock CUTLASS) and, for the quantizer, baseline/_ref/pyref (the reference's Python package, `--python`).
 For every case both sides get the same device tensors, are timed the same way (CUDA events around `iters`
 back-to-back launches after warm-up, weights rotated through more than the L2 holds) and their outputs are
-compared element by element in bf16 units in the last place.  One JSON line per case:
+compared element by element in bf16 units in the last place.  Launches are replayed from CUDA graphs.  One JSON line per case:
     {"case": ..., "ours_us": ..., "ref_us": ..., "ours_over_ref_speed": ref_us / ours_us,
      "max_ulp": ..., "frac_within_1ulp": ..., "frac_equal": ...}
 """
@@ -41,13 +41,22 @@ def compare(y, y_ref):
 
 
 def time_us(fn, n_variants, iters, warmup):
+    """us per launch, `iters` launches replayed from one CUDA graph: both sides are then timed by the device, not
+    by how fast their host paths (ctypes here, the torch dispatcher there) can issue short kernels."""
     for i in range(warmup):
         fn(i % n_variants)
     torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for i in range(iters):
+                fn(i % n_variants)
+    g.replay()
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(iters):
-        fn(i % n_variants)
+    g.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters * 1e3

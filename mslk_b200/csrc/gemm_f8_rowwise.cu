@@ -331,9 +331,22 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   const int64_t group_m = total_m / G;
   if (!m_sizes && group_m * G != total_m) return fail(1, "%s: rows are not a multiple of the batch count", name);
   const int64_t m_tiles_ub = m_sizes ? (total_m + kBM - 1) / kBM + G : G * ((group_m + kBM - 1) / kBM);
-  // widest column block that still yields at least one tile per SM
+  // Column block of the one-CTA kernel: a tile streams (128 + BN) rows of K bytes, and the tiles run in waves of one
+  // per SM, so the launch costs about waves x (128 + BN) row loads (+ a constant per tile).  M = 128, N = 6144:
+  // BN = 32 gives 192 tiles = two waves (15.7 us), BN = 64 gives 96 tiles in one (the reference's 128 x 64 tiles: 9.8 us).
   int bn = 256;
-  while (bn > 32 && (bn / 2 >= N || m_tiles_ub * ((N + bn - 1) / bn) < sms)) bn /= 2;
+  {
+    int64_t best_cost = -1;
+    for (int cand = 256; cand >= 32; cand /= 2) {
+      if (cand > 32 && cand / 2 >= N) continue;   // half the width already covers N
+      const int64_t tiles = m_tiles_ub * ((N + cand - 1) / cand);
+      const int64_t cost = ((tiles + sms - 1) / sms) * (128 + cand + 32);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        bn = cand;
+      }
+    }
+  }
 
   GemmParams p;
   p.x_scale = xs;
@@ -390,9 +403,11 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   // grouped problems run on pairs with swapped operand roles (tokens as the N operand, padded to 16
   // only), which pays off unless the groups are tiny
   const bool groups_tall = !m_sizes || total_m / G >= 128;
+  // (a dense problem of at most 128 rows stays on one CTA per tile: half of every 256-row pair tile would be padding)
   // scatter-add epilogue: in the pair kernel for grouped problems with swapped roles, else in this file's kernel
   const bool want_pair = (!p.scatter_idx || (m_sizes && total_m / G < 2048)) &&
-                         (force == 2 || p.rs_rows > 0 || (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2));
+                         (force == 2 || p.rs_rows > 0 ||
+                          (force == 0 && groups_tall && bn == 256 && pair_tiles >= sms / 2 && (m_sizes || G > 1 || total_m > kBM)));
   if (want_pair) {
     const int rc = launch_pair_kernel(xq, wq, p, st);
     if (rc >= 0) return rc;  // -1: pairs unavailable on this device, fall through to one CTA per tile
