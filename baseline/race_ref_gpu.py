@@ -6,7 +6,8 @@ Needs baseline/_ref/libmslk_ref_gpu.so (built by baseline/build_ref_gpu.py from 
 stock CUTLASS) and, for the quantizer, baseline/_ref/pyref (the reference's Python package, `--python`).
 For every case both sides get the same device tensors, are timed the same way (CUDA events around `iters`
 back-to-back launches after warm-up, weights rotated through more than the L2 holds) and their outputs are
-compared element by element in bf16 units in the last place.  Launches are replayed from CUDA graphs.  One JSON line per case:
+compared element by element in bf16 units in the last place.  Launches are replayed from CUDA graphs, the two
+sides alternately (median of three rounds each).  One JSON line per case:
     {"case": ..., "ours_us": ..., "ref_us": ..., "ours_over_ref_speed": ref_us / ours_us,
      "max_ulp": ..., "frac_within_1ulp": ..., "frac_equal": ...}
 """
@@ -62,6 +63,18 @@ def time_us(fn, n_variants, iters, warmup):
     return e0.elapsed_time(e1) / iters * 1e3
 
 
+def race_pair(ours_fn, ref_fn, n_variants, iters, warmup, rounds=3):
+    """Median us per launch of both sides, measured alternately (ours, reference, ours, ...) so that clock and
+    temperature drift over the run hits both alike."""
+    a, b = [], []
+    for _ in range(rounds):
+        a.append(time_us(ours_fn, n_variants, iters, warmup))
+        b.append(time_us(ref_fn, n_variants, iters, warmup))
+    a.sort()
+    b.sort()
+    return a[len(a) // 2], b[len(b) // 2]
+
+
 def randn(shape, std=1.0, seed=0):
     g = torch.Generator(device="cuda").manual_seed(seed)
     return (torch.randn(shape, generator=g, device="cuda", dtype=torch.float32) * std).to(torch.bfloat16)
@@ -78,8 +91,8 @@ def race_dense(ops, ref, M, N, K, iters, warmup, w_std=0.02):
     y, y_ref = (torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2))
     # the instance the reference's heuristic picks on sm_100 (csrc/gemm/cutlass/f8f8bf16_rowwise.cu:24-50)
     ref_fn = ref.f8f8bf16_rowwise_small if M <= 128 else ref.f8f8bf16_rowwise_large
-    ours = time_us(lambda i: ops.f8f8bf16_rowwise_out(xq, ws[i][0], xs, ws[i][1], y), nv, iters, warmup)
-    theirs = time_us(lambda i: ref_fn(xq, ws[i][0], xs, ws[i][1], y_ref), nv, iters, warmup)
+    ours, theirs = race_pair(lambda i: ops.f8f8bf16_rowwise_out(xq, ws[i][0], xs, ws[i][1], y),
+                             lambda i: ref_fn(xq, ws[i][0], xs, ws[i][1], y_ref), nv, iters, warmup)
     ops.f8f8bf16_rowwise_out(xq, ws[0][0], xs, ws[0][1], y)
     ref_fn(xq, ws[0][0], xs, ws[0][1], y_ref)
     torch.cuda.synchronize()
@@ -96,8 +109,8 @@ def race_grouped(ops, ref, E, tokens, N, K, iters, warmup):
     xq, xs = ops.quantize_fp8_row(randn((tokens, K), seed=2))
     wq, ws = ops.quantize_fp8_row(randn((E, N, K), 0.02, seed=3))
     y_ref = torch.empty((tokens * N,), dtype=torch.bfloat16, device="cuda")
-    ours = time_us(lambda i: ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws.view(-1), ms), 1, iters, warmup)
-    theirs = time_us(lambda i: ref.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms, y_ref), 1, iters, warmup)
+    ours, theirs = race_pair(lambda i: ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws.view(-1), ms),
+                             lambda i: ref.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms, y_ref), 1, iters, warmup)
     y = ops.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws.view(-1), ms)
     yr = ref.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms, y_ref)
     torch.cuda.synchronize()
@@ -121,8 +134,8 @@ def race_nvfp4(ops, ref, M, N, K, iters, warmup):
     y, y_ref = (torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2))
     # csrc/gemm/cutlass/f4f4bf16.cu:44-1266: 256_256_2_1_1 for 8192^3, 256_128_4_1_1 for M <= 64 at (28672, 8192)
     ref_fn = ref.f4f4bf16_small if M <= 128 else ref.f4f4bf16_large
-    ours = time_us(lambda i: ops.f4f4bf16(xq, ws[i][0], sx, ws[i][1], output=y, global_scale=ws[i][2]), nv, iters, warmup)
-    theirs = time_us(lambda i: ref_fn(xq, ws[i][0], sx, ws[i][1], y_ref, ws[i][2]), nv, iters, warmup)
+    ours, theirs = race_pair(lambda i: ops.f4f4bf16(xq, ws[i][0], sx, ws[i][1], output=y, global_scale=ws[i][2]),
+                             lambda i: ref_fn(xq, ws[i][0], sx, ws[i][1], y_ref, ws[i][2]), nv, iters, warmup)
     ops.f4f4bf16(xq, ws[0][0], sx, ws[0][1], output=y, global_scale=ws[0][2])
     ref_fn(xq, ws[0][0], sx, ws[0][1], y_ref, ws[0][2])
     torch.cuda.synchronize()
@@ -135,8 +148,7 @@ def race_nvfp4(ops, ref, M, N, K, iters, warmup):
 def race_quantize(ops, ref_quant, M, K, iters, warmup):
     nv = variants(M * K * 2)
     xs = [randn((M, K), seed=30 + i) for i in range(nv)]
-    ours = time_us(lambda i: ops.quantize_fp8_row(xs[i]), nv, iters, warmup)
-    theirs = time_us(lambda i: ref_quant(xs[i]), nv, iters, warmup)
+    ours, theirs = race_pair(lambda i: ops.quantize_fp8_row(xs[i]), lambda i: ref_quant(xs[i]), nv, iters, warmup)
     q, s = ops.quantize_fp8_row(xs[0])
     qr, sr = ref_quant(xs[0])
     byts = 3.0 * M * K + 4.0 * M

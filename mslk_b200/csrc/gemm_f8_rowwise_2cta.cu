@@ -507,7 +507,7 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
     const double slab = static_cast<double>(kPairRows) * q.K, budget = 45.0 * (1 << 20), P = static_cast<double>(pairs);
     auto tallest = [&](int64_t tiles) {
       int64_t best = 0;
-      for (int64_t b = 8; b <= tiles; ++b)
+      for (int64_t b = std::min<int64_t>(8, tiles); b <= tiles; ++b)
         if ((b + P / b) * slab <= budget) best = b;
       return best;
     };

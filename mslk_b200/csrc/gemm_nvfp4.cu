@@ -431,10 +431,23 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
     return nvfp4_decode::launch_decode_kernel(xq, wq, x_scale, w_scale, global_scale, y, status, M, N, K, scratch,
                                               scratch_size, st);
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-  // (few-token shapes stay on one CTA per tile: a 256-row pair tile would be mostly padding)
-  if (!grouped && (force == 2 || (force == 0 && M > 128 && pair_tiles >= sms / 2))) {
-    nvfp4_pair::PairParams pp{global_scale, static_cast<__nv_bfloat16 *>(y), status, static_cast<int>(M),
-                              static_cast<int>(N), static_cast<int>(K), static_cast<int>((K + 63) / 64)};
+  // (few-token shapes stay on one CTA per tile: a 256-row pair tile would be mostly padding; grouped problems take
+  // pairs when their groups average at least 128 rows and there are few enough groups for the kernel's tables)
+  const bool pair_ok = grouped ? (G <= nvfp4_pair::kPairMaxGroups && M / G >= 128) : M > 128;
+  if (force == 2 || (force == 0 && pair_ok && pair_tiles >= sms / 2)) {
+    nvfp4_pair::PairParams pp{};
+    pp.alpha = global_scale;
+    pp.y = static_cast<__nv_bfloat16 *>(y);
+    pp.status = status;
+    pp.M = static_cast<int>(M);
+    pp.N = static_cast<int>(N);
+    pp.K = static_cast<int>(K);
+    pp.ncb = static_cast<int>((K + 63) / 64);
+    pp.m_sizes = m_sizes;
+    pp.end_offsets = end_offsets;
+    pp.sfa_row_start = sfa_row_start;
+    pp.G = static_cast<int>(G);
+    pp.alpha_per_group = grouped ? 1 : 0;
     const int rc = nvfp4_pair::launch_pair_kernel(xq, wq, x_scale, w_scale, pp, st);
     if (rc >= 0) return rc;   // -1: pairs unavailable, fall through to one CTA per tile
   }

@@ -1,4 +1,5 @@
-// NVFP4 GEMM on CTA pairs (tcgen05 cta_group::2, block-scaled) for sm_100a; dense problems.
+// NVFP4 GEMM on CTA pairs (tcgen05 cta_group::2, block-scaled) for sm_100a; dense problems and grouped (stacked)
+// ones, whose tiles come from the device-side scheduler over the per-group row counts (gemm_f8_common.cuh).
 //
 // Two CTAs on neighbouring SMs compute one 256 x 256 output tile with 256 x 256 x 64 instructions.
 // Each CTA loads its own 128 rows of A and its own 128 of the 256 rows of B: 38 KB per SM and K block
@@ -26,6 +27,7 @@
 #include "gemm_nvfp4_pair.h"
 
 #include "common.cuh"
+#include "gemm_f8_common.cuh"
 
 #include <algorithm>
 #include <atomic>
@@ -71,6 +73,9 @@ struct SmemTail {
   uint64_t tmem_empty;
   uint32_t tmem_base;
   int abort_flag;
+  int row_start[kPairMaxGroups + 2];    // first stacked row of every group
+  int tile_start[kPairMaxGroups + 2];   // first linear tile of every group
+  int blk_start[kPairMaxGroups + 2];    // first 128-row block of every group in the padded scale matrix of A
 };
 
 constexpr int kOutCols = 64;                        // columns of one staged output slab (128-byte rows)
@@ -78,16 +83,6 @@ constexpr int kOutSlabBytes = 32 * kOutCols * 2;    // 32 rows x 64 bf16
 constexpr int kOutStageBytes = kNumEpilogueWarps * kOutSlabBytes;
 constexpr size_t kSmemBytes = 1024 + static_cast<size_t>(kStages) * kStageBytes + kOutStageBytes + sizeof(SmemTail);
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
-
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int band_rows, int &m_tile, int &n_tile) {
-  const int per_band = band_rows * n_tiles;
-  const int band = tile / per_band;
-  const int in_band = tile - band * per_band;
-  const int first_m = band * band_rows;
-  const int band_m = min(m_tiles - first_m, band_rows);
-  n_tile = in_band / band_m;
-  m_tile = first_m + (in_band - n_tile * band_m);
-}
 
 __device__ __forceinline__ long long clock_now() {
   long long t;
@@ -110,9 +105,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x / 2;
   const int num_pairs = gridDim.x / 2;
-  const int m_tiles = (p.M + kPairRows - 1) / kPairRows;
   const int n_tiles = (p.N + kPairBN - 1) / kPairBN;
-  const int num_tiles = m_tiles * n_tiles;
+  const int n_row_blocks_b = (p.N + kBM - 1) / kBM;
   const int k_blocks = (p.K + kBKElems - 1) / kBKElems;
   volatile int *abort_flag = &S.abort_flag;
   const bool timed = p.timers != nullptr;
@@ -137,11 +131,32 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tmem_alloc_pair(&S.tmem_base, kTmemCols);
     tmem_relinquish_pair();
   }
+  if (warp == 2) {
+    // group tables: rows and tiles as in the FP8 kernels, plus the 128-row scale blocks in front of every group
+    gemm_f8::GemmParams gp{};
+    gp.m_sizes = p.m_sizes;
+    gp.end_offsets = p.end_offsets;
+    gp.G = p.G;
+    gp.total_m = p.M;
+    gp.group_m = p.M;   // dense: one group of all rows (only read when both size arrays are null)
+    gemm_f8::build_group_tables(gp, n_tiles, kPairRows, lane, S.row_start, S.tile_start);
+    __syncwarp();
+    if (lane == 0) {
+      int blocks = 0;
+      for (int g = 0; g < p.G; ++g) {
+        S.blk_start[g] = p.sfa_row_start ? static_cast<int>(p.sfa_row_start[g] / kBM) : blocks;
+        blocks += (S.row_start[g + 1] - S.row_start[g] + kBM - 1) / kBM;
+      }
+    }
+  }
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // the peer's barriers are initialised before anything is signalled on them
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
+  const int num_tiles = S.tile_start[p.G];
+  gemm_f8::Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, kPairBN, kPairRows, p.band, 0};
+  gemm_f8::Tile t;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (both CTAs)
@@ -150,10 +165,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       long long t_empty = 0;
-      for (int tile = pair_id; ok && tile < num_tiles; tile += num_pairs) {
-        int m_tile, n_tile;
-        tile_coords(tile, m_tiles, n_tiles, p.band, m_tile, n_tile);
-        const int a_block = m_tile * 2 + static_cast<int>(rank);   // 128-row block of this CTA's A rows
+      for (int tile = pair_id; ok && sched.get(tile, t); tile += num_pairs) {
+        const int g = sched.g;
+        const int a_row = t.row0 + static_cast<int>(rank) * kBM;        // first of this CTA's 128 rows of A
+        // 128-row block of those rows in the padded scale matrix of A, and of the tile's columns in that of B
+        const int sfa_block = S.blk_start[g] + (t.row0 - S.row_start[g]) / kBM + static_cast<int>(rank);
+        const int sfb_block = g * n_row_blocks_b + t.n0 / kBM;
         for (int kb = 0; kb < k_blocks; ++kb) {
           const long long t0 = timed ? clock_now() : 0;
           if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
@@ -169,12 +186,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           // every box is transferred whole (out-of-range rows and atoms are zero-filled), so the byte
           // count is the same for every stage
           if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * kStageBytes);
-          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBKBytes, a_block * kBM);
-          tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBKBytes, n_tile * kPairBN + static_cast<int>(rank) * kBM);
-          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, a_block * p.ncb + kMmasPerStage * kb);
-          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, (n_tile * 2) * p.ncb + kMmasPerStage * kb);
+          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBKBytes, a_row);
+          tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBKBytes, t.wrow0 + static_cast<int>(rank) * kBM);
+          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, sfa_block * p.ncb + kMmasPerStage * kb);
+          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, sfb_block * p.ncb + kMmasPerStage * kb);
           tma_load_2d_pair(ssfb + kMmasPerStage * kAtomBytes, &tmap_sfb, leader_full, 0,
-                           (n_tile * 2 + 1) * p.ncb + kMmasPerStage * kb);
+                           (sfb_block + 1) * p.ncb + kMmasPerStage * kb);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -273,15 +290,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
     const int quad = warp & 3;                 // tensor-memory lanes this warp may read: 32 * (warp % 4) ...
     const int half = (warp - 2) >> 2;          // which 128 of the tile's 256 columns
-    const int row_in_cta = quad * 32 + lane;
-    const float alpha = *p.alpha;
     uint8_t *buf = out_stage + (warp - 2) * kOutSlabBytes;
     int local = 0;
-    for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++local) {
-      int m_tile, n_tile;
-      tile_coords(tile, m_tiles, n_tiles, p.band, m_tile, n_tile);
-      const int row0 = m_tile * kPairRows + static_cast<int>(rank) * kBM + quad * 32;   // first row of this warp's slab
-      const int col0 = n_tile * kPairBN + half * 128;
+    for (int tile = pair_id; sched.get(tile, t); tile += num_pairs, ++local) {
+      const float alpha = p.alpha[p.alpha_per_group ? sched.g : 0];
+      const int slab0 = static_cast<int>(rank) * kBM + quad * 32;   // first row of this warp's slab inside the tile
+      const int row0 = t.row0 + slab0;
+      const int col0 = t.n0 + half * 128;
+      const int slab_rows = min(32, t.rows - slab0);                // rows of the slab that belong to the tile's group (<= 0: none)
       const bool got = mbar_wait(&S.tmem_full, local & 1, abort_flag, p.status, kStatusEpilogueTimeout);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
@@ -310,10 +326,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty), 0));
-      if (p.tma_store) {
+      if (p.tma_store && slab_rows == 32) {
 #pragma unroll
         for (int s2 = 0; s2 < 2; ++s2) {
-          if (col0 + s2 * kOutCols >= p.N || row0 >= p.M) break;     // slab entirely outside the matrix (warp-uniform)
+          if (col0 + s2 * kOutCols >= p.N) break;     // slab entirely outside the matrix (warp-uniform)
           if (lane == 0) tma_store_wait_read<0>();   // the store that last read this buffer is done with it
           __syncwarp();
 #pragma unroll
@@ -326,11 +342,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_y, buf, col0 + s2 * kOutCols, row0);   // rows / columns past the matrix are clipped
+            tma_store_2d(&tmap_y, buf, col0 + s2 * kOutCols, row0);   // columns past the matrix are clipped
             tma_store_commit();
           }
         }
-      } else if (row0 + lane < p.M) {
+      } else if (lane < slab_rows) {
+        // ragged slab (the group or the matrix ends inside it) or unaligned output: rows of this group only
         __nv_bfloat16 *yrow = p.y + static_cast<size_t>(row0 + lane) * p.N + col0;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -398,17 +415,23 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   }
   if (max_pairs[dev] < 0) return -1;
 
-  const int64_t m_tiles = (static_cast<int64_t>(p.M) + kPairRows - 1) / kPairRows;
+  const bool grouped = p.m_sizes || p.end_offsets;
+  if (p.G < 1 || p.G > kPairMaxGroups) return -1;
+  // upper bound of the 256-row blocks: one ragged block per group
+  const int64_t m_tiles = (static_cast<int64_t>(p.M) + kPairRows - 1) / kPairRows + (grouped ? p.G : 0);
   const int64_t n_tiles = (static_cast<int64_t>(p.N) + kPairBN - 1) / kPairBN;
   const int64_t tiles = m_tiles * n_tiles;
   const int64_t mp = max_pairs[dev].load();
   const int pairs = static_cast<int>(tiles < mp ? tiles : mp);
 
   const int64_t kbytes = p.K / 2;
-  const uint64_t a_blocks = (static_cast<uint64_t>(p.M) + kBM - 1) / kBM, b_blocks = (static_cast<uint64_t>(p.N) + kBM - 1) / kBM;
+  // 128-row blocks of the padded scale matrices: A's groups are padded one by one (the stacked quantizer's buffer
+  // holds M + 127 G rows), B holds G blocks of roundup(N, 128) rows
+  const uint64_t a_blocks = grouped ? (static_cast<uint64_t>(p.M) + 127ull * p.G) / kBM : (static_cast<uint64_t>(p.M) + kBM - 1) / kBM;
+  const uint64_t b_blocks = static_cast<uint64_t>(p.G) * ((static_cast<uint64_t>(p.N) + kBM - 1) / kBM);
   CUtensorMap ta, tb, tsa, tsb;
   if (int rc = make_tmap_2d_bytes(&ta, xq, kbytes, p.M, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, p.N, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, static_cast<uint64_t>(p.G) * p.N, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   // scale buffers as [atoms, 128 words]: a box holds the atoms of one K block of one 128-row block
   if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, kMmasPerStage))
     return rc;
@@ -432,9 +455,9 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   {
     const double slab = static_cast<double>(kPairRows) * (kbytes + kbytes / 8), budget = 45.0 * (1 << 20), P = static_cast<double>(pairs);
     int64_t best = 0;
-    for (int64_t b2 = 8; b2 <= m_tiles; ++b2)
+    for (int64_t b2 = std::min<int64_t>(8, m_tiles); b2 <= m_tiles; ++b2)
       if ((b2 + P / b2) * slab <= budget) best = b2;
-    q.band = static_cast<int>(best ? best : std::min<int64_t>(8, m_tiles));
+    q.band = static_cast<int>(best && !grouped ? best : 8);   // grouped: the groups are short, bands of 8 blocks
   }
   static const int env_band = [] { const char *e = getenv("MSLK_B200_NVFP4_BAND"); return e ? atoi(e) : 0; }();        // tuning aid
   if (env_band > 0) q.band = env_band;

@@ -10,6 +10,8 @@
 namespace mslk_b200 {
 namespace nvfp4_pair {
 
+constexpr int kPairMaxGroups = 255;
+
 struct PairParams {
   const float *alpha;   // device scalar
   __nv_bfloat16 *y;
@@ -18,11 +20,19 @@ struct PairParams {
   int ncb;              // scale atoms per 128-row block = ceil(K / 64)
   int band;             // 256-row blocks per scheduling band (tiles of a band run column by column)
   int tma_store;        // set by the launcher: y is 16-byte aligned and N % 8 == 0, the epilogue may use TMA stores
+  // Grouped (stacked) problems: G weight blocks of N rows, group g owning m_sizes[g] (or the rows up to
+  // end_offsets[g]) consecutive rows of X / Y; the scale rows of every group start on a 128-row boundary,
+  // sfa_row_start[g] when given, else the groups follow each other, each padded to 128 rows.  Dense: G = 1, all null.
+  const int64_t *m_sizes;
+  const int32_t *end_offsets;
+  const int64_t *sfa_row_start;
+  int G;
+  int alpha_per_group;
   unsigned long long *timers;   // optional: [0] ns the MMA lane waited for operand stages, [1] for a free accumulator,
                                 // [2] ns of its whole loop, [3] ns the producer of the leader waited for free stages (sums over pairs)
 };
 
-// Dense problems only.  Returns 0 on success, a non-zero code after recording an error, or -1 when
+// Dense problems and grouped ones with at most kPairMaxGroups groups.  Returns 0 on success, a non-zero code after recording an error, or -1 when
 // the device cannot run CTA pairs (the caller then takes the one-CTA kernel).
 int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
                        cudaStream_t st);

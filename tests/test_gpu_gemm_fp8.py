@@ -58,7 +58,10 @@ def test_small_shapes_vs_c_oracle(ops, M, N, K):
 LLAMA = [(M, N, K) for M in (1, 16, 128, 2048) for (N, K) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336))]
 
 
-@pytest.mark.parametrize("M,N,K", LLAMA + [(4096, 4096, 4096), (2048, 2048, 4096), (4096, 4096, 8192), (8192, 4096, 4096)])
+# (8192, 2048, 8192) and (6000, 1024, 16384): few column blocks, many row blocks -> the pair kernel orders its tiles in
+# column bands (W resident in L2, X streamed); (5000, 5000, 2048): ragged edges under the tallest row band
+@pytest.mark.parametrize("M,N,K", LLAMA + [(4096, 4096, 4096), (2048, 2048, 4096), (4096, 4096, 8192), (8192, 4096, 4096),
+                                           (8192, 2048, 8192), (6000, 1024, 16384), (5000, 5008, 2048)])
 def test_model_shapes_vs_fp32_formula(ops, M, N, K):
     xq, wq, xs, ws = _quant(ops, M, N, K, seed=1)
     y = ops.f8f8bf16_rowwise(xq, wq, xs, ws)

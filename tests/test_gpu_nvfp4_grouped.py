@@ -102,6 +102,11 @@ def _check_grouped(y, X, W, m_sizes, xq, wq, x_scale, w_scale, alpha, tag):
     ([0, 129, 1, 128, 0, 300], 384, 512),    # empty groups, N not a multiple of the tile
     ([3, 0, 5, 1], 72, 64),
     ([1000, 24], 2048, 256),
+    # enough 256 x 256 tiles and rows per group for the CTA-pair kernel: ragged groups (slabs that end inside a
+    # 32-row block, a group shorter than one CTA's 128 rows, empty groups), N not a multiple of 256
+    ([300, 0, 1000, 129, 2047, 620], 2048, 1024),
+    ([1, 4000, 0, 95], 2304, 512),
+    ([256] * 16, 1280, 256),
 ])
 def test_grouped_stacked_gemm(ops, m_sizes, N, K):
     X, W, ms, xq, wq, x_scale, w_scale, alpha = _grouped_problem(ops, m_sizes, N, K, seed=sum(m_sizes) + N)

@@ -47,7 +47,8 @@ def _both_bounds(y, y_ref, tag):
 
 
 @pytest.mark.parametrize("M,N,K", [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336),
-                                   (8192, 8192, 8192), (4096, 4096, 4096)])
+                                   (8192, 8192, 8192), (4096, 4096, 4096),
+                                   (16384, 8192, 8192)])   # two column bands of 18 + 14 blocks (W resident, X streamed)
 def test_dense_bench_shapes_every_element(ops, M, N, K):
     xq, xs = ops.quantize_fp8_row(_randn((M, K), 1))
     wq, ws = ops.quantize_fp8_row(_randn((N, K), 2, 0.02))
