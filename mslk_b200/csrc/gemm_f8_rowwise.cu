@@ -389,7 +389,7 @@ int run(const void *xq, const void *wq, const float *xs, const float *ws, const 
   // M = 128: (8192, 28672) 50.9 against 69.8, but (8192, 8192) 24.4 against 24.1.
   const bool few_blocks = 2 * ((static_cast<int64_t>(N) + 127) / 128) <= sm_count();
   const bool more_tokens_ok = few_blocks && ((total_m <= 64 && K >= 8192) || (total_m <= 128 && K >= 16384));
-  if (!m_sizes && G == 1 && !placement && !scratch && N >= 2048 && !getenv("MSLK_B200_NO_DECODE") &&
+  if (!m_sizes && G == 1 && !placement && !scratch && N >= 2048 &&
       (total_m <= kDecodeMaxTokens || more_tokens_ok))
     return launch_decode_kernel(xq, wq, p, nullptr, 0, false, st);
 

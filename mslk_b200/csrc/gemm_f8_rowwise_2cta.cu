@@ -501,7 +501,6 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
   // evict_first on the streamed operand and the stores raised the DRAM reads by 15-20 %: lines were dropped before
   // every pair of the wave had fetched them.)
   if (q.G == 1 && !q.m_sizes && !q.end_offsets) {
-    static const int env_band = [] { const char *e = getenv("MSLK_B200_F8_BAND"); return e ? atoi(e) : 0; }();   // tuning aid: >0 row bands, <0 column bands
     const int64_t m_tiles = (static_cast<int64_t>(q.total_m) + kPairRows - 1) / kPairRows;
     const int64_t n_tiles = (static_cast<int64_t>(q.N) + kPairBN - 1) / kPairBN;
     const double slab = static_cast<double>(kPairRows) * q.K, budget = 45.0 * (1 << 20), P = static_cast<double>(pairs);
@@ -518,23 +517,18 @@ int launch_pair_kernel(const void *xq, const void *wq, const GemmParams &p, cuda
     q.band_m = kPairBandM;
     if (bm && traffic_m <= traffic_n) q.band_m = static_cast<int>(bm);
     else if (bn) q.band_n = static_cast<int>(bn);
-    if (env_band > 0) { q.band_m = env_band; q.band_n = 0; }
-    if (env_band < 0) { q.band_n = -env_band; q.band_m = 0; }
   }
 
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   // grouped problems (ragged token counts) run with swapped operand roles
-  static const int swap_env = [] {
-    const char *e = getenv("MSLK_B200_GROUPED_SWAP");   // "0" | "1": tuning aid, default = heuristic
-    return !e ? -1 : (e[0] == '1' ? 1 : 0);
-  }();
   // measured on E = 8 ... 128 experts: a gain of 16-19 % at a mean of 256 tokens per group, break-even near 1024,
-  // a loss of 7 % at 4096 (the transposed epilogue costs more than the padding it saves)
+  // a loss of 7 % at 4096 (the transposed epilogue costs more than the padding it saves); at a mean of 1024 (16 experts,
+  // Zipf counts) normal roles were 2.6 % faster on (16384, 5120) and equal on (5120, 8192) once both ran with dependent launch
   bool swap = q.m_sizes != nullptr && q.bias_kind == MSLK_B200_BIAS_NONE && q.n_extra == 0 && q.rs_rows == 0;
   if (q.scatter_idx) {
     if (!swap) return -1;   // the scatter-add epilogue of this kernel exists for swapped roles only
   } else if (swap) {
-    swap = swap_env >= 0 ? swap_env == 1 : q.total_m / q.G < 2048;
+    swap = q.total_m / q.G < 1024;
   }
   if (swap) {
     // its epilogue stores 32-token x 32-column blocks: box {32 columns = 64 bytes, 32 rows}, no swizzle, in map slot 1

@@ -329,15 +329,10 @@ int decode_token_tile(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 
 // ceil(tiles * s / (2 * SMs)): a split count that leaves a mostly empty last wave (e.g. 224 tiles
 // x 2 splits on 296 slots) is worse than none.  Each split keeps at least two K blocks.
 int decode_splits(int64_t N, int64_t K, int sms) {
-  static const int forced = [] {
-    const char *e = getenv("MSLK_B200_DECODE_SPLITS");   // tuning aid
-    return e ? atoi(e) : 0;
-  }();
   const int64_t n_tiles = (N + kWRows - 1) / kWRows;
   const int64_t k_blocks = (K + kBK - 1) / kBK;
   const int64_t slots = 2 * static_cast<int64_t>(sms);
   const int64_t s_max = std::max<int64_t>(1, std::min<int64_t>(32, k_blocks / 2));
-  if (forced > 0) return static_cast<int>(std::min<int64_t>(forced, s_max));
   int64_t best = 1, best_cost = -1;
   for (int64_t s = 1; s <= s_max; ++s) {
     const int64_t waves = (n_tiles * s + slots - 1) / slots;
@@ -357,13 +352,8 @@ int decode_splits(int64_t N, int64_t K, int sms) {
 // general kernel; (4096, 14336) 13.7 (8) against 27.6 / 20.5; (8192, 8192) 15.8 (4) against 19.5 / 23.3;
 // (14336, 4096): 112 row blocks, unsplit 14.2 us, clusters of 2 15.7.
 int cluster_splits(int64_t N, int64_t K, int sms) {
-  static const int forced = [] {
-    const char *e = getenv("MSLK_B200_DECODE_CLUSTER");   // tuning aid: 1, 2, 4 or 8
-    return e ? atoi(e) : 0;
-  }();
   const int64_t n_tiles = (N + kWRows - 1) / kWRows;
   const int64_t k_blocks = (K + kBK - 1) / kBK;
-  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return k_blocks >= forced ? forced : 1;
   if (2 * n_tiles > sms) return 1;
   int s = 1;
   while (s < 8 && n_tiles * (2 * s) <= 2 * static_cast<int64_t>(sms) && k_blocks / (2 * s) >= 8) s *= 2;

@@ -455,7 +455,6 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   // 256-wide tiles halve the A traffic per flop but hold one accumulator only; use them when
   // there are enough tiles to fill the device, 128-wide (double-buffered) otherwise
   int bn = (m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
-  if (const char *e = getenv("MSLK_B200_NVFP4_BN")) bn = atoi(e) == 128 ? 128 : 256;  // tuning aid
   CUtensorMap ta, tb;
   if (int rc = make_tmap_2d_bytes(&ta, xq, K / 2, M, K / 2, kBKBytes, p.a_box_rows, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d_bytes(&tb, wq, K / 2, G * N, K / 2, kBKBytes, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;

@@ -459,8 +459,6 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
       if ((b2 + P / b2) * slab <= budget) best = b2;
     q.band = static_cast<int>(best && !grouped ? best : 8);   // grouped: the groups are short, bands of 8 blocks
   }
-  static const int env_band = [] { const char *e = getenv("MSLK_B200_NVFP4_BAND"); return e ? atoi(e) : 0; }();        // tuning aid
-  if (env_band > 0) q.band = env_band;
   q.timers = g_timers.load();
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel, ta, tb, tsa, tsb, ty, q), "f4f4bf16 pair launch");

@@ -348,15 +348,10 @@ int token_tile(int64_t M) { return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 
 // N = 28672: 24 us unsplit, 33 us in two).  Rule: splits of at least 32 K blocks, at most as many
 // CTAs as the device holds at two per SM.
 int choose_splits(int64_t N, int64_t K, int sms) {
-  static const int forced = [] {
-    const char *e = getenv("MSLK_B200_NVFP4_DECODE_SPLITS");   // tuning aid
-    return e ? atoi(e) : 0;
-  }();
   const int64_t n_tiles = (N + kWRows - 1) / kWRows;
   const int64_t k_blocks = (K / 2 + kBKBytes - 1) / kBKBytes;
   const int64_t slots = 2 * static_cast<int64_t>(sms);
   const int64_t s_max = std::max<int64_t>(1, std::min<int64_t>(32, k_blocks / 2));
-  if (forced > 0) return static_cast<int>(std::min<int64_t>(forced, s_max));
   const int64_t s = std::min<int64_t>(k_blocks / 32, slots / n_tiles);
   return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(s, s_max)));
 }
@@ -365,13 +360,8 @@ int choose_splits(int64_t N, int64_t K, int sms) {
 // unsplit launch would leave more than half of the SMs without a CTA; then the largest size that still
 // fits all CTAs on the device at once (two per SM) and leaves every CTA at least eight K blocks.
 int cluster_splits(int64_t N, int64_t K, int sms) {
-  static const int forced = [] {
-    const char *e = getenv("MSLK_B200_NVFP4_DECODE_CLUSTER");   // tuning aid: 1, 2, 4 or 8
-    return e ? atoi(e) : 0;
-  }();
   const int64_t n_tiles = (N + kWRows - 1) / kWRows;
   const int64_t k_blocks = (K / 2 + kBKBytes - 1) / kBKBytes;
-  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) return k_blocks >= forced ? forced : 1;
   if (2 * n_tiles > sms) return 1;
   int s = 1;
   while (s < 8 && n_tiles * (2 * s) <= 2 * static_cast<int64_t>(sms) && k_blocks / (2 * s) >= 8) s *= 2;
