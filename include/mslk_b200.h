@@ -240,6 +240,35 @@ int mslk_b200_f4f4bf16_ws(const void *xq, const void *wq, const void *x_scale,
                           void *stream);
 
 /*
+ * MXFP4 quantization: e2m1 data with one e8m0 (power-of-two) scale per group of `group_size` elements (32 = OCP MXFP4,
+ * 16 = the reference's MXFP4-16 recipe), scales in the same 128 x 4 swizzled layout as the NVFP4 scales, no global scale.
+ * Replaces: mslk/quantize/triton/quantize_kernels/mx4.py:28-355 (quantize_mx4_kernel + quantize_mx4) with
+ *           fp4_primitives/scale.py:96-265 (shared exponent, normalize, e8m0 encode).
+ * x is bf16 or fp16 [M, K] with row stride `row_stride` elements, K % group_size == 0.  rounding_mode follows the
+ * reference's RoundingMode: 1 floor, 2 even, 4 ceil (its default); nearest (0) and stochastic (3) are rejected.
+ * q is [M, K/2] bytes; scales is [ceil(M/128)*128 * ceil(K/group_size/4)*4] bytes, written completely (padding = 0).
+ */
+int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, int group_size,
+                           int rounding_mode, void *q, void *scales, void *stream);
+
+/*
+ * MXFP4 GEMMs:  y = bf16(sum_blocks 2^(sx-127) * 2^(sw-127) * sum_block x^ * w^), the forms of f4f4bf16,
+ * f4f4bf16_grouped_stacked and f4f4bf16_grouped_mm the reference runs when no global scale is given
+ * (csrc/gemm/cutlass/f4f4bf16.cu:6413-6473 MXFP4 / MXFP4_16 branches; f4f4bf16_grouped.cu:321-475 with use_mx).
+ * Operands as for the NVFP4 entry points, scales as mslk_b200_quantize_mx4 writes them (grouped: every group's scale
+ * rows start on a 128-row boundary); block_size = 32 or 16; K % 32 == 0.
+ */
+int mslk_b200_f4f4bf16_mx(const void *xq, const void *wq, const void *x_scale, const void *w_scale, void *y, int64_t M,
+                          int64_t N, int64_t K, int block_size, void *stream);
+int mslk_b200_f4f4bf16_grouped_stacked_mx(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                          const int64_t *M_sizes, const int64_t *starting_row_after_padding,
+                                          int64_t G, int64_t total_M, int64_t N, int64_t K, int block_size, void *y,
+                                          void *stream);
+int mslk_b200_f4f4bf16_grouped_mm_mx(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                     const int32_t *offsets, int64_t G, int64_t total_M, int64_t N, int64_t K,
+                                     int block_size, void *y, void *stream);
+
+/*
  * Diagnostics of the CTA-pair NVFP4 kernel's pipeline.  `dev_counters` is a device array of four 64-bit
  * counters (zeroed by the caller) or NULL to switch the measurement off; while set, every launch of the pair
  * kernel adds SM clock cycles summed over its CTA pairs: [0] the MMA-issuing lane waiting for operand stages

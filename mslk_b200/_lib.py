@@ -51,6 +51,14 @@ lib.mslk_b200_quantize_nvfp4.argtypes = [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _
 lib.mslk_b200_quantize_nvfp4.restype = _int
 lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f4f4bf16.restype = _int
+lib.mslk_b200_quantize_mx4.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]
+lib.mslk_b200_quantize_mx4.restype = _int
+lib.mslk_b200_f4f4bf16_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]
+lib.mslk_b200_f4f4bf16_mx.restype = _int
+lib.mslk_b200_f4f4bf16_grouped_stacked_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]
+lib.mslk_b200_f4f4bf16_grouped_stacked_mx.restype = _int
+lib.mslk_b200_f4f4bf16_grouped_mm_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]
+lib.mslk_b200_f4f4bf16_grouped_mm_mx.restype = _int
 lib.mslk_b200_debug_nvfp4_pair_timers.argtypes = [_vp]
 lib.mslk_b200_debug_nvfp4_pair_timers.restype = _int
 lib.mslk_b200_f4f4bf16_workspace_bytes.argtypes = [_i64, _i64, _i64]

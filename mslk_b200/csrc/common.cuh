@@ -196,6 +196,18 @@ __device__ __forceinline__ void mma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uint
       : "memory");
 }
 
+// The same instruction reading TWO scales per row (scale_vec::2X: one scale per 32 K-elements, MXFP4); which two of
+// the four bytes of a scale column it reads is chosen by the scale-id fields of the instruction descriptor.
+__device__ __forceinline__ void mma_mxf4_2x(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+
 // smem -> TMEM copy of 32 lanes x 128 bit, replicated to the four 32-lane quadrants
 // (the shape scale factors are staged with).
 __device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t s_desc) {
@@ -299,6 +311,15 @@ __device__ __forceinline__ void mma_nvfp4_pair(uint32_t d_tmem, uint64_t a_desc,
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void mma_mxf4_2x_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
 // Pair-wide smem -> TMEM copy: each CTA copies from its own shared memory (same offset) into its own
 // tensor memory (same column).
 __device__ __forceinline__ void tc_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t s_desc) {
@@ -339,6 +360,19 @@ __device__ __forceinline__ uint64_t make_sf_atom_desc(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(1) << 46;         // descriptor version (Blackwell)
   return d;                                    // layout type 0 = no swizzle
 }
+
+// Fields of the block-scaled instruction descriptor beyond the operand formats and the tile shape: bit 23 selects
+// ue8m0 scales (0 = ue4m3); with two scales per row and instruction (scale_vec::2X) bits 29-30 / 4-5 give the byte of
+// the 32-bit scale column at which the A / B scales of this instruction start (0 or 2).
+constexpr uint32_t kIdescScaleE8M0 = 1u << 23;
+__host__ __device__ constexpr uint32_t idesc_scale_ids(uint32_t byte) { return (byte << 29) | (byte << 4); }
+
+// Scale formats of the FP4 GEMMs.
+enum : int {
+  kScaleNvfp4 = 0,     // ue4m3, one scale per 16 K-elements, fp32 global scale (NVFP4)
+  kScaleMxfp4 = 1,     // ue8m0, one scale per 32 K-elements (OCP MXFP4)
+  kScaleMxfp4_16 = 2,  // ue8m0, one scale per 16 K-elements
+};
 
 // named barrier among a subset of warps
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {

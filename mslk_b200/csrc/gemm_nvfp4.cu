@@ -52,7 +52,7 @@ struct Fp4Params {
   __nv_bfloat16 *y;
   int *status;
   int M, N, K;          // M = stacked rows of all groups
-  int ncb;              // scale atoms per 128-row block = ceil(K / 64)
+  int ncb;              // scale atoms per 128-row block = ceil(K / 64), MXFP4 (one scale per 32): ceil(K / 128)
   // Grouped (stacked) problems: G weight blocks of N rows, group g owning m_sizes[g] consecutive rows
   // of X / Y.  The scale rows of every group start on a 128-row boundary of their own:
   // sfa_row_start[g] (a multiple of 128) is the first row of group g in the padded scale matrix.
@@ -63,6 +63,7 @@ struct Fp4Params {
   int G;
   int alpha_per_group;
   int a_box_rows;       // rows of the A box: 128, or fewer for a dense problem with fewer rows (no out-of-range fill)
+  int scale_mode;       // kScaleNvfp4 / kScaleMxfp4 / kScaleMxfp4_16 (common.cuh); ncb counts the atoms of that format
 };
 
 template <int BN>
@@ -191,18 +192,20 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           uint8_t *sb = sa + C::kStageA;
           uint8_t *ssfa = sb + C::kStageB;
           uint8_t *ssfb = ssfa + C::kStageSFA;
-          const int atoms = min(4, p.ncb - 4 * kb);  // scale atoms (64 K-elements each) left in this K block
+          // scale atoms (4 scales per row each: 64 K-elements, MXFP4 128) left in this K block of 256 elements
+          const int apk = p.scale_mode == kScaleMxfp4 ? 2 : 4;
+          const int atoms = min(apk, p.ncb - apk * kb);
           const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
           int nb_live = 0;  // 128-row blocks of B that exist for this tile
           for (int b = 0; b < C::kNB; ++b) nb_live += (n_tile * C::kNB + b) < n_row_blocks_b ? 1 : 0;
           mbar_arrive_expect_tx(&S.full[stage], p.a_box_rows * kBKBytes + C::kStageB + sf_bytes * (1 + nb_live));
           tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBKBytes, t.row0);
           tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBKBytes, t.wrow0);
-          bulk_load_1d(ssfa, p.sfa + (static_cast<size_t>(sfa_block) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
+          bulk_load_1d(ssfa, p.sfa + (static_cast<size_t>(sfa_block) * p.ncb + apk * kb) * kAtomBytes, sf_bytes,
                        &S.full[stage]);
           for (int b = 0; b < nb_live; ++b)
             bulk_load_1d(ssfb + b * 4 * kAtomBytes,
-                         p.sfb + (static_cast<size_t>(sfb_block0 + b) * p.ncb + 4 * kb) * kAtomBytes, sf_bytes,
+                         p.sfb + (static_cast<size_t>(sfb_block0 + b) * p.ncb + apk * kb) * kAtomBytes, sf_bytes,
                          &S.full[stage]);
           if (++stage == C::kStages) {
             stage = 0;
@@ -248,6 +251,25 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           const uint64_t da = da0 + soff, db = db0 + soff, dsfa = dsfa0 + soff, dsfb = dsfb0 + soff;
           const uint32_t sfa_t = tmem_base + C::kSfaCol + (n & 1u) * C::kSfCols;
           const uint32_t sfb_t = sfa_t + 16;
+          if (p.scale_mode == kScaleMxfp4) {
+            // one scale per 32 K-elements: an atom holds the scales of TWO instructions, which pick their two bytes
+            // of the scale column through the scale-id fields of the descriptor
+            const int mmas = min(4, (p.K - kb * kBKElems + 63) / 64);
+            const int atoms = (mmas + 1) / 2;
+            for (int a = 0; a < atoms; ++a) {
+              tc_cp_32x128b_warpx4(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+#pragma unroll
+              for (int b = 0; b < C::kNB; ++b)
+                tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * a + 4 * b,
+                                     dsfb + static_cast<uint64_t>((b * 4 + a) * (kAtomBytes >> 4)));
+            }
+            for (int k = 0; k < mmas; ++k)
+              mma_mxf4_2x(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                          db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                          C::kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
+                          sfb_t + 4 * C::kNB * (k >> 1), (kb | k) != 0 ? 1u : 0u);
+          } else {
+          const uint32_t idesc = C::kIdesc | (p.scale_mode == kScaleMxfp4_16 ? kIdescScaleE8M0 : 0u);
           const int atoms = min(4, p.ncb - 4 * kb);
           if (atoms == 4) {
 #pragma unroll
@@ -261,7 +283,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                        db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t + 4 * k,
+                        db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), idesc, sfa_t + 4 * k,
                         sfb_t + 4 * C::kNB * k, (kb | k) != 0 ? 1u : 0u);
           } else {
             for (int k = 0; k < atoms; ++k) {
@@ -273,8 +295,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             }
             for (int k = 0; k < atoms; ++k)
               mma_nvfp4(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                        db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfa_t + 4 * k,
+                        db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), idesc, sfa_t + 4 * k,
                         sfb_t + 4 * C::kNB * k, (kb | k) != 0 ? 1u : 0u);
+          }
           }
           tc_commit(&S.empty[stage]);
           if (++stage == C::kStages) {
@@ -297,7 +320,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     for (int tile = blockIdx.x; epilogue_tile(S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, tile, g, row0, rows, n0);
          tile += gridDim.x, ++local) {
       const int n_tile = n0 / BN;
-      const float alpha = p.alpha[p.alpha_per_group ? g : 0];
+      const float alpha = p.alpha ? p.alpha[p.alpha_per_group ? g : 0] : 1.0f;   // the MX formats have no global scale
       const int acc = local % C::kAccStages;
       const uint32_t acc_phase = (local / C::kAccStages) & 1;
       const int row = row0 + row_in_tile;
@@ -380,14 +403,15 @@ namespace {
 int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scale, const void *w_scale,
             const float *global_scale, void *y, const int64_t *m_sizes, const int32_t *end_offsets,
             const int64_t *sfa_row_start, int64_t G, int64_t M, int64_t N, int64_t K, cudaStream_t st,
-            void *scratch = nullptr, size_t scratch_size = 0) {
+            void *scratch = nullptr, size_t scratch_size = 0, int scale_mode = kScaleNvfp4) {
   const bool grouped = m_sizes || end_offsets;
+  const bool mx = scale_mode != kScaleNvfp4;
   if (M < 0 || N < 0 || K < 0 || G < 1) return fail(1, "%s: bad shape", name);
   if (M == 0 || N == 0) return 0;
   if (G > kMaxGroups) return fail(1, "%s: at most %d groups are supported (got %lld)", name, kMaxGroups, (long long)G);
   if (!y) return fail(1, "%s: null output pointer", name);
   if (K == 0) return check_cuda(cudaMemsetAsync(y, 0, static_cast<size_t>(M) * N * 2, st), "memset");
-  if (!xq || !wq || !x_scale || !w_scale || !global_scale) return fail(1, "%s: null pointer argument", name);
+  if (!xq || !wq || !x_scale || !w_scale || (!global_scale && !mx)) return fail(1, "%s: null pointer argument", name);
   if (K % 32 != 0) return fail(1, "%s: K (%lld) must be a multiple of 32 (16-byte rows of packed e2m1)", name, (long long)K);
   if (M > 0x7fffff00LL || G * N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(1, "%s: dimension too large", name);
   if ((reinterpret_cast<uintptr_t>(x_scale) | reinterpret_cast<uintptr_t>(w_scale)) & 15u)
@@ -404,12 +428,13 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
-  p.ncb = static_cast<int>((K + 63) / 64);
+  p.ncb = static_cast<int>(scale_mode == kScaleMxfp4 ? (K + 127) / 128 : (K + 63) / 64);
+  p.scale_mode = scale_mode;
   p.m_sizes = m_sizes;
   p.end_offsets = end_offsets;
   p.sfa_row_start = sfa_row_start;
   p.G = static_cast<int>(G);
-  p.alpha_per_group = grouped ? 1 : 0;
+  p.alpha_per_group = (grouped && global_scale) ? 1 : 0;
   p.a_box_rows = (!grouped && M < kBM) ? static_cast<int>((M + 7) / 8 * 8) : kBM;
 
   const int sms = sm_count();
@@ -426,7 +451,7 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   // (4096, 14336): 18.1 against 29.7 us, M = 100, (8192, 28672): 32.1 against 54.0, (8192, 8192): 18.5 against
   // 19.9; with K = 4096 the general kernel wins, (4096, 4096): 12.5 against 19.2 us)
   const int64_t w_blocks = (N + 127) / 128;
-  if (!grouped && force == 0 && N >= 128 &&
+  if (!mx && !grouped && force == 0 && N >= 128 &&
       (M <= 64 || (M <= nvfp4_decode::kMaxTokens && (w_blocks > sms || (2 * w_blocks <= sms && K >= 8192)))))
     return nvfp4_decode::launch_decode_kernel(xq, wq, x_scale, w_scale, global_scale, y, status, M, N, K, scratch,
                                               scratch_size, st);
@@ -442,12 +467,13 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
     pp.M = static_cast<int>(M);
     pp.N = static_cast<int>(N);
     pp.K = static_cast<int>(K);
-    pp.ncb = static_cast<int>((K + 63) / 64);
+    pp.ncb = p.ncb;
+    pp.scale_mode = scale_mode;
     pp.m_sizes = m_sizes;
     pp.end_offsets = end_offsets;
     pp.sfa_row_start = sfa_row_start;
     pp.G = static_cast<int>(G);
-    pp.alpha_per_group = grouped ? 1 : 0;
+    pp.alpha_per_group = p.alpha_per_group;
     const int rc = nvfp4_pair::launch_pair_kernel(xq, wq, x_scale, w_scale, pp, st);
     if (rc >= 0) return rc;   // -1: pairs unavailable, fall through to one CTA per tile
   }
@@ -492,6 +518,52 @@ MSLK_API int mslk_b200_f4f4bf16_ws(const void *xq, const void *wq, const void *x
   clear_error();
   return run_fp4("f4f4bf16", xq, wq, x_scale, w_scale, global_scale, y, nullptr, nullptr, nullptr, 1, M, N, K,
                  static_cast<cudaStream_t>(stream), workspace, workspace_bytes);
+}
+
+// ---- MXFP4 forms (e8m0 scales, no global scale): block_size 32 = OCP MXFP4, 16 = e8m0 scales per 16 elements
+static int mx_mode(const char *name, int block_size, int *mode) {
+  if (block_size == 32) *mode = mslk_b200::kScaleMxfp4;
+  else if (block_size == 16) *mode = mslk_b200::kScaleMxfp4_16;
+  else return mslk_b200::fail(1, "%s: block size must be 32 or 16 (got %d)", name, block_size);
+  return 0;
+}
+
+MSLK_API int mslk_b200_f4f4bf16_mx(const void *xq, const void *wq, const void *x_scale, const void *w_scale, void *y,
+                                   int64_t M, int64_t N, int64_t K, int block_size, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  int mode;
+  if (int rc = mx_mode("f4f4bf16 (MXFP4)", block_size, &mode)) return rc;
+  return run_fp4("f4f4bf16 (MXFP4)", xq, wq, x_scale, w_scale, nullptr, y, nullptr, nullptr, nullptr, 1, M, N, K,
+                 static_cast<cudaStream_t>(stream), nullptr, 0, mode);
+}
+
+MSLK_API int mslk_b200_f4f4bf16_grouped_stacked_mx(const void *xq, const void *wq, const void *x_scale,
+                                                   const void *w_scale, const int64_t *M_sizes,
+                                                   const int64_t *starting_row_after_padding, int64_t G,
+                                                   int64_t total_M, int64_t N, int64_t K, int block_size, void *y,
+                                                   void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  const char *name = "f4f4bf16_grouped_stacked (MXFP4)";
+  int mode;
+  if (int rc = mx_mode(name, block_size, &mode)) return rc;
+  if (!M_sizes) return fail(1, "%s: M_sizes is null", name);
+  return run_fp4(name, xq, wq, x_scale, w_scale, nullptr, y, M_sizes, nullptr, starting_row_after_padding, G, total_M, N, K,
+                 static_cast<cudaStream_t>(stream), nullptr, 0, mode);
+}
+
+MSLK_API int mslk_b200_f4f4bf16_grouped_mm_mx(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                              const int32_t *offsets, int64_t G, int64_t total_M, int64_t N, int64_t K,
+                                              int block_size, void *y, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  const char *name = "f4f4bf16_grouped_mm (MXFP4)";
+  int mode;
+  if (int rc = mx_mode(name, block_size, &mode)) return rc;
+  if (!offsets) return fail(1, "%s: offsets is null", name);
+  return run_fp4(name, xq, wq, x_scale, w_scale, nullptr, y, nullptr, offsets, nullptr, G, total_M, N, K,
+                 static_cast<cudaStream_t>(stream), nullptr, 0, mode);
 }
 
 MSLK_API int mslk_b200_f4f4bf16_grouped_stacked(const void *xq, const void *wq, const void *x_scale,

@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       long long t_empty = 0;
+      const int apk = p.scale_mode == kScaleMxfp4 ? 2 : kMmasPerStage;   // scale atoms per K block and 128-row block
       for (int tile = pair_id; ok && sched.get(tile, t); tile += num_pairs) {
         const int g = sched.g;
         const int a_row = t.row0 + static_cast<int>(rank) * kBM;        // first of this CTA's 128 rows of A
@@ -185,13 +186,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           const uint32_t leader_full = mapa_u32(smem_u32(&S.full[stage]), 0);
           // every box is transferred whole (out-of-range rows and atoms are zero-filled), so the byte
           // count is the same for every stage
-          if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * kStageBytes);
+          // (the scale boxes hold apk atoms per 128-row block: four, or two when one scale covers 32 elements)
+          if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * (kStageA + kStageB + 3 * apk * kAtomBytes));
           tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBKBytes, a_row);
           tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBKBytes, t.wrow0 + static_cast<int>(rank) * kBM);
-          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, sfa_block * p.ncb + kMmasPerStage * kb);
-          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, sfb_block * p.ncb + kMmasPerStage * kb);
+          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, sfa_block * p.ncb + apk * kb);
+          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, sfb_block * p.ncb + apk * kb);
           tma_load_2d_pair(ssfb + kMmasPerStage * kAtomBytes, &tmap_sfb, leader_full, 0,
-                           (sfb_block + 1) * p.ncb + kMmasPerStage * kb);
+                           (sfb_block + 1) * p.ncb + apk * kb);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -240,6 +242,32 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           const uint64_t da = da0 + soff, db = db0 + soff, dsfa = dsfa0 + soff, dsfb = dsfb0 + soff;
           const uint32_t sfa_t = tmem_base + kSfBase + (n & 1u) * kSfCols;
           const uint32_t sfb_t = sfa_t + 4 * kMmasPerStage;
+          if (p.scale_mode == kScaleMxfp4) {
+            // one scale per 32 K-elements: an atom holds the scales of TWO instructions, which pick their two bytes
+            // of the scale column through the scale-id fields of the descriptor
+            const int mmas = min(kMmasPerStage, (p.K - kb * kBKElems + 63) / 64);
+            const int atoms = (mmas + 1) / 2;
+            for (int a = 0; a < atoms; ++a) {
+              tc_cp_32x128b_warpx4_pair(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a, dsfb + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a + 4,
+                                        dsfb + static_cast<uint64_t>((kMmasPerStage + a) * (kAtomBytes >> 4)));
+            }
+            for (int k = 0; k < mmas; ++k)
+              mma_mxf4_2x_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                               db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                               kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
+                               sfb_t + 8 * (k >> 1), (kb | k) != 0 ? 1u : 0u);
+            const uint32_t e = smem_u32(&S.empty[stage]);
+            tc_commit_pair(mapa_u32(e, 0));
+            tc_commit_pair(mapa_u32(e, 1));
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
+          const uint32_t idesc = kIdesc | (p.scale_mode == kScaleMxfp4_16 ? kIdescScaleE8M0 : 0u);
           const int atoms = min(kMmasPerStage, p.ncb - kMmasPerStage * kb);
           if (atoms == kMmasPerStage) {
 #pragma unroll
@@ -252,7 +280,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 #pragma unroll
             for (int k = 0; k < kMmasPerStage; ++k)
               mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                             db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), kIdesc, sfa_t + 4 * k, sfb_t + 8 * k,
+                             db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), idesc, sfa_t + 4 * k, sfb_t + 8 * k,
                              (kb | k) != 0 ? 1u : 0u);
           } else {
             for (int k = 0; k < atoms; ++k) {
@@ -263,7 +291,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             }
             for (int k = 0; k < atoms; ++k)
               mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                             db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), kIdesc, sfa_t + 4 * k, sfb_t + 8 * k,
+                             db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), idesc, sfa_t + 4 * k, sfb_t + 8 * k,
                              (kb | k) != 0 ? 1u : 0u);
           }
           const uint32_t e = smem_u32(&S.empty[stage]);
@@ -293,7 +321,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     uint8_t *buf = out_stage + (warp - 2) * kOutSlabBytes;
     int local = 0;
     for (int tile = pair_id; sched.get(tile, t); tile += num_pairs, ++local) {
-      const float alpha = p.alpha[p.alpha_per_group ? sched.g : 0];
+      const float alpha = p.alpha ? p.alpha[p.alpha_per_group ? sched.g : 0] : 1.0f;   // the MX formats have no global scale
       const int slab0 = static_cast<int>(rank) * kBM + quad * 32;   // first row of this warp's slab inside the tile
       const int row0 = t.row0 + slab0;
       const int col0 = t.n0 + half * 128;
@@ -433,10 +461,9 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   if (int rc = make_tmap_2d_bytes(&ta, xq, kbytes, p.M, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, static_cast<uint64_t>(p.G) * p.N, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   // scale buffers as [atoms, 128 words]: a box holds the atoms of one K block of one 128-row block
-  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, kMmasPerStage))
-    return rc;
-  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, kMmasPerStage))
-    return rc;
+  const uint32_t apk = p.scale_mode == kScaleMxfp4 ? 2 : kMmasPerStage;   // scale atoms of one K block
+  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, apk)) return rc;
+  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, apk)) return rc;
 
   PairParams q = p;
   // TMA stores need a 16-byte aligned base and row pitch; otherwise the epilogue stores element by element

@@ -17,7 +17,8 @@ struct PairParams {
   __nv_bfloat16 *y;
   int *status;
   int M, N, K;
-  int ncb;              // scale atoms per 128-row block = ceil(K / 64)
+  int ncb;              // scale atoms per 128-row block = ceil(K / 64); one scale per 32 elements: ceil(K / 128)
+  int scale_mode;       // kScaleNvfp4 / kScaleMxfp4 / kScaleMxfp4_16 (common.cuh); alpha may be null for the MX formats
   int band;             // 256-row blocks per scheduling band (tiles of a band run column by column)
   int tma_store;        // set by the launcher: y is 16-byte aligned and N % 8 == 0, the epilogue may use TMA stores
   // Grouped (stacked) problems: G weight blocks of N rows, group g owning m_sizes[g] (or the rows up to

@@ -184,8 +184,6 @@ at::Tensor f4f4bf16(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor
   TORCH_CHECK(x_scale.is_cuda() && x_scale.is_contiguous() && w_scale.is_cuda() && w_scale.is_contiguous(),
               "f4f4bf16: scales must be contiguous CUDA tensors");
   TORCH_CHECK(mxfp4_block_size == 16 || mxfp4_block_size == 32, "f4f4bf16: mxfp4_block_size must be 16 or 32");
-  TORCH_CHECK(global_scale.has_value(),
-              "f4f4bf16: only the NVFP4 mode (global_scale given) is implemented by this library");
   TORCH_CHECK(XQ.dim() == 2 && WQ.dim() == 2, "f4f4bf16: XQ and WQ must be 2-D");
   const int64_t M = XQ.size(0), K = XQ.size(1) * 2, N = WQ.size(0);
   TORCH_CHECK(WQ.size(1) * 2 == K, "f4f4bf16: XQ and WQ disagree on K");
@@ -193,15 +191,17 @@ at::Tensor f4f4bf16(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor
   same_device(WQ, XQ, "f4f4bf16", "WQ");
   same_device(x_scale, XQ, "f4f4bf16", "x_scale");
   same_device(w_scale, XQ, "f4f4bf16", "w_scale");
-  same_device(*global_scale, XQ, "f4f4bf16", "global_scale");
-  // the kernels copy whole 512-byte scale atoms of the swizzled layout padded to [roundup(rows,128), roundup(K/16,4)]
-  TORCH_CHECK(x_scale.element_size() == 1 && w_scale.element_size() == 1, "f4f4bf16: scales must be 1-byte (e4m3) tensors");
-  TORCH_CHECK(x_scale.numel() >= round_up(M, 128) * round_up(K / 16, 4),
-              "f4f4bf16: x_scale holds ", x_scale.numel(), " scales, the padded swizzled layout of [", M, ", ", K / 16,
-              "] needs ", round_up(M, 128) * round_up(K / 16, 4));
-  TORCH_CHECK(w_scale.numel() >= round_up(N, 128) * round_up(K / 16, 4),
-              "f4f4bf16: w_scale holds ", w_scale.numel(), " scales, the padded swizzled layout of [", N, ", ", K / 16,
-              "] needs ", round_up(N, 128) * round_up(K / 16, 4));
+  if (global_scale.has_value()) same_device(*global_scale, XQ, "f4f4bf16", "global_scale");
+  // NVFP4 (global_scale given): one e4m3 scale per 16 elements; else MXFP4: one e8m0 scale per mxfp4_block_size
+  const int64_t block = global_scale.has_value() ? 16 : mxfp4_block_size;
+  // the kernels copy whole 512-byte scale atoms of the swizzled layout padded to [roundup(rows,128), roundup(K/block,4)]
+  TORCH_CHECK(x_scale.element_size() == 1 && w_scale.element_size() == 1, "f4f4bf16: scales must be 1-byte tensors");
+  TORCH_CHECK(x_scale.numel() >= round_up(M, 128) * round_up(K / block, 4),
+              "f4f4bf16: x_scale holds ", x_scale.numel(), " scales, the padded swizzled layout of [", M, ", ", K / block,
+              "] needs ", round_up(M, 128) * round_up(K / block, 4));
+  TORCH_CHECK(w_scale.numel() >= round_up(N, 128) * round_up(K / block, 4),
+              "f4f4bf16: w_scale holds ", w_scale.numel(), " scales, the padded swizzled layout of [", N, ", ", K / block,
+              "] needs ", round_up(N, 128) * round_up(K / block, 4));
   at::Tensor Y;
   if (output.has_value()) {
     Y = *output;
@@ -213,6 +213,12 @@ at::Tensor f4f4bf16(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor
   }
   if (M == 0 || N == 0 || K == 0) return Y.zero_();
   c10::cuda::CUDAGuard guard(XQ.device());
+  if (!global_scale.has_value()) {
+    check_rc(mslk_b200_f4f4bf16_mx(XQ.data_ptr(), WQ.data_ptr(), x_scale.data_ptr(), w_scale.data_ptr(), Y.data_ptr(), M, N,
+                                   K, static_cast<int>(mxfp4_block_size), stream_of(XQ)),
+             "f4f4bf16");
+    return Y;
+  }
   const at::Tensor gs = global_scale->reshape({-1}).to(at::kFloat);
   // few-token shapes may split K over CTAs: scratch for the partial tiles comes from the caching allocator
   const size_t wsz = mslk_b200_f4f4bf16_workspace_bytes(M, N, K);

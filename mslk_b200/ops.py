@@ -258,12 +258,13 @@ def nvfp4_scale_shape(rows: int, K: int):
     return ((rows + 127) // 128 * 128, (K // 16 + 3) // 4 * 4)
 
 
-def _check_nvfp4_scale_extent(name: str, arg: str, scale: torch.Tensor, rows: int, K: int, groups: int = 1) -> None:
+def _check_nvfp4_scale_extent(name: str, arg: str, scale: torch.Tensor, rows: int, K: int, groups: int = 1,
+                              block: int = 16) -> None:
     """The kernels bulk-copy whole 512-byte atoms of the swizzled scale layout, padded to
-    ``[roundup(rows, 128), roundup(K/16, 4)]`` per group: a shorter tensor would be read past its end."""
+    ``[roundup(rows, 128), roundup(K/block, 4)]`` per group: a shorter tensor would be read past its end."""
     if scale.element_size() != 1:
-        raise RuntimeError(f"{name}: {arg} must be a 1-byte (e4m3) tensor, got {scale.dtype}")
-    pr, pc = nvfp4_scale_shape(rows, K)
+        raise RuntimeError(f"{name}: {arg} must be a 1-byte (e4m3 / e8m0) tensor, got {scale.dtype}")
+    pr, pc = (rows + 127) // 128 * 128, (K // block + 3) // 4 * 4
     need = groups * pr * pc
     if scale.numel() < need:
         raise RuntimeError(f"{name}: {arg} holds {scale.numel()} scales; the padded swizzled layout needs {need}")
@@ -292,13 +293,35 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
     return q.view(*lead, -1, K // 2), s.view(*lead, -1, pc)
 
 
+def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
+    """MXFP4 quantize (``mslk/quantize/triton/quantize_kernels/mx4.py:216-355``): ``(xq uint8 [..., K/2], scales int8,
+    flattened swizzled [roundup(M,128) * roundup(K/group,4)])``.  ``rounding_mode``: 1 floor, 2 even, 4 ceil."""
+    name = "quantize_mx4"
+    dev = _require_cuda(name, x)
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"Expected fp16/bf16, got {x.dtype}")
+    lead, K = x.shape[:-2], x.shape[-1]
+    assert K % group_size == 0, f"N must be divisible by {group_size}, got {K}"
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    pr, pc = (M + 127) // 128 * 128, (K // group_size + 3) // 4 * 4
+    q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    s = torch.empty((pr * pc,), dtype=torch.int8, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_quantize_mx4(_ptr(x2), _DTYPE_CODE[x.dtype], M, K, x2.stride(0), int(group_size),
+                                         int(rounding_mode), _ptr(q), _ptr(s), _stream(dev)), name)
+    return q.view(*lead, -1, K // 2), s
+
+
 def f4f4bf16(XQ, WQ, x_scale, w_scale, output=None, global_scale=None, mxfp4_block_size: int = 32) -> torch.Tensor:
-    """NVFP4 GEMM (``global_scale`` given).  The MXFP4 modes of the reference operator
-    (``global_scale=None``) are outside this library's scope and raise."""
+    """FP4 GEMM: NVFP4 when ``global_scale`` is given (e4m3 scales per 16 elements), else MXFP4 (e8m0 scales per
+    ``mxfp4_block_size`` = 32 or 16 elements), as the reference operator (``csrc/gemm/cutlass/f4f4bf16.cu:6413-6473``)."""
     name = "f4f4bf16"
     dev = _require_cuda(name, XQ, WQ, x_scale, w_scale, global_scale, output)
-    if global_scale is None:
-        raise RuntimeError(f"{name}: only the NVFP4 mode (global_scale given) is implemented")
+    if mxfp4_block_size not in (16, 32):
+        raise RuntimeError(f"mxfp4_block_size must be 32 or 16, got {mxfp4_block_size}")
     if not (XQ.is_contiguous() and WQ.is_contiguous() and x_scale.is_contiguous() and w_scale.is_contiguous()):
         raise RuntimeError(f"{name}: XQ, WQ, x_scale and w_scale must be contiguous")
     M, K = XQ.shape[0], XQ.shape[1] * 2
@@ -307,14 +330,22 @@ def f4f4bf16(XQ, WQ, x_scale, w_scale, output=None, global_scale=None, mxfp4_blo
         raise RuntimeError(f"{name}: K mismatch")
     if N % 16 != 0 or K % 16 != 0:
         raise RuntimeError(f"{name}: N and K must be multiples of 16")
-    _check_nvfp4_scale_extent(name, "x_scale", x_scale, M, K)
-    _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K)
+    block = 16 if global_scale is not None else mxfp4_block_size
+    if K % 32 != 0:
+        raise RuntimeError(f"{name}: K must be a multiple of 32")
+    _check_nvfp4_scale_extent(name, "x_scale", x_scale, M, K, block=block)
+    _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, block=block)
     if output is None:
         output = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
     elif output.dtype != torch.bfloat16 or tuple(output.shape) != (M, N) or not output.is_contiguous():
         raise RuntimeError(f"{name}: output must be a contiguous bfloat16 [M,N] tensor")
     if M == 0 or N == 0 or K == 0:
         return output.zero_()
+    if global_scale is None:
+        with torch.cuda.device(dev):
+            check(lib.mslk_b200_f4f4bf16_mx(_ptr(_as_bytes(XQ)), _ptr(_as_bytes(WQ)), _ptr(x_scale), _ptr(w_scale), _ptr(output),
+                                            M, N, K, mxfp4_block_size, _stream(dev)), name)
+        return output
     gs = global_scale.reshape(-1).to(torch.float32)
     with torch.cuda.device(dev):
         wsz = lib.mslk_b200_f4f4bf16_workspace_bytes(M, N, K)   # few tokens: scratch for K splitting
@@ -449,8 +480,12 @@ def f4f4bf16_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes, global_scale=Non
     """Grouped NVFP4 GEMM over stacked rows: ``XQ [total_M, K/2]``, ``WQ [G, N, K/2]``, fp32 ``global_scale [G]``."""
     name = "f4f4bf16_grouped_stacked"
     dev = _require_cuda(name, XQ, WQ, x_scale, w_scale, M_sizes, global_scale, starting_row_after_padding)
-    if global_scale is None or use_mx:
-        raise RuntimeError(f"{name}: only the NVFP4 mode (global_scale given, use_mx=False) is implemented")
+    # the reference's rule (csrc/gemm/cutlass/f4f4bf16_grouped.cu:321-374): MXFP4 unless use_mx is off, then NVFP4
+    # with its per-group global scales
+    if not use_mx and global_scale is None:
+        raise RuntimeError(f"{name}: the NVFP4 mode (use_mx=False) needs global_scale")
+    if use_mx and global_scale is not None:
+        raise RuntimeError(f"{name}: global_scale is for the NVFP4 mode; pass use_mx=False with it")
     if M_sizes.dtype != torch.int64:
         raise RuntimeError("M_sizes must be int64.")
     if WQ.dim() != 3 or WQ.shape[0] != M_sizes.shape[0]:
@@ -464,13 +499,23 @@ def f4f4bf16_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes, global_scale=Non
         if starting_row_after_padding.numel() % (G + 1) != 0 or starting_row_after_padding.dtype != torch.int64:
             raise RuntimeError(f"{name}: starting_row_after_padding must be int64 with a multiple of G+1 entries")
         srp = starting_row_after_padding.contiguous()
+    block = 32 if use_mx else 16
+    if total_M:
+        _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, groups=G, block=block)
+        # the group sizes live on the device: the host can only check the smallest layout any split of total_M needs
+        _check_nvfp4_scale_extent(name, "x_scale", x_scale, total_M, K, block=block)
+    if use_mx:
+        Y = torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
+        if total_M == 0:
+            return Y
+        with torch.cuda.device(dev):
+            check(lib.mslk_b200_f4f4bf16_grouped_stacked_mx(
+                _ptr(_as_bytes(XQ)), _ptr(_as_bytes(WQ)), _ptr(x_scale), _ptr(w_scale), _ptr(M_sizes.contiguous()),
+                _ptr(srp), G, total_M, N, K, 32, _ptr(Y), _stream(dev)), name)
+        return Y
     gs = global_scale.reshape(-1).to(torch.float32)
     if gs.numel() != G:
         raise RuntimeError(f"{name}: global_scale must hold one value per group")
-    if total_M:
-        _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, groups=G)
-        # the group sizes live on the device: the host can only check the smallest layout any split of total_M needs
-        _check_nvfp4_scale_extent(name, "x_scale", x_scale, total_M, K)
     Y = torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
     if total_M == 0:
         return Y
@@ -496,8 +541,13 @@ def f4f4bf16_grouped_mm(XQ, WQ, x_scale, w_scale, offsets, output=None, global_s
         raise RuntimeError("WQ must be column major.")
     if not (x_scale.is_contiguous() and w_scale.is_contiguous()):
         raise RuntimeError("x_scale and w_scale must be contiguous.")
-    if global_scale is None or x_scale.dtype != FP8_DTYPE:
-        raise RuntimeError(f"{name}: only NVFP4 (float8_e4m3fn scales with a global_scale) is implemented")
+    # the reference tells the formats apart by the scale dtype (csrc/gemm/cutlass/f4f4bf16_grouped.cu:396-440):
+    # float8_e4m3fn = NVFP4 (needs global_scale), float8_e8m0fnu = MXFP4
+    nvfp4 = x_scale.dtype == FP8_DTYPE
+    if nvfp4 and global_scale is None:
+        raise RuntimeError(f"{name}: NVFP4 (float8_e4m3fn scales) needs global_scale")
+    if not nvfp4 and global_scale is not None:
+        raise RuntimeError(f"{name}: global_scale is for NVFP4 (float8_e4m3fn scales)")
     if XQ.dim() != 2 or WQ.dim() != 3:
         raise RuntimeError(f"{name}: only the 2D-3D form (XQ [total_M, K], WQ [G, K, N]) is implemented")
     G = offsets.shape[0]
@@ -506,17 +556,23 @@ def f4f4bf16_grouped_mm(XQ, WQ, x_scale, w_scale, offsets, output=None, global_s
     if XQ.shape[1] * 2 != K or WQ.shape[0] != G:
         raise RuntimeError("for 2d-3d grouped GEMM, XQ shape must be (total_M, K) and WQ shape must be (G, K, N).")
     if total_M and N:
-        _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, groups=G)
-        _check_nvfp4_scale_extent(name, "x_scale", x_scale, total_M, K)
+        _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, groups=G, block=16 if nvfp4 else 32)
+        _check_nvfp4_scale_extent(name, "x_scale", x_scale, total_M, K, block=16 if nvfp4 else 32)
     out = output if output is not None else torch.empty((total_M, N), dtype=torch.bfloat16, device=dev)
     if out.dim() != 2 or out.shape[0] != total_M or out.shape[1] != N or out.dtype != torch.bfloat16 or not out.is_contiguous():
         raise RuntimeError("for 2d-3d grouped GEMM, output shape must be (total_M, N).")
     if out.numel() == 0:
         return out
+    wq = WQ.transpose(-2, -1)
+    if not nvfp4:
+        with torch.cuda.device(dev):
+            check(lib.mslk_b200_f4f4bf16_grouped_mm_mx(
+                _ptr(_as_bytes(XQ)), _ptr(_as_bytes(wq)), _ptr(x_scale), _ptr(w_scale), _ptr(offsets.contiguous()),
+                G, total_M, N, K, 32, _ptr(out), _stream(dev)), name)
+        return out
     gs = global_scale.reshape(-1).to(torch.float32)
     if gs.numel() != G:
         raise RuntimeError(f"{name}: global_scale must hold one value per group")
-    wq = WQ.transpose(-2, -1)
     with torch.cuda.device(dev):
         check(lib.mslk_b200_f4f4bf16_grouped_mm(
             _ptr(_as_bytes(XQ)), _ptr(_as_bytes(wq)), _ptr(x_scale), _ptr(w_scale), _ptr(offsets.contiguous()), _ptr(gs),

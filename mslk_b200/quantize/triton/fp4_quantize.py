@@ -27,6 +27,25 @@ def triton_quantize_nvfp4(
     return xq, scales
 
 
+def triton_quantize_mx4_unpack(input: torch.Tensor, group_size: int = 32, ebits: int = 2, mbits: int = 1,
+                               rounding_mode: int = 4, stochastic_casting: bool = False, *, seed=None):
+    """MXFP4 quantize with the reference's symbol (``mslk/quantize/triton/fp4_quantize.py:46-90``): packed e2m1 bytes
+    ``[..., K // 2]`` and flattened swizzled e8m0 scales (int8).  Rounding modes floor (1), even (2) and ceil (4, the
+    default) are implemented; nearest and stochastic raise."""
+    from ... import ops as _ops
+    if ebits != 2 or mbits != 1:
+        raise NotImplementedError(f"triton_quantize_mx4_unpack: only E2M1 (ebits=2, mbits=1) is supported, got ebits={ebits}, mbits={mbits}.")
+    if stochastic_casting:
+        raise NotImplementedError("stochastic rounding is not implemented by this library")
+    xq, scale = _ops.quantize_mx4(input, group_size, int(rounding_mode))
+    return xq.reshape(list(input.shape[:-1]) + [-1]), scale
+
+
+def triton_quantize_mx4(input: torch.Tensor, *, rounding_mode: int = 4, seed=None):
+    """``mslk/quantize/triton/fp4_quantize.py:93-120``: group size 32."""
+    return triton_quantize_mx4_unpack(input, 32, rounding_mode=rounding_mode)
+
+
 def calculate_group_max(input: torch.Tensor, m_sizes: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-group NVFP4 global scales for stacked MoE activations
     (``mslk/quantize/triton/legacy/global_scale.py:156-230``): ``(global_scale [G] fp32, group of each row [M] int64)``."""

@@ -69,6 +69,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_nvfp4_scale_offset.restype = i64
         L.oracle_quantize_nvfp4.argtypes = [vp, i64, i64, vp, vp, vp]
         L.oracle_quantize_nvfp4.restype = None
+        L.oracle_quantize_mx4.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp]
+        L.oracle_quantize_mx4.restype = None
         L.oracle_gemm_nvfp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
         L.oracle_gemm_nvfp4.restype = None
         L.oracle_check_fma_division.argtypes = [vp, vp, i64]
@@ -324,6 +326,42 @@ def gemm_nvfp4(xq, wq, x_scale, w_scale, global_scale):
     sw = w_scale.contiguous().view(torch.uint8)
     lib().oracle_gemm_nvfp4(_p(xq), _p(wq), _p(sx), _p(sw), _p(gs), M, N, K, _p(y))
     return y
+
+
+# --------------------------------------------------------------------------
+# MXFP4 (e8m0 scales per 32 or 16 elements)
+# --------------------------------------------------------------------------
+
+MX_ROUND_ADD = {1: 0, 2: (1 << 21) - 1, 4: (1 << 23) - 1}     # floor / even / ceil of the shared exponent
+
+
+def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
+    """MXFP4 quantize (``mslk/quantize/triton/quantize_kernels/mx4.py:28-355``): returns
+    ``(xq uint8 [M, K/2], scales uint8, flattened swizzled [ceil(M/128)*128 * ceil(K/group/4)*4])``."""
+    x2 = _cpu(x).reshape(-1, x.shape[-1]).contiguous()
+    M, K = x2.shape
+    assert K % group_size == 0 and x2.dtype in (torch.bfloat16, torch.float16)
+    pr, pc = (M + 127) // 128 * 128, (K // group_size + 3) // 4 * 4
+    q = torch.empty((M, K // 2), dtype=torch.uint8)
+    s = torch.empty((pr * pc,), dtype=torch.uint8)
+    lib().oracle_quantize_mx4(_p(x2.view(torch.int16)), 1 if x2.dtype == torch.bfloat16 else 2, M, K, group_size,
+                              MX_ROUND_ADD[int(rounding_mode)], _p(q), _p(s))
+    return q, s
+
+
+def gemm_mx4_torch(xq, wq, x_scale, w_scale, group_size: int = 32, out_dtype=torch.bfloat16):
+    """fp32 dequantize-matmul formula of the MXFP4 GEMM: ``(fp4(xq) * 2^(sx-127)) @ (fp4(wq) * 2^(sw-127)).T`` with the
+    e8m0 scales un-swizzled (the check the reference's tests make against the unquantized product, in exact form)."""
+    M, K = xq.shape[0], xq.shape[1] * 2
+    N = wq.shape[0]
+    dev = xq.device
+    sx = from_blocked(x_scale.view(torch.uint8).cpu().reshape(-1), M, K // group_size).to(torch.int32)
+    sw = from_blocked(w_scale.view(torch.uint8).cpu().reshape(-1), N, K // group_size).to(torch.int32)
+    fx = torch.ldexp(torch.ones(sx.shape, dtype=torch.float32), sx - 127).to(dev)
+    fw = torch.ldexp(torch.ones(sw.shape, dtype=torch.float32), sw - 127).to(dev)
+    xf = fp4_to_float(xq) * fx.repeat_interleave(group_size, dim=1)
+    wf = fp4_to_float(wq) * fw.repeat_interleave(group_size, dim=1)
+    return (xf @ wf.T).to(out_dtype)
 
 
 # --------------------------------------------------------------------------

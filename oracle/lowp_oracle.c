@@ -350,6 +350,44 @@ ORACLE_API void oracle_quantize_nvfp4(const uint16_t *x_bf16, int64_t M, int64_t
 }
 
 /*
+ * MXFP4 quantize, the reference's arithmetic (mslk/quantize/triton/quantize_kernels/mx4.py:118-214 with
+ * fp4_primitives/scale.py:96-265): per group of `group` elements (32 or 16)
+ *   e     = ((bits(max|x|) + round_add) & 0x7F800000) >> 23) - 127 - 2, clamped to [-127, 125]
+ *           round_add = 0 (floor), 2^21 - 1 (even), 2^23 - 1 (ceil)
+ *   scale = byte e + 127 (e8m0);   x^ = e2m1( x * 2^-e ), the factor built from its exponent bits.
+ * x: bf16 (dtype 1) or fp16 (dtype 2).  q: [M, K/2]; scales: swizzled like the NVFP4 scales, padded to
+ * [ceil(M/128)*128, ceil(K/group/4)*4], padding zero.
+ */
+ORACLE_API void oracle_quantize_mx4(const uint16_t *x, int dtype, int64_t M, int64_t K, int group, int round_add,
+                                    uint8_t *q, uint8_t *scales_swizzled) {
+  int64_t nblk = K / group;
+  int64_t ncb = (nblk + 3) / 4;
+  int64_t nrb = (M + 127) / 128;
+  memset(scales_swizzled, 0, (size_t)(nrb * ncb * 512));
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    for (int64_t j = 0; j < nblk; ++j) {
+      const uint16_t *xb = x + m * K + j * group;
+      float amax = 0.f;
+      for (int i = 0; i < group; ++i) {
+        float v = fabsf(dtype == 2 ? f16_to_f32(xb[i]) : bf16_to_f32(xb[i]));
+        if (v > amax) amax = v;
+      }
+      int e = (int)(((f32_to_bits(amax) + (uint32_t)round_add) & 0x7F800000u) >> 23) - 127 - 2;
+      if (e > 125) e = 125;
+      if (e < -127) e = -127;
+      scales_swizzled[oracle_nvfp4_scale_offset(m, j, ncb)] = (uint8_t)(e + 127);
+      float inv = bits_to_f32((uint32_t)(127 - e) << 23);
+      for (int i = 0; i < group; i += 2) {
+        volatile float a = (dtype == 2 ? f16_to_f32(xb[i]) : bf16_to_f32(xb[i])) * inv;
+        volatile float b = (dtype == 2 ? f16_to_f32(xb[i + 1]) : bf16_to_f32(xb[i + 1])) * inv;
+        q[m * (K / 2) + (j * group + i) / 2] = (uint8_t)(oracle_f32_to_e2m1(a) | (oracle_f32_to_e2m1(b) << 4));
+      }
+    }
+  }
+}
+
+/*
  * NVFP4 GEMM: y = bf16( alpha * sum_blocks (sx*sw) * sum_16 x^*w^ ), fp32 math,
  * alpha = *global_scale (csrc/gemm/cutlass/f4f4bf16/f4f4bf16_common.cuh:78-315;
  * dequantisation as mslk/quantize/triton/legacy/fp4_utils.py:19-45,95-120).

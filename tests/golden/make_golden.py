@@ -17,6 +17,9 @@ Two legs, both writing ``.npz`` files next to this script:
 ``--leg gpu_gather``  (needs a B200) runs the reference's ``gather_scale_quant_dense_tokens``
     (``mslk/moe/gather_scatter.py``).  These two legs store outputs only; the tests regenerate the
     seeded inputs with ``silu_inputs`` / ``gather_inputs`` (CPU generator, same torch build).
+``--leg gpu_mx4``  (needs a B200) runs the reference's MXFP4 quantizer ``quantize_mx4``
+    (``mslk/quantize/triton/quantize_kernels/mx4.py``) for group sizes 32 / 16 and the floor / even / ceil rounding
+    modes; outputs only (the tests regenerate the inputs with ``mx4_inputs``).
 ``--leg gpu``  (needs a B200) runs the reference's Triton kernels
     ``triton_quantize_fp8_row`` and ``triton_quantize_nvfp4`` on the same seeded
     inputs; these are the bit-level pins for the GPU arithmetic.
@@ -355,9 +358,44 @@ def leg_gpu_fp4_stacked(ref_root: str):
     print("gpu fp4 stacked leg written")
 
 
+# (name, shape, dtype) of the MXFP4 quantizer cases: rows below / at / above the 128-row scale block, K with a partial
+# group of four scales, fp16 input, values spanning many binades, an all-zero group and exact powers of two
+MX4_CASES = [("r128_k64", (128, 64), "bf16"), ("r5_k128", (5, 128), "bf16"), ("r150_k1024", (150, 1024), "bf16"),
+             ("r70_k3584", (70, 3584), "bf16"), ("r1_k5120", (1, 5120), "bf16"), ("r129_k96", (129, 96), "bf16"),
+             ("r64_k512_f16", (64, 512), "f16"), ("r256_k256_wide", (256, 256), "bf16")]
+
+
+def mx4_inputs(name, shape, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g, dtype=torch.float32)
+    if name.endswith("wide"):
+        x = x * torch.exp2(torch.randint(-40, 40, (shape[0], 1), generator=g).float())
+        x[0, :32] = 0.0                       # an all-zero group
+        x[1, :32] = 4.0                       # exact powers of two: ceil and floor of log2 coincide
+        x[2, :32] = 6.0
+    return x.to(torch.bfloat16 if dtype == "bf16" else torch.float16)
+
+
+def leg_gpu_mx4(ref_root: str):
+    """quantize_mx4 of the reference (Triton) on a B200: group sizes 32 / 16, rounding floor / even / ceil."""
+    _import_reference(ref_root)
+    from mslk.quantize.triton.quantize_kernels.mx4 import quantize_mx4
+    out = {}
+    for i, (name, shape, dtype) in enumerate(MX4_CASES):
+        x = mx4_inputs(name, shape, dtype, 700 + i).cuda()
+        for group in (32, 16):
+            for mode in (4, 1, 2):
+                q, s = quantize_mx4(x, group_size=group, rounding_mode=mode)
+                torch.cuda.synchronize()
+                out[f"{name}.g{group}.m{mode}.q"] = _raw(q.view(torch.uint8))
+                out[f"{name}.g{group}.m{mode}.s"] = _raw(s.view(torch.uint8))
+    np.savez_compressed(os.path.join(HERE, "mx4_triton_b200.npz"), **out)
+    print("gpu mx4 leg written")
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu", "gpu_gather", "gpu_fp4_stacked"], required=True)
+    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu", "gpu_gather", "gpu_fp4_stacked", "gpu_mx4"], required=True)
     ap.add_argument("--ref-root", required=True)
     ap.add_argument("--out-dir", default=None, help="write here instead of beside this script")
     args = ap.parse_args()
@@ -365,4 +403,4 @@ if __name__ == "__main__":
         HERE = args.out_dir
         os.makedirs(HERE, exist_ok=True)
     {"cpu": leg_cpu, "gpu": leg_gpu, "gpu_silu": leg_gpu_silu, "gpu_gather": leg_gpu_gather,
-     "gpu_fp4_stacked": leg_gpu_fp4_stacked}[args.leg](args.ref_root)
+     "gpu_fp4_stacked": leg_gpu_fp4_stacked, "gpu_mx4": leg_gpu_mx4}[args.leg](args.ref_root)

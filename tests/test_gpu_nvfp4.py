@@ -90,8 +90,8 @@ def test_gemm_large_tiles_and_output_arg(ops):
     out = torch.empty_like(y)
     y2 = ops.f4f4bf16(xq, wq, sx, sw, output=out, global_scale=alpha)
     assert y2.data_ptr() == out.data_ptr() and torch.equal(out, y)
-    with pytest.raises(RuntimeError, match="NVFP4"):
-        ops.f4f4bf16(xq, wq, sx, sw)
+    with pytest.raises(RuntimeError, match="mxfp4_block_size"):
+        ops.f4f4bf16(xq, wq, sx, sw, global_scale=alpha, mxfp4_block_size=8)
     assert _status() == 0
 
 

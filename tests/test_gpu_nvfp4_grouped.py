@@ -148,7 +148,9 @@ def test_rows_past_the_sum_untouched_and_errors(ops):
     y = torch.ops.mslk.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, None, False)
     assert y.shape == (30, N)
     with pytest.raises(RuntimeError, match="NVFP4"):
-        ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, None, None)
+        ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, None, None, use_mx=False)
+    with pytest.raises(RuntimeError, match="use_mx=False"):
+        ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, None)       # use_mx defaults to True
     with pytest.raises(RuntimeError, match="int64"):
         ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms.int(), alpha, None, use_mx=False)
     with pytest.raises(RuntimeError, match="int32"):

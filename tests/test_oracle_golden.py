@@ -8,7 +8,7 @@ import torch
 
 import oracle
 from helpers import bf16, fp8, load_golden, u8, randn_bf16
-from golden.make_golden import FP8_ROW_CASES, NVFP4_CASES
+from golden.make_golden import FP8_ROW_CASES, MX4_CASES, NVFP4_CASES, mx4_inputs
 
 
 def test_e4m3_encode_matches_torch_exhaustive_grid():
@@ -169,6 +169,50 @@ def test_nvfp4_triton_fixture():
         q, s = oracle.quantize_nvfp4(x, gs)
         assert torch.equal(u8(s).reshape(-1), torch.from_numpy(gold[f"{name}.s_blocked"]).reshape(-1)), name
         assert torch.equal(q, torch.from_numpy(gold[f"{name}.q"])), name
+
+
+def test_mx4_triton_fixture_pins_the_mx4_oracle():
+    """Outputs of the reference's triton_quantize_mx4_unpack on a B200 (packed bytes and swizzled e8m0 scales, block
+    sizes 32 and 16, floor / even / ceil rounding of the shared exponent) against the C restatement, bit for bit."""
+    gold = load_golden("mx4_triton_b200.npz")
+    if gold is None:
+        pytest.skip("fixture captured on a B200 not present yet")
+    for i, (name, shape, dtype) in enumerate(MX4_CASES):
+        x = mx4_inputs(name, shape, dtype, 700 + i)
+        for group in (32, 16):
+            for mode in (4, 1, 2):
+                q, s = oracle.quantize_mx4(x, group, mode)
+                key = f"{name}.g{group}.m{mode}"
+                assert torch.equal(q, torch.from_numpy(gold[key + ".q"])), key
+                assert torch.equal(s.reshape(-1), torch.from_numpy(gold[key + ".s"]).reshape(-1)), key
+
+
+def test_mx4_oracle_against_a_plain_statement():
+    """Independent of the fixture: ceil rounding picks the smallest power of two 2^e with amax <= 6 * 2^e ... up to the
+    reference's shift by two binades (e = ceil(log2(amax)) - 2), values are x * 2^-e rounded to e2m1 (ties to even)."""
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn((64, 256), generator=g) * torch.exp2(torch.randint(-20, 20, (64, 1), generator=g).float())).bfloat16()
+    q, s = oracle.quantize_mx4(x, 32, 4)
+    xf = x.float().reshape(64, 8, 32)
+    amax = xf.abs().amax(dim=-1)
+    e = torch.ceil(torch.log2(amax.double())).to(torch.int32) - 2
+    e = e.clamp(-127, 125)
+    # the scale bytes sit in 128-row x 4-column swizzled atoms: row r, column c -> (r % 32) * 16 + (r // 32) * 4 + c
+    s = s.reshape(-1)
+    for r in range(64):
+        for c in range(8):
+            atom = c // 4
+            off = atom * 512 + (r % 32) * 16 + (r // 32) * 4 + (c % 4)
+            assert int(s[off]) == int(e[r, c]) + 127, (r, c)
+    grid = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    scaled = (xf.double() * torch.exp2(-e.double()).unsqueeze(-1)).float().reshape(64, 256)
+    lo = (q & 0xF).long()
+    hi = (q >> 4).long()
+    codes = torch.stack([lo, hi], dim=-1).reshape(64, 256)
+    val = grid[codes & 7] * torch.where((codes & 8) != 0, -1.0, 1.0)
+    # nearest grid point (ties checked by the e2m1 test above): no other grid value is strictly closer
+    d = (scaled.unsqueeze(-1).abs().clamp(max=6.0) - grid).abs()
+    assert torch.all((val.abs() - scaled.abs().clamp(max=6.0)).abs() <= d.min(dim=-1).values + 1e-7)
 
 
 def test_nvfp4_gemm_oracles_agree_and_dequant_matches_reference():
