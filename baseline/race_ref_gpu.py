@@ -41,9 +41,30 @@ def compare(y, y_ref):
     return {"max_ulp": int(d.max()), "frac_within_1ulp": float((d <= 1).sum()) / n, "frac_equal": float((d == 0).sum()) / n}
 
 
+_NVML = None
+
+
+def sm_clock_mhz():
+    """Current SM clock of the device in use (read-only NVML query); None without NVML."""
+    global _NVML
+    try:
+        import pynvml
+        if _NVML is None:
+            pynvml.nvmlInit()
+            _NVML = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        return int(pynvml.nvmlDeviceGetClockInfo(_NVML, pynvml.NVML_CLOCK_SM))
+    except Exception:
+        return None
+
+
+LAST_MHZ = [None]
+
+
 def time_us(fn, n_variants, iters, warmup):
     """us per launch, `iters` launches replayed from one CUDA graph: both sides are then timed by the device, not
-    by how fast their host paths (ctypes here, the torch dispatcher there) can issue short kernels."""
+    by how fast their host paths (ctypes here, the torch dispatcher there) can issue short kernels.  The SM clock is
+    sampled while the timed replay runs (LAST_MHZ): on a power-capped part the clock, not the kernel, can differ
+    between two runs."""
     for i in range(warmup):
         fn(i % n_variants)
     torch.cuda.synchronize()
@@ -59,7 +80,15 @@ def time_us(fn, n_variants, iters, warmup):
     e0.record()
     g.replay()
     e1.record()
+    mhz = []
+    while not e1.query() and len(mhz) < 64:
+        c = sm_clock_mhz()
+        if c is None:
+            break
+        mhz.append(c)
     torch.cuda.synchronize()
+    mhz.sort()
+    LAST_MHZ[0] = mhz[len(mhz) // 2] if mhz else sm_clock_mhz()
     return e0.elapsed_time(e1) / iters * 1e3
 
 
@@ -68,11 +97,15 @@ def race_pair(ours_fn, ref_fn, n_variants, iters, warmup, rounds=3):
     temperature drift over the run hits both alike."""
     a, b = [], []
     for _ in range(rounds):
-        a.append(time_us(ours_fn, n_variants, iters, warmup))
-        b.append(time_us(ref_fn, n_variants, iters, warmup))
-    a.sort()
-    b.sort()
-    return a[len(a) // 2], b[len(b) // 2]
+        a.append((time_us(ours_fn, n_variants, iters, warmup), LAST_MHZ[0]))
+        b.append((time_us(ref_fn, n_variants, iters, warmup), LAST_MHZ[0]))
+    a.sort(key=lambda t: t[0])
+    b.sort(key=lambda t: t[0])
+    RACE_MHZ[:] = [a[len(a) // 2][1], b[len(b) // 2][1]]
+    return a[len(a) // 2][0], b[len(b) // 2][0]
+
+
+RACE_MHZ = [None, None]        # SM clock seen during the median run of each side of the last race_pair
 
 
 def randn(shape, std=1.0, seed=0):
@@ -175,6 +208,7 @@ def main():
     lines = []
 
     def emit(r):
+        r["ours_sm_mhz"], r["ref_sm_mhz"] = RACE_MHZ
         lines.append(r)
         print(json.dumps(r), flush=True)
 
@@ -206,6 +240,18 @@ def main():
         with open(args.out, "w") as f:
             for r in lines:
                 f.write(json.dumps(r) + "\n")
+        with open(os.path.splitext(args.out)[0] + "_table.md", "w") as f:
+            f.write("| case | this library | reference | speed ratio (>1: this library faster) | SM MHz (ours / ref) | output difference |\n")
+            f.write("|---|---|---|---|---|---|\n")
+            for r in lines:
+                if "max_ulp" in r:
+                    diff = "bit-identical" if r["max_ulp"] == 0 else \
+                        f"max {r['max_ulp']} bf16 ulp, {100 * r['frac_equal']:.3f} % identical"
+                else:
+                    diff = "bytes and scales bit-identical" if r["bytes_equal"] and r["scales_equal"] else "DIFFERENT"
+                inst = r.get("ref_instance") or r.get("ref_kernel", "").split(" ")[0]
+                f.write(f"| {r['case']} | {r['ours_us']:.1f} us | {r['ref_us']:.1f} us (`{inst}`) | "
+                        f"{r['ours_over_ref_speed']:.2f} | {r['ours_sm_mhz']} / {r['ref_sm_mhz']} | {diff} |\n")
 
 
 if __name__ == "__main__":

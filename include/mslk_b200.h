@@ -278,6 +278,24 @@ int mslk_b200_f4f4bf16_grouped_mm_mx(const void *xq, const void *wq, const void 
 int mslk_b200_debug_nvfp4_pair_timers(unsigned long long *dev_counters);
 
 /*
+ * K-grouped ("2D-2D") FP4 GEMM:  y[g] = X[:, k_{g-1}:k_g] * W[:, k_{g-1}:k_g]^T  for G groups along K (the weight-gradient
+ * shape of a grouped layer).  Replaces: csrc/gemm/cutlass/f4f4bf16_grouped.cu:434-446 (f4f4bf16_grouped_mm with 2D XQ
+ * and 2D WQ) with include/mslk/gemm/cutlass/grouped_common.cuh:104-213.
+ * xq [M, total_K/2], wq [N, total_K/2] packed e2m1 (the reference passes wq as the transposed view [total_K, N]);
+ * k_end_offsets: device int32 [G] END offsets along K, multiples of 32, non-decreasing, <= total_K (a group that breaks
+ * this yields zeros and sets bit 0x400 of the device status word; an empty group yields zeros).  Scales: one swizzled
+ * block per group, [ceil(M/128)*128 (or N) rows][ceil(K_g/block/4)*4 columns], the blocks following each other;
+ * global_scale fp32 [G] selects NVFP4 (e4m3 scales per 16), NULL selects MXFP4 with block_size 32 or 16 (e8m0).
+ * x_scale_bytes / w_scale_bytes: sizes of the two scale tensors; offsets whose padded scale blocks would not fit are
+ * rejected on the device the same way (zeros, bit 0x400), the kernel never reads past these sizes.
+ * y [G, M, N] bf16.  G <= 1024.
+ */
+int mslk_b200_f4f4bf16_grouped_mm_2d2d(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                       const int32_t *k_end_offsets, const float *global_scale, int64_t G, int64_t M,
+                                       int64_t N, int64_t total_K, int block_size, size_t x_scale_bytes,
+                                       size_t w_scale_bytes, void *y, void *stream);
+
+/*
  * Grouped (stacked) NVFP4 GEMM for mixture-of-experts layers: group g multiplies its m_g stacked rows
  * of xq by its own weight block wq[g] and scales the result by global_scale[g].
  * Replaces: csrc/gemm/cutlass/f4f4bf16_grouped.cu:321-374 (f4f4bf16_grouped_stacked, NVFP4 mode) with

@@ -59,6 +59,9 @@ lib.mslk_b200_f4f4bf16_grouped_stacked_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _
 lib.mslk_b200_f4f4bf16_grouped_stacked_mx.restype = _int
 lib.mslk_b200_f4f4bf16_grouped_mm_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]
 lib.mslk_b200_f4f4bf16_grouped_mm_mx.restype = _int
+lib.mslk_b200_f4f4bf16_grouped_mm_2d2d.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int,
+                                                   ctypes.c_size_t, ctypes.c_size_t, _vp, _vp]
+lib.mslk_b200_f4f4bf16_grouped_mm_2d2d.restype = _int
 lib.mslk_b200_debug_nvfp4_pair_timers.argtypes = [_vp]
 lib.mslk_b200_debug_nvfp4_pair_timers.restype = _int
 lib.mslk_b200_f4f4bf16_workspace_bytes.argtypes = [_i64, _i64, _i64]

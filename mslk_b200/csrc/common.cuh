@@ -21,6 +21,7 @@ enum : int {
   // bits OR-ed in by kernels that met an index outside its tensor (the row is skipped, not followed)
   kStatusBadGatherIndex = 0x100,
   kStatusBadScatterIndex = 0x200,
+  kStatusBadGroupOffset = 0x400,   // K-grouped GEMM: an end offset that is not a multiple of 32, decreases or exceeds K (the group's output is zero)
 };
 
 // Upper bound for any single pipeline wait.  Generous against the longest legal

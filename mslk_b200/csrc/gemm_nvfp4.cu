@@ -62,6 +62,12 @@ struct Fp4Params {
   const int64_t *sfa_row_start;    // may be null: groups then follow each other, each padded to 128 rows
   int G;
   int alpha_per_group;
+  // K-grouped problems (the "2D-2D" form: X [M, K], W [N, K], group g contracting the K range
+  // (k_end_offsets[g-1], k_end_offsets[g]] into y[g] of a [G, M, N] output): int32 END offsets along K, multiples
+  // of 32.  Every group's scales are a swizzled block of their own ([row blocks][atoms of that group]), the blocks
+  // following each other.  Null for every other form.
+  const int32_t *k_end_offsets;
+  long long sfa_atoms, sfb_atoms;   // K-grouped: 512-byte atoms the two scale tensors hold (the kernel reads no further)
   int a_box_rows;       // rows of the A box: 128, or fewer for a dense problem with fewer rows (no out-of-range fill)
   int scale_mode;       // kScaleNvfp4 / kScaleMxfp4 / kScaleMxfp4_16 (common.cuh); ncb counts the atoms of that format
 };
@@ -93,6 +99,7 @@ struct SmemTail {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int kgroup_reject;                // K-grouped: the scale tensors are too short for the offsets, every group yields zeros
   int row_start[kMaxGroups + 1];    // first stacked row of every group
   int tile_start[kMaxGroups + 1];   // first linear tile of every group
 };
@@ -116,7 +123,31 @@ __device__ __noinline__ bool epilogue_tile(const int *tile_start, const int *row
   return true;
 }
 
-template <int BN>
+// One tile of a K-grouped problem: tiles of a group are consecutive, columns fastest.  k_start / atom_start are the
+// group tables (first K element and first scale atom per 128-row block of every group).
+struct KTile {
+  int g, m_tile, n_tile;
+  int k0, kg;        // first K element of the group and its extent (0: empty group, the output is zero)
+  int ncb, atom0;    // scale atoms per 128-row block of this group, and of all groups before it
+};
+
+__device__ __noinline__ bool kgroup_tile(const int *k_start, const int *atom_start, int reject, int G, int m_tiles,
+                                         int n_tiles, int tile, KTile &t) {
+  const int per_group = m_tiles * n_tiles;
+  if (tile >= G * per_group) return false;
+  t.g = tile / per_group;
+  const int r = tile - t.g * per_group;
+  t.m_tile = r / n_tiles;
+  t.n_tile = r - t.m_tile * n_tiles;
+  t.k0 = k_start[t.g];
+  t.kg = k_start[t.g + 1] - t.k0;
+  if (((t.k0 | t.kg) & 31) || reject) t.kg = 0;   // rejected (the prologue has recorded kStatusBadGroupOffset)
+  t.atom0 = atom_start[t.g];
+  t.ncb = atom_start[t.g + 1] - t.atom0;
+  return true;
+}
+
+template <int BN, bool KG>
 __global__ void __launch_bounds__(kNumThreads, 1)
     gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const Fp4Params p) {
@@ -158,13 +189,32 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     gp.G = p.G;
     gp.total_m = p.M;
     gp.group_m = p.M;   // dense: one group of all rows (only read when m_sizes is null)
-    build_group_tables(gp, n_tiles, kBM, lane, S.row_start, S.tile_start);
+    if constexpr (KG) {
+      // the same prefix sums over the K extents: row_start = first K element of every group, tile_start = scale
+      // atoms (of 4 scales per row) in front of it
+      gp.end_offsets = p.k_end_offsets;
+      gp.total_m = p.K;
+      build_group_tables(gp, 1, p.scale_mode == kScaleMxfp4 ? 128 : 64, lane, S.row_start, S.tile_start);
+      bool bad = false;
+      for (int g = lane; g < p.G; g += 32) {
+        const int e = p.k_end_offsets[g];
+        bad |= (e & 31) != 0 || e < (g > 0 ? p.k_end_offsets[g - 1] : 0) || e > p.K;
+      }
+      __syncwarp();
+      const long long atoms = S.tile_start[p.G];
+      const bool too_short = atoms * ((p.M + kBM - 1) / kBM) > p.sfa_atoms || atoms * n_row_blocks_b > p.sfb_atoms;
+      if (lane == 0) S.kgroup_reject = too_short ? 1 : 0;
+      if ((bad || too_short) && blockIdx.x == 0) atomicOr(p.status, kStatusBadGroupOffset);
+    } else {
+      build_group_tables(gp, n_tiles, kBM, lane, S.row_start, S.tile_start);
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
-  const int num_tiles = S.tile_start[p.G];
+  const int m_tiles_kg = (p.M + kBM - 1) / kBM;
+  const int num_tiles = KG ? p.G * m_tiles_kg * n_tiles : S.tile_start[p.G];
   Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, kBM, kBandM, 0};
 
   if (warp == 0) {
@@ -174,16 +224,42 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       uint32_t phase = 0;
       bool ok = true;
       Tile t;
-      for (int tile = blockIdx.x; ok && sched.get(tile, t); tile += gridDim.x) {
-        const int g = sched.g;
-        const int n_tile = t.n0 / BN;
-        // 128-row block of this tile in the padded scale matrix of A, and of its columns in that of B
-        // (without an explicit table the padded blocks of the groups are consecutive, so the first block
-        // of group g is its first tile divided by the tiles per row block)
-        const int64_t sfa_block = (p.sfa_row_start ? p.sfa_row_start[g] / kBM : S.tile_start[g] / n_tiles) +
-                                  (t.row0 - S.row_start[g]) / kBM;
-        const int64_t sfb_block0 = static_cast<int64_t>(g) * n_row_blocks_b + n_tile * C::kNB;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+      KTile kt;
+      for (int tile = blockIdx.x; ok && (KG ? kgroup_tile(S.row_start, S.tile_start, S.kgroup_reject, p.G, m_tiles_kg, n_tiles, tile, kt)
+                                            : sched.get(tile, t));
+           tile += gridDim.x) {
+        // per tile: rows of the two operand boxes, first packed K byte, K blocks, scale atoms per 128-row block
+        // and the first atom of the tile's row block of A / of its first row block of B
+        int n_tile, a_row, b_row, kbyte0, kbs, ncb;
+        int64_t sfa_atom0, sfb_atom0;
+        if constexpr (KG) {
+          n_tile = kt.n_tile;
+          a_row = kt.m_tile * kBM;
+          b_row = n_tile * BN;
+          kbyte0 = kt.k0 / 2;
+          kbs = (kt.kg + kBKElems - 1) / kBKElems;
+          ncb = kt.ncb;
+          sfa_atom0 = static_cast<int64_t>(kt.atom0) * m_tiles_kg + static_cast<int64_t>(kt.m_tile) * ncb;
+          sfb_atom0 = static_cast<int64_t>(kt.atom0) * n_row_blocks_b + static_cast<int64_t>(n_tile) * C::kNB * ncb;
+        } else {
+          const int g = sched.g;
+          n_tile = t.n0 / BN;
+          a_row = t.row0;
+          b_row = t.wrow0;
+          kbyte0 = 0;
+          kbs = k_blocks;
+          ncb = p.ncb;
+          // 128-row block of this tile in the padded scale matrix of A, and of its columns in that of B
+          // (without an explicit table the padded blocks of the groups are consecutive, so the first block
+          // of group g is its first tile divided by the tiles per row block)
+          const int64_t sfa_block = (p.sfa_row_start ? p.sfa_row_start[g] / kBM : S.tile_start[g] / n_tiles) +
+                                    (t.row0 - S.row_start[g]) / kBM;
+          sfa_atom0 = sfa_block * ncb;
+          sfb_atom0 = (static_cast<int64_t>(g) * n_row_blocks_b + n_tile * C::kNB) * ncb;
+        }
+        int nb_live = 0;  // 128-row blocks of B that exist for this tile
+        for (int b = 0; b < C::kNB; ++b) nb_live += (n_tile * C::kNB + b) < n_row_blocks_b ? 1 : 0;
+        for (int kb = 0; kb < kbs; ++kb) {
           if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
             ok = false;
             break;
@@ -194,19 +270,16 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           uint8_t *ssfb = ssfa + C::kStageSFA;
           // scale atoms (4 scales per row each: 64 K-elements, MXFP4 128) left in this K block of 256 elements
           const int apk = p.scale_mode == kScaleMxfp4 ? 2 : 4;
-          const int atoms = min(apk, p.ncb - apk * kb);
+          const int atoms = min(apk, ncb - apk * kb);
           const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
-          int nb_live = 0;  // 128-row blocks of B that exist for this tile
-          for (int b = 0; b < C::kNB; ++b) nb_live += (n_tile * C::kNB + b) < n_row_blocks_b ? 1 : 0;
           mbar_arrive_expect_tx(&S.full[stage], p.a_box_rows * kBKBytes + C::kStageB + sf_bytes * (1 + nb_live));
-          tma_load_2d(sa, &tmap_a, &S.full[stage], kb * kBKBytes, t.row0);
-          tma_load_2d(sb, &tmap_b, &S.full[stage], kb * kBKBytes, t.wrow0);
-          bulk_load_1d(ssfa, p.sfa + (static_cast<size_t>(sfa_block) * p.ncb + apk * kb) * kAtomBytes, sf_bytes,
-                       &S.full[stage]);
+          tma_load_2d(sa, &tmap_a, &S.full[stage], kbyte0 + kb * kBKBytes, a_row);
+          tma_load_2d(sb, &tmap_b, &S.full[stage], kbyte0 + kb * kBKBytes, b_row);
+          bulk_load_1d(ssfa, p.sfa + static_cast<size_t>(sfa_atom0 + apk * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
           for (int b = 0; b < nb_live; ++b)
             bulk_load_1d(ssfb + b * 4 * kAtomBytes,
-                         p.sfb + (static_cast<size_t>(sfb_block0 + b) * p.ncb + apk * kb) * kAtomBytes, sf_bytes,
-                         &S.full[stage]);
+                         p.sfb + static_cast<size_t>(sfb_atom0 + static_cast<int64_t>(b) * ncb + apk * kb) * kAtomBytes,
+                         sf_bytes, &S.full[stage]);
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1;
@@ -241,7 +314,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb, ++n) {
+        int kbs = k_blocks, k_len = p.K, ncb = p.ncb;
+        if constexpr (KG) {
+          KTile kt;
+          kgroup_tile(S.row_start, S.tile_start, S.kgroup_reject, p.G, m_tiles_kg, n_tiles, tile, kt);
+          k_len = kt.kg;
+          kbs = (kt.kg + kBKElems - 1) / kBKElems;
+          ncb = kt.ncb;
+        }
+        for (int kb = 0; kb < kbs; ++kb, ++n) {
           if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
             ok = false;
             break;
@@ -254,7 +335,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (p.scale_mode == kScaleMxfp4) {
             // one scale per 32 K-elements: an atom holds the scales of TWO instructions, which pick their two bytes
             // of the scale column through the scale-id fields of the descriptor
-            const int mmas = min(4, (p.K - kb * kBKElems + 63) / 64);
+            const int mmas = min(4, (k_len - kb * kBKElems + 63) / 64);
             const int atoms = (mmas + 1) / 2;
             for (int a = 0; a < atoms; ++a) {
               tc_cp_32x128b_warpx4(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
@@ -270,7 +351,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
                           sfb_t + 4 * C::kNB * (k >> 1), (kb | k) != 0 ? 1u : 0u);
           } else {
           const uint32_t idesc = C::kIdesc | (p.scale_mode == kScaleMxfp4_16 ? kIdescScaleE8M0 : 0u);
-          const int atoms = min(4, p.ncb - 4 * kb);
+          const int atoms = min(4, ncb - 4 * kb);
           if (atoms == 4) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -317,8 +398,19 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const bool y_vec_ok = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0);
     int local = 0;
     int g = 0, row0, rows, n0;
-    for (int tile = blockIdx.x; epilogue_tile(S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, tile, g, row0, rows, n0);
+    KTile kt;
+    kt.kg = 1;
+    for (int tile = blockIdx.x;
+         KG ? kgroup_tile(S.row_start, S.tile_start, S.kgroup_reject, p.G, m_tiles_kg, n_tiles, tile, kt)
+            : epilogue_tile(S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, tile, g, row0, rows, n0);
          tile += gridDim.x, ++local) {
+      if constexpr (KG) {
+        g = kt.g;
+        row0 = kt.g * p.M + kt.m_tile * kBM;   // y is [G, M, N]
+        rows = min(kBM, p.M - kt.m_tile * kBM);
+        n0 = kt.n_tile * BN;
+      }
+      const bool empty_group = KG && kt.kg == 0;   // nothing was accumulated: the tile is zero
       const int n_tile = n0 / BN;
       const float alpha = p.alpha ? p.alpha[p.alpha_per_group ? g : 0] : 1.0f;   // the MX formats have no global scale
       const int acc = local % C::kAccStages;
@@ -341,7 +433,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; j += 2)
-          packed[c * 16 + j / 2] = pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+          packed[c * 16 + j / 2] =
+              empty_group ? 0u : pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
       }
       tc_fence_before();
       __syncwarp();
@@ -376,7 +469,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   }
 }
 
-template <int BN>
+template <int BN, bool KG = false>
 int launch(const CUtensorMap &ta, const CUtensorMap &tb, const Fp4Params &p, int grid, cudaStream_t st) {
   static std::atomic<bool> attr_set[64];   // zero-initialised; two first calls may both set the (idempotent) attribute
   int dev = 0;
@@ -384,13 +477,13 @@ int launch(const CUtensorMap &ta, const CUtensorMap &tb, const Fp4Params &p, int
   constexpr size_t smem = smem_bytes<BN>();
   static_assert(smem <= 232448, "shared memory budget exceeded");
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_kernel<BN, KG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(smem)),
                             "cudaFuncSetAttribute(gemm_nvfp4)"))
       return rc;
     attr_set[dev] = true;
   }
-  gemm_nvfp4_kernel<BN><<<grid, kNumThreads, smem, st>>>(ta, tb, p);
+  gemm_nvfp4_kernel<BN, KG><<<grid, kNumThreads, smem, st>>>(ta, tb, p);
   return check_cuda(cudaGetLastError(), "f4f4bf16 launch");
 }
 
@@ -433,6 +526,7 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   p.m_sizes = m_sizes;
   p.end_offsets = end_offsets;
   p.sfa_row_start = sfa_row_start;
+  p.k_end_offsets = nullptr;
   p.G = static_cast<int>(G);
   p.alpha_per_group = (grouped && global_scale) ? 1 : 0;
   p.a_box_rows = (!grouped && M < kBM) ? static_cast<int>((M + 7) / 8 * 8) : kBM;
@@ -489,8 +583,70 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   return bn == 256 ? launch<256>(ta, tb, p, grid, st) : launch<128>(ta, tb, p, grid, st);
 }
 
+// K-grouped ("2D-2D") form on the one-CTA kernel: G problems of M x N, group g contracting its own K range.
+int run_fp4_kgrouped(const char *name, const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                     const float *global_scale, void *y, const int32_t *k_end_offsets, int64_t G, int64_t M, int64_t N,
+                     int64_t K, int scale_mode, size_t x_scale_bytes, size_t w_scale_bytes, cudaStream_t st) {
+  const bool mx = scale_mode != kScaleNvfp4;
+  if (M < 0 || N < 0 || K < 0 || G < 1) return fail(1, "%s: bad shape", name);
+  if (M == 0 || N == 0) return 0;
+  if (G > kMaxGroups) return fail(1, "%s: at most %d groups are supported (got %lld)", name, kMaxGroups, (long long)G);
+  if (!y) return fail(1, "%s: null output pointer", name);
+  if (K == 0) return check_cuda(cudaMemsetAsync(y, 0, static_cast<size_t>(G) * M * N * 2, st), "memset");
+  if (!xq || !wq || !x_scale || !w_scale || !k_end_offsets || (!global_scale && !mx))
+    return fail(1, "%s: null pointer argument", name);
+  if (K % 32 != 0) return fail(1, "%s: K (%lld) must be a multiple of 32 (16-byte rows of packed e2m1)", name, (long long)K);
+  if (G * M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(1, "%s: dimension too large", name);
+  if ((reinterpret_cast<uintptr_t>(x_scale) | reinterpret_cast<uintptr_t>(w_scale)) & 15u)
+    return fail(1, "%s: scale tensors must be 16-byte aligned", name);
+  int *status = device_status_ptr();
+  if (!status) return 2;
+  Fp4Params p{};
+  p.sfa = static_cast<const uint8_t *>(x_scale);
+  p.sfb = static_cast<const uint8_t *>(w_scale);
+  p.alpha = global_scale;
+  p.y = static_cast<__nv_bfloat16 *>(y);
+  p.status = status;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.scale_mode = scale_mode;
+  p.k_end_offsets = k_end_offsets;
+  p.sfa_atoms = static_cast<long long>(x_scale_bytes / kAtomBytes);
+  p.sfb_atoms = static_cast<long long>(w_scale_bytes / kAtomBytes);
+  p.G = static_cast<int>(G);
+  p.alpha_per_group = global_scale ? 1 : 0;
+  p.a_box_rows = M < kBM ? static_cast<int>((M + 7) / 8 * 8) : kBM;
+  const int sms = sm_count();
+  const int64_t m_tiles = (M + kBM - 1) / kBM;
+  const int bn = (G * m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d_bytes(&ta, xq, K / 2, M, K / 2, kBKBytes, p.a_box_rows, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, K / 2, N, K / 2, kBKBytes, bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  const int64_t tiles = G * m_tiles * ((N + bn - 1) / bn);
+  const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+  return bn == 256 ? launch<256, true>(ta, tb, p, grid, st) : launch<128, true>(ta, tb, p, grid, st);
+}
+
 }  // namespace
 }  // namespace mslk_b200
+
+MSLK_API int mslk_b200_f4f4bf16_grouped_mm_2d2d(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
+                                                const int32_t *k_end_offsets, const float *global_scale, int64_t G,
+                                                int64_t M, int64_t N, int64_t total_K, int block_size,
+                                                size_t x_scale_bytes, size_t w_scale_bytes, void *y, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  const char *name = "f4f4bf16_grouped_mm (2D-2D)";
+  int mode = kScaleNvfp4;
+  if (!global_scale) {
+    if (block_size == 32) mode = kScaleMxfp4;
+    else if (block_size == 16) mode = kScaleMxfp4_16;
+    else return fail(1, "%s: block size must be 32 or 16 (got %d)", name, block_size);
+  }
+  return run_fp4_kgrouped(name, xq, wq, x_scale, w_scale, global_scale, y, k_end_offsets, G, M, N, total_K, mode,
+                          x_scale_bytes, w_scale_bytes, static_cast<cudaStream_t>(stream));
+}
 
 MSLK_API int mslk_b200_f4f4bf16(const void *xq, const void *wq, const void *x_scale, const void *w_scale,
                                 const float *global_scale, void *y, int64_t M, int64_t N, int64_t K, void *stream) {

@@ -39,4 +39,6 @@ def _grouped_mm_cuda(XQ, WQ, x_scale, w_scale, offsets, output=None, global_scal
 
 @torch.library.impl("mslk::f4f4bf16_grouped_mm", "Meta")
 def _grouped_mm_meta(XQ, WQ, x_scale, w_scale, offsets, output=None, global_scale: Optional[torch.Tensor] = None):
+    if WQ.dim() == 2:   # 2D-2D: groups along K, one [M, N] product per group
+        return torch.empty((offsets.shape[0], XQ.shape[0], WQ.shape[-1]), dtype=torch.bfloat16, device=XQ.device)
     return torch.empty((XQ.shape[0], WQ.shape[-1]), dtype=torch.bfloat16, device=XQ.device)

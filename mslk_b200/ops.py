@@ -526,9 +526,39 @@ def f4f4bf16_grouped_stacked(XQ, WQ, x_scale, w_scale, M_sizes, global_scale=Non
     return Y
 
 
+def _f4f4bf16_grouped_mm_2d2d(name, dev, XQ, WQ, x_scale, w_scale, offsets, output, global_scale, nvfp4):
+    G = offsets.shape[0]
+    M, N, K = XQ.shape[0], WQ.shape[-1], WQ.shape[-2] * 2
+    if XQ.shape[1] * 2 != K:
+        raise RuntimeError("for 2d-2d grouped GEMM, XQ shape must be (M, total_K) and WQ shape must be (total_K, N).")
+    out = output if output is not None else torch.empty((G, M, N), dtype=torch.bfloat16, device=dev)
+    if out.dim() != 3 or tuple(out.shape) != (G, M, N) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise RuntimeError("for 2d-2d grouped GEMM, output shape must be (G, M, N).")
+    if out.numel() == 0:
+        return out
+    block = 16 if nvfp4 else 32
+    # every group's scale block is padded on its own, so these are lower bounds; the kernel checks the real need
+    _check_nvfp4_scale_extent(name, "x_scale", x_scale, M, K, block=block)
+    _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, block=block)
+    gs = None
+    if nvfp4:
+        gs = global_scale.reshape(-1).to(torch.float32)
+        if gs.numel() != G:
+            raise RuntimeError(f"{name}: global_scale must hold one value per group")
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_f4f4bf16_grouped_mm_2d2d(
+            _ptr(_as_bytes(XQ)), _ptr(_as_bytes(WQ.transpose(-2, -1))), _ptr(x_scale), _ptr(w_scale),
+            _ptr(offsets.contiguous()), _ptr(gs), G, M, N, K, block, x_scale.numel(), w_scale.numel(), _ptr(out),
+            _stream(dev)), name)
+    return out
+
+
 def f4f4bf16_grouped_mm(XQ, WQ, x_scale, w_scale, offsets, output=None, global_scale=None) -> torch.Tensor:
-    """``torch._scaled_grouped_mm``-style 2D-3D grouped NVFP4 GEMM: ``XQ [total_M, K/2]``, ``WQ [G, K/2, N]`` given as
-    the transposed view of a contiguous ``[G, N, K/2]`` tensor, int32 END ``offsets [G]``."""
+    """``torch._scaled_grouped_mm``-style grouped FP4 GEMM (NVFP4 or MXFP4 by the scale dtype), int32 END ``offsets [G]``.
+    2D-3D: ``XQ [total_M, K/2]``, ``WQ [G, K/2, N]`` (the transposed view of a contiguous ``[G, N, K/2]`` tensor),
+    offsets along M, output ``[total_M, N]``.  2D-2D: ``XQ [M, total_K/2]``, ``WQ [total_K/2, N]`` (transposed view of
+    ``[N, total_K/2]``), offsets along K (multiples of 32), output ``[G, M, N]``
+    (csrc/gemm/cutlass/f4f4bf16_grouped.cu:376-475)."""
     name = "f4f4bf16_grouped_mm"
     dev = _require_cuda(name, XQ, WQ, x_scale, w_scale, offsets, global_scale, output)
     if offsets.dtype != torch.int32:
@@ -548,8 +578,10 @@ def f4f4bf16_grouped_mm(XQ, WQ, x_scale, w_scale, offsets, output=None, global_s
         raise RuntimeError(f"{name}: NVFP4 (float8_e4m3fn scales) needs global_scale")
     if not nvfp4 and global_scale is not None:
         raise RuntimeError(f"{name}: global_scale is for NVFP4 (float8_e4m3fn scales)")
+    if XQ.dim() == 2 and WQ.dim() == 2:
+        return _f4f4bf16_grouped_mm_2d2d(name, dev, XQ, WQ, x_scale, w_scale, offsets, output, global_scale, nvfp4)
     if XQ.dim() != 2 or WQ.dim() != 3:
-        raise RuntimeError(f"{name}: only the 2D-3D form (XQ [total_M, K], WQ [G, K, N]) is implemented")
+        raise RuntimeError("Invalid input shapes. Must be one of 2D-2D, 2D-3D.")
     G = offsets.shape[0]
     total_M = XQ.shape[0]
     N, K = WQ.shape[-1], WQ.shape[-2] * 2

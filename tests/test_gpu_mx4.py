@@ -145,3 +145,103 @@ def test_grouped_mxfp4(ops, m_sizes, N, K):
         y2 = ops.f4f4bf16_grouped_mm(xq, wq.transpose(-2, -1), x_scale.view(e8), w_scale.view(e8), offsets)
         assert torch.equal(y, y2)
     assert _status() == 0
+
+
+# --------------------------------------------------------------------------- K-grouped ("2D-2D") form
+
+def _kgrouped_case(ops, M, N, k_sizes, nvfp4, seed):
+    """X [M, total_K], W [N, total_K] quantized group by group along K (every group its own swizzled scale block),
+    packed bytes concatenated along K, scale blocks concatenated flat."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    xqs, wqs, xss, wss, gss, xs, ws = [], [], [], [], [], [], []
+    for kg in k_sizes:
+        x = (torch.randn((M, kg), generator=g, device="cuda") * 0.1).bfloat16()
+        w = (torch.randn((N, kg), generator=g, device="cuda") * 0.01).bfloat16()
+        xs.append(x)
+        ws.append(w)
+        if kg == 0:
+            xqs.append(torch.empty((M, 0), dtype=torch.uint8, device="cuda"))
+            wqs.append(torch.empty((N, 0), dtype=torch.uint8, device="cuda"))
+            xss.append(torch.empty((0,), dtype=torch.uint8, device="cuda"))
+            wss.append(torch.empty((0,), dtype=torch.uint8, device="cuda"))
+            gss.append(torch.ones((), device="cuda"))
+            continue
+        if nvfp4:
+            gx = (448.0 * 6.0) / x.abs().amax().float()
+            gw = (448.0 * 6.0) / w.abs().amax().float()
+            q, s = ops.quantize_nvfp4(x, gx)
+            xqs.append(q.view(torch.uint8))
+            xss.append(s.view(torch.uint8).reshape(-1))
+            q, s = ops.quantize_nvfp4(w, gw)
+            wqs.append(q.view(torch.uint8))
+            wss.append(s.view(torch.uint8).reshape(-1))
+            gss.append(1.0 / (gx * gw))
+        else:
+            q, s = ops.quantize_mx4(x, 32)
+            xqs.append(q.view(torch.uint8))
+            xss.append(s.view(torch.uint8).reshape(-1))
+            q, s = ops.quantize_mx4(w, 32)
+            wqs.append(q.view(torch.uint8))
+            wss.append(s.view(torch.uint8).reshape(-1))
+    return xs, ws, xqs, wqs, xss, wss, gss
+
+
+@pytest.mark.parametrize("nvfp4", [False, True])
+@pytest.mark.parametrize("M,N,k_sizes", [(256, 256, [2048]), (500, 1024, [2048] * 4), (200, 384, [256, 0, 800, 992, 32]),
+                                         (1000, 2048, [3584] * 3), (64, 136, [96, 4096])])
+def test_grouped_mm_2d2d(ops, M, N, k_sizes, nvfp4):
+    """f4f4bf16_grouped_mm with 2D XQ and 2D WQ (test/gemm/gemm_test.py:2731-2790): groups along K, out [G, M, N];
+    ragged and empty groups beside the reference's equal ones."""
+    xs, ws, xqs, wqs, xss, wss, gss = _kgrouped_case(ops, M, N, k_sizes, nvfp4, seed=M + N + len(k_sizes))
+    xq = torch.cat(xqs, dim=1).contiguous()
+    wq = torch.cat(wqs, dim=1).contiguous()
+    sdt = torch.float8_e4m3fn if nvfp4 else getattr(torch, "float8_e8m0fnu", None)
+    if sdt is None:
+        pytest.skip("this torch has no float8_e8m0fnu")
+    x_scale = torch.cat(xss).view(sdt)
+    w_scale = torch.cat(wss).view(sdt)
+    offsets = torch.tensor(k_sizes, device="cuda").cumsum(0).to(torch.int32)
+    gs = torch.stack([torch.as_tensor(v, device="cuda").float().reshape(()) for v in gss]) if nvfp4 else None
+    out = ops.f4f4bf16_grouped_mm(xq, wq.transpose(-2, -1), x_scale, w_scale, offsets, None, gs)
+    assert out.shape == (len(k_sizes), M, N)
+    for g, kg in enumerate(k_sizes):
+        if kg == 0:
+            assert torch.count_nonzero(out[g]) == 0
+            continue
+        if nvfp4:
+            y_ref = oracle.gemm_nvfp4_torch(xqs[g], wqs[g], xss[g].view(torch.float8_e4m3fn), wss[g].view(torch.float8_e4m3fn),
+                                            gss[g].reshape(1))
+        else:
+            y_ref = oracle.gemm_mx4_torch(xqs[g], wqs[g], xss[g], wss[g], 32)
+        assert_sharp_bf16(out[g], y_ref, f"2D-2D group {g} of {k_sizes} nvfp4={nvfp4}")
+        torch.testing.assert_close(out[g], (xs[g] @ ws[g].T).to(torch.bfloat16), atol=8.0e-2, rtol=8.0e-2)
+    assert _status() == 0
+
+
+def test_grouped_mm_2d2d_through_the_operator_and_rejections(ops):
+    from mslk_b200 import compat
+    compat.install()
+    import mslk.gemm  # noqa: F401
+    e8 = getattr(torch, "float8_e8m0fnu", None)
+    if e8 is None:
+        pytest.skip("this torch has no float8_e8m0fnu")
+    M, N, K, G = 256, 256, 2048, 2
+    xs, ws, xqs, wqs, xss, wss, _ = _kgrouped_case(ops, M, N, [K] * G, False, seed=9)
+    xq = torch.cat(xqs, dim=1).contiguous()
+    wq = torch.cat(wqs, dim=1).contiguous()
+    x_scale, w_scale = torch.cat(xss).view(e8), torch.cat(wss).view(e8)
+    offsets = torch.arange(K, G * (K + 1), K, dtype=torch.int32, device="cuda")
+    f4 = getattr(torch, "float4_e2m1fn_x2", None)
+    a, b = (xq.view(f4), wq.view(f4)) if f4 is not None else (xq, wq)
+    out = torch.ops.mslk.f4f4bf16_grouped_mm(a, b.transpose(-2, -1), x_scale, w_scale, offsets)
+    X, W = torch.cat(xs, dim=1), torch.cat(ws, dim=1)
+    for g in range(G):
+        ref = X[:, g * K:(g + 1) * K] @ W[:, g * K:(g + 1) * K].T
+        torch.testing.assert_close(out[g], ref, atol=8.0e-2, rtol=8.0e-2)
+    assert _status() == 0
+    # an offset that is no multiple of 32: that group's product is zero and the status word says why
+    bad = torch.tensor([K + 16, 2 * K], dtype=torch.int32, device="cuda")
+    out = ops.f4f4bf16_grouped_mm(xq, wq.transpose(-2, -1), x_scale, w_scale, bad)
+    assert torch.count_nonzero(out) == 0          # group 0 ends and group 1 starts off the 32-element grid
+    assert _status() & 0x400                      # reading the status word clears it
+    assert _status() == 0
