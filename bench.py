@@ -603,6 +603,22 @@ def other_configs(ops, device, peaks):
         it[0] += 1
     ms = _time_graph(fq, 12)
     out["quantize_nvfp4_8192x8192"] = hbm_roof(8192 * 8192 * 2.5625, ms)
+    # ---- MXFP4 (e8m0 scales per 32 elements, the reference's default mode of the FP4 operators): 8192^3 and its quantizer
+    def fqm():
+        ops.quantize_mx4(xs_[it[0] % 3], 32)
+        it[0] += 1
+    ms = _time_graph(fqm, 12)
+    out["quantize_mx4_8192x8192"] = hbm_roof(8192 * 8192 * (2.0 + 0.5 + 1.0 / 32.0), ms)
+    xq, sx = ops.quantize_mx4(xs_[0], 32)
+    wqs = [ops.quantize_mx4(xs_[1 + i], 32) for i in range(2)]
+    y = torch.empty((8192, 8192), dtype=torch.bfloat16, device=device)
+
+    def fm():
+        i = it[0] % 2
+        it[0] += 1
+        ops.f4f4bf16(xq, wqs[i][0], sx, wqs[i][1], output=y)
+    ms = _time_plain(fm, 30)
+    out["mxfp4_8192_cubed"] = tensor_roof(2.0 * 8192 ** 3, ms, fp4_peak, NOMINAL_FP4_TFLOPS)
     return out
 
 
@@ -792,7 +808,7 @@ def e2e_run(tp, dd, steps):
     step()
     join()
     dd.barrier()
-    e_steps = max(1, min(steps, 5))
+    e_steps = max(1, min(steps, 10))
     s0, s1 = _ev(), _ev()
     s0.record()
     for _ in range(e_steps):

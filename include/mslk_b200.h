@@ -252,6 +252,18 @@ int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t K, int64
                            int rounding_mode, void *q, void *scales, void *stream);
 
 /*
+ * MXFP4 quantization of stacked segments (MoE activations): segment g owns m_sizes[g] (device int64 [G]) consecutive
+ * rows of x [M, K]; its scale rows start on a 128-row boundary of the padded scale matrix, at sum_{i<g} roundup(m_i, 128)
+ * -- the x_scale layout of mslk_b200_f4f4bf16_grouped_stacked_mx.
+ * Replaces: mslk/quantize/triton/quantize_kernels/mx4_stacked.py:34-360 (quantize_mx4_stacked).
+ * q is [M, K/2] bytes; scales is [(M + 127 G) * ceil(K/group_size/4)*4] bytes (the reference's upper bound, no host
+ * read of the sizes), written completely: everything that is not a scale of a live row is 0.  G <= 1024.
+ */
+int mslk_b200_quantize_mx4_stacked(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                   const int64_t *m_sizes, int64_t G, int group_size, int rounding_mode, void *q,
+                                   void *scales, void *stream);
+
+/*
  * MXFP4 GEMMs:  y = bf16(sum_blocks 2^(sx-127) * 2^(sw-127) * sum_block x^ * w^), the forms of f4f4bf16,
  * f4f4bf16_grouped_stacked and f4f4bf16_grouped_mm the reference runs when no global scale is given
  * (csrc/gemm/cutlass/f4f4bf16.cu:6413-6473 MXFP4 / MXFP4_16 branches; f4f4bf16_grouped.cu:321-475 with use_mx).

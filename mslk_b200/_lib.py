@@ -53,6 +53,8 @@ lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i6
 lib.mslk_b200_f4f4bf16.restype = _int
 lib.mslk_b200_quantize_mx4.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]
 lib.mslk_b200_quantize_mx4.restype = _int
+lib.mslk_b200_quantize_mx4_stacked.argtypes = [_vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _int, _vp, _vp, _vp]
+lib.mslk_b200_quantize_mx4_stacked.restype = _int
 lib.mslk_b200_f4f4bf16_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]
 lib.mslk_b200_f4f4bf16_mx.restype = _int
 lib.mslk_b200_f4f4bf16_grouped_stacked_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]

@@ -20,6 +20,10 @@ _ALIASES = {
     "mslk.quantize.triton.fp8_quantize": "mslk_b200.quantize.triton.fp8_quantize",
     "mslk.quantize.triton.fp4_quantize": "mslk_b200.quantize.triton.fp4_quantize",
     "mslk.quantize.triton.fp4_utils": "mslk_b200.quantize.triton.fp4_utils",
+    "mslk.quantize.triton.fp4_primitives": "mslk_b200.quantize.triton.fp4_primitives",
+    "mslk.quantize.triton.quantize_kernels": "mslk_b200.quantize.triton.quantize_kernels",
+    "mslk.quantize.triton.quantize_kernels.mx4": "mslk_b200.quantize.triton.quantize_kernels.mx4",
+    "mslk.quantize.triton.quantize_kernels.mx4_stacked": "mslk_b200.quantize.triton.quantize_kernels.mx4_stacked",
     "mslk.moe": "mslk_b200.moe",
     "mslk.moe.activation": "mslk_b200.moe.activation",
     "mslk.moe.gather_scatter": "mslk_b200.moe.gather_scatter",

@@ -10,8 +10,15 @@
 //     x^     = e2m1_rn_satfinite(x * 2^-e)          (the factor built from its exponent bits)
 // Padded scale slots (rows up to a multiple of 128, groups up to a multiple of 4 per row) are written as 0.
 //
-// One thread per scale slot of the padded scale matrix: it loads its group (64 or 32 bytes), reduces, converts and
-// stores 16 or 8 packed bytes and one scale byte.  HBM-bound: 2.53 bytes per element at group size 32.
+// A warp iteration handles 256 consecutive elements of one row (512 input bytes in one coalesced load, 128 packed
+// bytes in one coalesced store): 4 lanes (group of 32) or 2 lanes (group of 16) share a group and combine their maxima
+// by shuffles.  HBM-bound: 2.53 bytes per element at group size 32.
+//
+// Stacked form (mslk/quantize/triton/quantize_kernels/mx4_stacked.py:34-360): rows of G segments stacked in one
+// [M, K] tensor, segment g owning m_sizes[g] rows (device int64); its scale rows start on a 128-row boundary of the
+// padded scale matrix (at sum_{i<g} roundup(m_i, 128)), which is what the grouped MXFP4 GEMM reads.  The scale buffer
+// has M + 127 G rows (an upper bound that needs no host read of the sizes); every byte of it that is not a scale of a
+// live group is written as 0.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -43,75 +50,118 @@ __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return
 template <>
 __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 
+constexpr int kMaxSegments = 1024;
+
 struct Mx4Params {
   const void *x;
   uint8_t *q;
   uint8_t *scales;
   int64_t M, K, row_stride;
-  int64_t padded_rows;      // multiple of 128
+  int64_t scale_rows;       // rows of the scale buffer (dense: a multiple of 128; stacked: M + 127 G)
   int padded_cols;          // scale slots per padded row, multiple of 4
   int scale_cols;           // K / group
   int round_add;            // added to the fp32 bits of the group maximum before its exponent is taken
+  const int64_t *m_sizes;   // stacked form: rows per segment (device), else null
+  int G;
 };
 
-template <typename T, int kGroup>
-__global__ void __launch_bounds__(256) quant_mx4_kernel(const Mx4Params p) {
-  const int64_t slots = p.padded_rows * p.padded_cols;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < slots;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / p.padded_cols;
-    const int c = static_cast<int>(i - r * p.padded_cols);
-    // swizzled position of scale (r, c): 128-row block, 4-column block, then (r % 32) * 16 + (r / 32 % 4) * 4 + c % 4
-    const int64_t soff = (r / 128) * (static_cast<int64_t>(p.padded_cols / 4) * 512) + (c / 4) * 512 + (r % 32) * 16 +
-                         ((r % 128) / 32) * 4 + (c % 4);
-    if (r >= p.M || c >= p.scale_cols) {
-      p.scales[soff] = 0;
-      continue;
-    }
-    const T *src = static_cast<const T *>(p.x) + r * p.row_stride + static_cast<int64_t>(c) * kGroup;
-    float v[kGroup];
+// Inclusive prefix sums of the segment sizes (rows) and of their 128-row padded extents; one warp.
+__device__ __forceinline__ void build_segment_tables(const int64_t *m_sizes, int G, int64_t M, int lane, int *row_end,
+                                                     int *pad_end) {
+  int row_carry = 0, pad_carry = 0;
+  for (int base = 0; base < G; base += 32) {
+    const int g = base + lane;
+    long long mg = g < G ? m_sizes[g] : 0;
+    mg = mg < 0 ? 0 : (mg > M ? M : mg);
+    int rows = static_cast<int>(mg), pads = (rows + 127) / 128 * 128;
 #pragma unroll
-    for (int j = 0; j < kGroup / 8; ++j) {
-      const uint4 raw = *reinterpret_cast<const uint4 *>(src + 8 * j);
-      const T *h = reinterpret_cast<const T *>(&raw);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[8 * j + e] = to_f32<T>(h[e]);
-    }
-    float amax = 0.f;
-#pragma unroll
-    for (int j = 0; j < kGroup; ++j) amax = fmaxf(amax, fabsf(v[j]));
-    int e = static_cast<int>(((__float_as_uint(amax) + static_cast<uint32_t>(p.round_add)) & 0x7f800000u) >> 23) - 127 - 2;
-    e = max(-127, min(125, e));
-    const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-    uint8_t *dst = p.q + r * (p.K / 2) + static_cast<int64_t>(c) * (kGroup / 2);
-#pragma unroll
-    for (int j = 0; j < kGroup / 16; ++j) {
-      uint32_t w[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float y[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) y[k] = v[16 * j + 8 * h + k] * inv;
-        w[h] = cvt_e2m1x8(y);
+    for (int o = 1; o < 32; o <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, rows, o), b = __shfl_up_sync(0xffffffffu, pads, o);
+      if (lane >= o) {
+        rows += r;
+        pads += b;
       }
-      *reinterpret_cast<uint2 *>(dst + 8 * j) = make_uint2(w[0], w[1]);
     }
-    p.scales[soff] = static_cast<uint8_t>(e + 127);
+    if (g < G) {
+      row_end[g] = static_cast<int>(min(M, static_cast<int64_t>(row_carry) + rows));
+      pad_end[g] = pad_carry + pads;
+    }
+    row_carry = static_cast<int>(min(M, static_cast<int64_t>(row_carry) + __shfl_sync(0xffffffffu, rows, 31)));
+    pad_carry += __shfl_sync(0xffffffffu, pads, 31);
   }
 }
 
-}  // namespace
-}  // namespace mslk_b200
+template <typename T, int kGroup, bool kStacked>
+__global__ void __launch_bounds__(256) quant_mx4_kernel(const Mx4Params p) {
+  constexpr int kLanesPerGroup = kGroup / 8;       // a lane holds 8 elements
+  constexpr int kSlotsPerChunk = 256 / kGroup;     // scale slots of one warp iteration
+  __shared__ int s_row_end[kStacked ? kMaxSegments : 1];
+  __shared__ int s_pad_end[kStacked ? kMaxSegments : 1];
+  const int lane = threadIdx.x & 31;
+  if constexpr (kStacked) {
+    if (threadIdx.x < 32) build_segment_tables(p.m_sizes, p.G, p.M, lane, s_row_end, s_pad_end);
+    __syncthreads();
+  }
+  const int chunks = (p.padded_cols * kGroup + 255) / 256;
+  const int64_t padded_rows = (p.scale_rows + 127) / 128 * 128;
+  const int64_t units = padded_rows * chunks;
+  const int64_t scale_bytes = p.scale_rows * p.padded_cols;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * (blockDim.x / 32);
+  int g = 0;
+  for (int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x >> 5); unit < units;
+       unit += stride) {
+    const int64_t pr = unit / chunks;                 // row of the padded scale matrix
+    const int ch = static_cast<int>(unit - pr * chunks);
+    int64_t row = pr;                                 // source row
+    bool live = pr < p.M;
+    if constexpr (kStacked) {
+      while (g < p.G - 1 && s_pad_end[g] <= pr) ++g;  // padded rows only grow along a warp's units
+      const int pad0 = g ? s_pad_end[g - 1] : 0, row0 = g ? s_row_end[g - 1] : 0;
+      row = row0 + (pr - pad0);
+      live = pr < s_pad_end[g] && row < s_row_end[g];
+    }
+    const int c = ch * kSlotsPerChunk + lane / kLanesPerGroup;   // scale column of this lane's group
+    live = live && c < p.scale_cols;
+    float v[8];
+    float amax = 0.f;
+    if (live) {
+      const uint4 raw = *reinterpret_cast<const uint4 *>(static_cast<const T *>(p.x) + row * p.row_stride +
+                                                        static_cast<int64_t>(ch) * 256 + lane * 8);
+      const T *h = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[e] = to_f32<T>(h[e]);
+        amax = fmaxf(amax, fabsf(v[e]));
+      }
+    }
+#pragma unroll
+    for (int o = 1; o < kLanesPerGroup; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    int e = static_cast<int>(((__float_as_uint(amax) + static_cast<uint32_t>(p.round_add)) & 0x7f800000u) >> 23) - 127 - 2;
+    e = max(-127, min(125, e));
+    if (live) {
+      const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+      float y[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) y[k] = v[k] * inv;
+      *reinterpret_cast<uint32_t *>(p.q + row * (p.K / 2) + static_cast<int64_t>(ch) * 128 + lane * 4) = cvt_e2m1x8(y);
+    }
+    if (lane % kLanesPerGroup == 0 && c < p.padded_cols) {
+      // swizzled position of scale (pr, c): 128-row block, 4-column block, then (r % 32) * 16 + (r / 32 % 4) * 4 + c % 4
+      const int64_t soff = (pr / 128) * (static_cast<int64_t>(p.padded_cols / 4) * 512) + (c / 4) * 512 + (pr % 32) * 16 +
+                           ((pr % 128) / 32) * 4 + (c % 4);
+      if (soff < scale_bytes) p.scales[soff] = live ? static_cast<uint8_t>(e + 127) : 0;
+    }
+  }
+}
 
-MSLK_API int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, int group_size,
-                                    int rounding_mode, void *q, void *scales, void *stream) {
-  using namespace mslk_b200;
-  clear_error();
-  const char *name = "quantize_mx4";
+int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, const int64_t *m_sizes,
+            int64_t G, int group_size, int rounding_mode, void *q, void *scales, cudaStream_t st) {
+  const bool stacked = m_sizes != nullptr;
   if (M < 0 || K < 0) return fail(1, "%s: bad shape", name);
   if (group_size != 32 && group_size != 16) return fail(1, "%s: group_size must be 32 or 16 (got %d)", name, group_size);
   if (K % group_size != 0) return fail(1, "%s: K (%lld) must be a multiple of the group size %d", name, (long long)K, group_size);
   if (dtype != MSLK_B200_BF16 && dtype != MSLK_B200_F16) return fail(1, "%s: input must be bf16 or fp16", name);
+  if (stacked && (G < 1 || G > kMaxSegments)) return fail(1, "%s: between 1 and %d segments are supported", name, kMaxSegments);
   int round_add;
   switch (rounding_mode) {
     case 1: round_add = 0; break;                 // floor
@@ -121,11 +171,12 @@ MSLK_API int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t
       return fail(1, "%s: rounding mode %d is not implemented (floor = 1, even = 2, ceil = 4 are; nearest and stochastic "
                      "depend on the GPU's approximate log2 / a Philox stream)", name, rounding_mode);
   }
-  if (M == 0 || K == 0) return 0;
-  if (!x || !q || !scales) return fail(1, "%s: null pointer argument", name);
+  if (K == 0 || (M == 0 && !stacked)) return 0;
+  if (!q || !scales || (M > 0 && !x)) return fail(1, "%s: null pointer argument", name);
+  if (M > 0x7fff0000LL - 127 * G) return fail(1, "%s: too many rows", name);
   if ((reinterpret_cast<uintptr_t>(x) & 15u) || (row_stride * 2) % 16 != 0)
     return fail(1, "%s: input rows must be 16-byte aligned", name);
-  if (reinterpret_cast<uintptr_t>(q) & 7u) return fail(1, "%s: output must be 8-byte aligned", name);
+  if (reinterpret_cast<uintptr_t>(q) & 3u) return fail(1, "%s: output must be 4-byte aligned", name);
   Mx4Params p;
   p.x = x;
   p.q = static_cast<uint8_t *>(q);
@@ -133,20 +184,46 @@ MSLK_API int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t
   p.M = M;
   p.K = K;
   p.row_stride = row_stride;
-  p.padded_rows = (M + 127) / 128 * 128;
+  p.scale_rows = stacked ? M + 127 * G : (M + 127) / 128 * 128;
   p.scale_cols = static_cast<int>(K / group_size);
   p.padded_cols = (p.scale_cols + 3) / 4 * 4;
   p.round_add = round_add;
-  const int64_t slots = p.padded_rows * p.padded_cols;
-  const int64_t want = (slots + 255) / 256;
-  const unsigned blocks = static_cast<unsigned>(want < 148 * 32 ? want : 148 * 32);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == MSLK_B200_BF16) {
-    if (group_size == 32) quant_mx4_kernel<__nv_bfloat16, 32><<<blocks, 256, 0, st>>>(p);
-    else quant_mx4_kernel<__nv_bfloat16, 16><<<blocks, 256, 0, st>>>(p);
+  p.m_sizes = m_sizes;
+  p.G = static_cast<int>(G);
+  const int64_t chunks = (static_cast<int64_t>(p.padded_cols) * group_size + 255) / 256;
+  const int64_t units = ((p.scale_rows + 127) / 128 * 128) * chunks;
+  const int64_t want = (units + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+  auto go = [&](auto kernel) { kernel<<<blocks, 256, 0, st>>>(p); };
+  const bool bf = dtype == MSLK_B200_BF16;
+  if (stacked) {
+    if (bf) group_size == 32 ? go(quant_mx4_kernel<__nv_bfloat16, 32, true>) : go(quant_mx4_kernel<__nv_bfloat16, 16, true>);
+    else group_size == 32 ? go(quant_mx4_kernel<__half, 32, true>) : go(quant_mx4_kernel<__half, 16, true>);
   } else {
-    if (group_size == 32) quant_mx4_kernel<__half, 32><<<blocks, 256, 0, st>>>(p);
-    else quant_mx4_kernel<__half, 16><<<blocks, 256, 0, st>>>(p);
+    if (bf) group_size == 32 ? go(quant_mx4_kernel<__nv_bfloat16, 32, false>) : go(quant_mx4_kernel<__nv_bfloat16, 16, false>);
+    else group_size == 32 ? go(quant_mx4_kernel<__half, 32, false>) : go(quant_mx4_kernel<__half, 16, false>);
   }
-  return check_cuda(cudaGetLastError(), "quantize_mx4 launch");
+  return check_cuda(cudaGetLastError(), name);
+}
+
+}  // namespace
+}  // namespace mslk_b200
+
+MSLK_API int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, int group_size,
+                                    int rounding_mode, void *q, void *scales, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  return run_mx4("quantize_mx4", x, dtype, M, K, row_stride, nullptr, 1, group_size, rounding_mode, q, scales,
+                 static_cast<cudaStream_t>(stream));
+}
+
+MSLK_API int mslk_b200_quantize_mx4_stacked(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                            const int64_t *m_sizes, int64_t G, int group_size, int rounding_mode, void *q,
+                                            void *scales, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  if (!m_sizes) return fail(1, "quantize_mx4_stacked: m_sizes is null");
+  return run_mx4("quantize_mx4_stacked", x, dtype, M, K, row_stride, m_sizes, G, group_size, rounding_mode, q, scales,
+                 static_cast<cudaStream_t>(stream));
 }

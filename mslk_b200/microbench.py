@@ -222,6 +222,17 @@ def bench_quantize_nvfp4(ops, M, K, args):
     return {"op": "quantize_nvfp4", "M": M, "K": K, "us": sec * 1e6, "GBps": byts / sec / 1e9}
 
 
+def bench_quantize_mx4(ops, M, K, args):
+    nv = _variants(M * K * 2, args.rotate_mb)
+    xs = [_randn((M, K)) for _ in range(nv)]
+    out = []
+    for group in (32, 16):
+        sec = _time(lambda i: ops.quantize_mx4(xs[i], group), nv, args.iters, args.warmup, args.graph)
+        byts = 2.0 * M * K + M * K / 2 + M * K / group
+        out.append({"op": "quantize_mx4", "group": group, "M": M, "K": K, "us": sec * 1e6, "GBps": byts / sec / 1e9})
+    return out
+
+
 def bench_f4f4bf16(ops, M, N, K, args):
     nv = _variants(N * K // 2, args.rotate_mb)
     x = _randn((M, K))
@@ -244,7 +255,7 @@ def bench_f4f4bf16(ops, M, N, K, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "decode", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "moe_gather_scatter", "quantize_nvfp4", "silu_mul_quant",
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "decode", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "moe_gather_scatter", "quantize_nvfp4", "quantize_mx4", "silu_mul_quant",
                                    "sweep"])
     ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
     ap.add_argument("--experts", type=int, default=16)
@@ -273,6 +284,8 @@ def main():
         out.append(bench_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
     elif args.op == "quantize_nvfp4":
         out.append(bench_quantize_nvfp4(ops, *(shape or [8192, 8192]), args))
+    elif args.op == "quantize_mx4":
+        out.extend(bench_quantize_mx4(ops, *(shape or [8192, 8192]), args))
     elif args.op == "f4f4bf16_grouped":
         out.append(bench_f4f4bf16_grouped(ops, args.experts, args.tokens, *(shape or [16384, 5120]), args))
     elif args.op == "moe_gather_scatter":

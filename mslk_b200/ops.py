@@ -315,6 +315,31 @@ def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
     return q.view(*lead, -1, K // 2), s
 
 
+def quantize_mx4_stacked(m_sizes: torch.Tensor, x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
+    """MXFP4 quantize of stacked MoE segments (``mslk/quantize/triton/quantize_kernels/mx4_stacked.py:221-360``):
+    ``(xq uint8 [M, K/2], scales int8 flattened [(M + 127 G) * roundup(K/group, 4)])`` with every segment's scale rows
+    starting on a 128-row boundary; padding is zero."""
+    name = "quantize_mx4_stacked"
+    dev = _require_cuda(name, x, m_sizes)
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"Expected fp16/bf16, got {x.dtype}")
+    x2 = x.reshape(-1, x.shape[-1])
+    M, K = x2.shape
+    assert K % group_size == 0, f"N must be divisible by {group_size}, got {K}"
+    assert m_sizes.dtype == torch.int64, f"Expected m_sizes int64, got {m_sizes.dtype}"
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    G = m_sizes.shape[0]
+    pc = (K // group_size + 3) // 4 * 4
+    q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
+    s = torch.empty(((M + 127 * G) * pc,), dtype=torch.int8, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.mslk_b200_quantize_mx4_stacked(_ptr(x2), _DTYPE_CODE[x.dtype], M, K, x2.stride(0),
+                                                 _ptr(m_sizes.contiguous()), G, int(group_size), int(rounding_mode),
+                                                 _ptr(q), _ptr(s), _stream(dev)), name)
+    return q, s
+
+
 def f4f4bf16(XQ, WQ, x_scale, w_scale, output=None, global_scale=None, mxfp4_block_size: int = 32) -> torch.Tensor:
     """FP4 GEMM: NVFP4 when ``global_scale`` is given (e4m3 scales per 16 elements), else MXFP4 (e8m0 scales per
     ``mxfp4_block_size`` = 32 or 16 elements), as the reference operator (``csrc/gemm/cutlass/f4f4bf16.cu:6413-6473``)."""

@@ -27,6 +27,9 @@ def triton_quantize_nvfp4(
     return xq, scales
 
 
+from .fp4_primitives import RoundingMode  # noqa: E402,F401  (the reference re-exports it here)
+
+
 def triton_quantize_mx4_unpack(input: torch.Tensor, group_size: int = 32, ebits: int = 2, mbits: int = 1,
                                rounding_mode: int = 4, stochastic_casting: bool = False, *, seed=None):
     """MXFP4 quantize with the reference's symbol (``mslk/quantize/triton/fp4_quantize.py:46-90``): packed e2m1 bytes

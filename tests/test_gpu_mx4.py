@@ -245,3 +245,53 @@ def test_grouped_mm_2d2d_through_the_operator_and_rejections(ops):
     assert torch.count_nonzero(out) == 0          # group 0 ends and group 1 starts off the 32-element grid
     assert _status() & 0x400                      # reading the status word clears it
     assert _status() == 0
+
+
+# --------------------------------------------------------------------------- stacked quantizer
+
+@pytest.mark.parametrize("m_sizes,K,group", [([64, 64], 64, 32), ([50, 30, 48], 64, 32), ([16, 64, 128, 256], 128, 32),
+                                             ([256, 512], 512, 32), ([50, 30, 48], 64, 16), ([64, 0, 64], 64, 32),
+                                             ([16] * 64, 128, 32), ([128, 128], 80, 16), ([1, 1, 1, 1], 64, 16),
+                                             ([5, 11, 19], 64, 16), ([300, 0, 1000, 129, 2047, 620], 1024, 32)])
+def test_quantize_mx4_stacked_equals_per_segment(ops, m_sizes, K, group):
+    """The reference's cases (test/quantize/triton/test_stacked_quantize_mx4.py:56-160): packed bytes equal the
+    per-segment quantizer's, every segment's swizzled scale block sits at its 128-row-aligned offset, and every other
+    byte of the scale buffer is zero."""
+    M, G = sum(m_sizes), len(m_sizes)
+    g = torch.Generator().manual_seed(M + K)
+    x = (torch.randn((M, K), generator=g) * torch.exp2(torch.randint(-8, 8, (M, 1), generator=g).float())).bfloat16()
+    ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+    q, s = ops.quantize_mx4_stacked(ms, x.cuda(), group)
+    pc = (K // group + 3) // 4 * 4
+    assert q.shape == (M, K // 2) and s.numel() == (M + 127 * G) * pc
+    want = torch.zeros_like(s, device="cpu").view(torch.uint8)
+    r = pad = 0
+    for m in m_sizes:
+        if m:
+            q_ref, s_ref = oracle.quantize_mx4(x[r:r + m], group, 4)
+            assert torch.equal(q[r:r + m].cpu(), q_ref), (m_sizes, r)
+            want[pad * pc:pad * pc + s_ref.numel()] = s_ref.reshape(-1)
+        r += m
+        pad += (m + 127) // 128 * 128
+    assert torch.equal(s.cpu().view(torch.uint8), want)
+    assert _status() == 0
+
+
+def test_quantize_mx4_stacked_feeds_the_grouped_gemm(ops):
+    from mslk_b200 import compat
+    compat.install()
+    from mslk.quantize.triton.quantize_kernels.mx4_stacked import quantize_mx4_stacked
+    from mslk.quantize.triton.fp4_quantize import RoundingMode, triton_quantize_mx4_unpack
+    m_sizes, N, K = [300, 0, 77, 1024], 512, 2048
+    xs = [torch.randn((m, K), device="cuda").bfloat16() * 0.1 for m in m_sizes]
+    ws = [torch.randn((N, K), device="cuda").bfloat16() * 0.01 for _ in m_sizes]
+    ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+    xq, x_scale = quantize_mx4_stacked(ms, torch.cat(xs), rounding_mode=RoundingMode.ceil)
+    wq, w_scale = zip(*[triton_quantize_mx4_unpack(w) for w in ws])
+    y = ops.f4f4bf16_grouped_stacked(xq, torch.stack(wq), x_scale, torch.stack(w_scale), ms)
+    r = 0
+    for g, m in enumerate(m_sizes):
+        if m:
+            torch.testing.assert_close(y[r:r + m], (xs[g] @ ws[g].T).to(torch.bfloat16), atol=8.0e-2, rtol=8.0e-2)
+        r += m
+    assert _status() == 0
