@@ -10,9 +10,12 @@
 //     x^     = e2m1_rn_satfinite(x * 2^-e)          (the factor built from its exponent bits)
 // Padded scale slots (rows up to a multiple of 128, groups up to a multiple of 4 per row) are written as 0.
 //
-// A warp iteration handles 256 consecutive elements of one row (512 input bytes in one coalesced load, 128 packed
-// bytes in one coalesced store): 4 lanes (group of 32) or 2 lanes (group of 16) share a group and combine their maxima
-// by shuffles.  HBM-bound: 2.53 bytes per element at group size 32.
+// Work unit = one warp's share of a 128-row x 4-group tile (one 512-byte scale atom): warp w of the tile takes rows
+// {2w, 2w+1} + {0, 32, 64, 96} and the 4 groups of each, one group (64 or 32 input bytes) per lane.  With
+// lane = (row & 1) * 16 + (row / 32) * 4 + group, the 32 scale bytes of a unit are the contiguous bytes [32w, 32w + 32)
+// of the atom: one sector per warp store.  Units are walked grid-stride, the (tile row, tile column, warp slot) digits
+// carried along without divisions, the next unit's group prefetched into registers.  HBM-bound: 2.53 bytes per
+// element at group size 32.
 //
 // Stacked form (mslk/quantize/triton/quantize_kernels/mx4_stacked.py:34-360): rows of G segments stacked in one
 // [M, K] tensor, segment g owning m_sizes[g] rows (device int64); its scale rows start on a 128-row boundary of the
@@ -91,66 +94,122 @@ __device__ __forceinline__ void build_segment_tables(const int64_t *m_sizes, int
   }
 }
 
+constexpr int kWarpsPerTile = 16;   // one warp quantizes 8 rows x 4 groups of a 128 x 4 tile
+constexpr int kThreadsMx = 256;
+
+template <int kGroup>
+struct GroupIn {
+  uint4 v[kGroup / 8];   // 32 or 16 two-byte elements
+};
+
 template <typename T, int kGroup, bool kStacked>
-__global__ void __launch_bounds__(256) quant_mx4_kernel(const Mx4Params p) {
-  constexpr int kLanesPerGroup = kGroup / 8;       // a lane holds 8 elements
-  constexpr int kSlotsPerChunk = 256 / kGroup;     // scale slots of one warp iteration
+__global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Params p) {
   __shared__ int s_row_end[kStacked ? kMaxSegments : 1];
   __shared__ int s_pad_end[kStacked ? kMaxSegments : 1];
-  const int lane = threadIdx.x & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
   if constexpr (kStacked) {
-    if (threadIdx.x < 32) build_segment_tables(p.m_sizes, p.G, p.M, lane, s_row_end, s_pad_end);
+    if (tid < 32) build_segment_tables(p.m_sizes, p.G, p.M, lane, s_row_end, s_pad_end);
     __syncthreads();
   }
-  const int chunks = (p.padded_cols * kGroup + 255) / 256;
-  const int64_t padded_rows = (p.scale_rows + 127) / 128 * 128;
-  const int64_t units = padded_rows * chunks;
+  const int n_col_tiles = p.padded_cols / 4;
+  const int n_row_tiles = static_cast<int>((p.scale_rows + 127) / 128);
+  const int total_units = n_row_tiles * n_col_tiles * kWarpsPerTile;
   const int64_t scale_bytes = p.scale_rows * p.padded_cols;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * (blockDim.x / 32);
+  const int c = lane & 3, row_in_tile = ((lane >> 2) & 3) * 32 + (lane >> 4);
+  const int stride = gridDim.x * (kThreadsMx / 32);
+  int unit = blockIdx.x * (kThreadsMx / 32) + (tid >> 5);
+  if (unit >= total_units) return;
+  int tile = unit / kWarpsPerTile, w = unit - tile * kWarpsPerTile;
+  int tr = tile / n_col_tiles, tc = tile - tr * n_col_tiles;
+  const int d_tile = stride / kWarpsPerTile, d_w = stride - d_tile * kWarpsPerTile;
+  const int d_tr = d_tile / n_col_tiles, d_tc = d_tile - d_tr * n_col_tiles;
   int g = 0;
-  for (int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x >> 5); unit < units;
-       unit += stride) {
-    const int64_t pr = unit / chunks;                 // row of the padded scale matrix
-    const int ch = static_cast<int>(unit - pr * chunks);
-    int64_t row = pr;                                 // source row
+  auto locate_here = [&](int64_t &row, int &col) {
+    const int pr = tr * 128 + row_in_tile + 2 * w;   // row of the padded scale matrix
+    col = tc * 4 + c;
     bool live = pr < p.M;
+    row = pr;
     if constexpr (kStacked) {
-      while (g < p.G - 1 && s_pad_end[g] <= pr) ++g;  // padded rows only grow along a warp's units
+      while (g < p.G - 1 && s_pad_end[g] <= tr * 128) ++g;   // tile rows only grow along a warp's units
       const int pad0 = g ? s_pad_end[g - 1] : 0, row0 = g ? s_row_end[g - 1] : 0;
       row = row0 + (pr - pad0);
       live = pr < s_pad_end[g] && row < s_row_end[g];
     }
-    const int c = ch * kSlotsPerChunk + lane / kLanesPerGroup;   // scale column of this lane's group
-    live = live && c < p.scale_cols;
-    float v[8];
-    float amax = 0.f;
-    if (live) {
-      const uint4 raw = *reinterpret_cast<const uint4 *>(static_cast<const T *>(p.x) + row * p.row_stride +
-                                                        static_cast<int64_t>(ch) * 256 + lane * 8);
-      const T *h = reinterpret_cast<const T *>(&raw);
+    return live && col < p.scale_cols;
+  };
+  auto advance = [&]() {
+    w += d_w;
+    const int carry = w >= kWarpsPerTile ? 1 : 0;
+    w -= carry * kWarpsPerTile;
+    tc += d_tc + carry;
+    tr += d_tr;
+    if (tc >= n_col_tiles) {
+      tc -= n_col_tiles;
+      ++tr;
+    }
+  };
+  auto load = [&](int64_t row, int col, GroupIn<kGroup> &gi) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const T *>(p.x) + row * p.row_stride +
+                                                       static_cast<int64_t>(col) * kGroup);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        v[e] = to_f32<T>(h[e]);
-        amax = fmaxf(amax, fabsf(v[e]));
+    for (int j = 0; j < kGroup / 8; ++j)
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(gi.v[j].x), "=r"(gi.v[j].y), "=r"(gi.v[j].z), "=r"(gi.v[j].w) : "l"(src + j));
+  };
+  int64_t row;
+  int col;
+  bool live = locate_here(row, col);
+  GroupIn<kGroup> cur{};
+  if (live) load(row, col, cur);
+  while (unit < total_units) {
+    const int nunit = unit + stride;
+    int64_t nrow = 0;
+    int ncol = 0;
+    bool nlive = false;
+    GroupIn<kGroup> nxt{};
+    if (nunit < total_units) {
+      advance();
+      nlive = locate_here(nrow, ncol);
+      if (nlive) load(nrow, ncol, nxt);
+    }
+    uint8_t s8 = 0;
+    if (live) {
+      float v[kGroup];
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < kGroup / 8; ++j) {
+        const T *h = reinterpret_cast<const T *>(&cur.v[j]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          v[8 * j + e] = to_f32<T>(h[e]);
+          amax = fmaxf(amax, fabsf(v[8 * j + e]));
+        }
       }
-    }
-#pragma unroll
-    for (int o = 1; o < kLanesPerGroup; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    int e = static_cast<int>(((__float_as_uint(amax) + static_cast<uint32_t>(p.round_add)) & 0x7f800000u) >> 23) - 127 - 2;
-    e = max(-127, min(125, e));
-    if (live) {
+      int e = static_cast<int>(((__float_as_uint(amax) + static_cast<uint32_t>(p.round_add)) & 0x7f800000u) >> 23) - 127 - 2;
+      e = max(-127, min(125, e));
       const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
-      float y[8];
+      uint8_t *dst = p.q + row * (p.K / 2) + static_cast<int64_t>(col) * (kGroup / 2);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) y[k] = v[k] * inv;
-      *reinterpret_cast<uint32_t *>(p.q + row * (p.K / 2) + static_cast<int64_t>(ch) * 128 + lane * 4) = cvt_e2m1x8(y);
+      for (int j = 0; j < kGroup / 16; ++j) {
+        uint32_t wd[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float y[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) y[k] = v[16 * j + 8 * h + k] * inv;
+          wd[h] = cvt_e2m1x8(y);
+        }
+        *reinterpret_cast<uint2 *>(dst + 8 * j) = make_uint2(wd[0], wd[1]);
+      }
+      s8 = static_cast<uint8_t>(e + 127);
     }
-    if (lane % kLanesPerGroup == 0 && c < p.padded_cols) {
-      // swizzled position of scale (pr, c): 128-row block, 4-column block, then (r % 32) * 16 + (r / 32 % 4) * 4 + c % 4
-      const int64_t soff = (pr / 128) * (static_cast<int64_t>(p.padded_cols / 4) * 512) + (c / 4) * 512 + (pr % 32) * 16 +
-                           ((pr % 128) / 32) * 4 + (c % 4);
-      if (soff < scale_bytes) p.scales[soff] = live ? static_cast<uint8_t>(e + 127) : 0;
-    }
+    const int64_t soff = static_cast<int64_t>(unit) * 32 + lane;   // zero for padding rows / columns / slack
+    if (soff < scale_bytes) p.scales[soff] = s8;
+    unit = nunit;
+    row = nrow;
+    col = ncol;
+    live = nlive;
+    cur = nxt;
   }
 }
 
@@ -176,7 +235,7 @@ int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, in
   if (M > 0x7fff0000LL - 127 * G) return fail(1, "%s: too many rows", name);
   if ((reinterpret_cast<uintptr_t>(x) & 15u) || (row_stride * 2) % 16 != 0)
     return fail(1, "%s: input rows must be 16-byte aligned", name);
-  if (reinterpret_cast<uintptr_t>(q) & 3u) return fail(1, "%s: output must be 4-byte aligned", name);
+  if (reinterpret_cast<uintptr_t>(q) & 7u) return fail(1, "%s: output must be 8-byte aligned", name);
   Mx4Params p;
   p.x = x;
   p.q = static_cast<uint8_t *>(q);
@@ -190,12 +249,12 @@ int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, in
   p.round_add = round_add;
   p.m_sizes = m_sizes;
   p.G = static_cast<int>(G);
-  const int64_t chunks = (static_cast<int64_t>(p.padded_cols) * group_size + 255) / 256;
-  const int64_t units = ((p.scale_rows + 127) / 128 * 128) * chunks;
+  const int64_t units = ((p.scale_rows + 127) / 128) * (p.padded_cols / 4) * kWarpsPerTile;
+  if (units > 0x7fff0000LL) return fail(1, "%s: tensor too large", name);
   const int64_t want = (units + 7) / 8;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
   const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
-  auto go = [&](auto kernel) { kernel<<<blocks, 256, 0, st>>>(p); };
+  auto go = [&](auto kernel) { kernel<<<blocks, kThreadsMx, 0, st>>>(p); };
   const bool bf = dtype == MSLK_B200_BF16;
   if (stacked) {
     if (bf) group_size == 32 ? go(quant_mx4_kernel<__nv_bfloat16, 32, true>) : go(quant_mx4_kernel<__nv_bfloat16, 16, true>);
