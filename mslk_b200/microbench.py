@@ -233,6 +233,16 @@ def bench_quantize_mx4(ops, M, K, args):
     return out
 
 
+def bench_f4f4bf16_mx(ops, M, N, K, args):
+    nv = _variants(N * K // 2, args.rotate_mb)
+    xq, sx = ops.quantize_mx4(_randn((M, K)), 32)
+    ws = [ops.quantize_mx4(_randn((N, K)), 32) for _ in range(nv)]
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    sec = _time(lambda i: ops.f4f4bf16(xq, ws[i][0], sx, ws[i][1], output=y), nv, args.iters, args.warmup, args.graph)
+    flops = 2.0 * M * N * K
+    return {"op": "f4f4bf16 (MXFP4, block 32)", "M": M, "N": N, "K": K, "us": sec * 1e6, "TFLOPs": flops / sec / 1e12}
+
+
 def bench_f4f4bf16(ops, M, N, K, args):
     nv = _variants(N * K // 2, args.rotate_mb)
     x = _randn((M, K))
@@ -255,7 +265,7 @@ def bench_f4f4bf16(ops, M, N, K, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "decode", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "moe_gather_scatter", "quantize_nvfp4", "quantize_mx4", "silu_mul_quant",
+    ap.add_argument("op", choices=["quantize_fp8_row", "f8f8bf16_rowwise", "decode", "batched", "grouped", "f4f4bf16", "f4f4bf16_grouped", "moe_gather_scatter", "quantize_nvfp4", "quantize_mx4", "f4f4bf16_mx", "silu_mul_quant",
                                    "sweep"])
     ap.add_argument("--shape", default=None, help="comma-separated sizes (see module docstring)")
     ap.add_argument("--experts", type=int, default=16)
@@ -292,6 +302,8 @@ def main():
         out.extend(bench_moe_gather_scatter(ops, args.tokens, *(shape or [5120, 16, 2]), args))
     elif args.op == "silu_mul_quant":
         out.append(bench_silu_mul_quant(ops, *(shape or [16384, 14336]), args))
+    elif args.op == "f4f4bf16_mx":
+        out.append(bench_f4f4bf16_mx(ops, *(shape or [8192, 8192, 8192]), args))
     elif args.op == "f4f4bf16":
         out.append(bench_f4f4bf16(ops, *(shape or [8192, 8192, 8192]), args))
     else:
