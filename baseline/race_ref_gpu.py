@@ -178,6 +178,26 @@ def race_nvfp4(ops, ref, M, N, K, iters, warmup):
             "ref_instance": "256_128_4_1_1" if M <= 128 else "256_256_2_1_1", **compare(y, y_ref)}
 
 
+def race_mxfp4(ops, ref, M, N, K, iters, warmup):
+    nv = variants(N * K // 2)
+    xq, sx = ops.quantize_mx4(randn((M, K), 0.1, seed=5), 32)
+    ws = [ops.quantize_mx4(randn((N, K), 0.01, seed=40 + i), 32) for i in range(nv)]
+    e8 = getattr(torch, "float8_e8m0fnu")
+    f4 = getattr(torch, "float4_e2m1fn_x2")
+    y, y_ref = (torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2))
+    rx, rsx = xq.view(f4), sx.view(e8)
+    rws = [(w.view(f4), s.view(e8)) for w, s in ws]
+    ours, theirs = race_pair(lambda i: ops.f4f4bf16(xq, ws[i][0], sx, ws[i][1], output=y),
+                             lambda i: ref.f4f4bf16_large_mx(rx, rws[i][0], rsx, rws[i][1], y_ref), nv, iters, warmup)
+    ops.f4f4bf16(xq, ws[0][0], sx, ws[0][1], output=y)
+    ref.f4f4bf16_large_mx(rx, rws[0][0], rsx, rws[0][1], y_ref)
+    torch.cuda.synchronize()
+    flops = 2.0 * M * N * K
+    return {"case": f"f4f4bf16 (MXFP4, block 32) M={M} N={N} K={K}", "ours_us": ours, "ref_us": theirs,
+            "ours_tflops": flops / ours / 1e6, "ref_tflops": flops / theirs / 1e6, "ours_over_ref_speed": theirs / ours,
+            "ref_instance": "256_256_2_1_1", **compare(y, y_ref)}
+
+
 def race_quantize(ops, ref_quant, M, K, iters, warmup):
     nv = variants(M * K * 2)
     xs = [randn((M, K), seed=30 + i) for i in range(nv)]
@@ -226,6 +246,8 @@ def main():
     emit(race_nvfp4(ops, ref, 8192, 8192, 8192, args.iters, args.warmup))
     for M in (1, 32):
         emit(race_nvfp4(ops, ref, M, 28672, 8192, 4 * args.iters, args.warmup))
+    if hasattr(ref, "f4f4bf16_large_mx") and hasattr(torch, "float8_e8m0fnu"):
+        emit(race_mxfp4(ops, ref, 8192, 8192, 8192, args.iters, args.warmup))
     pyref = os.path.join(HERE, "_ref", "pyref")
     if os.path.isdir(pyref):
         os.environ["MSLK_PYTHON_ONLY"] = "1"

@@ -48,6 +48,10 @@ Tensor grouped_stacked(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor M_size
 Tensor f4_large(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor out, Tensor gs) {
   return mslk::gemm::f4f4bf16_256_256_2_1_1(XQ, WQ, xs, ws, out, gs, 32);
 }
+// the same instance in its MXFP4 mode (e8m0 scales per 32 elements, no global scale)
+Tensor f4_large_mx(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor out) {
+  return mslk::gemm::f4f4bf16_256_256_2_1_1(XQ, WQ, xs, ws, out, std::nullopt, 32);
+}
 Tensor f4_small(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor out, Tensor gs) {
   return mslk::gemm::f4f4bf16_256_128_4_1_1(XQ, WQ, xs, ws, out, gs, 32);
 }
@@ -59,5 +63,6 @@ TORCH_LIBRARY(mslk_ref, m) {
   m.def("f8f8bf16_rowwise_small(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output) -> Tensor(a!)", rowwise_small);
   m.def("f8f8bf16_rowwise_grouped_stacked(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor M_sizes, Tensor(a!) output) -> Tensor", grouped_stacked);
   m.def("f4f4bf16_large(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output, Tensor global_scale) -> Tensor(a!)", f4_large);
+  m.def("f4f4bf16_large_mx(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output) -> Tensor(a!)", f4_large_mx);
   m.def("f4f4bf16_small(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output, Tensor global_scale) -> Tensor(a!)", f4_small);
 }

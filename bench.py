@@ -759,12 +759,16 @@ def e2e_run(tp, dd, steps):
     this rank's fp8 slice of the down activation from pinned host memory, and copies the results back (this rank's
     rows of the gathered gate+up output and its rows of the down output).  Three streams (copies in, kernels,
     copies out) ordered by events."""
+    import torch.distributed as dist
     device, P, r = tp.device, tp.world, tp.rank
-    hx1 = torch.empty(tp.x1.shape, dtype=torch.bfloat16).pin_memory()
-    hx1.copy_(tp.x1)
+    rows = tp.rows
+    # the activation is replicated: with P ranks each uploads its 1/P of the rows and an all-gather over NVLink
+    # completes the copy on every GPU (P x fewer bytes through the host's PCIe complex)
+    hx1 = torch.empty((rows, tp.x1.shape[1]), dtype=torch.bfloat16).pin_memory()
+    hx1.copy_(tp.x1[r * rows:(r + 1) * rows])
+    x1_slice = torch.empty((rows, tp.x1.shape[1]), dtype=torch.bfloat16, device=device) if P > 1 else None
     hx2 = torch.empty(tp.xq2_k.shape, dtype=torch.uint8).pin_memory()
     hx2.copy_(tp.xq2_k.view(torch.uint8))
-    rows = tp.rows
     hy1 = torch.empty((rows, GATE_UP[0]), dtype=torch.bfloat16).pin_memory()
     hy2 = torch.empty((rows, DOWN[0]), dtype=torch.bfloat16).pin_memory()
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
@@ -777,7 +781,11 @@ def e2e_run(tp, dd, steps):
     def step():
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_used)             # the previous step has consumed the device copies
-            tp.x1.copy_(hx1, non_blocking=True)
+            if P > 1:
+                x1_slice.copy_(hx1, non_blocking=True)
+                dist.all_gather_into_tensor(tp.x1, x1_slice)
+            else:
+                tp.x1.copy_(hx1, non_blocking=True)
             x2_u8.copy_(hx2, non_blocking=True)
             ev_in.record(s_in)
         s_main.wait_event(ev_in)
@@ -819,7 +827,9 @@ def e2e_run(tp, dd, steps):
     ms = dd.max(s0.elapsed_time(s1) / e_steps)
     return {"value": ffn_flops() / ms / 1e9, "unit": "TFLOP/s", "ms_per_step": ms,
             "h2d_bytes_per_step": hx1.numel() * 2 + hx2.numel(), "d2h_bytes_per_step": (hy1.numel() + hy2.numel()) * 2,
-            "note": "bytes are per rank; every rank copies the replicated activation in and its own rows of both results out"}
+            "note": "bytes are per rank; every rank copies its 1/P of the rows of the replicated activation in (an NCCL "
+                    "all-gather completes it on every GPU), its K slice of the down operand in, and its own rows of both "
+                    "results out"}
 
 
 # ----------------------------------------------------------------------------- main arm

@@ -337,18 +337,35 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             // of the scale column through the scale-id fields of the descriptor
             const int mmas = min(4, (k_len - kb * kBKElems + 63) / 64);
             const int atoms = (mmas + 1) / 2;
-            for (int a = 0; a < atoms; ++a) {
-              tc_cp_32x128b_warpx4(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+            if (mmas == 4) {
 #pragma unroll
-              for (int b = 0; b < C::kNB; ++b)
-                tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * a + 4 * b,
-                                     dsfb + static_cast<uint64_t>((b * 4 + a) * (kAtomBytes >> 4)));
+              for (int a = 0; a < 2; ++a) {
+                tc_cp_32x128b_warpx4(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+#pragma unroll
+                for (int b = 0; b < C::kNB; ++b)
+                  tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * a + 4 * b,
+                                       dsfb + static_cast<uint64_t>((b * 4 + a) * (kAtomBytes >> 4)));
+              }
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                mma_mxf4_2x(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                            db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                            C::kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
+                            sfb_t + 4 * C::kNB * (k >> 1), (kb | k) != 0 ? 1u : 0u);
+            } else {
+              for (int a = 0; a < atoms; ++a) {
+                tc_cp_32x128b_warpx4(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+#pragma unroll
+                for (int b = 0; b < C::kNB; ++b)
+                  tc_cp_32x128b_warpx4(sfb_t + 4 * C::kNB * a + 4 * b,
+                                       dsfb + static_cast<uint64_t>((b * 4 + a) * (kAtomBytes >> 4)));
+              }
+              for (int k = 0; k < mmas; ++k)
+                mma_mxf4_2x(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                            db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                            C::kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
+                            sfb_t + 4 * C::kNB * (k >> 1), (kb | k) != 0 ? 1u : 0u);
             }
-            for (int k = 0; k < mmas; ++k)
-              mma_mxf4_2x(d_tmem, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                          db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                          C::kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
-                          sfb_t + 4 * C::kNB * (k >> 1), (kb | k) != 0 ? 1u : 0u);
           } else {
           const uint32_t idesc = C::kIdesc | (p.scale_mode == kScaleMxfp4_16 ? kIdescScaleE8M0 : 0u);
           const int atoms = min(4, ncb - 4 * kb);

@@ -247,17 +247,33 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             // of the scale column through the scale-id fields of the descriptor
             const int mmas = min(kMmasPerStage, (p.K - kb * kBKElems + 63) / 64);
             const int atoms = (mmas + 1) / 2;
-            for (int a = 0; a < atoms; ++a) {
-              tc_cp_32x128b_warpx4_pair(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
-              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a, dsfb + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
-              tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a + 4,
-                                        dsfb + static_cast<uint64_t>((kMmasPerStage + a) * (kAtomBytes >> 4)));
+            if (mmas == kMmasPerStage) {
+#pragma unroll
+              for (int a = 0; a < 2; ++a) {
+                tc_cp_32x128b_warpx4_pair(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+                tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a, dsfb + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+                tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a + 4,
+                                          dsfb + static_cast<uint64_t>((kMmasPerStage + a) * (kAtomBytes >> 4)));
+              }
+#pragma unroll
+              for (int k = 0; k < kMmasPerStage; ++k)
+                mma_mxf4_2x_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                                 db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                                 kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
+                                 sfb_t + 8 * (k >> 1), (kb | k) != 0 ? 1u : 0u);
+            } else {
+              for (int a = 0; a < atoms; ++a) {
+                tc_cp_32x128b_warpx4_pair(sfa_t + 4 * a, dsfa + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+                tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a, dsfb + static_cast<uint64_t>(a * (kAtomBytes >> 4)));
+                tc_cp_32x128b_warpx4_pair(sfb_t + 8 * a + 4,
+                                          dsfb + static_cast<uint64_t>((kMmasPerStage + a) * (kAtomBytes >> 4)));
+              }
+              for (int k = 0; k < mmas; ++k)
+                mma_mxf4_2x_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                                 db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                                 kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
+                                 sfb_t + 8 * (k >> 1), (kb | k) != 0 ? 1u : 0u);
             }
-            for (int k = 0; k < mmas; ++k)
-              mma_mxf4_2x_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                               db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                               kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
-                               sfb_t + 8 * (k >> 1), (kb | k) != 0 ? 1u : 0u);
             const uint32_t e = smem_u32(&S.empty[stage]);
             tc_commit_pair(mapa_u32(e, 0));
             tc_commit_pair(mapa_u32(e, 1));

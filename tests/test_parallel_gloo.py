@@ -75,3 +75,21 @@ def test_shard_helpers():
     with pytest.raises(ValueError):
         par.shard_range(10, 0, 4)
     assert par.expert_token_range([4, 0, 6, 2], 1, 2) == (4, 12, (2, 4))
+
+
+def test_balanced_expert_assignment():
+    from mslk_b200 import parallel as par
+    counts = [279, 343, 365, 576, 320, 412, 248, 716, 1645, 0, 0, 6481, 840, 1078, 475, 2606]
+    for world in (1, 2, 4, 8):
+        experts, load = par.balanced_expert_assignment(counts, world)
+        assert sorted(e for r in experts for e in r) == list(range(16))          # every expert exactly once
+        assert load == [sum(counts[e] for e in r) for r in experts]
+        assert all(r == sorted(r) for r in experts)
+        # greedy longest-first is within 4/3 of the optimum, and never worse than the contiguous split
+        contiguous = max(sum(counts[r * (16 // world):(r + 1) * (16 // world)]) for r in range(world))
+        bound = max(max(counts), -(-sum(counts) // world))
+        assert max(load) <= contiguous and max(load) <= (4 * bound + 2) // 3
+    experts, load = par.balanced_expert_assignment(counts, 8)
+    assert max(load) == 6481                                                      # the largest expert alone is the bound
+    rows = par.expert_rows(counts, experts[0])
+    assert all(b - a == counts[e] for (a, b), e in zip(rows, experts[0]))
