@@ -556,15 +556,17 @@ def _f4f4bf16_grouped_mm_2d2d(name, dev, XQ, WQ, x_scale, w_scale, offsets, outp
     M, N, K = XQ.shape[0], WQ.shape[-1], WQ.shape[-2] * 2
     if XQ.shape[1] * 2 != K:
         raise RuntimeError("for 2d-2d grouped GEMM, XQ shape must be (M, total_K) and WQ shape must be (total_K, N).")
-    out = output if output is not None else torch.empty((G, M, N), dtype=torch.bfloat16, device=dev)
-    if out.dim() != 3 or tuple(out.shape) != (G, M, N) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+    if output is not None and (output.dim() != 3 or tuple(output.shape) != (G, M, N) or output.dtype != torch.bfloat16
+                               or not output.is_contiguous()):
         raise RuntimeError("for 2d-2d grouped GEMM, output shape must be (G, M, N).")
+    block = 16 if nvfp4 else 32
+    if G and M and N:
+        # every group's scale block is padded on its own, so these are lower bounds; the kernel checks the real need
+        _check_nvfp4_scale_extent(name, "x_scale", x_scale, M, K, block=block)
+        _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, block=block)
+    out = output if output is not None else torch.empty((G, M, N), dtype=torch.bfloat16, device=dev)
     if out.numel() == 0:
         return out
-    block = 16 if nvfp4 else 32
-    # every group's scale block is padded on its own, so these are lower bounds; the kernel checks the real need
-    _check_nvfp4_scale_extent(name, "x_scale", x_scale, M, K, block=block)
-    _check_nvfp4_scale_extent(name, "w_scale", w_scale, N, K, block=block)
     gs = None
     if nvfp4:
         gs = global_scale.reshape(-1).to(torch.float32)

@@ -151,6 +151,48 @@ def test_ops_reject_scale_tensors_shorter_than_the_padded_swizzled_layout():
         ops.f4f4bf16_grouped_stacked(q, wg, ok_x, ok_w, ms, gs2, use_mx=False)
 
 
+def test_mxfp4_and_k_grouped_argument_checks():
+    """Host-side checks of the MXFP4 forms and of the 2D-2D grouped form: mode / global-scale mismatches, scale
+    extents, offsets dtype, output shape -- all raised before any kernel could run."""
+    from mslk_b200 import ops
+    f8 = torch.float8_e4m3fn
+    e8 = getattr(torch, "float8_e8m0fnu", torch.uint8)
+    M, N, K, G = 128, 128, 256, 2
+    q, wq, wq3, ms, offs, gs = _fake_cuda(lambda: (
+        torch.empty((M, K // 2), dtype=torch.uint8, device="cuda"), torch.empty((N, K // 2), dtype=torch.uint8, device="cuda"),
+        torch.empty((G, N, K // 2), dtype=torch.uint8, device="cuda"), torch.empty((G,), dtype=torch.int64, device="cuda"),
+        torch.empty((G,), dtype=torch.int32, device="cuda"), torch.empty((G,), device="cuda")))
+    sx_mx, sw_mx, sw3_mx, sx_nv, sw_nv, short = _fake_cuda(lambda: (
+        torch.empty((128 * 8,), dtype=e8, device="cuda"), torch.empty((128 * 8,), dtype=e8, device="cuda"),
+        torch.empty((G, 128 * 8), dtype=e8, device="cuda"), torch.empty((128, 16), dtype=f8, device="cuda"),
+        torch.empty((128, 16), dtype=f8, device="cuda"), torch.empty((64,), dtype=e8, device="cuda")))
+    with pytest.raises(RuntimeError, match="mxfp4_block_size"):
+        ops.f4f4bf16(q, wq, sx_mx, sw_mx, mxfp4_block_size=8)
+    with pytest.raises(RuntimeError, match="x_scale holds"):
+        ops.f4f4bf16(q, wq, short, sw_mx)                      # MXFP4 needs [128, 8] scales for K = 256
+    with pytest.raises(RuntimeError, match="use_mx=False"):
+        ops.f4f4bf16_grouped_stacked(q, wq3, sx_mx, sw3_mx, ms, gs)          # a global scale with the MX default
+    with pytest.raises(RuntimeError, match="needs global_scale"):
+        ops.f4f4bf16_grouped_stacked(q, wq3, sx_mx, sw3_mx, ms, None, use_mx=False)
+    # grouped_mm: the scale dtype names the format
+    with pytest.raises(RuntimeError, match="needs global_scale"):
+        ops.f4f4bf16_grouped_mm(q, wq3.transpose(-2, -1), sx_nv, sw_nv, offs)
+    if e8 is not torch.uint8:
+        with pytest.raises(RuntimeError, match="global_scale is for NVFP4"):
+            ops.f4f4bf16_grouped_mm(q, wq3.transpose(-2, -1), sx_mx, sw3_mx, offs, None, gs)
+        # 2D-2D: output must be [G, M, N]
+        bad_out = _fake_cuda(lambda: torch.empty((M, N), dtype=torch.bfloat16, device="cuda"))
+        with pytest.raises(RuntimeError, match=r"\(G, M, N\)"):
+            ops.f4f4bf16_grouped_mm(q, wq.transpose(-2, -1), sx_mx, sw_mx, offs, bad_out)
+        with pytest.raises(RuntimeError, match="x_scale holds"):
+            ops.f4f4bf16_grouped_mm(q, wq.transpose(-2, -1), short, sw_mx, offs)
+    with pytest.raises(RuntimeError, match="offsets must be int32"):
+        ops.f4f4bf16_grouped_mm(q, wq.transpose(-2, -1), sx_mx, sw_mx, ms)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.quantize_mx4_stacked(torch.zeros(2, dtype=torch.int64), _fake_cuda(
+            lambda: torch.empty((M, K), dtype=torch.bfloat16, device="cuda")))
+
+
 def test_export_strict_traces_through_the_fake_kernels(mslk):
     """torch.export(strict=True) of a module that quantizes and multiplies, as the reference's
     ExportCompileTests.test_f8f8bf16_export does (test/gemm/gemm_test.py:236-289); meta tensors need no GPU."""
