@@ -76,11 +76,14 @@ def patched_nvfp4_copy(ref_cutlass_dir, rel, scratch):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-root", default="/root/reference")
+    ap.add_argument("--ref-root", default=os.environ.get("MSLK_REF_ROOT", ""),
+                    help="checkout of the reference (meta-pytorch/MSLK); default: $MSLK_REF_ROOT")
     ap.add_argument("--jobs", type=int, default=5)
     ap.add_argument("--only", default="", help="comma-separated substrings of instance names to (re)build")
     ap.add_argument("--python", action="store_true", help="mirror the reference's Python package to _ref/pyref/mslk")
     args = ap.parse_args()
+    if not os.path.isdir(os.path.join(args.ref_root, "csrc", "gemm", "cutlass")):
+        sys.exit("build_ref_gpu.py: pass --ref-root <checkout of the reference> (or set MSLK_REF_ROOT)")
     if args.python:
         import shutil
         dst = os.path.join(OUT, "pyref", "mslk")

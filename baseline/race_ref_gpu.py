@@ -1,6 +1,6 @@
 """Races this library's kernels against the reference's own sm_100 kernels on one B200.
 
-    python baseline/race_ref_gpu.py [--quick] [--out gpurun_out/race_ref_gpu.jsonl]
+    python baseline/race_ref_gpu.py [--quick] [--out <file>.jsonl]
 
 Needs baseline/_ref/libmslk_ref_gpu.so (built by baseline/build_ref_gpu.py from the reference's sources at
 stock CUTLASS) and, for the quantizer, baseline/_ref/pyref (the reference's Python package, `--python`).
