@@ -562,10 +562,10 @@ int run_fp4(const char *name, const void *xq, const void *wq, const void *x_scal
   // (4096, 14336): 18.1 against 29.7 us, M = 100, (8192, 28672): 32.1 against 54.0, (8192, 8192): 18.5 against
   // 19.9; with K = 4096 the general kernel wins, (4096, 4096): 12.5 against 19.2 us)
   const int64_t w_blocks = (N + 127) / 128;
-  if (!mx && !grouped && force == 0 && N >= 128 &&
+  if (!grouped && force == 0 && N >= 128 &&
       (M <= 64 || (M <= nvfp4_decode::kMaxTokens && (w_blocks > sms || (2 * w_blocks <= sms && K >= 8192)))))
     return nvfp4_decode::launch_decode_kernel(xq, wq, x_scale, w_scale, global_scale, y, status, M, N, K, scratch,
-                                              scratch_size, st);
+                                              scratch_size, st, scale_mode);
   const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
   // (few-token shapes stay on one CTA per tile: a 256-row pair tile would be mostly padding; grouped problems take
   // pairs when their groups average at least 128 rows and there are few enough groups for the kernel's tables)

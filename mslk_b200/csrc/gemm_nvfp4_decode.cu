@@ -81,7 +81,8 @@ struct KParams {
   unsigned int *tickets;   // scratch (splits > 1), zero at launch, self-resetting
   int *status;
   int M, N, K;
-  int ncb;                 // scale atoms per 128-row block = ceil(K / 64)
+  int ncb;                 // scale atoms per 128-row block = ceil(K / 64); one scale per 32 elements: ceil(K / 128)
+  int scale_mode;          // kScaleNvfp4 / kScaleMxfp4 / kScaleMxfp4_16 (common.cuh); alpha is null for the MX formats
   int x_box_rows;          // rows of the token box (M rounded up to 8): no out-of-range fill
   int splits;
   int kb_per_split;        // K blocks (of 256 elements) per split
@@ -147,13 +148,15 @@ __global__ void __launch_bounds__(kNumThreads, 2)
         uint8_t *sx = sw + C::kStageW;
         uint8_t *ssfw = sx + C::kStageX;
         uint8_t *ssfx = ssfw + C::kStageSF;
-        const int atoms = min(4, p.ncb - 4 * kb);  // scale atoms (64 K-elements each) left in this K block
+        // scale atoms (4 scales per row each: 64 K-elements, MXFP4 128) left in this K block of 256 elements
+        const int apk = p.scale_mode == kScaleMxfp4 ? 2 : 4;
+        const int atoms = min(apk, p.ncb - apk * kb);
         const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
         mbar_arrive_expect_tx(&S.full[stage], C::kStageW + p.x_box_rows * kBKBytes + 2 * sf_bytes);
         tma_load_2d(sw, &tmap_w, &S.full[stage], kb * kBKBytes, n_tile * kWRows);
         tma_load_2d(sx, &tmap_x, &S.full[stage], kb * kBKBytes, 0);
-        bulk_load_1d(ssfw, sfw_row + static_cast<size_t>(4 * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
-        bulk_load_1d(ssfx, p.sfx + static_cast<size_t>(4 * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
+        bulk_load_1d(ssfw, sfw_row + static_cast<size_t>(apk * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
+        bulk_load_1d(ssfx, p.sfx + static_cast<size_t>(apk * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
         if (++stage == C::kStages) {
           stage = 0;
           phase ^= 1;
@@ -180,15 +183,32 @@ __global__ void __launch_bounds__(kNumThreads, 2)
         const uint32_t sfx_t = sfw_t + 16;
         const uint64_t dw = make_kmajor_sw128_desc(sw);
         const uint64_t dx = make_kmajor_sw128_desc(sw + C::kStageW);
-        const int atoms = min(4, p.ncb - 4 * (kb0 + i));
-        for (int k = 0; k < atoms; ++k) {
-          tc_cp_32x128b_warpx4(sfw_t + 4 * k, make_sf_atom_desc(ssfw + k * kAtomBytes));
-          tc_cp_32x128b_warpx4(sfx_t + 4 * k, make_sf_atom_desc(ssfx + k * kAtomBytes));
+        if (p.scale_mode == kScaleMxfp4) {
+          // one scale per 32 K-elements: an atom holds the scales of TWO instructions, which pick their two bytes of
+          // the scale column through the scale-id fields of the descriptor
+          const int mmas = min(4, (p.K - (kb0 + i) * (2 * kBKBytes) + 63) / 64);
+          const int atoms = (mmas + 1) / 2;
+          for (int a = 0; a < atoms; ++a) {
+            tc_cp_32x128b_warpx4(sfw_t + 4 * a, make_sf_atom_desc(ssfw + a * kAtomBytes));
+            tc_cp_32x128b_warpx4(sfx_t + 4 * a, make_sf_atom_desc(ssfx + a * kAtomBytes));
+          }
+          for (int k = 0; k < mmas; ++k)
+            mma_mxf4_2x(tmem_base, dw + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                        dx + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                        C::kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfw_t + 4 * (k >> 1),
+                        sfx_t + 4 * (k >> 1), (i | k) != 0 ? 1u : 0u);
+        } else {
+          const uint32_t idesc = C::kIdesc | (p.scale_mode == kScaleMxfp4_16 ? kIdescScaleE8M0 : 0u);
+          const int atoms = min(4, p.ncb - 4 * (kb0 + i));
+          for (int k = 0; k < atoms; ++k) {
+            tc_cp_32x128b_warpx4(sfw_t + 4 * k, make_sf_atom_desc(ssfw + k * kAtomBytes));
+            tc_cp_32x128b_warpx4(sfx_t + 4 * k, make_sf_atom_desc(ssfx + k * kAtomBytes));
+          }
+          for (int k = 0; k < atoms; ++k)
+            mma_nvfp4(tmem_base, dw + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                      dx + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), idesc, sfw_t + 4 * k, sfx_t + 4 * k,
+                      (i | k) != 0 ? 1u : 0u);
         }
-        for (int k = 0; k < atoms; ++k)
-          mma_nvfp4(tmem_base, dw + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
-                    dx + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), C::kIdesc, sfw_t + 4 * k, sfx_t + 4 * k,
-                    (i | k) != 0 ? 1u : 0u);
         tc_commit(&S.empty[stage]);
         if (++stage == C::kStages) {
           stage = 0;
@@ -272,7 +292,7 @@ __global__ void __launch_bounds__(kNumThreads, 2)
     // memory, no tickets, no extra launch.
     cluster_sync_all();
     if (warp >= 2 && do_epilogue && n_ok) {
-      const float alpha = *p.alpha;
+      const float alpha = p.alpha ? *p.alpha : 1.0f;   // the MX formats have no global scale
       const uint32_t mine = smem_u32(ring) + static_cast<uint32_t>(quad * 32 + lane) * 4u;
       uint32_t peer[8];
 #pragma unroll
@@ -290,7 +310,7 @@ __global__ void __launch_bounds__(kNumThreads, 2)
     }
     cluster_sync_all();
   } else if (warp >= 2 && do_epilogue && n_ok) {
-    const float alpha = *p.alpha;
+    const float alpha = p.alpha ? *p.alpha : 1.0f;   // the MX formats have no global scale
 #pragma unroll
     for (int m = 0; m < BT; ++m)
       if (m < p.M) p.y[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(acc[m] * alpha);
@@ -381,7 +401,7 @@ size_t scratch_bytes(int64_t M, int64_t N, int64_t K, int sms) {
 
 int launch_decode_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const float *alpha,
                          void *y, int *status, int64_t M, int64_t N, int64_t K, void *scratch, size_t scratch_size,
-                         cudaStream_t st) {
+                         cudaStream_t st, int scale_mode) {
   const int sms = sm_count();
   const int64_t n_tiles = (N + kWRows - 1) / kWRows;
   const int k_blocks = static_cast<int>((K / 2 + kBKBytes - 1) / kBKBytes);
@@ -407,7 +427,8 @@ int launch_decode_kernel(const void *xq, const void *wq, const void *x_scale, co
   p.M = static_cast<int>(M);
   p.N = static_cast<int>(N);
   p.K = static_cast<int>(K);
-  p.ncb = static_cast<int>((K + 63) / 64);
+  p.ncb = static_cast<int>(scale_mode == kScaleMxfp4 ? (K + 127) / 128 : (K + 63) / 64);
+  p.scale_mode = scale_mode;
   p.x_box_rows = std::min<int>(bt, static_cast<int>((M + 7) / 8 * 8));
   p.splits = splits;
   p.kb_per_split = (k_blocks + splits - 1) / splits;

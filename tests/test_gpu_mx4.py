@@ -87,6 +87,18 @@ def test_gemm_mxfp4(ops, M, N, K, group):
     assert _status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 28672, 8192), (32, 28672, 8192), (16, 4096, 14336), (64, 8192, 8192), (7, 6144, 4096),
+                                   (100, 8192, 28672), (3, 384, 1056)])
+@pytest.mark.parametrize("group", [32, 16])
+def test_gemm_mxfp4_few_tokens(ops, M, N, K, group):
+    """Few-token shapes: the weight-streaming kernel (K split inside clusters on the long-K shapes) in both MX modes."""
+    x, w, xq, wq, sx, sw = _mx_case(ops, M, N, K, group, seed=M + N)
+    y = ops.f4f4bf16(xq, wq, sx, sw, mxfp4_block_size=group)
+    y_ref = oracle.gemm_mx4_torch(xq, wq, sx, sw, group)
+    assert_sharp_bf16(y, y_ref, f"f4f4bf16 MXFP4 few tokens, group {group} {M}x{N}x{K}")
+    assert _status() == 0
+
+
 def test_gemm_mxfp4_through_the_operator(ops):
     from mslk_b200 import compat
     compat.install()
