@@ -136,7 +136,7 @@ def race_dense(ops, ref, M, N, K, iters, warmup, w_std=0.02):
 
 
 def race_grouped(ops, ref, E, tokens, N, K, iters, warmup):
-    from mslk_b200.microbench import zipf_counts
+    from microbench import zipf_counts
     counts = zipf_counts(E, tokens)
     ms = counts.to(torch.int64).cuda()
     xq, xs = ops.quantize_fp8_row(randn((tokens, K), seed=2))

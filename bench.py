@@ -378,7 +378,7 @@ def moe_expert_sharded(ops, par, dd, rank, world, device, steps, warmup):
     """configs: 16 experts (hidden 5120, FFN 8192), 16384 tokens, Zipf(1.2) counts with empty experts; experts
     sharded over the ranks, tokens bucketed per rank, no collective.  Whole-job TFLOP/s = total flops / slowest
     rank, for contiguous expert ranges and for the token-count-aware placement."""
-    from mslk_b200.microbench import zipf_counts
+    from microbench import zipf_counts
     E, tokens = 16, 16384
     counts = zipf_counts(E, tokens).tolist()
     placements = {"contiguous": [list(range(*par.expert_slice(E, r, world))) for r in range(world)]}
@@ -557,7 +557,7 @@ def other_configs(ops, device, peaks):
     out["quantize_fp8_row"] = quant
     torch.cuda.empty_cache()
     # ---- configs[3]: grouped MoE, both projections
-    from mslk_b200.microbench import zipf_counts
+    from microbench import zipf_counts
     counts = zipf_counts(16, 16384)
     msz = counts.to(torch.int64).to(device)
     moe = {"counts": counts.tolist()}

@@ -1,16 +1,16 @@
 """Shape-level micro-benchmarks of the individual kernels (one JSON line per case).
 
-    python -m mslk_b200.microbench quantize_fp8_row --shape 8192,4096
-    python -m mslk_b200.microbench f8f8bf16_rowwise --shape 8192,8192,8192
-    python -m mslk_b200.microbench decode --graph                            # M = 1, 16, 32: general vs split-K kernel
-    python -m mslk_b200.microbench batched --shape 8,2048,4096,4096          # B,M,N,K
-    python -m mslk_b200.microbench grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
-    python -m mslk_b200.microbench f4f4bf16_grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
-    python -m mslk_b200.microbench f4f4bf16 --shape 8192,8192,8192
-    python -m mslk_b200.microbench quantize_nvfp4 --shape 8192,8192
-    python -m mslk_b200.microbench moe_gather_scatter --tokens 16384 --shape 5120,16,2      # D,E,top-k
-    python -m mslk_b200.microbench silu_mul_quant --shape 16384,14336      # T,D; also times the unfused pair
-    python -m mslk_b200.microbench sweep          # the Llama-3-8B sweep: M x (N,K), quantize + GEMM
+    python microbench.py quantize_fp8_row --shape 8192,4096
+    python microbench.py f8f8bf16_rowwise --shape 8192,8192,8192
+    python microbench.py decode --graph                            # M = 1, 16, 32: general vs split-K kernel
+    python microbench.py batched --shape 8,2048,4096,4096          # B,M,N,K
+    python microbench.py grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
+    python microbench.py f4f4bf16_grouped --experts 16 --tokens 16384 --shape 16384,5120   # N,K per expert
+    python microbench.py f4f4bf16 --shape 8192,8192,8192
+    python microbench.py quantize_nvfp4 --shape 8192,8192
+    python microbench.py moe_gather_scatter --tokens 16384 --shape 5120,16,2      # D,E,top-k
+    python microbench.py silu_mul_quant --shape 16384,14336      # T,D; also times the unfused pair
+    python microbench.py sweep          # the Llama-3-8B sweep: M x (N,K), quantize + GEMM
 
 Timing: CUDA events around `--iters` launches after `--warmup` launches, on torch's current
 stream.  Inputs rotate through enough buffers to exceed the 126 MB L2 (`--rotate-mb`, default 512).
@@ -24,8 +24,12 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
 def _time(fn, n_variants, iters, warmup, graph):
@@ -138,7 +142,7 @@ def bench_batched(ops, B, M, N, K, args):
 
 def bench_decode(ops, M, N, K, args):
     """Few-token GEMM: the general kernel against the split-K weight-streaming kernel (caller-provided workspace)."""
-    from ._lib import check, lib
+    from mslk_b200._lib import check, lib
     nv = _variants(N * K, args.rotate_mb)
     xq, xs = ops.quantize_fp8_row(_randn((M, K)))
     ws = [ops.quantize_fp8_row(_randn((N, K), args.w_std)) for _ in range(nv)]
@@ -276,8 +280,8 @@ def main():
     ap.add_argument("--w-std", type=float, default=0.02)
     ap.add_argument("--graph", action="store_true")
     args = ap.parse_args()
-    from . import ops
-    from ._lib import device_status
+    from mslk_b200 import ops
+    from mslk_b200._lib import device_status
     shape = [int(v) for v in args.shape.split(",")] if args.shape else None
     out = []
     if args.op == "quantize_fp8_row":

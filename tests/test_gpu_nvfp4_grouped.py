@@ -160,7 +160,7 @@ def test_rows_past_the_sum_untouched_and_errors(ops):
 
 def test_moe_shape_zipf(ops):
     # 16 experts, Zipf counts with empty experts, hidden 2048 -> 1024 (reduced from the FP8 MoE configuration)
-    from mslk_b200.microbench import zipf_counts
+    from microbench import zipf_counts
     m_sizes = zipf_counts(16, 4096).tolist()
     X, W, ms, xq, wq, x_scale, w_scale, alpha = _grouped_problem(ops, m_sizes, 1024, 2048, seed=3)
     y = ops.f4f4bf16_grouped_stacked(xq, wq, x_scale, w_scale, ms, alpha, None, use_mx=False)

@@ -68,7 +68,7 @@ def test_dense_smaller_token_counts_sharp(ops, M, N, K):
 
 @pytest.mark.parametrize("N,K", [(16384, 5120), (5120, 8192)])
 def test_moe_full_size_zipf(ops, N, K):
-    from mslk_b200.microbench import zipf_counts
+    from microbench import zipf_counts
     E, tokens = 16, 16384
     counts = zipf_counts(E, tokens).tolist()
     assert sum(counts) == tokens and counts.count(0) >= 2
@@ -192,7 +192,7 @@ def test_nvfp4_bench_shapes_every_element(ops, M, N, K):
 def test_grouped_nvfp4_zipf_against_per_group_oracle(ops):
     """Grouped NVFP4 with Zipf counts and empty experts against the per-group dequantize-matmul oracle
     (a whole wrong scale block would pass a norm bound against the unquantized product, not this)."""
-    from mslk_b200.microbench import zipf_counts
+    from microbench import zipf_counts
     from test_gpu_nvfp4_grouped import _grouped_problem
     m_sizes = zipf_counts(16, 4096).tolist()
     N, K = 1024, 2048
