@@ -628,6 +628,33 @@ def other_configs(ops, device, peaks):
         ops.f4f4bf16(xq, wqs[i][0], sx, wqs[i][1], output=y)
     ms = _time_plain(fm, 30)
     out["mxfp4_8192_cubed"] = tensor_roof(2.0 * 8192 ** 3, ms, fp4_peak, NOMINAL_FP4_TFLOPS)
+    del xs_, wqs, xq, sx, y
+    torch.cuda.empty_cache()
+    # ---- grouped FP4 MoE (configs[3] shapes, E = 16, Zipf counts): stacked quantizers and grouped GEMMs, NVFP4 and MXFP4
+    x = _randn((16384, 5120), g)
+    w = _randn((16 * 16384, 5120), g, 0.02)
+    w_ms = torch.full((16,), 16384, dtype=torch.int64, device=device)
+    grouped = {}
+    x_gs, _ = ops.calculate_group_max(x, msz)
+    w_gs, _ = ops.calculate_group_max(w, w_ms)
+    q_ms = _time_graph(lambda: ops.nvfp4_quantize_stacked(msz, x, x_gs), 12)
+    xq, sx = ops.nvfp4_quantize_stacked(msz, x, x_gs)
+    wq, sw = ops.nvfp4_quantize_stacked(w_ms, w, w_gs)
+    alpha = torch.reciprocal(x_gs * w_gs)
+    sw3 = sw[: 16 * 16384].view(16, 16384, -1)
+    ms = _time_plain(lambda: ops.f4f4bf16_grouped_stacked(xq, wq.view(16, 16384, 2560), sx, sw3, msz, alpha, None,
+                                                          use_mx=False), 20)
+    grouped["nvfp4"] = {"quantize_stacked": hbm_roof(16384 * 5120 * 2.5625, q_ms),
+                        "gemm_gate_up": tensor_roof(2.0 * 16384 * 16384 * 5120, ms, fp4_peak, NOMINAL_FP4_TFLOPS)}
+    q_ms = _time_graph(lambda: ops.quantize_mx4_stacked(msz, x), 12)
+    xq, sx = ops.quantize_mx4_stacked(msz, x)
+    wq, sw = ops.quantize_mx4_stacked(w_ms, w)
+    pc = 5120 // 32
+    sw3 = sw[: 16 * 16384 * pc].view(16, -1)
+    ms = _time_plain(lambda: ops.f4f4bf16_grouped_stacked(xq, wq.view(16, 16384, 2560), sx, sw3, msz), 20)
+    grouped["mxfp4"] = {"quantize_stacked": hbm_roof(16384 * 5120 * (2.5 + 1.0 / 32.0), q_ms),
+                        "gemm_gate_up": tensor_roof(2.0 * 16384 * 16384 * 5120, ms, fp4_peak, NOMINAL_FP4_TFLOPS)}
+    out["fp4_grouped_moe_e16"] = grouped
     return out
 
 
