@@ -41,6 +41,8 @@ ROWWISE = ["f8f8bf16_rowwise/f8f8bf16_rowwise_128_256_128_2_1_1_10_f_f.cu",
            "f8f8bf16_rowwise/f8f8bf16_rowwise_128_64_128_1_1_1_10_f_f.cu"]
 GROUPED = ["f8f8bf16_rowwise_grouped_sm100/f8f8bf16_rowwise_grouped_256_256_128_2_1_1_10_f.cu"]
 NVFP4 = ["f4f4bf16/f4f4bf16_256_256_2_1_1.cu", "f4f4bf16/f4f4bf16_256_128_4_1_1.cu"]
+# grouped FP4 (NVFP4 and MXFP4 branches; stacked, 2D-3D and 2D-2D forms): the instance the heuristic picks for the MoE shapes
+GROUPED_FP4 = ["f4f4bf16_grouped/f4f4bf16_grouped_256_256_256_2_1_1.cu"]
 
 
 def cutlass_include_dirs():
@@ -108,7 +110,7 @@ def main():
              "-DMSLK_DISABLE_SM90_CUTLASS", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
              "-Xcompiler", "-fPIC", "-w"]
     jobs = []
-    for rel in ROWWISE + GROUPED:
+    for rel in ROWWISE + GROUPED + GROUPED_FP4:
         jobs.append((os.path.join(ref_cutlass, rel), [os.path.join(ref_cutlass, os.path.dirname(rel))]))
     for rel in NVFP4:
         jobs.append((patched_nvfp4_copy(ref_cutlass, rel, scratch), [os.path.join(scratch, "f4f4bf16")]))

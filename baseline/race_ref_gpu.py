@@ -92,13 +92,19 @@ def time_us(fn, n_variants, iters, warmup):
     return e0.elapsed_time(e1) / iters * 1e3
 
 
-def race_pair(ours_fn, ref_fn, n_variants, iters, warmup, rounds=3):
-    """Median us per launch of both sides, measured alternately (ours, reference, ours, ...) so that clock and
-    temperature drift over the run hits both alike."""
+def race_pair(ours_fn, ref_fn, n_variants, iters, warmup, rounds=5):
+    """Median us per launch of both sides, measured alternately so that clock and temperature drift over the run
+    hits both alike: the side that goes first changes every round, and a short idle gap in front of every
+    measurement lets the power state of this 1000 W part settle the same way for both."""
+    import time
     a, b = [], []
-    for _ in range(rounds):
-        a.append((time_us(ours_fn, n_variants, iters, warmup), LAST_MHZ[0]))
-        b.append((time_us(ref_fn, n_variants, iters, warmup), LAST_MHZ[0]))
+    for r in range(rounds):
+        for side in ((0, 1) if r % 2 == 0 else (1, 0)):
+            time.sleep(0.2)
+            if side == 0:
+                a.append((time_us(ours_fn, n_variants, iters, warmup), LAST_MHZ[0]))
+            else:
+                b.append((time_us(ref_fn, n_variants, iters, warmup), LAST_MHZ[0]))
     a.sort(key=lambda t: t[0])
     b.sort(key=lambda t: t[0])
     RACE_MHZ[:] = [a[len(a) // 2][1], b[len(b) // 2][1]]
@@ -198,6 +204,80 @@ def race_mxfp4(ops, ref, M, N, K, iters, warmup):
             "ref_instance": "256_256_2_1_1", **compare(y, y_ref)}
 
 
+def race_grouped_fp4(ops, ref, E, tokens, N, K, mx, iters, warmup):
+    """Grouped (stacked) FP4 GEMM, NVFP4 or MXFP4, against the reference instance its heuristic picks for these shapes
+    (csrc/gemm/cutlass/f4f4bf16_grouped.cu:60-230 -> f4f4bf16_grouped_256_256_256_2_1_1)."""
+    from microbench import zipf_counts
+    counts = zipf_counts(E, tokens)
+    ms = counts.to(torch.int64).cuda()
+    w_ms = torch.full((E,), N, dtype=torch.int64, device="cuda")
+    x, w = randn((tokens, K), 0.1, seed=6), randn((E * N, K), 0.01, seed=7)
+    f4 = getattr(torch, "float4_e2m1fn_x2")
+    starts = torch.zeros(E + 1, dtype=torch.int64)
+    starts[1:] = torch.cumsum((counts.to(torch.int64) + 127) // 128 * 128, 0)
+    starts = starts.cuda()
+    if mx:
+        e8 = getattr(torch, "float8_e8m0fnu")
+        xq, sx = ops.quantize_mx4_stacked(ms, x)
+        wq, sw = ops.quantize_mx4_stacked(w_ms, w)
+        sw3 = sw[: E * N * (K // 32)].view(E, -1)
+        gs = None
+        r_sx, r_sw = sx.view(e8), sw3.view(e8)
+    else:
+        x_gs, _ = ops.calculate_group_max(x, ms)
+        w_gs, _ = ops.calculate_group_max(w, w_ms)
+        xq, sx = ops.nvfp4_quantize_stacked(ms, x, x_gs)
+        wq, sw = ops.nvfp4_quantize_stacked(w_ms, w, w_gs)
+        sw3 = sw[: E * N].view(E, N, -1)
+        gs = torch.reciprocal(x_gs * w_gs)
+        r_sx, r_sw = sx, sw3
+    wq3 = wq.view(torch.uint8).view(E, N, K // 2)
+    xq8 = xq.view(torch.uint8)
+    y_ref = torch.empty((tokens, N), dtype=torch.bfloat16, device="cuda")
+    ours_fn = lambda i: ops.f4f4bf16_grouped_stacked(xq8, wq3, sx, sw3, ms, gs, starts, use_mx=mx)
+    ref_fn = lambda i: ref.f4f4bf16_grouped_stacked(xq8.view(f4), wq3.view(f4), r_sx, r_sw, ms, gs, starts, y_ref)
+    ours, theirs = race_pair(ours_fn, ref_fn, 1, iters, warmup)
+    y = ours_fn(0)
+    ref_fn(0)
+    torch.cuda.synchronize()
+    flops = 2.0 * tokens * N * K
+    return {"case": f"f4f4bf16_grouped_stacked ({'MXFP4' if mx else 'NVFP4'}) E={E} tokens={tokens} N={N} K={K} (Zipf 1.2, two empty experts)",
+            "ours_us": ours, "ref_us": theirs, "ours_tflops": flops / ours / 1e6, "ref_tflops": flops / theirs / 1e6,
+            "ours_over_ref_speed": theirs / ours, "ref_instance": "grouped_256_256_256_2_1_1", **compare(y, y_ref)}
+
+
+def race_kgrouped_mxfp4(ops, ref, M, N, k_sizes, iters, warmup):
+    """K-grouped ("2D-2D") MXFP4 GEMM against the same reference instance through its offsets path."""
+    e8, f4 = getattr(torch, "float8_e8m0fnu"), getattr(torch, "float4_e2m1fn_x2")
+    xqs, wqs, xss, wss = [], [], [], []
+    for i, kg in enumerate(k_sizes):
+        if kg == 0:
+            continue
+        q, s = ops.quantize_mx4(randn((M, kg), 0.1, seed=50 + i), 32)
+        xqs.append(q)
+        xss.append(s.view(torch.uint8).reshape(-1))
+        q, s = ops.quantize_mx4(randn((N, kg), 0.01, seed=70 + i), 32)
+        wqs.append(q)
+        wss.append(s.view(torch.uint8).reshape(-1))
+    xq, wq = torch.cat(xqs, dim=1).contiguous(), torch.cat(wqs, dim=1).contiguous()
+    sx, sw = torch.cat(xss).view(e8), torch.cat(wss).view(e8)
+    offs = torch.tensor(k_sizes, device="cuda").cumsum(0).to(torch.int32)
+    G = len(k_sizes)
+    y = torch.empty((G, M, N), dtype=torch.bfloat16, device="cuda")
+    y_ref = torch.zeros((G, M, N), dtype=torch.bfloat16, device="cuda")
+    ours_fn = lambda i: ops.f4f4bf16_grouped_mm(xq, wq.transpose(-2, -1), sx, sw, offs, y)
+    ref_fn = lambda i: ref.f4f4bf16_grouped_mm(xq.view(f4), wq.view(f4), sx, sw, offs, None, y_ref)
+    ours, theirs = race_pair(ours_fn, ref_fn, 1, iters, warmup)
+    ours_fn(0)
+    ref_fn(0)
+    torch.cuda.synchronize()
+    live = [g for g, kg in enumerate(k_sizes) if kg]          # the reference leaves the output of an empty group untouched
+    flops = 2.0 * M * N * sum(k_sizes)
+    return {"case": f"f4f4bf16_grouped_mm 2D-2D (MXFP4) M={M} N={N} K groups={k_sizes}", "ours_us": ours, "ref_us": theirs,
+            "ours_tflops": flops / ours / 1e6, "ref_tflops": flops / theirs / 1e6, "ours_over_ref_speed": theirs / ours,
+            "ref_instance": "grouped_256_256_256_2_1_1", **compare(y[live], y_ref[live])}
+
+
 def race_quantize(ops, ref_quant, M, K, iters, warmup):
     nv = variants(M * K * 2)
     xs = [randn((M, K), seed=30 + i) for i in range(nv)]
@@ -248,6 +328,11 @@ def main():
         emit(race_nvfp4(ops, ref, M, 28672, 8192, 4 * args.iters, args.warmup))
     if hasattr(ref, "f4f4bf16_large_mx") and hasattr(torch, "float8_e8m0fnu"):
         emit(race_mxfp4(ops, ref, 8192, 8192, 8192, args.iters, args.warmup))
+    if hasattr(ref, "f4f4bf16_grouped_stacked") and hasattr(torch, "float8_e8m0fnu"):
+        for mx in (False, True):
+            emit(race_grouped_fp4(ops, ref, 16, 16384, 16384, 5120, mx, args.iters, args.warmup))
+        emit(race_kgrouped_mxfp4(ops, ref, 5120, 8192, [4096] * 4, args.iters, args.warmup))
+        emit(race_kgrouped_mxfp4(ops, ref, 2048, 2048, [2048, 0, 6144, 992, 8192], args.iters, args.warmup))
     pyref = os.path.join(HERE, "_ref", "pyref")
     if os.path.isdir(pyref):
         os.environ["MSLK_PYTHON_ONLY"] = "1"

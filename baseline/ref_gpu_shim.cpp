@@ -22,6 +22,11 @@ at::Tensor f8f8bf16_rowwise_grouped_256_256_128_2_1_1_10_f(at::Tensor XQ, at::Te
                                                            std::optional<at::Tensor> zero_start_index_M,
                                                            std::optional<at::Tensor> M_sizes);
 // csrc/gemm/cutlass/f4f4bf16/f4f4bf16_manifest.cuh
+// csrc/gemm/cutlass/f4f4bf16_grouped/f4f4bf16_grouped_manifest.cuh
+at::Tensor f4f4bf16_grouped_256_256_256_2_1_1(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor w_scale,
+                                              at::Tensor output, std::optional<at::Tensor> offsets,
+                                              std::optional<at::Tensor> M_sizes, std::optional<at::Tensor> global_scale,
+                                              std::optional<at::Tensor> starting_row_after_padding);
 at::Tensor f4f4bf16_256_256_2_1_1(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor w_scale, at::Tensor output,
                                   std::optional<at::Tensor> global_scale, int64_t mxfp4_block_size);
 at::Tensor f4f4bf16_256_128_4_1_1(at::Tensor XQ, at::Tensor WQ, at::Tensor x_scale, at::Tensor w_scale, at::Tensor output,
@@ -52,6 +57,17 @@ Tensor f4_large(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor out, Tensor g
 Tensor f4_large_mx(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor out) {
   return mslk::gemm::f4f4bf16_256_256_2_1_1(XQ, WQ, xs, ws, out, std::nullopt, 32);
 }
+// grouped FP4 as f4f4bf16_grouped_stacked calls its kernel (csrc/gemm/cutlass/f4f4bf16_grouped.cu:321-374); no global
+// scale = MXFP4
+Tensor f4_grouped_stacked(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor M_sizes, std::optional<Tensor> gs,
+                          Tensor starting_row_after_padding, Tensor out) {
+  return mslk::gemm::f4f4bf16_grouped_256_256_256_2_1_1(XQ, WQ, xs, ws, out, std::nullopt, M_sizes, gs,
+                                                        starting_row_after_padding);
+}
+// ... and as f4f4bf16_grouped_mm does (:376-475): WQ already transposed to [G, N, K/2] (2D-3D) or [N, total_K/2] (2D-2D)
+Tensor f4_grouped_mm(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor offsets, std::optional<Tensor> gs, Tensor out) {
+  return mslk::gemm::f4f4bf16_grouped_256_256_256_2_1_1(XQ, WQ, xs, ws, out, offsets, std::nullopt, gs, std::nullopt);
+}
 Tensor f4_small(Tensor XQ, Tensor WQ, Tensor xs, Tensor ws, Tensor out, Tensor gs) {
   return mslk::gemm::f4f4bf16_256_128_4_1_1(XQ, WQ, xs, ws, out, gs, 32);
 }
@@ -64,5 +80,7 @@ TORCH_LIBRARY(mslk_ref, m) {
   m.def("f8f8bf16_rowwise_grouped_stacked(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor M_sizes, Tensor(a!) output) -> Tensor", grouped_stacked);
   m.def("f4f4bf16_large(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output, Tensor global_scale) -> Tensor(a!)", f4_large);
   m.def("f4f4bf16_large_mx(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output) -> Tensor(a!)", f4_large_mx);
+  m.def("f4f4bf16_grouped_stacked(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor M_sizes, Tensor? global_scale, Tensor starting_row_after_padding, Tensor(a!) output) -> Tensor(a!)", f4_grouped_stacked);
+  m.def("f4f4bf16_grouped_mm(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor offsets, Tensor? global_scale, Tensor(a!) output) -> Tensor(a!)", f4_grouped_mm);
   m.def("f4f4bf16_small(Tensor XQ, Tensor WQ, Tensor x_scale, Tensor w_scale, Tensor(a!) output, Tensor global_scale) -> Tensor(a!)", f4_small);
 }

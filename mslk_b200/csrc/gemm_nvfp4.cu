@@ -635,6 +635,31 @@ int run_fp4_kgrouped(const char *name, const void *xq, const void *wq, const voi
   p.alpha_per_group = global_scale ? 1 : 0;
   p.a_box_rows = M < kBM ? static_cast<int>((M + 7) / 8 * 8) : kBM;
   const int sms = sm_count();
+  static const int force = [] {
+    const char *e = getenv("MSLK_B200_NVFP4_KERNEL");  // "1cta" | "2cta": tuning aid, default = heuristic
+    return !e ? 0 : (e[0] == '2' ? 2 : 1);
+  }();
+  // CTA pairs (256 x 256 tiles) when there are enough such tiles to occupy every pair of SMs
+  const int64_t pair_tiles = G * ((M + 255) / 256) * ((N + 255) / 256);
+  if (force == 2 || (force == 0 && M > 128 && G <= nvfp4_pair::kPairMaxGroups && pair_tiles >= sms / 2)) {
+    nvfp4_pair::PairParams pp{};
+    pp.alpha = global_scale;
+    pp.y = static_cast<__nv_bfloat16 *>(y);
+    pp.status = status;
+    pp.M = static_cast<int>(M);
+    pp.N = static_cast<int>(N);
+    pp.K = static_cast<int>(K);
+    pp.scale_mode = scale_mode;
+    pp.k_end_offsets = k_end_offsets;
+    pp.sfa_atoms = p.sfa_atoms;
+    pp.sfb_atoms = p.sfb_atoms;
+    pp.G = static_cast<int>(G);
+    pp.alpha_per_group = p.alpha_per_group;
+    if (G <= nvfp4_pair::kPairMaxGroups) {
+      const int rc = nvfp4_pair::launch_pair_kernel(xq, wq, x_scale, w_scale, pp, st);
+      if (rc >= 0) return rc;   // -1: pairs unavailable, fall through to one CTA per tile
+    }
+  }
   const int64_t m_tiles = (M + kBM - 1) / kBM;
   const int bn = (G * m_tiles * ((N + 255) / 256) >= 2 * sms) ? 256 : 128;
   CUtensorMap ta, tb;

@@ -90,6 +90,45 @@ __device__ __forceinline__ long long clock_now() {
   return t;
 }
 
+// What the three roles need to know about one 256 x 256 tile.
+struct PairTile {
+  int g;                   // group (alpha index)
+  int row0, rows, n0;      // first output row (stacked), rows that belong to the group, first output column
+  int a_row, b_row;        // row coordinates of the tile in the tensor maps of A and B
+  int kbyte0;              // first packed K byte of the tile's K range in both maps
+  int k_len, kbs, ncb;     // K elements, K blocks of 256, scale atoms per 128-row block of that range
+  int sfa_atom, sfb_atom;  // atom index of the tile's first 128-row block of A / of B at its first K block
+};
+
+// K-grouped problems: tiles of a group are consecutive, columns fastest; k_start / atom_start are the group tables
+// (first K element and first scale atom per 128-row block of every group).
+__device__ __noinline__ bool pair_kgroup_tile(const int *k_start, const int *atom_start, int reject, int G, int M, int N,
+                                              int tile, PairTile &t) {
+  const int m_tiles = (M + kPairRows - 1) / kPairRows, n_tiles = (N + kPairBN - 1) / kPairBN;
+  const int per_group = m_tiles * n_tiles;
+  if (tile >= G * per_group) return false;
+  t.g = tile / per_group;
+  const int r = tile - t.g * per_group;
+  const int m_tile = r / n_tiles, n_tile = r - m_tile * n_tiles;
+  const int k0 = k_start[t.g];
+  int kg = k_start[t.g + 1] - k0;
+  if (((k0 | kg) & 31) || reject) kg = 0;   // rejected (the prologue has recorded kStatusBadGroupOffset): zeros
+  const int atom0 = atom_start[t.g];
+  t.ncb = atom_start[t.g + 1] - atom0;
+  t.row0 = t.g * M + m_tile * kPairRows;     // y is [G, M, N]
+  t.rows = min(kPairRows, M - m_tile * kPairRows);
+  t.n0 = n_tile * kPairBN;
+  t.a_row = m_tile * kPairRows;
+  t.b_row = t.n0;
+  t.kbyte0 = k0 / 2;
+  t.k_len = kg;
+  t.kbs = (kg + kBKElems - 1) / kBKElems;
+  t.sfa_atom = atom0 * ((M + kBM - 1) / kBM) + m_tile * 2 * t.ncb;
+  t.sfb_atom = atom0 * ((N + kBM - 1) / kBM) + n_tile * 2 * t.ncb;
+  return true;
+}
+
+template <bool KG>
 __global__ void __launch_bounds__(kNumThreads, 1)
     gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                            const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -139,13 +178,31 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     gp.G = p.G;
     gp.total_m = p.M;
     gp.group_m = p.M;   // dense: one group of all rows (only read when both size arrays are null)
-    gemm_f8::build_group_tables(gp, n_tiles, kPairRows, lane, S.row_start, S.tile_start);
-    __syncwarp();
-    if (lane == 0) {
-      int blocks = 0;
-      for (int g = 0; g < p.G; ++g) {
-        S.blk_start[g] = p.sfa_row_start ? static_cast<int>(p.sfa_row_start[g] / kBM) : blocks;
-        blocks += (S.row_start[g + 1] - S.row_start[g] + kBM - 1) / kBM;
+    if constexpr (KG) {
+      // the same prefix sums over the K extents: row_start = first K element of every group, tile_start = scale
+      // atoms (of 4 scales per row) in front of it
+      gp.end_offsets = p.k_end_offsets;
+      gp.total_m = p.K;
+      gemm_f8::build_group_tables(gp, 1, p.scale_mode == kScaleMxfp4 ? 128 : 64, lane, S.row_start, S.tile_start);
+      bool bad = false;
+      for (int g = lane; g < p.G; g += 32) {
+        const int e = p.k_end_offsets[g];
+        bad |= (e & 31) != 0 || e < (g > 0 ? p.k_end_offsets[g - 1] : 0) || e > p.K;
+      }
+      __syncwarp();
+      const long long atoms = S.tile_start[p.G];
+      const bool too_short = atoms * ((p.M + kBM - 1) / kBM) > p.sfa_atoms || atoms * n_row_blocks_b > p.sfb_atoms;
+      if (lane == 0) S.blk_start[0] = too_short ? 1 : 0;   // reject flag (the block table is not used in this mode)
+      if ((bad || too_short) && blockIdx.x == 0) atomicOr(p.status, kStatusBadGroupOffset);
+    } else {
+      gemm_f8::build_group_tables(gp, n_tiles, kPairRows, lane, S.row_start, S.tile_start);
+      __syncwarp();
+      if (lane == 0) {
+        int blocks = 0;
+        for (int g = 0; g < p.G; ++g) {
+          S.blk_start[g] = p.sfa_row_start ? static_cast<int>(p.sfa_row_start[g] / kBM) : blocks;
+          blocks += (S.row_start[g + 1] - S.row_start[g] + kBM - 1) / kBM;
+        }
       }
     }
   }
@@ -154,9 +211,32 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   cluster_sync_all();  // the peer's barriers are initialised before anything is signalled on them
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
-  const int num_tiles = S.tile_start[p.G];
+  const int num_tiles = KG ? p.G * ((p.M + kPairRows - 1) / kPairRows) * n_tiles : S.tile_start[p.G];
   gemm_f8::Scheduler sched{S.tile_start, S.row_start, p.G, p.N, n_tiles, kPairBN, kPairRows, p.band, 0};
-  gemm_f8::Tile t;
+  PairTile t;
+  auto next_tile = [&](int tile) -> bool {
+    if constexpr (KG) {
+      return pair_kgroup_tile(S.row_start, S.tile_start, S.blk_start[0], p.G, p.M, p.N, tile, t);
+    } else {
+      gemm_f8::Tile st;
+      if (!sched.get(tile, st)) return false;
+      const int g = sched.g;
+      t.g = g;
+      t.row0 = st.row0;
+      t.rows = st.rows;
+      t.n0 = st.n0;
+      t.a_row = st.row0;
+      t.b_row = st.wrow0;
+      t.kbyte0 = 0;
+      t.k_len = p.K;
+      t.kbs = k_blocks;
+      t.ncb = p.ncb;
+      // 128-row block of the tile's rows in the padded scale matrix of A, and of its columns in that of B
+      t.sfa_atom = (S.blk_start[g] + (st.row0 - S.row_start[g]) / kBM) * p.ncb;
+      t.sfb_atom = (g * n_row_blocks_b + st.n0 / kBM) * p.ncb;
+      return true;
+    }
+  };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (both CTAs)
@@ -166,13 +246,12 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       bool ok = true;
       long long t_empty = 0;
       const int apk = p.scale_mode == kScaleMxfp4 ? 2 : kMmasPerStage;   // scale atoms per K block and 128-row block
-      for (int tile = pair_id; ok && sched.get(tile, t); tile += num_pairs) {
-        const int g = sched.g;
-        const int a_row = t.row0 + static_cast<int>(rank) * kBM;        // first of this CTA's 128 rows of A
-        // 128-row block of those rows in the padded scale matrix of A, and of the tile's columns in that of B
-        const int sfa_block = S.blk_start[g] + (t.row0 - S.row_start[g]) / kBM + static_cast<int>(rank);
-        const int sfb_block = g * n_row_blocks_b + t.n0 / kBM;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+      for (int tile = pair_id; ok && next_tile(tile); tile += num_pairs) {
+        const int a_row = t.a_row + static_cast<int>(rank) * kBM;        // first of this CTA's 128 rows of A
+        const int b_row = t.b_row + static_cast<int>(rank) * kBM;        // ... and of B
+        const int sfa_atom = t.sfa_atom + static_cast<int>(rank) * t.ncb;   // this CTA's 128-row block of A's scales
+        const int sfb_atom = t.sfb_atom, ncb = t.ncb, kbyte0 = t.kbyte0, kbs = t.kbs;
+        for (int kb = 0; kb < kbs; ++kb) {
           const long long t0 = timed ? clock_now() : 0;
           if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
             ok = false;
@@ -188,12 +267,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           // count is the same for every stage
           // (the scale boxes hold apk atoms per 128-row block: four, or two when one scale covers 32 elements)
           if (leader) mbar_arrive_expect_tx(&S.full[stage], 2 * (kStageA + kStageB + 3 * apk * kAtomBytes));
-          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * kBKBytes, a_row);
-          tma_load_2d_pair(sb, &tmap_b, leader_full, kb * kBKBytes, t.wrow0 + static_cast<int>(rank) * kBM);
-          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, sfa_block * p.ncb + apk * kb);
-          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, sfb_block * p.ncb + apk * kb);
-          tma_load_2d_pair(ssfb + kMmasPerStage * kAtomBytes, &tmap_sfb, leader_full, 0,
-                           (sfb_block + 1) * p.ncb + apk * kb);
+          tma_load_2d_pair(sa, &tmap_a, leader_full, kbyte0 + kb * kBKBytes, a_row);
+          tma_load_2d_pair(sb, &tmap_b, leader_full, kbyte0 + kb * kBKBytes, b_row);
+          tma_load_2d_pair(ssfa, &tmap_sfa, leader_full, 0, sfa_atom + apk * kb);
+          tma_load_2d_pair(ssfb, &tmap_sfb, leader_full, 0, sfb_atom + apk * kb);
+          tma_load_2d_pair(ssfb + kMmasPerStage * kAtomBytes, &tmap_sfb, leader_full, 0, sfb_atom + ncb + apk * kb);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1;
@@ -230,7 +308,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (timed) t_acc += clock_now() - t0;
         }
         tc_fence_after();
-        for (int kb = 0; kb < k_blocks; ++kb, ++n) {
+        int kbs = k_blocks, k_len = p.K, ncb = p.ncb;
+        if constexpr (KG) {
+          next_tile(tile);
+          kbs = t.kbs;
+          k_len = t.k_len;
+          ncb = t.ncb;
+        }
+        for (int kb = 0; kb < kbs; ++kb, ++n) {
           const long long t0 = timed ? clock_now() : 0;
           if (!mbar_wait(&S.full[stage], phase, abort_flag, p.status, kStatusMmaTimeout)) {
             ok = false;
@@ -245,7 +330,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (p.scale_mode == kScaleMxfp4) {
             // one scale per 32 K-elements: an atom holds the scales of TWO instructions, which pick their two bytes
             // of the scale column through the scale-id fields of the descriptor
-            const int mmas = min(kMmasPerStage, (p.K - kb * kBKElems + 63) / 64);
+            const int mmas = min(kMmasPerStage, (k_len - kb * kBKElems + 63) / 64);
             const int atoms = (mmas + 1) / 2;
             if (mmas == kMmasPerStage) {
 #pragma unroll
@@ -284,7 +369,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             continue;
           }
           const uint32_t idesc = kIdesc | (p.scale_mode == kScaleMxfp4_16 ? kIdescScaleE8M0 : 0u);
-          const int atoms = min(kMmasPerStage, p.ncb - kMmasPerStage * kb);
+          const int atoms = min(kMmasPerStage, ncb - kMmasPerStage * kb);
           if (atoms == kMmasPerStage) {
 #pragma unroll
             for (int k = 0; k < kMmasPerStage; ++k) {
@@ -336,8 +421,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     const int half = (warp - 2) >> 2;          // which 128 of the tile's 256 columns
     uint8_t *buf = out_stage + (warp - 2) * kOutSlabBytes;
     int local = 0;
-    for (int tile = pair_id; sched.get(tile, t); tile += num_pairs, ++local) {
-      const float alpha = p.alpha ? p.alpha[p.alpha_per_group ? sched.g : 0] : 1.0f;   // the MX formats have no global scale
+    for (int tile = pair_id; next_tile(tile); tile += num_pairs, ++local) {
+      const float alpha = p.alpha ? p.alpha[p.alpha_per_group ? t.g : 0] : 1.0f;   // the MX formats have no global scale
+      const bool empty_group = KG && t.k_len == 0;   // nothing was accumulated: the tile is zero
       const int slab0 = static_cast<int>(rank) * kBM + quad * 32;   // first row of this warp's slab inside the tile
       const int row0 = t.row0 + slab0;
       const int col0 = t.n0 + half * 128;
@@ -353,7 +439,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       auto pack = [&](const uint32_t (&r)[32], int c) {
 #pragma unroll
         for (int j = 0; j < 32; j += 2)
-          packed[c * 16 + j / 2] = pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
+          packed[c * 16 + j / 2] =
+              empty_group ? 0u : pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
       };
       tmem_ld_32x32(taddr, ra);
       tmem_ld_wait();
@@ -423,8 +510,9 @@ std::atomic<unsigned long long *> g_timers{nullptr};
 
 void set_pipe_timers(unsigned long long *dev_counters) { g_timers.store(dev_counters); }
 
-int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
-                       cudaStream_t st) {
+template <bool KG>
+int launch_pair_kernel_t(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
+                         cudaStream_t st) {
   static std::atomic<int> max_pairs[64];   // zero-initialised; a racing first call computes the same value
   int dev = 0;
   if (int rc = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return rc;
@@ -443,13 +531,13 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   cfg.numAttrs = 1;
 
   if (max_pairs[dev] == 0) {
-    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (int rc = check_cuda(cudaFuncSetAttribute(gemm_nvfp4_pair_kernel<KG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  static_cast<int>(kSmemBytes)),
                             "cudaFuncSetAttribute(gemm_nvfp4_pair)"))
       return rc;
     cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
     int n = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_nvfp4_pair_kernel, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_nvfp4_pair_kernel<KG>, &cfg);
     if (e != cudaSuccess || n <= 0) {
       cudaGetLastError();
       max_pairs[dev] = -1;
@@ -461,8 +549,9 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
 
   const bool grouped = p.m_sizes || p.end_offsets;
   if (p.G < 1 || p.G > kPairMaxGroups) return -1;
-  // upper bound of the 256-row blocks: one ragged block per group
-  const int64_t m_tiles = (static_cast<int64_t>(p.M) + kPairRows - 1) / kPairRows + (grouped ? p.G : 0);
+  // upper bound of the 256-row blocks: one ragged block per group (K-grouped: every group has all of them)
+  const int64_t m_tiles = KG ? static_cast<int64_t>(p.G) * ((static_cast<int64_t>(p.M) + kPairRows - 1) / kPairRows)
+                             : (static_cast<int64_t>(p.M) + kPairRows - 1) / kPairRows + (grouped ? p.G : 0);
   const int64_t n_tiles = (static_cast<int64_t>(p.N) + kPairBN - 1) / kPairBN;
   const int64_t tiles = m_tiles * n_tiles;
   const int64_t mp = max_pairs[dev].load();
@@ -473,20 +562,25 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   // holds M + 127 G rows), B holds G blocks of roundup(N, 128) rows
   const uint64_t a_blocks = grouped ? (static_cast<uint64_t>(p.M) + 127ull * p.G) / kBM : (static_cast<uint64_t>(p.M) + kBM - 1) / kBM;
   const uint64_t b_blocks = static_cast<uint64_t>(p.G) * ((static_cast<uint64_t>(p.N) + kBM - 1) / kBM);
+  // K-grouped: both operands are plain [rows, K] matrices, the scale tensors are as long as the caller says
+  const uint64_t b_rows = KG ? static_cast<uint64_t>(p.N) : static_cast<uint64_t>(p.G) * p.N;
+  const uint64_t a_atoms = KG ? static_cast<uint64_t>(p.sfa_atoms) : a_blocks * p.ncb;
+  const uint64_t b_atoms = KG ? static_cast<uint64_t>(p.sfb_atoms) : b_blocks * p.ncb;
+  const uint64_t y_rows = KG ? static_cast<uint64_t>(p.G) * p.M : static_cast<uint64_t>(p.M);
   CUtensorMap ta, tb, tsa, tsb;
   if (int rc = make_tmap_2d_bytes(&ta, xq, kbytes, p.M, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
-  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, static_cast<uint64_t>(p.G) * p.N, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  if (int rc = make_tmap_2d_bytes(&tb, wq, kbytes, b_rows, kbytes, kBKBytes, kBM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   // scale buffers as [atoms, 128 words]: a box holds the atoms of one K block of one 128-row block
   const uint32_t apk = p.scale_mode == kScaleMxfp4 ? 2 : kMmasPerStage;   // scale atoms of one K block
-  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, apk)) return rc;
-  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_blocks * p.ncb, kAtomBytes, kAtomBytes / 4, apk)) return rc;
+  if (int rc = make_tmap_2d_u32(&tsa, x_scale, kAtomBytes / 4, a_atoms, kAtomBytes, kAtomBytes / 4, apk)) return rc;
+  if (int rc = make_tmap_2d_u32(&tsb, w_scale, kAtomBytes / 4, b_atoms, kAtomBytes, kAtomBytes / 4, apk)) return rc;
 
   PairParams q = p;
   // TMA stores need a 16-byte aligned base and row pitch; otherwise the epilogue stores element by element
   CUtensorMap ty;
   q.tma_store = ((reinterpret_cast<uintptr_t>(p.y) & 15u) == 0 && p.N % 8 == 0) ? 1 : 0;
   if (q.tma_store) {
-    if (int rc = make_tmap_2d_bf16(&ty, p.y, p.N, p.M, static_cast<uint64_t>(p.N) * 2, kOutCols, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_tmap_2d_bf16(&ty, p.y, p.N, y_rows, static_cast<uint64_t>(p.N) * 2, kOutCols, 32, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   } else {
     ty = ta;   // never dereferenced
@@ -504,7 +598,13 @@ int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, cons
   }
   q.timers = g_timers.load();
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel, ta, tb, tsa, tsb, ty, q), "f4f4bf16 pair launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel<KG>, ta, tb, tsa, tsb, ty, q), "f4f4bf16 pair launch");
+}
+
+int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
+                       cudaStream_t st) {
+  return p.k_end_offsets ? launch_pair_kernel_t<true>(xq, wq, x_scale, w_scale, p, st)
+                         : launch_pair_kernel_t<false>(xq, wq, x_scale, w_scale, p, st);
 }
 
 }  // namespace nvfp4_pair

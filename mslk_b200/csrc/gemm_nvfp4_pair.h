@@ -27,6 +27,11 @@ struct PairParams {
   const int64_t *m_sizes;
   const int32_t *end_offsets;
   const int64_t *sfa_row_start;
+  // K-grouped problems (the "2D-2D" form): X [M, K], W [N, K], group g contracting its own K range into y[g] of a
+  // [G, M, N] output: int32 END offsets along K (multiples of 32), one scale block per group, and the 512-byte atoms the
+  // two scale tensors hold.  Null / 0 for every other form.
+  const int32_t *k_end_offsets;
+  long long sfa_atoms, sfb_atoms;
   int G;
   int alpha_per_group;
   unsigned long long *timers;   // optional: [0] ns the MMA lane waited for operand stages, [1] for a free accumulator,

@@ -200,7 +200,8 @@ def _kgrouped_case(ops, M, N, k_sizes, nvfp4, seed):
 
 @pytest.mark.parametrize("nvfp4", [False, True])
 @pytest.mark.parametrize("M,N,k_sizes", [(256, 256, [2048]), (500, 1024, [2048] * 4), (200, 384, [256, 0, 800, 992, 32]),
-                                         (1000, 2048, [3584] * 3), (64, 136, [96, 4096])])
+                                         (1000, 2048, [3584] * 3), (64, 136, [96, 4096]),
+                                         (600, 1536, [256, 0, 800, 992, 32, 4096]), (2048, 2048, [2048, 0, 6144, 992, 8192])])
 def test_grouped_mm_2d2d(ops, M, N, k_sizes, nvfp4):
     """f4f4bf16_grouped_mm with 2D XQ and 2D WQ (test/gemm/gemm_test.py:2731-2790): groups along K, out [G, M, N];
     ragged and empty groups beside the reference's equal ones."""
@@ -226,7 +227,10 @@ def test_grouped_mm_2d2d(ops, M, N, k_sizes, nvfp4):
         else:
             y_ref = oracle.gemm_mx4_torch(xqs[g], wqs[g], xss[g], wss[g], 32)
         assert_sharp_bf16(out[g], y_ref, f"2D-2D group {g} of {k_sizes} nvfp4={nvfp4}")
-        torch.testing.assert_close(out[g], (xs[g] @ ws[g].T).to(torch.bfloat16), atol=8.0e-2, rtol=8.0e-2)
+        # the reference's bound against the UNQUANTIZED product holds up to its largest K (3584); the quantization noise
+        # of a sum grows with sqrt(K), so longer groups get that factor
+        tol = 8.0e-2 * max(1.0, (kg / 3584.0) ** 0.5)
+        torch.testing.assert_close(out[g], (xs[g] @ ws[g].T).to(torch.bfloat16), atol=tol, rtol=tol)
     assert _status() == 0
 
 
