@@ -428,35 +428,40 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const int row0 = t.row0 + slab0;
       const int col0 = t.n0 + half * 128;
       const int slab_rows = min(32, t.rows - slab0);                // rows of the slab that belong to the tile's group (<= 0: none)
+      const long long te0 = timed ? clock_now() : 0;
       const bool got = mbar_wait(&S.tmem_full, local & 1, abort_flag, p.status, kStatusEpilogueTimeout);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
+      const long long te1 = timed ? clock_now() : 0;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * 128);
       // drain this warp's 128 columns (scaled, packed to bf16) with the next load in flight while a chunk is
       // packed, and hand the accumulator back before anything is stored
+      // drain this warp's 128 columns with all four loads in flight at once, hand the accumulator back as soon as
+      // they have landed, and only then scale and pack (two fp32 registers become one packed pair in place)
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld_32x32(taddr, r0);
+      tmem_ld_32x32(taddr + 32, r1);
+      tmem_ld_32x32(taddr + 64, r2);
+      tmem_ld_32x32(taddr + 96, r3);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty), 0));
+      if (timed && leader && warp == 2 && lane == 0) {
+        atomicAdd(p.timers + 4, static_cast<unsigned long long>(clock_now() - te1));   // drain: accumulator ready -> handed back
+        atomicAdd(p.timers + 5, static_cast<unsigned long long>(te1 - te0));           // waiting for the accumulator
+      }
       uint32_t packed[64];
-      uint32_t ra[32], rb[32];
       auto pack = [&](const uint32_t (&r)[32], int c) {
 #pragma unroll
         for (int j = 0; j < 32; j += 2)
           packed[c * 16 + j / 2] =
               empty_group ? 0u : pack_bf16x2(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha);
       };
-      tmem_ld_32x32(taddr, ra);
-      tmem_ld_wait();
-      tmem_ld_32x32(taddr + 32, rb);
-      pack(ra, 0);
-      tmem_ld_wait();
-      tmem_ld_32x32(taddr + 64, ra);
-      pack(rb, 1);
-      tmem_ld_wait();
-      tmem_ld_32x32(taddr + 96, rb);
-      pack(ra, 2);
-      tmem_ld_wait();
-      pack(rb, 3);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty), 0));
+      pack(r0, 0);
+      pack(r1, 1);
+      pack(r2, 2);
+      pack(r3, 3);
       if (p.tma_store && slab_rows == 32) {
 #pragma unroll
         for (int s2 = 0; s2 < 2; ++s2) {

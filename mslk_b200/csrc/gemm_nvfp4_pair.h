@@ -34,8 +34,9 @@ struct PairParams {
   long long sfa_atoms, sfb_atoms;
   int G;
   int alpha_per_group;
-  unsigned long long *timers;   // optional: [0] ns the MMA lane waited for operand stages, [1] for a free accumulator,
-                                // [2] ns of its whole loop, [3] ns the producer of the leader waited for free stages (sums over pairs)
+  unsigned long long *timers;   // optional SM-cycle counters (sums over pairs): [0] the MMA lane waiting for operand stages,
+                                // [1] for a free accumulator, [2] its whole loop, [3] the leader's producer waiting for free
+                                // stages, [4] the leader's first epilogue warp draining the accumulator, [5] waiting for it
 };
 
 // Dense problems and grouped ones with at most kPairMaxGroups groups.  Returns 0 on success, a non-zero code after recording an error, or -1 when
@@ -43,7 +44,7 @@ struct PairParams {
 int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
                        cudaStream_t st);
 
-// Diagnostics: device array of four 64-bit counters the kernel adds its wait cycles to (nullptr = off).
+// Diagnostics: device array of six 64-bit counters the kernel adds its wait cycles to (nullptr = off).
 void set_pipe_timers(unsigned long long *dev_counters);
 
 }  // namespace nvfp4_pair
