@@ -182,6 +182,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tmem_alloc(&S.tmem_base, C::kTmemCols);
     tmem_relinquish();
   }
+  // everything above touched shared and tensor memory only: it may run under the tail of the previous kernel of the
+  // stream; from here on global memory is read (group sizes, operands, scales) and written
+  griddep_wait();
+  griddep_launch_dependents();
   if (warp == 2) {
     GemmParams gp{};
     gp.m_sizes = p.m_sizes;
@@ -500,8 +504,15 @@ int launch(const CUtensorMap &ta, const CUtensorMap &tb, const Fp4Params &p, int
       return rc;
     attr_set[dev] = true;
   }
-  gemm_nvfp4_kernel<BN, KG><<<grid, kNumThreads, smem, st>>>(ta, tb, p);
-  return check_cuda(cudaGetLastError(), "f4f4bf16 launch");
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_attribute(&attr[0]);   // the prologue may overlap the tail of the previous kernel of the stream
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_kernel<BN, KG>, ta, tb, p), "f4f4bf16 launch");
 }
 
 }  // namespace

@@ -170,6 +170,10 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     tmem_alloc_pair(&S.tmem_base, kTmemCols);
     tmem_relinquish_pair();
   }
+  // everything above touched shared and tensor memory only: it may run under the tail of the previous kernel of the
+  // stream; from here on global memory is read (group sizes, operands, scales) and written
+  griddep_wait();
+  griddep_launch_dependents();
   if (warp == 2) {
     // group tables: rows and tiles as in the FP8 kernels, plus the 128-row scale blocks in front of every group
     gemm_f8::GemmParams gp{};
@@ -524,7 +528,7 @@ int launch_pair_kernel_t(const void *xq, const void *wq, const void *x_scale, co
   if (dev < 0 || dev >= 64) return -1;
 
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
@@ -603,6 +607,7 @@ int launch_pair_kernel_t(const void *xq, const void *wq, const void *x_scale, co
   }
   q.timers = g_timers.load();
   cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.numAttrs = 1 + pdl_attribute(&attr[1]);   // the prologue may overlap the tail of the previous kernel of the stream
   return check_cuda(cudaLaunchKernelEx(&cfg, gemm_nvfp4_pair_kernel<KG>, ta, tb, tsa, tsb, ty, q), "f4f4bf16 pair launch");
 }
 
