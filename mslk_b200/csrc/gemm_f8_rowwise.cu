@@ -100,15 +100,40 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     fence_barrier_init();
     fence_proxy_async_smem();
   }
+  // Dense problems: the thread that has just initialised the barriers also issues the first stages of this CTA's first
+  // tile, before the CTA-wide barrier below -- the copies then fly while tensor memory is allocated and the other
+  // warps arrive (a microsecond on few-token shapes whose whole launch takes ten).  The group tables of a dense
+  // problem are two entries each, written here; every thread derives the number of stages issued early by itself.
+  const bool dense = p.G == 1 && p.m_sizes == nullptr && p.end_offsets == nullptr;
+  const int dense_tiles = ((p.total_m + kBM - 1) / kBM) * n_tiles;
+  const int pre = (dense && static_cast<int>(blockIdx.x) < dense_tiles) ? min(Cfg::kStages, k_blocks) : 0;
+  if (threadIdx.x == 0 && dense) {
+    S.row_start[0] = 0;
+    S.row_start[1] = p.total_m;
+    S.tile_start[0] = 0;
+    S.tile_start[1] = dense_tiles;
+    griddep_wait();   // the operands may come from the previous kernel of the stream
+    Scheduler first{S.tile_start, S.row_start, p.G, p.N, n_tiles, BN, kBM, kBandM, 0};
+    Tile t0;
+    if (pre > 0 && first.get(blockIdx.x, t0)) {
+      for (int kb = 0; kb < pre; ++kb) {
+        uint8_t *sa = ring + static_cast<size_t>(kb) * Cfg::kStageBytes;
+        mbar_arrive_expect_tx(&S.full[kb], p.a_box_rows * kBK + Cfg::kStageB);
+        tma_load_2d(sa, &tmap_a, &S.full[kb], kb * kBK, t0.row0);
+        tma_load_2d(sa + Cfg::kStageA, &tmap_b, &S.full[kb], kb * kBK, t0.wrow0);
+      }
+    }
+  }
   if (warp == 1) {
     tmem_alloc(&S.tmem_base, Cfg::kTmemCols);
     tmem_relinquish();
   }
-  // everything above touched shared and tensor memory only: it may run under the tail of the previous kernel
-  // of the stream; from here on global memory is read (group sizes, operands, scales) and written
+  // everything above touched shared and tensor memory only (and, after its own wait, the early copies): it may run
+  // under the tail of the previous kernel of the stream; from here on global memory is read (group sizes, operands,
+  // scales) and written
   griddep_wait();
   griddep_launch_dependents();
-  if (warp == 2) build_group_tables(p, n_tiles, kBM, lane, S.row_start, S.tile_start);
+  if (warp == 2 && !dense) build_group_tables(p, n_tiles, kBM, lane, S.row_start, S.tile_start);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -119,13 +144,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
-      int stage = 0;
-      uint32_t phase = 0;
-      long long issued = 0;
+      // the first `pre` stages of the first tile are already on their way (setup above)
+      int stage = pre == Cfg::kStages ? 0 : pre;
+      uint32_t phase = pre == Cfg::kStages ? 1u : 0u;
+      long long issued = pre;
       bool ok = true;
       Tile t;
+      int kb_first = pre;
       for (int tile = blockIdx.x; ok && sched.get(tile, t); tile += gridDim.x) {
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb_first; kb < k_blocks; ++kb) {
           if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) {
             ok = false;
             break;
@@ -141,6 +168,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             phase ^= 1;
           }
         }
+        kb_first = 0;
       }
       if (!ok) {
         // bounded drain: give copies already issued time to land before the CTA exits
