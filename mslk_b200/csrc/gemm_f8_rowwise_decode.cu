@@ -104,7 +104,16 @@ __global__ void __launch_bounds__(kNumThreads, 2)
     S.abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
+    // the first stages go out right away: the copies fly while tensor memory is allocated and the warps meet below
+    for (int kb = kb0; kb < kb0 + min(C::kStages, my_kb); ++kb) {
+      const int st = kb - kb0;
+      uint8_t *sw = ring + static_cast<size_t>(st) * C::kStageBytes;
+      mbar_arrive_expect_tx(&S.full[st], C::kStageW + p.x_box_rows * kBK);
+      tma_load_2d(sw, &tmap_w, &S.full[st], kb * kBK, n_tile * kWRows);
+      tma_load_2d(sw + C::kStageW, &tmap_x, &S.full[st], kb * kBK, 0);
+    }
   }
+  const int pre = min(C::kStages, my_kb);   // stages issued above
   if (warp == 1) {
     tmem_alloc(&S.tmem_base, C::kTmemCols);
     tmem_relinquish();
@@ -123,9 +132,9 @@ __global__ void __launch_bounds__(kNumThreads, 2)
 
   if (warp == 0) {
     if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      int stage = pre == C::kStages ? 0 : pre;
+      uint32_t phase = pre == C::kStages ? 1u : 0u;
+      for (int kb = kb0 + pre; kb < kb1; ++kb) {
         if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) break;
         uint8_t *sw = ring + static_cast<size_t>(stage) * C::kStageBytes;
         uint8_t *sx = sw + C::kStageW;

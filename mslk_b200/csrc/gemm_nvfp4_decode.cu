@@ -120,6 +120,27 @@ __global__ void __launch_bounds__(kNumThreads, 2)
     fence_barrier_init();
     fence_proxy_async_smem();
   }
+  // one stage: 128 weight rows, the token rows and the scale atoms of both for K block kb
+  auto issue_stage = [&](int kb, int stage) {
+    const uint8_t *sfw_row = p.sfw + static_cast<size_t>(n_tile) * p.ncb * kAtomBytes;
+    uint8_t *sw = ring + static_cast<size_t>(stage) * C::kStageBytes;
+    uint8_t *sx = sw + C::kStageW;
+    uint8_t *ssfw = sx + C::kStageX;
+    uint8_t *ssfx = ssfw + C::kStageSF;
+    // scale atoms (4 scales per row each: 64 K-elements, MXFP4 128) left in this K block of 256 elements
+    const int apk = p.scale_mode == kScaleMxfp4 ? 2 : 4;
+    const int atoms = min(apk, p.ncb - apk * kb);
+    const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
+    mbar_arrive_expect_tx(&S.full[stage], C::kStageW + p.x_box_rows * kBKBytes + 2 * sf_bytes);
+    tma_load_2d(sw, &tmap_w, &S.full[stage], kb * kBKBytes, n_tile * kWRows);
+    tma_load_2d(sx, &tmap_x, &S.full[stage], kb * kBKBytes, 0);
+    bulk_load_1d(ssfw, sfw_row + static_cast<size_t>(apk * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
+    bulk_load_1d(ssfx, p.sfx + static_cast<size_t>(apk * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
+  };
+  // the first stages go out right away: the copies fly while tensor memory is allocated and the warps meet below
+  const int pre = min(C::kStages, my_kb);
+  if (threadIdx.x == 0)
+    for (int i = 0; i < pre; ++i) issue_stage(kb0 + i, i);
   if (warp == 1) {
     tmem_alloc(&S.tmem_base, C::kTmemCols);
     tmem_relinquish();
@@ -139,24 +160,11 @@ __global__ void __launch_bounds__(kNumThreads, 2)
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (elect_one()) {  // one lane, chosen so that the compiler keeps the issue loop on the uniform datapath
-      int stage = 0;
-      uint32_t phase = 0;
-      const uint8_t *sfw_row = p.sfw + static_cast<size_t>(n_tile) * p.ncb * kAtomBytes;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      int stage = pre == C::kStages ? 0 : pre;
+      uint32_t phase = pre == C::kStages ? 1u : 0u;
+      for (int kb = kb0 + pre; kb < kb1; ++kb) {
         if (!mbar_wait(&S.empty[stage], phase ^ 1, abort_flag, p.status, kStatusProducerTimeout)) break;
-        uint8_t *sw = ring + static_cast<size_t>(stage) * C::kStageBytes;
-        uint8_t *sx = sw + C::kStageW;
-        uint8_t *ssfw = sx + C::kStageX;
-        uint8_t *ssfx = ssfw + C::kStageSF;
-        // scale atoms (4 scales per row each: 64 K-elements, MXFP4 128) left in this K block of 256 elements
-        const int apk = p.scale_mode == kScaleMxfp4 ? 2 : 4;
-        const int atoms = min(apk, p.ncb - apk * kb);
-        const uint32_t sf_bytes = static_cast<uint32_t>(atoms) * kAtomBytes;
-        mbar_arrive_expect_tx(&S.full[stage], C::kStageW + p.x_box_rows * kBKBytes + 2 * sf_bytes);
-        tma_load_2d(sw, &tmap_w, &S.full[stage], kb * kBKBytes, n_tile * kWRows);
-        tma_load_2d(sx, &tmap_x, &S.full[stage], kb * kBKBytes, 0);
-        bulk_load_1d(ssfw, sfw_row + static_cast<size_t>(apk * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
-        bulk_load_1d(ssfx, p.sfx + static_cast<size_t>(apk * kb) * kAtomBytes, sf_bytes, &S.full[stage]);
+        issue_stage(kb, stage);
         if (++stage == C::kStages) {
           stage = 0;
           phase ^= 1;
