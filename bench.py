@@ -476,6 +476,10 @@ def _time_graph(fn, rounds):
 
 
 def _time_plain(fn, iters, warmup=3):
+    """ms per call over `iters` launches after `warmup`; half a second of idle first, so that every extra configuration
+    starts from the same power state instead of inheriting the throttled clock of the one measured before it."""
+    torch.cuda.synchronize()
+    time.sleep(0.5)
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
