@@ -231,7 +231,7 @@ int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, in
                      "depend on the GPU's approximate log2 / a Philox stream)", name, rounding_mode);
   }
   if (K == 0 || (M == 0 && !stacked)) return 0;
-  if (!q || !scales || (M > 0 && !x)) return fail(1, "%s: null pointer argument", name);
+  if (!scales || (M > 0 && (!x || !q))) return fail(1, "%s: null pointer argument", name);
   if (M > 0x7fff0000LL - 127 * G) return fail(1, "%s: too many rows", name);
   if ((reinterpret_cast<uintptr_t>(x) & 15u) || (row_stride * 2) % 16 != 0)
     return fail(1, "%s: input rows must be 16-byte aligned", name);

@@ -311,3 +311,41 @@ def test_quantize_mx4_stacked_feeds_the_grouped_gemm(ops):
             torch.testing.assert_close(y[r:r + m], (xs[g] @ ws[g].T).to(torch.bfloat16), atol=8.0e-2, rtol=8.0e-2)
         r += m
     assert _status() == 0
+
+
+# --------------------------------------------------------------------------- edge cases of the MXFP4 entry points
+
+def test_mxfp4_edge_cases(ops):
+    e8 = getattr(torch, "float8_e8m0fnu", None)
+    # one row, one group
+    x = torch.randn((1, 32), device="cuda").bfloat16()
+    q, s = ops.quantize_mx4(x)
+    q_ref, s_ref = oracle.quantize_mx4(x.cpu(), 32, 4)
+    assert torch.equal(q.cpu(), q_ref) and torch.equal(s.cpu().view(torch.uint8), s_ref)
+    # no rows at all: nothing to do, shapes right
+    q0, s0 = ops.quantize_mx4(torch.empty((0, 64), device="cuda", dtype=torch.bfloat16))
+    assert q0.shape == (0, 32) and s0.numel() == 0
+    w = torch.randn((128, 64), device="cuda").bfloat16()
+    wq, ws = ops.quantize_mx4(w)
+    y0 = ops.f4f4bf16(q0, wq, s0, ws)
+    assert y0.shape == (0, 128)
+    # stacked quantizer with only empty segments: the scale buffer is all padding, all zero
+    ms = torch.zeros(3, dtype=torch.int64, device="cuda")
+    qs, ss = ops.quantize_mx4_stacked(ms, torch.empty((0, 128), device="cuda", dtype=torch.bfloat16))
+    assert qs.shape == (0, 64) and ss.numel() == 3 * 127 * 4 and torch.count_nonzero(ss) == 0
+    # grouped GEMM whose groups are all empty
+    wq3, ws3 = ops.quantize_mx4(torch.randn((3, 128, 128), device="cuda").bfloat16())
+    yg = ops.f4f4bf16_grouped_stacked(qs, wq3, ss, ws3.view(3, -1), ms)
+    assert yg.shape == (0, 128)
+    if e8 is not None:
+        # K-grouped form with one tiny group and few rows
+        xs, ws_, xqs, wqs, xss, wss, _ = _kgrouped_case(ops, 5, 16, [64], False, seed=1)
+        offs = torch.tensor([64], dtype=torch.int32, device="cuda")
+        out = ops.f4f4bf16_grouped_mm(xqs[0], wqs[0].transpose(-2, -1), xss[0].view(e8), wss[0].view(e8), offs)
+        assert out.shape == (1, 5, 16)
+        assert_sharp_bf16(out[0], oracle.gemm_mx4_torch(xqs[0], wqs[0], xss[0], wss[0], 32), "2D-2D 5x16x64")
+        # offsets past the end of K: that group is rejected on the device, no out-of-bounds read
+        bad = torch.tensor([128], dtype=torch.int32, device="cuda")
+        out = ops.f4f4bf16_grouped_mm(xqs[0], wqs[0].transpose(-2, -1), xss[0].view(e8), wss[0].view(e8), bad)
+        assert _status() & 0x400
+    assert _status() == 0
