@@ -349,3 +349,25 @@ def test_mxfp4_edge_cases(ops):
         out = ops.f4f4bf16_grouped_mm(xqs[0], wqs[0].transpose(-2, -1), xss[0].view(e8), wss[0].view(e8), bad)
         assert _status() & 0x400
     assert _status() == 0
+
+
+@pytest.mark.parametrize("M,N,G", [(300, 272, 300), (512, 512, 200)])
+def test_grouped_mm_2d2d_many_small_groups(ops, M, N, G):
+    """Hundreds of K groups of 0..256 elements: the one-CTA kernel above 255 groups, CTA pairs below."""
+    e8 = getattr(torch, "float8_e8m0fnu", None)
+    if e8 is None:
+        pytest.skip("this torch has no float8_e8m0fnu")
+    g = torch.Generator().manual_seed(G)
+    k_sizes = (torch.randint(0, 9, (G,), generator=g) * 32).tolist()
+    xs, ws, xqs, wqs, xss, wss, _ = _kgrouped_case(ops, M, N, k_sizes, False, seed=G)
+    xq, wq = torch.cat(xqs, dim=1).contiguous(), torch.cat(wqs, dim=1).contiguous()
+    offs = torch.tensor(k_sizes, device="cuda").cumsum(0).to(torch.int32)
+    out = ops.f4f4bf16_grouped_mm(xq, wq.transpose(-2, -1), torch.cat(xss).view(e8), torch.cat(wss).view(e8), offs)
+    assert out.shape == (G, M, N)
+    for i, kg in enumerate(k_sizes):
+        if kg == 0:
+            assert torch.count_nonzero(out[i]) == 0, i
+        else:
+            y_ref = oracle.gemm_mx4_torch(xqs[i], wqs[i], xss[i], wss[i], 32)
+            assert torch.equal(out[i], y_ref.to(out.dtype)) or (out[i].float() - y_ref.float()).abs().max() <= 2 ** -7 * y_ref.float().abs().max(), i
+    assert _status() == 0
