@@ -141,9 +141,9 @@ def race_dense(ops, ref, M, N, K, iters, warmup, w_std=0.02):
             "ref_instance": "128_64_128_1_1_1" if M <= 128 else "128_256_128_2_1_1", **compare(y, y_ref)}
 
 
-def race_grouped(ops, ref, E, tokens, N, K, iters, warmup):
+def race_grouped(ops, ref, E, tokens, N, K, iters, warmup, equal=False):
     from microbench import zipf_counts
-    counts = zipf_counts(E, tokens)
+    counts = torch.full((E,), tokens // E) if equal else zipf_counts(E, tokens)
     ms = counts.to(torch.int64).cuda()
     xq, xs = ops.quantize_fp8_row(randn((tokens, K), seed=2))
     wq, ws = ops.quantize_fp8_row(randn((E, N, K), 0.02, seed=3))
@@ -154,7 +154,8 @@ def race_grouped(ops, ref, E, tokens, N, K, iters, warmup):
     yr = ref.f8f8bf16_rowwise_grouped_stacked(xq, wq, xs, ws, ms, y_ref)
     torch.cuda.synchronize()
     flops = 2.0 * tokens * N * K
-    return {"case": f"f8f8bf16_rowwise_grouped_stacked E={E} tokens={tokens} N={N} K={K} (Zipf 1.2, two empty experts)",
+    how = f"{tokens // E} tokens each" if equal else "Zipf 1.2, two empty experts"
+    return {"case": f"f8f8bf16_rowwise_grouped_stacked E={E} tokens={tokens} N={N} K={K} ({how})",
             "ours_us": ours, "ref_us": theirs, "ours_tflops": flops / ours / 1e6, "ref_tflops": flops / theirs / 1e6,
             "ours_over_ref_speed": theirs / ours, "ref_instance": "grouped_256_256_128_2_1_1", **compare(y, yr)}
 
@@ -323,6 +324,10 @@ def main():
             emit(race_dense(ops, ref, 8192, N, K, args.iters, args.warmup, w_std=0.01))
     for N, K in ((16384, 5120), (5120, 8192)):
         emit(race_grouped(ops, ref, 16, 16384, N, K, args.iters, args.warmup))
+    if not args.quick:
+        # many small experts: equal groups of one 256-row tile, and groups far below a tile
+        emit(race_grouped(ops, ref, 128, 128 * 256, 4096, 4096, args.iters, args.warmup, equal=True))
+        emit(race_grouped(ops, ref, 128, 128 * 64, 4096, 4096, args.iters, args.warmup, equal=True))
     emit(race_nvfp4(ops, ref, 8192, 8192, 8192, args.iters, args.warmup))
     for M in (1, 32):
         emit(race_nvfp4(ops, ref, M, 28672, 8192, 4 * args.iters, args.warmup))
