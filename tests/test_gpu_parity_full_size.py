@@ -203,3 +203,30 @@ def test_grouped_nvfp4_zipf_against_per_group_oracle(ops):
     total = sum(m_sizes)
     _both_bounds(y[:total].cpu(), y_or[:total], "f4f4bf16_grouped_stacked Zipf E=16 tokens=4096 N=1024 K=2048")
     assert _status() == 0
+
+
+def _mx4_formula_chunked(xq, wq, sx, sw, group, rows_per_chunk=1024):
+    """fp32 dequantize-matmul formula of the MXFP4 GEMM (e8m0 scales per `group` elements) in row chunks on the GPU."""
+    M, K = xq.shape[0], xq.shape[1] * 2
+    N = wq.shape[0]
+    e_x = oracle.from_blocked(sx.view(torch.uint8).cpu().reshape(-1), M, K // group).to(torch.int32).cuda()
+    e_w = oracle.from_blocked(sw.view(torch.uint8).cpu().reshape(-1), N, K // group).to(torch.int32).cuda()
+    wf = oracle.fp4_to_float(wq) * torch.exp2((e_w - 127).float()).repeat_interleave(group, dim=1)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    for r in range(0, M, rows_per_chunk):
+        xf = oracle.fp4_to_float(xq[r:r + rows_per_chunk]) * torch.exp2((e_x[r:r + rows_per_chunk] - 127).float()).repeat_interleave(group, dim=1)
+        out[r:r + rows_per_chunk] = (xf @ wf.T).to(torch.bfloat16)
+    return out
+
+
+@pytest.mark.parametrize("M,N,K,group", [(8192, 8192, 8192, 32), (8192, 8192, 8192, 16), (32, 28672, 8192, 32),
+                                         (1, 28672, 8192, 16), (2048, 8192, 8192, 32)])
+def test_mxfp4_bench_shapes_every_element(ops, M, N, K, group):
+    """The MXFP4 modes at the sizes the bench times: CTA pairs with the two-instruction scale atoms, the few-token
+    weight-streaming kernel, both block sizes; every element against the exact formula."""
+    x, w = _randn((M, K), 21) * 0.1, _randn((N, K), 22) * 0.01
+    xq, sx = ops.quantize_mx4(x, group)
+    wq, sw = ops.quantize_mx4(w, group)
+    y = ops.f4f4bf16(xq, wq, sx, sw, mxfp4_block_size=group)
+    _both_bounds(y, _mx4_formula_chunked(xq, wq, sx, sw, group), f"f4f4bf16 MXFP4/{group} {M}x{N}x{K}")
+    assert _status() == 0
