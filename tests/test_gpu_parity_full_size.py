@@ -211,10 +211,10 @@ def _mx4_formula_chunked(xq, wq, sx, sw, group, rows_per_chunk=1024):
     N = wq.shape[0]
     e_x = oracle.from_blocked(sx.view(torch.uint8).cpu().reshape(-1), M, K // group).to(torch.int32).cuda()
     e_w = oracle.from_blocked(sw.view(torch.uint8).cpu().reshape(-1), N, K // group).to(torch.int32).cuda()
-    wf = oracle.fp4_to_float(wq) * torch.exp2((e_w - 127).float()).repeat_interleave(group, dim=1)
+    wf = oracle.fp4_to_float(wq) * torch.ldexp(torch.ones(e_w.shape, dtype=torch.float32, device="cuda"), e_w - 127).repeat_interleave(group, dim=1)
     out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     for r in range(0, M, rows_per_chunk):
-        xf = oracle.fp4_to_float(xq[r:r + rows_per_chunk]) * torch.exp2((e_x[r:r + rows_per_chunk] - 127).float()).repeat_interleave(group, dim=1)
+        xf = oracle.fp4_to_float(xq[r:r + rows_per_chunk]) * torch.ldexp(torch.ones(e_x[r:r + rows_per_chunk].shape, dtype=torch.float32, device="cuda"), e_x[r:r + rows_per_chunk] - 127).repeat_interleave(group, dim=1)
         out[r:r + rows_per_chunk] = (xf @ wf.T).to(torch.bfloat16)
     return out
 
