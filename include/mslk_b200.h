@@ -214,6 +214,9 @@ int mslk_b200_f8f8bf16_rowwise_grouped_stacked_scatter_add(
  */
 int mslk_b200_quantize_nvfp4(const void *x, int64_t M, int64_t K, int64_t row_stride,
                              const float *global_scale, void *q, void *scales, void *stream);
+/* The same with the input type given: dtype = MSLK_B200_BF16 or MSLK_B200_F16 (the reference's kernel takes either). */
+int mslk_b200_quantize_nvfp4_dt(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                const float *global_scale, void *q, void *scales, void *stream);
 
 /*
  * NVFP4 GEMM:  y = bf16(*global_scale * sum_blocks (sx*sw) * sum_16 x^*w^).
@@ -344,6 +347,9 @@ int mslk_b200_f4f4bf16_grouped_mm(const void *xq, const void *wq, const void *x_
 int mslk_b200_quantize_nvfp4_stacked(const void *x, int64_t M, int64_t K, int64_t row_stride,
                                      const int64_t *m_sizes, int64_t G, const float *global_scale,
                                      void *q, void *scales, void *stream);
+int mslk_b200_quantize_nvfp4_stacked_dt(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                        const int64_t *m_sizes, int64_t G, const float *global_scale, void *q,
+                                        void *scales, void *stream);   /* dtype: MSLK_B200_BF16 or MSLK_B200_F16 */
 
 /*
  * Per-group NVFP4 global scale:  global_scale[g] = 2688 / max|x[rows of g]| (1e-8 for an all-zero group,
@@ -353,6 +359,9 @@ int mslk_b200_quantize_nvfp4_stacked(const void *x, int64_t M, int64_t K, int64_
 int mslk_b200_calculate_group_max(const void *x, int64_t M, int64_t K, int64_t row_stride,
                                   const int64_t *m_sizes, int64_t G, float *global_scale,
                                   int64_t *tensor_idx, void *stream);
+int mslk_b200_calculate_group_max_dt(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                     const int64_t *m_sizes, int64_t G, float *global_scale, int64_t *tensor_idx,
+                                     void *stream);   /* dtype: MSLK_B200_BF16 or MSLK_B200_F16 */
 
 /*
  * Fused SwiGLU + per-row FP8 quantization:  y = x0 * sigmoid(x0) * x1 (fp32),

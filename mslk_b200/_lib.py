@@ -49,6 +49,8 @@ lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked.argtypes = [_vp, _vp, _vp, _vp, _
 lib.mslk_b200_f8f8bf16_rowwise_grouped_stacked.restype = _int
 lib.mslk_b200_quantize_nvfp4.argtypes = [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]
 lib.mslk_b200_quantize_nvfp4.restype = _int
+lib.mslk_b200_quantize_nvfp4_dt.argtypes = [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp]
+lib.mslk_b200_quantize_nvfp4_dt.restype = _int
 lib.mslk_b200_f4f4bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp]
 lib.mslk_b200_f4f4bf16.restype = _int
 lib.mslk_b200_quantize_mx4.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _int, _vp, _vp, _vp]
@@ -83,6 +85,10 @@ lib.mslk_b200_quantize_nvfp4_stacked.argtypes = [_vp, _i64, _i64, _i64, _vp, _i6
 lib.mslk_b200_quantize_nvfp4_stacked.restype = _int
 lib.mslk_b200_calculate_group_max.argtypes = [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _vp]
 lib.mslk_b200_calculate_group_max.restype = _int
+lib.mslk_b200_quantize_nvfp4_stacked_dt.argtypes = [_vp, _int, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _vp]
+lib.mslk_b200_quantize_nvfp4_stacked_dt.restype = _int
+lib.mslk_b200_calculate_group_max_dt.argtypes = [_vp, _int, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _vp]
+lib.mslk_b200_calculate_group_max_dt.restype = _int
 lib.mslk_b200_gather_scale_dense_tokens.argtypes = [_vp, _int, _i64, _i64, _vp, _int, _vp, _int, _vp, _int, _i64, _i64, _i64,
                                                     _i64, _vp, _vp, _vp]
 lib.mslk_b200_gather_scale_dense_tokens.restype = _int

@@ -66,6 +66,34 @@ __device__ __forceinline__ float div_rn_via_rcp(float a, float b, float rb) {
   return __fdiv_rn(a, b);
 }
 
+// The two 16-bit input types differ only in how a 32-bit word of two elements yields its maximum magnitude and its
+// two fp32 values; everything after that is fp32 arithmetic.
+template <bool kHalf>
+__device__ __forceinline__ float pair_amax8(const uint32_t (&w)[8]) {
+  if constexpr (kHalf) {
+    __half2 mx = __habs2(*reinterpret_cast<const __half2 *>(&w[0]));
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mx = __hmax2(mx, __habs2(*reinterpret_cast<const __half2 *>(&w[i])));
+    return fmaxf(__low2float(mx), __high2float(mx));
+  } else {
+    __nv_bfloat162 mx = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mx = __hmax2(mx, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
+    return fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
+  }
+}
+
+template <bool kHalf>
+__device__ __forceinline__ float word_lo(uint32_t w) {
+  if constexpr (kHalf) return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu)));
+  else return __uint_as_float(w << 16);
+}
+template <bool kHalf>
+__device__ __forceinline__ float word_hi(uint32_t w) {
+  if constexpr (kHalf) return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+  else return __uint_as_float(w & 0xffff0000u);
+}
+
 template <int kVec>
 __device__ __forceinline__ BlockIn load_block(const __nv_bfloat16 *src) {
   BlockIn v;
@@ -92,7 +120,7 @@ __device__ __forceinline__ BlockIn load_block(const __nv_bfloat16 *src) {
 // and no barrier between warps.  Units are walked grid-stride with the next unit's block prefetched
 // into registers.  total = gs / float(s) comes from a 127-entry table of IEEE quotients built
 // once per CTA.
-template <int kVec>
+template <int kVec, bool kHalf>
 __global__ void __launch_bounds__(kThreads, 6)
     quant_nvfp4_kernel(const __nv_bfloat16 *__restrict__ x, int M, int nblk, int64_t row_stride,
                        const float *__restrict__ gs_ptr, uint8_t *__restrict__ q, uint8_t *__restrict__ scales,
@@ -150,10 +178,7 @@ __global__ void __launch_bounds__(kThreads, 6)
     if (live) {
       const uint32_t w[8] = {cur.a.x, cur.a.y, cur.a.z, cur.a.w, cur.b.x, cur.b.y, cur.b.z, cur.b.w};
       // block amax on the packed pairs (exact: max and abs do not round)
-      __nv_bfloat162 mx = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[0]));
-#pragma unroll
-      for (int i = 1; i < 8; ++i) mx = __hmax2(mx, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])));
-      const float bamax = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
+      const float bamax = pair_amax8<kHalf>(w);
       float s = __fmul_rn(div_rn_via_rcp(bamax, 6.0f, 0x1.555556p-3f), gs);
       s = fminf(fmaxf(s, 0.001953125f), 448.0f);
       s8 = f32_to_e4m3(s);
@@ -161,10 +186,10 @@ __global__ void __launch_bounds__(kThreads, 6)
       float lo[8], hi[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        lo[2 * i] = __fmul_rn(__uint_as_float(w[i] << 16), total);
-        lo[2 * i + 1] = __fmul_rn(__uint_as_float(w[i] & 0xffff0000u), total);
-        hi[2 * i] = __fmul_rn(__uint_as_float(w[4 + i] << 16), total);
-        hi[2 * i + 1] = __fmul_rn(__uint_as_float(w[4 + i] & 0xffff0000u), total);
+        lo[2 * i] = __fmul_rn(word_lo<kHalf>(w[i]), total);
+        lo[2 * i + 1] = __fmul_rn(word_hi<kHalf>(w[i]), total);
+        hi[2 * i] = __fmul_rn(word_lo<kHalf>(w[4 + i]), total);
+        hi[2 * i + 1] = __fmul_rn(word_hi<kHalf>(w[4 + i]), total);
       }
       *reinterpret_cast<uint2 *>(q + m * q_pitch + j * 8) = make_uint2(cvt_e2m1x8(lo), cvt_e2m1x8(hi));
     }
@@ -212,7 +237,7 @@ __device__ __forceinline__ void build_stacked_tables(const int64_t *m_sizes, int
   }
 }
 
-template <int kVec>
+template <int kVec, bool kHalf>
 __global__ void __launch_bounds__(kThreads, 6)
     quant_nvfp4_stacked_kernel(const __nv_bfloat16 *__restrict__ x, int M, int nblk, int64_t row_stride,
                                const float *__restrict__ gs_ptr, const int64_t *__restrict__ m_sizes, int G,
@@ -243,10 +268,7 @@ __global__ void __launch_bounds__(kThreads, 6)
     uint8_t s8 = 0;
     if (l.live) {
       const uint32_t wd[8] = {cur.a.x, cur.a.y, cur.a.z, cur.a.w, cur.b.x, cur.b.y, cur.b.z, cur.b.w};
-      __nv_bfloat162 mx = __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&wd[0]));
-#pragma unroll
-      for (int i = 1; i < 8; ++i) mx = __hmax2(mx, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&wd[i])));
-      const float bamax = fmaxf(__bfloat162float(mx.x), __bfloat162float(mx.y));
+      const float bamax = pair_amax8<kHalf>(wd);
       float sc = __fmul_rn(div_rn_via_rcp(bamax, 6.0f, 0x1.555556p-3f), gs);
       sc = fminf(fmaxf(sc, 0.001953125f), 448.0f);
       s8 = f32_to_e4m3(sc);
@@ -255,10 +277,10 @@ __global__ void __launch_bounds__(kThreads, 6)
       float lo8[8], hi8[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        lo8[2 * i] = __fmul_rn(__uint_as_float(wd[i] << 16), total);
-        lo8[2 * i + 1] = __fmul_rn(__uint_as_float(wd[i] & 0xffff0000u), total);
-        hi8[2 * i] = __fmul_rn(__uint_as_float(wd[4 + i] << 16), total);
-        hi8[2 * i + 1] = __fmul_rn(__uint_as_float(wd[4 + i] & 0xffff0000u), total);
+        lo8[2 * i] = __fmul_rn(word_lo<kHalf>(wd[i]), total);
+        lo8[2 * i + 1] = __fmul_rn(word_hi<kHalf>(wd[i]), total);
+        hi8[2 * i] = __fmul_rn(word_lo<kHalf>(wd[4 + i]), total);
+        hi8[2 * i + 1] = __fmul_rn(word_hi<kHalf>(wd[4 + i]), total);
       }
       *reinterpret_cast<uint2 *>(q + l.m * q_pitch + l.j * 8) = make_uint2(cvt_e2m1x8(lo8), cvt_e2m1x8(hi8));
     }
@@ -303,7 +325,7 @@ __global__ void __launch_bounds__(kThreads, 6)
 __global__ void __launch_bounds__(256) group_amax_kernel(const __nv_bfloat16 *__restrict__ x, int M, int K,
                                                          int64_t row_stride, const int64_t *__restrict__ m_sizes, int G,
                                                          unsigned int *__restrict__ amax_bits,
-                                                         int64_t *__restrict__ tensor_idx) {
+                                                         int64_t *__restrict__ tensor_idx, unsigned int inf_bits) {
   __shared__ int s_row_end[kMaxStackedGroups];
   __shared__ int s_blk_end[kMaxStackedGroups];
   __shared__ unsigned int s_max[8];
@@ -327,19 +349,19 @@ __global__ void __launch_bounds__(256) group_amax_kernel(const __nv_bfloat16 *__
         for (int i = 0; i < 4; ++i) {
           const unsigned int a = wd[i] & 0x7fff7fffu;
           const unsigned int l = a & 0xffffu, h = a >> 16;
-          // NaN patterns (> 0x7f80) are ignored, like max() does
-          if (l <= 0x7f80u) mx = max(mx, l);
-          if (h <= 0x7f80u) mx = max(mx, h);
+          // NaN patterns (above the infinity pattern: 0x7f80 for bf16, 0x7c00 for fp16) are ignored, like max() does
+          if (l <= inf_bits) mx = max(mx, l);
+          if (h <= inf_bits) mx = max(mx, h);
         }
       }
       for (int k = (K / 8) * 8 + threadIdx.x; k < K; k += blockDim.x) {
         const unsigned int a = src[k] & 0x7fffu;
-        if (a <= 0x7f80u) mx = max(mx, a);
+        if (a <= inf_bits) mx = max(mx, a);
       }
     } else {
       for (int k = threadIdx.x; k < K; k += blockDim.x) {
         const unsigned int a = src[k] & 0x7fffu;
-        if (a <= 0x7f80u) mx = max(mx, a);
+        if (a <= inf_bits) mx = max(mx, a);
       }
     }
 #pragma unroll
@@ -359,14 +381,15 @@ __global__ void __launch_bounds__(256) group_amax_kernel(const __nv_bfloat16 *__
 // Phase 2: out[g] = 2688 / amax_g with the approximate division the reference's kernel lowers to
 // (div.full), 1e-8 standing in for an all-zero group; groups without rows keep FLT_MAX.
 __global__ void group_scale_finish_kernel(const unsigned int *__restrict__ amax_bits, const int64_t *__restrict__ m_sizes,
-                                          int G, float *__restrict__ out) {
+                                          int G, float *__restrict__ out, int is_half) {
   const int g = blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= G) return;
   if (m_sizes[g] <= 0) {
     out[g] = 3.4028234663852886e38f;
     return;
   }
-  const float amax = __uint_as_float(amax_bits[g] << 16);
+  const float amax = is_half ? __half2float(__ushort_as_half(static_cast<unsigned short>(amax_bits[g])))
+                             : __uint_as_float(amax_bits[g] << 16);
   float r;
   const float d = amax == 0.f ? 1e-8f : amax;
   asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(2688.0f), "f"(d));
@@ -376,10 +399,12 @@ __global__ void group_scale_finish_kernel(const unsigned int *__restrict__ amax_
 }  // namespace
 }  // namespace mslk_b200
 
-MSLK_API int mslk_b200_quantize_nvfp4(const void *x, int64_t M, int64_t K, int64_t row_stride,
-                                      const float *global_scale, void *q, void *scales, void *stream) {
+MSLK_API int mslk_b200_quantize_nvfp4_dt(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                         const float *global_scale, void *q, void *scales, void *stream) {
   using namespace mslk_b200;
   clear_error();
+  if (dtype != MSLK_B200_BF16 && dtype != MSLK_B200_F16) return fail(1, "quantize_nvfp4: input must be bf16 or fp16");
+  const bool half = dtype == MSLK_B200_F16;
   if (M < 0 || K < 0 || K % 16 != 0) return fail(1, "quantize_nvfp4: K must be a non-negative multiple of 16");
   if (M == 0 || K == 0) return 0;
   if (!x || !q || !scales) return fail(1, "quantize_nvfp4: null pointer argument");
@@ -397,25 +422,29 @@ MSLK_API int mslk_b200_quantize_nvfp4(const void *x, int64_t M, int64_t K, int64
   const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
   auto *xb = static_cast<const __nv_bfloat16 *>(x);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (vec_ok)
-    quant_nvfp4_kernel<1><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
-                                                          global_scale, static_cast<uint8_t *>(q),
-                                                          static_cast<uint8_t *>(scales), static_cast<int>(n_col_tiles),
-                                                          static_cast<int>(units));
-  else
-    quant_nvfp4_kernel<0><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
-                                                           global_scale, static_cast<uint8_t *>(q),
-                                                           static_cast<uint8_t *>(scales), static_cast<int>(n_col_tiles),
-                                                           static_cast<int>(units));
+  auto go = [&](auto kernel) {
+    kernel<<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride, global_scale,
+                                        static_cast<uint8_t *>(q), static_cast<uint8_t *>(scales),
+                                        static_cast<int>(n_col_tiles), static_cast<int>(units));
+  };
+  if (vec_ok) half ? go(quant_nvfp4_kernel<1, true>) : go(quant_nvfp4_kernel<1, false>);
+  else half ? go(quant_nvfp4_kernel<0, true>) : go(quant_nvfp4_kernel<0, false>);
   return check_cuda(cudaGetLastError(), "quantize_nvfp4 launch");
 }
 
-MSLK_API int mslk_b200_quantize_nvfp4_stacked(const void *x, int64_t M, int64_t K, int64_t row_stride,
-                                              const int64_t *m_sizes, int64_t G, const float *global_scale, void *q,
-                                              void *scales, void *stream) {
+MSLK_API int mslk_b200_quantize_nvfp4(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                                      const float *global_scale, void *q, void *scales, void *stream) {
+  return mslk_b200_quantize_nvfp4_dt(x, MSLK_B200_BF16, M, K, row_stride, global_scale, q, scales, stream);
+}
+
+MSLK_API int mslk_b200_quantize_nvfp4_stacked_dt(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                                 const int64_t *m_sizes, int64_t G, const float *global_scale, void *q,
+                                                 void *scales, void *stream) {
   using namespace mslk_b200;
   clear_error();
   const char *name = "quantize_nvfp4_stacked";
+  if (dtype != MSLK_B200_BF16 && dtype != MSLK_B200_F16) return fail(1, "%s: input must be bf16 or fp16", name);
+  const bool half = dtype == MSLK_B200_F16;
   if (M < 0 || K < 0 || K % 16 != 0) return fail(1, "%s: K must be a non-negative multiple of 16", name);
   if (G < 1 || G > kMaxStackedGroups) return fail(1, "%s: between 1 and %d groups are supported", name, kMaxStackedGroups);
   if (M == 0 || K == 0) return 0;
@@ -431,25 +460,31 @@ MSLK_API int mslk_b200_quantize_nvfp4_stacked(const void *x, int64_t M, int64_t 
   const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
   auto *xb = static_cast<const __nv_bfloat16 *>(x);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (vec_ok)
-    quant_nvfp4_stacked_kernel<1><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
-                                                               global_scale, m_sizes, static_cast<int>(G),
-                                                               static_cast<uint8_t *>(q), static_cast<uint8_t *>(scales),
-                                                               static_cast<int>(n_col_tiles));
-  else
-    quant_nvfp4_stacked_kernel<0><<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride,
-                                                               global_scale, m_sizes, static_cast<int>(G),
-                                                               static_cast<uint8_t *>(q), static_cast<uint8_t *>(scales),
-                                                               static_cast<int>(n_col_tiles));
+  auto go = [&](auto kernel) {
+    kernel<<<blocks, kThreads, 0, st>>>(xb, static_cast<int>(M), static_cast<int>(K / 16), row_stride, global_scale, m_sizes,
+                                        static_cast<int>(G), static_cast<uint8_t *>(q), static_cast<uint8_t *>(scales),
+                                        static_cast<int>(n_col_tiles));
+  };
+  if (vec_ok) half ? go(quant_nvfp4_stacked_kernel<1, true>) : go(quant_nvfp4_stacked_kernel<1, false>);
+  else half ? go(quant_nvfp4_stacked_kernel<0, true>) : go(quant_nvfp4_stacked_kernel<0, false>);
   return check_cuda(cudaGetLastError(), "quantize_nvfp4_stacked launch");
 }
 
-MSLK_API int mslk_b200_calculate_group_max(const void *x, int64_t M, int64_t K, int64_t row_stride,
-                                           const int64_t *m_sizes, int64_t G, float *global_scale, int64_t *tensor_idx,
-                                           void *stream) {
+MSLK_API int mslk_b200_quantize_nvfp4_stacked(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                                              const int64_t *m_sizes, int64_t G, const float *global_scale, void *q,
+                                              void *scales, void *stream) {
+  return mslk_b200_quantize_nvfp4_stacked_dt(x, MSLK_B200_BF16, M, K, row_stride, m_sizes, G, global_scale, q, scales,
+                                             stream);
+}
+
+MSLK_API int mslk_b200_calculate_group_max_dt(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                              const int64_t *m_sizes, int64_t G, float *global_scale,
+                                              int64_t *tensor_idx, void *stream) {
   using namespace mslk_b200;
   clear_error();
   const char *name = "calculate_group_max";
+  if (dtype != MSLK_B200_BF16 && dtype != MSLK_B200_F16) return fail(1, "%s: input must be bf16 or fp16", name);
+  const bool half = dtype == MSLK_B200_F16;
   if (M < 0 || K < 0) return fail(1, "%s: bad shape", name);
   if (G < 1 || G > kMaxStackedGroups) return fail(1, "%s: between 1 and %d groups are supported", name, kMaxStackedGroups);
   if (!m_sizes || !global_scale) return fail(1, "%s: null pointer argument", name);
@@ -463,10 +498,17 @@ MSLK_API int mslk_b200_calculate_group_max(const void *x, int64_t M, int64_t K, 
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     const unsigned blocks = static_cast<unsigned>(M < cap ? M : cap);
     group_amax_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<int>(M), static_cast<int>(K),
-                                              row_stride, m_sizes, static_cast<int>(G), bits, tensor_idx);
+                                              row_stride, m_sizes, static_cast<int>(G), bits, tensor_idx,
+                                              half ? 0x7c00u : 0x7f80u);
     if (int rc = check_cuda(cudaGetLastError(), "calculate_group_max launch")) return rc;
   }
   group_scale_finish_kernel<<<static_cast<unsigned>((G + 127) / 128), 128, 0, st>>>(bits, m_sizes, static_cast<int>(G),
-                                                                                   global_scale);
+                                                                                   global_scale, half ? 1 : 0);
   return check_cuda(cudaGetLastError(), "calculate_group_max launch");
+}
+
+MSLK_API int mslk_b200_calculate_group_max(const void *x, int64_t M, int64_t K, int64_t row_stride,
+                                           const int64_t *m_sizes, int64_t G, float *global_scale, int64_t *tensor_idx,
+                                           void *stream) {
+  return mslk_b200_calculate_group_max_dt(x, MSLK_B200_BF16, M, K, row_stride, m_sizes, G, global_scale, tensor_idx, stream);
 }

@@ -275,7 +275,8 @@ std::tuple<at::Tensor, at::Tensor> quantize_fp8_per_row(at::Tensor a, std::optio
 }
 
 std::tuple<at::Tensor, at::Tensor> quantize_nvfp4(at::Tensor x, std::optional<at::Tensor> global_scale) {
-  TORCH_CHECK(x.is_cuda() && x.dtype() == at::kBFloat16, "quantize_nvfp4: expected a bfloat16 CUDA tensor");
+  TORCH_CHECK(x.is_cuda() && (x.dtype() == at::kBFloat16 || x.dtype() == at::kHalf),
+              "quantize_nvfp4: expected a bfloat16 or float16 CUDA tensor");
   TORCH_CHECK(x.dim() >= 2, "quantize_nvfp4: expected at least 2 dimensions");
   const int64_t K = x.size(-1);
   TORCH_CHECK(K % 16 == 0, "N must be divisible by 16 for NVFP4 quantization");
@@ -292,7 +293,8 @@ std::tuple<at::Tensor, at::Tensor> quantize_nvfp4(at::Tensor x, std::optional<at
     gs = global_scale->reshape({-1}).to(at::kFloat);
   }
   c10::cuda::CUDAGuard guard(x.device());
-  check_rc(mslk_b200_quantize_nvfp4(x2.data_ptr(), M, K, x2.stride(0), gs.defined() ? gs.data_ptr<float>() : nullptr,
+  check_rc(mslk_b200_quantize_nvfp4_dt(x2.data_ptr(), x.dtype() == at::kHalf ? MSLK_B200_F16 : MSLK_B200_BF16, M, K, x2.stride(0),
+                                       gs.defined() ? gs.data_ptr<float>() : nullptr,
                                     q.data_ptr(), s.data_ptr(), stream_of(x)),
            "quantize_nvfp4");
   std::vector<int64_t> qshape(x.sizes().begin(), x.sizes().end() - 2), sshape = qshape;

@@ -273,8 +273,8 @@ def _check_nvfp4_scale_extent(name: str, arg: str, scale: torch.Tensor, rows: in
 def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
     """Returns ``(xq uint8 [..., K/2], scales float8_e4m3fn [rows_pad, cols_pad] swizzled)``."""
     dev = _require_cuda("quantize_nvfp4", x, global_scale)
-    if x.dtype != torch.bfloat16:
-        raise RuntimeError("quantize_nvfp4: input must be bfloat16")
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"quantize_nvfp4: input must be bfloat16 or float16, got {x.dtype}")
     lead, K = x.shape[:-2], x.shape[-1]
     x2 = x.reshape(-1, K)
     if x2.stride(1) != 1:
@@ -288,7 +288,7 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
     if global_scale is not None:
         gs = global_scale.reshape(-1).to(torch.float32)
     with torch.cuda.device(dev):
-        check(lib.mslk_b200_quantize_nvfp4(_ptr(x2), M, K, x2.stride(0), _ptr(gs), _ptr(q), _ptr(s), _stream(dev)),
+        check(lib.mslk_b200_quantize_nvfp4_dt(_ptr(x2), _DTYPE_CODE[x2.dtype], M, K, x2.stride(0), _ptr(gs), _ptr(q), _ptr(s), _stream(dev)),
               "quantize_nvfp4")
     return q.view(*lead, -1, K // 2), s.view(*lead, -1, pc)
 
@@ -451,8 +451,8 @@ def calculate_group_max(input: torch.Tensor, m_sizes: torch.Tensor):
     dev = _require_cuda(name, input, m_sizes)
     assert input.ndim >= 1, f"input.ndim needs to be >= 1, but got {input.ndim}."
     x2 = input.reshape(1 if input.ndim == 1 else -1, input.shape[-1])
-    if x2.dtype != torch.bfloat16:
-        raise RuntimeError(f"{name}: input must be bfloat16, got {x2.dtype}")
+    if x2.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"{name}: input must be bfloat16 or float16, got {x2.dtype}")
     if x2.stride(1) != 1:
         x2 = x2.contiguous()
     if m_sizes.dtype != torch.int64:
@@ -462,7 +462,7 @@ def calculate_group_max(input: torch.Tensor, m_sizes: torch.Tensor):
     out = torch.empty((G,), dtype=torch.float32, device=dev)
     tensor_idx = torch.empty((M,), dtype=torch.int64, device=dev)
     with torch.cuda.device(dev):
-        check(lib.mslk_b200_calculate_group_max(_ptr(x2), M, K, x2.stride(0), _ptr(m_sizes.contiguous()), G, _ptr(out),
+        check(lib.mslk_b200_calculate_group_max_dt(_ptr(x2), _DTYPE_CODE[x2.dtype], M, K, x2.stride(0), _ptr(m_sizes.contiguous()), G, _ptr(out),
                                                 _ptr(tensor_idx), _stream(dev)), name)
     return out, tensor_idx
 
@@ -476,8 +476,8 @@ def nvfp4_quantize_stacked(m_sizes: torch.Tensor, input: torch.Tensor, global_sc
     x2 = input.reshape(-1, input.shape[-1])
     M, K = x2.shape
     assert K % 16 == 0, f"K must be divisible by 16, but got {K}."
-    if x2.dtype != torch.bfloat16:
-        raise RuntimeError(f"{name}: input must be bfloat16, got {x2.dtype}")
+    if x2.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"{name}: input must be bfloat16 or float16, got {x2.dtype}")
     if x2.stride(1) != 1:
         x2 = x2.contiguous()
     if m_sizes.dtype != torch.int64:
@@ -490,7 +490,7 @@ def nvfp4_quantize_stacked(m_sizes: torch.Tensor, input: torch.Tensor, global_sc
     if gs.numel() != G:
         raise RuntimeError(f"{name}: global_scale must hold one value per group")
     with torch.cuda.device(dev):
-        check(lib.mslk_b200_quantize_nvfp4_stacked(_ptr(x2), M, K, x2.stride(0), _ptr(m_sizes.contiguous()), G, _ptr(gs),
+        check(lib.mslk_b200_quantize_nvfp4_stacked_dt(_ptr(x2), _DTYPE_CODE[x2.dtype], M, K, x2.stride(0), _ptr(m_sizes.contiguous()), G, _ptr(gs),
                                                    _ptr(xq), _ptr(scale), _stream(dev)), name)
     fp4 = getattr(torch, "float4_e2m1fn_x2", None)
     return (xq.view(fp4) if fp4 is not None else xq), scale.view(FP8_DTYPE)

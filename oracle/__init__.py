@@ -69,6 +69,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_nvfp4_scale_offset.restype = i64
         L.oracle_quantize_nvfp4.argtypes = [vp, i64, i64, vp, vp, vp]
         L.oracle_quantize_nvfp4.restype = None
+        L.oracle_quantize_nvfp4_dt.argtypes = [vp, ctypes.c_int, i64, i64, vp, vp, vp]
+        L.oracle_quantize_nvfp4_dt.restype = None
         L.oracle_quantize_mx4.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp]
         L.oracle_quantize_mx4.restype = None
         L.oracle_gemm_nvfp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
@@ -262,13 +264,13 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
     (``mslk/quantize/triton/quantize_kernels/nvfp4.py:62-296``).
     Returns ``(packed uint8 [M, K/2], swizzled e4m3 scales [rows_pad, cols_pad])``."""
     x = _cpu(x).contiguous()
-    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] % 16 == 0
+    assert x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 2 and x.shape[1] % 16 == 0
     M, K = x.shape
     pr, pc = nvfp4_scale_shape(M, K)
     q = torch.empty((M, K // 2), dtype=torch.uint8)
     s = torch.zeros((pr * pc,), dtype=torch.uint8)
     gs = None if global_scale is None else _cpu(global_scale).reshape(1).float().contiguous()
-    lib().oracle_quantize_nvfp4(_p(x), M, K, _p(gs), _p(q), _p(s))
+    lib().oracle_quantize_nvfp4_dt(_p(x), DTYPE_CODE[x.dtype], M, K, _p(gs), _p(q), _p(s))
     return q, s.view(torch.float8_e4m3fn).view(pr, pc)
 
 

@@ -314,9 +314,9 @@ ORACLE_API int64_t oracle_nvfp4_scale_offset(int64_t r, int64_t c, int64_t n_col
  * q: [M, K/2] bytes, element 2j in the low nibble.  scales: swizzled, padded to
  * [ceil(M/128)*128, ceil(K/16/4)*4], padding zero.  gs may be NULL (= 1.0).
  */
-ORACLE_API void oracle_quantize_nvfp4(const uint16_t *x_bf16, int64_t M, int64_t K,
-                                      const float *global_scale, uint8_t *q,
-                                      uint8_t *scales_swizzled) {
+ORACLE_API void oracle_quantize_nvfp4_dt(const uint16_t *x16, int dtype, int64_t M, int64_t K,
+                                         const float *global_scale, uint8_t *q,
+                                         uint8_t *scales_swizzled) {
   int64_t nblk = K / 16;
   int64_t ncb = (nblk + 3) / 4;
   int64_t nrb = (M + 127) / 128;
@@ -325,10 +325,10 @@ ORACLE_API void oracle_quantize_nvfp4(const uint16_t *x_bf16, int64_t M, int64_t
 #pragma omp parallel for schedule(static)
   for (int64_t m = 0; m < M; ++m) {
     for (int64_t j = 0; j < nblk; ++j) {
-      const uint16_t *xb = x_bf16 + m * K + j * 16;
+      const uint16_t *xb = x16 + m * K + j * 16;
       float bamax = 0.f;
       for (int i = 0; i < 16; ++i) {
-        float v = fabsf(bf16_to_f32(xb[i]));
+        float v = fabsf(dtype == 2 ? f16_to_f32(xb[i]) : bf16_to_f32(xb[i]));
         if (v > bamax) bamax = v;
       }
       volatile float d = bamax / 6.0f;
@@ -340,8 +340,8 @@ ORACLE_API void oracle_quantize_nvfp4(const uint16_t *x_bf16, int64_t M, int64_t
       scales_swizzled[oracle_nvfp4_scale_offset(m, j, ncb)] = s8;
       volatile float total = gs / oracle_e4m3_to_f32(s8);
       for (int i = 0; i < 16; i += 2) {
-        volatile float a = bf16_to_f32(xb[i]) * total;
-        volatile float b = bf16_to_f32(xb[i + 1]) * total;
+        volatile float a = (dtype == 2 ? f16_to_f32(xb[i]) : bf16_to_f32(xb[i])) * total;
+        volatile float b = (dtype == 2 ? f16_to_f32(xb[i + 1]) : bf16_to_f32(xb[i + 1])) * total;
         q[m * (K / 2) + j * 8 + i / 2] =
             (uint8_t)(oracle_f32_to_e2m1(a) | (oracle_f32_to_e2m1(b) << 4));
       }
@@ -358,6 +358,11 @@ ORACLE_API void oracle_quantize_nvfp4(const uint16_t *x_bf16, int64_t M, int64_t
  * x: bf16 (dtype 1) or fp16 (dtype 2).  q: [M, K/2]; scales: swizzled like the NVFP4 scales, padded to
  * [ceil(M/128)*128, ceil(K/group/4)*4], padding zero.
  */
+ORACLE_API void oracle_quantize_nvfp4(const uint16_t *x_bf16, int64_t M, int64_t K, const float *global_scale,
+                                      uint8_t *q, uint8_t *scales_swizzled) {
+  oracle_quantize_nvfp4_dt(x_bf16, 1, M, K, global_scale, q, scales_swizzled);
+}
+
 ORACLE_API void oracle_quantize_mx4(const uint16_t *x, int dtype, int64_t M, int64_t K, int group, int round_add,
                                     uint8_t *q, uint8_t *scales_swizzled) {
   int64_t nblk = K / group;

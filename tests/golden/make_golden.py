@@ -17,6 +17,7 @@ Two legs, both writing ``.npz`` files next to this script:
 ``--leg gpu_gather``  (needs a B200) runs the reference's ``gather_scale_quant_dense_tokens``
     (``mslk/moe/gather_scatter.py``).  These two legs store outputs only; the tests regenerate the
     seeded inputs with ``silu_inputs`` / ``gather_inputs`` (CPU generator, same torch build).
+``--leg gpu_fp4_f16``  (needs a B200) runs the NVFP4 quantizers (dense, group maximum, stacked) on fp16 inputs.
 ``--leg gpu_mx4``  (needs a B200) runs the reference's MXFP4 quantizer ``quantize_mx4``
     (``mslk/quantize/triton/quantize_kernels/mx4.py``) for group sizes 32 / 16 and the floor / even / ceil rounding
     modes; outputs only (the tests regenerate the inputs with ``mx4_inputs``).
@@ -358,6 +359,47 @@ def leg_gpu_fp4_stacked(ref_root: str):
     print("gpu fp4 stacked leg written")
 
 
+# fp16 inputs of the NVFP4 quantizers (the reference's kernels take fp16 or bf16): dense cases and one stacked case
+NVFP4_F16_CASES = [("h_r130_k256", (130, 256)), ("h_r5_k64", (5, 64)), ("h_r256_k1040", (256, 1040))]
+STACKED_F16_CASE = ("h_st_5g", [64, 200, 0, 129, 7], 512)
+
+
+def nvfp4_f16_inputs(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g, dtype=torch.float32)
+    x = x * torch.exp2(torch.randint(-6, 7, (shape[0], 1), generator=g).float())   # rows over a few binades of fp16
+    return x.to(torch.float16)
+
+
+def leg_gpu_fp4_f16(ref_root: str):
+    """quantize_nvfp4, calculate_group_max and nvfp4_quantize_stacked of the reference (Triton) on a B200, fp16 inputs."""
+    _import_reference(ref_root)
+    from mslk.quantize.triton.quantize_kernels.nvfp4 import quantize_nvfp4
+    from mslk.quantize.triton.legacy.global_scale import calculate_group_max
+    from mslk.quantize.triton.legacy.quantize_stacked import nvfp4_quantize_stacked
+    out = {}
+    for i, (name, shape) in enumerate(NVFP4_F16_CASES):
+        x = nvfp4_f16_inputs(shape, 800 + i).cuda()
+        gs = (448.0 * 6.0) / x.abs().amax().float()     # global_scale_nvfp4 (legacy/fp4_utils.py:78-92) asserts bf16
+        q, s = quantize_nvfp4(x, gs)
+        torch.cuda.synchronize()
+        out[f"{name}.gs"] = _raw(gs.reshape(1).float())
+        out[f"{name}.q"] = _raw(q)
+        out[f"{name}.s_blocked"] = _raw(s)
+    name, m_sizes, K = STACKED_F16_CASE
+    x = nvfp4_f16_inputs((sum(m_sizes), K), 850).cuda()
+    ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+    gs, idx = calculate_group_max(x, ms)
+    q, s = nvfp4_quantize_stacked(ms, x, gs)
+    torch.cuda.synchronize()
+    out[f"{name}.gs"] = _raw(gs)
+    out[f"{name}.idx"] = _raw(idx)
+    out[f"{name}.q"] = _raw(q.view(torch.uint8))
+    out[f"{name}.s_rows"] = _raw(unswizzle_stacked_scales(s, m_sizes, K))
+    np.savez_compressed(os.path.join(HERE, "nvfp4_f16_triton_b200.npz"), **out)
+    print("gpu fp4 f16 leg written")
+
+
 # (name, shape, dtype) of the MXFP4 quantizer cases: rows below / at / above the 128-row scale block, K with a partial
 # group of four scales, fp16 input, values spanning many binades, an all-zero group and exact powers of two
 MX4_CASES = [("r128_k64", (128, 64), "bf16"), ("r5_k128", (5, 128), "bf16"), ("r150_k1024", (150, 1024), "bf16"),
@@ -395,7 +437,7 @@ def leg_gpu_mx4(ref_root: str):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu", "gpu_gather", "gpu_fp4_stacked", "gpu_mx4"], required=True)
+    ap.add_argument("--leg", choices=["cpu", "gpu", "gpu_silu", "gpu_gather", "gpu_fp4_stacked", "gpu_mx4", "gpu_fp4_f16"], required=True)
     ap.add_argument("--ref-root", required=True)
     ap.add_argument("--out-dir", default=None, help="write here instead of beside this script")
     args = ap.parse_args()
@@ -403,4 +445,4 @@ if __name__ == "__main__":
         HERE = args.out_dir
         os.makedirs(HERE, exist_ok=True)
     {"cpu": leg_cpu, "gpu": leg_gpu, "gpu_silu": leg_gpu_silu, "gpu_gather": leg_gpu_gather,
-     "gpu_fp4_stacked": leg_gpu_fp4_stacked, "gpu_mx4": leg_gpu_mx4}[args.leg](args.ref_root)
+     "gpu_fp4_stacked": leg_gpu_fp4_stacked, "gpu_mx4": leg_gpu_mx4, "gpu_fp4_f16": leg_gpu_fp4_f16}[args.leg](args.ref_root)

@@ -153,3 +153,39 @@ def test_few_token_gemm_workspace_size_contract():
     assert lib.mslk_b200_f4f4bf16_workspace_bytes(0, 256, 32768) == 0
     need = lib.mslk_b200_f4f4bf16_workspace_bytes(5, 256, 32768)
     assert need > 0 and need % 16 == 0
+
+
+def test_quantizers_take_fp16_inputs_like_the_reference(ops):
+    """fp16 inputs of quantize_nvfp4, calculate_group_max and nvfp4_quantize_stacked: bit-exact against the oracle and
+    against outputs of the reference's Triton kernels captured on a B200."""
+    import oracle
+    from helpers import load_golden
+    from golden.make_golden import NVFP4_F16_CASES, STACKED_F16_CASE, nvfp4_f16_inputs, unswizzle_stacked_scales
+    gold = load_golden("nvfp4_f16_triton_b200.npz")
+    for i, (name, shape) in enumerate(NVFP4_F16_CASES):
+        x = nvfp4_f16_inputs(shape, 800 + i)
+        gs = (448.0 * 6.0) / x.cuda().abs().amax().float()
+        q, s = ops.quantize_nvfp4(x.cuda(), gs)
+        q_ref, s_ref = oracle.quantize_nvfp4(x, gs.cpu())
+        assert torch.equal(q.cpu().view(torch.uint8), q_ref), name
+        assert torch.equal(s.cpu().view(torch.uint8), s_ref.view(torch.uint8)), name
+        if gold is not None:
+            assert torch.equal(gs.cpu().reshape(1), torch.from_numpy(gold[f"{name}.gs"])), name
+            assert torch.equal(q.cpu().view(torch.uint8), torch.from_numpy(gold[f"{name}.q"])), name
+            assert torch.equal(s.cpu().view(torch.uint8).reshape(-1), torch.from_numpy(gold[f"{name}.s_blocked"]).view(torch.uint8).reshape(-1)), name
+    name, m_sizes, K = STACKED_F16_CASE
+    x = nvfp4_f16_inputs((sum(m_sizes), K), 850).cuda()
+    ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+    gs, idx = ops.calculate_group_max(x, ms)
+    q, s = ops.nvfp4_quantize_stacked(ms, x, gs)
+    q_ref, s_ref, _ = oracle.nvfp4_quantize_stacked(m_sizes, x.cpu(), gs.cpu())
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref)
+    rows = unswizzle_stacked_scales(s, m_sizes, K)
+    assert torch.equal(rows, unswizzle_stacked_scales(s_ref, m_sizes, K))
+    if gold is not None:
+        assert torch.equal(gs.cpu(), torch.from_numpy(gold[f"{name}.gs"]))
+        assert torch.equal(idx.cpu(), torch.from_numpy(gold[f"{name}.idx"]))
+        assert torch.equal(q.cpu().view(torch.uint8), torch.from_numpy(gold[f"{name}.q"]))
+        assert torch.equal(rows, torch.from_numpy(gold[f"{name}.s_rows"]))
+    from mslk_b200._lib import device_status
+    assert device_status() == 0

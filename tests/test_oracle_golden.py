@@ -171,6 +171,31 @@ def test_nvfp4_triton_fixture():
         assert torch.equal(q, torch.from_numpy(gold[f"{name}.q"])), name
 
 
+def test_nvfp4_f16_triton_fixture():
+    """fp16 inputs: the reference's Triton quantizers (dense and stacked, with the per-group global scales) against the
+    oracle, bit for bit except the approximate division of the group scales (a couple of ulps)."""
+    from golden.make_golden import NVFP4_F16_CASES, STACKED_F16_CASE, nvfp4_f16_inputs, unswizzle_stacked_scales
+    gold = load_golden("nvfp4_f16_triton_b200.npz")
+    if gold is None:
+        pytest.skip("fixture captured on a B200 not present yet")
+    for i, (name, shape) in enumerate(NVFP4_F16_CASES):
+        x = nvfp4_f16_inputs(shape, 800 + i)
+        gs = torch.from_numpy(gold[f"{name}.gs"])
+        q, s = oracle.quantize_nvfp4(x, gs)
+        assert torch.equal(q, torch.from_numpy(gold[f"{name}.q"])), name
+        assert torch.equal(u8(s).reshape(-1), torch.from_numpy(gold[f"{name}.s_blocked"]).view(torch.uint8).reshape(-1)), name
+    name, m_sizes, K = STACKED_F16_CASE
+    x = nvfp4_f16_inputs((sum(m_sizes), K), 850)
+    gs = torch.from_numpy(gold[f"{name}.gs"])
+    gs_or, idx_or = oracle.calculate_group_max(x, m_sizes)
+    live = torch.tensor([m > 0 for m in m_sizes])
+    assert torch.allclose(gs_or[live], gs[live], rtol=4e-7, atol=0.0)
+    assert torch.equal(idx_or, torch.from_numpy(gold[f"{name}.idx"]))
+    q, s, _ = oracle.nvfp4_quantize_stacked(m_sizes, x, gs)
+    assert torch.equal(q, torch.from_numpy(gold[f"{name}.q"]))
+    assert torch.equal(unswizzle_stacked_scales(s, m_sizes, K), torch.from_numpy(gold[f"{name}.s_rows"]))
+
+
 def test_mx4_triton_fixture_pins_the_mx4_oracle():
     """Outputs of the reference's triton_quantize_mx4_unpack on a B200 (packed bytes and swizzled e8m0 scales, block
     sizes 32 and 16, floor / even / ceil rounding of the shared exponent) against the C restatement, bit for bit."""
