@@ -248,7 +248,8 @@ int mslk_b200_f4f4bf16_ws(const void *xq, const void *wq, const void *x_scale,
  * Replaces: mslk/quantize/triton/quantize_kernels/mx4.py:28-355 (quantize_mx4_kernel + quantize_mx4) with
  *           fp4_primitives/scale.py:96-265 (shared exponent, normalize, e8m0 encode).
  * x is bf16 or fp16 [M, K] with row stride `row_stride` elements, K % group_size == 0.  rounding_mode follows the
- * reference's RoundingMode: 1 floor, 2 even, 4 ceil (its default); nearest (0) and stochastic (3) are rejected.
+ * reference's RoundingMode: 0 nearest (floor(log2(max) + 0.5)), 1 floor, 2 even, 4 ceil (its default); stochastic (3) is
+ * rejected.
  * q is [M, K/2] bytes; scales is [ceil(M/128)*128 * ceil(K/group_size/4)*4] bytes, written completely (padding = 0).
  */
 int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, int group_size,

@@ -63,7 +63,7 @@ struct Mx4Params {
   int64_t scale_rows;       // rows of the scale buffer (dense: a multiple of 128; stacked: M + 127 G)
   int padded_cols;          // scale slots per padded row, multiple of 4
   int scale_cols;           // K / group
-  int round_add;            // added to the fp32 bits of the group maximum before its exponent is taken
+  int round_add;            // added to the fp32 bits of the group maximum before its exponent is taken; -1: nearest
   const int64_t *m_sizes;   // stacked form: rows per segment (device), else null
   int G;
 };
@@ -185,7 +185,13 @@ __global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Param
           amax = fmaxf(amax, fabsf(v[8 * j + e]));
         }
       }
-      int e = static_cast<int>(((__float_as_uint(amax) + static_cast<uint32_t>(p.round_add)) & 0x7f800000u) >> 23) - 127 - 2;
+      int e;
+      if (p.round_add < 0) {
+        // nearest: floor(log2(max) + 0.5), a zero maximum standing in as the smallest normal bf16 (2^-126)
+        e = static_cast<int>(floorf(log2f(amax == 0.f ? 1.17549435e-38f : amax) + 0.5f)) - 2;
+      } else {
+        e = static_cast<int>(((__float_as_uint(amax) + static_cast<uint32_t>(p.round_add)) & 0x7f800000u) >> 23) - 127 - 2;
+      }
       e = max(-127, min(125, e));
       const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
       uint8_t *dst = p.q + row * (p.K / 2) + static_cast<int64_t>(col) * (kGroup / 2);
@@ -223,12 +229,13 @@ int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, in
   if (stacked && (G < 1 || G > kMaxSegments)) return fail(1, "%s: between 1 and %d segments are supported", name, kMaxSegments);
   int round_add;
   switch (rounding_mode) {
+    case 0: round_add = -1; break;                // nearest: floor(log2(max) + 0.5)
     case 1: round_add = 0; break;                 // floor
     case 2: round_add = (1 << 21) - 1; break;     // even: pre-round at the e2m1 mantissa
     case 4: round_add = (1 << 23) - 1; break;     // ceil (the reference's default)
     default:
-      return fail(1, "%s: rounding mode %d is not implemented (floor = 1, even = 2, ceil = 4 are; nearest and stochastic "
-                     "depend on the GPU's approximate log2 / a Philox stream)", name, rounding_mode);
+      return fail(1, "%s: rounding mode %d is not implemented (nearest = 0, floor = 1, even = 2, ceil = 4 are; stochastic "
+                     "depends on a Philox stream)", name, rounding_mode);
   }
   if (K == 0 || (M == 0 && !stacked)) return 0;
   if (!scales || (M > 0 && (!x || !q))) return fail(1, "%s: null pointer argument", name);

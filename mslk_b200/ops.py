@@ -295,7 +295,7 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
 
 def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
     """MXFP4 quantize (``mslk/quantize/triton/quantize_kernels/mx4.py:216-355``): ``(xq uint8 [..., K/2], scales int8,
-    flattened swizzled [roundup(M,128) * roundup(K/group,4)])``.  ``rounding_mode``: 1 floor, 2 even, 4 ceil."""
+    flattened swizzled [roundup(M,128) * roundup(K/group,4)])``.  ``rounding_mode``: 0 nearest, 1 floor, 2 even, 4 ceil."""
     name = "quantize_mx4"
     dev = _require_cuda(name, x)
     if x.dtype not in (torch.bfloat16, torch.float16):

@@ -33,8 +33,8 @@ from .fp4_primitives import RoundingMode  # noqa: E402,F401  (the reference re-e
 def triton_quantize_mx4_unpack(input: torch.Tensor, group_size: int = 32, ebits: int = 2, mbits: int = 1,
                                rounding_mode: int = 4, stochastic_casting: bool = False, *, seed=None):
     """MXFP4 quantize with the reference's symbol (``mslk/quantize/triton/fp4_quantize.py:46-90``): packed e2m1 bytes
-    ``[..., K // 2]`` and flattened swizzled e8m0 scales (int8).  Rounding modes floor (1), even (2) and ceil (4, the
-    default) are implemented; nearest and stochastic raise."""
+    ``[..., K // 2]`` and flattened swizzled e8m0 scales (int8).  Rounding modes nearest (0), floor (1), even (2) and
+    ceil (4, the default) are implemented; stochastic raises."""
     from ... import ops as _ops
     if ebits != 2 or mbits != 1:
         raise NotImplementedError(f"triton_quantize_mx4_unpack: only E2M1 (ebits=2, mbits=1) is supported, got ebits={ebits}, mbits={mbits}.")

@@ -334,7 +334,7 @@ def gemm_nvfp4(xq, wq, x_scale, w_scale, global_scale):
 # MXFP4 (e8m0 scales per 32 or 16 elements)
 # --------------------------------------------------------------------------
 
-MX_ROUND_ADD = {1: 0, 2: (1 << 21) - 1, 4: (1 << 23) - 1}     # floor / even / ceil of the shared exponent
+MX_ROUND_ADD = {0: -1, 1: 0, 2: (1 << 21) - 1, 4: (1 << 23) - 1}     # nearest / floor / even / ceil of the shared exponent
 
 
 def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):

@@ -353,7 +353,9 @@ ORACLE_API void oracle_quantize_nvfp4_dt(const uint16_t *x16, int dtype, int64_t
  * MXFP4 quantize, the reference's arithmetic (mslk/quantize/triton/quantize_kernels/mx4.py:118-214 with
  * fp4_primitives/scale.py:96-265): per group of `group` elements (32 or 16)
  *   e     = ((bits(max|x|) + round_add) & 0x7F800000) >> 23) - 127 - 2, clamped to [-127, 125]
- *           round_add = 0 (floor), 2^21 - 1 (even), 2^23 - 1 (ceil)
+ *           round_add = 0 (floor), 2^21 - 1 (even), 2^23 - 1 (ceil); round_add < 0: nearest,
+ *           e = floor(log2(max|x| or 2^-126 for 0) + 0.5) - 2 (the GPU's log2f may differ from libm's in the last
+ *           place, so groups whose maximum sits on a rounding boundary can differ by one binade)
  *   scale = byte e + 127 (e8m0);   x^ = e2m1( x * 2^-e ), the factor built from its exponent bits.
  * x: bf16 (dtype 1) or fp16 (dtype 2).  q: [M, K/2]; scales: swizzled like the NVFP4 scales, padded to
  * [ceil(M/128)*128, ceil(K/group/4)*4], padding zero.
@@ -378,7 +380,9 @@ ORACLE_API void oracle_quantize_mx4(const uint16_t *x, int dtype, int64_t M, int
         float v = fabsf(dtype == 2 ? f16_to_f32(xb[i]) : bf16_to_f32(xb[i]));
         if (v > amax) amax = v;
       }
-      int e = (int)(((f32_to_bits(amax) + (uint32_t)round_add) & 0x7F800000u) >> 23) - 127 - 2;
+      int e;
+      if (round_add < 0) e = (int)floorf(log2f(amax == 0.f ? 1.17549435e-38f : amax) + 0.5f) - 2;   /* nearest */
+      else e = (int)(((f32_to_bits(amax) + (uint32_t)round_add) & 0x7F800000u) >> 23) - 127 - 2;
       if (e > 125) e = 125;
       if (e < -127) e = -127;
       scales_swizzled[oracle_nvfp4_scale_offset(m, j, ncb)] = (uint8_t)(e + 127);

@@ -407,6 +407,9 @@ MX4_CASES = [("r128_k64", (128, 64), "bf16"), ("r5_k128", (5, 128), "bf16"), ("r
              ("r64_k512_f16", (64, 512), "f16"), ("r256_k256_wide", (256, 256), "bf16")]
 
 
+MX4_NEAREST_CASES = ("r128_k64", "r129_k96", "r64_k512_f16", "r256_k256_wide")   # rounding mode 0 is captured for these
+
+
 def mx4_inputs(name, shape, dtype, seed):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(shape, generator=g, dtype=torch.float32)
@@ -426,7 +429,9 @@ def leg_gpu_mx4(ref_root: str):
     for i, (name, shape, dtype) in enumerate(MX4_CASES):
         x = mx4_inputs(name, shape, dtype, 700 + i).cuda()
         for group in (32, 16):
-            for mode in (4, 1, 2):
+            for mode in (4, 1, 2, 0):
+                if mode == 0 and name not in MX4_NEAREST_CASES:
+                    continue
                 q, s = quantize_mx4(x, group_size=group, rounding_mode=mode)
                 torch.cuda.synchronize()
                 out[f"{name}.g{group}.m{mode}.q"] = _raw(q.view(torch.uint8))

@@ -7,7 +7,7 @@ import torch
 
 import oracle
 from helpers import assert_sharp_bf16, load_golden
-from golden.make_golden import MX4_CASES, mx4_inputs
+from golden.make_golden import MX4_CASES, MX4_NEAREST_CASES, mx4_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -48,6 +48,15 @@ def test_quantizer_matches_reference_triton_fixture(ops):
                 key = f"{name}.g{group}.m{mode}"
                 assert torch.equal(q.cpu(), torch.from_numpy(gold[key + ".q"])), key
                 assert torch.equal(s.cpu().view(torch.uint8), torch.from_numpy(gold[key + ".s"]).reshape(-1)), key
+            if name in MX4_NEAREST_CASES and f"{name}.g{group}.m0.q" in gold:
+                # nearest: floor(log2(max) + 0.5) through the GPU's log2f -- the same instruction sequence on both sides
+                q, s = ops.quantize_mx4(x, group, 0)
+                key = f"{name}.g{group}.m0"
+                assert torch.equal(q.cpu(), torch.from_numpy(gold[key + ".q"])), key
+                assert torch.equal(s.cpu().view(torch.uint8), torch.from_numpy(gold[key + ".s"]).reshape(-1)), key
+                # the C restatement uses libm's log2f: equal except where a maximum sits on a rounding boundary
+                q_or, s_or = oracle.quantize_mx4(x.cpu(), group, 0)
+                assert float((s.cpu().view(torch.uint8) != s_or).float().mean()) < 1e-3, key
     assert _status() == 0
 
 
@@ -61,7 +70,7 @@ def test_quantizer_python_symbols_and_errors(ops):
     q2, s2 = triton_quantize_mx4(x)
     assert torch.equal(q, q2) and torch.equal(s, s2)
     with pytest.raises(RuntimeError, match="rounding mode"):
-        ops.quantize_mx4(x, 32, 0)
+        ops.quantize_mx4(x, 32, 3)
     with pytest.raises(AssertionError):
         ops.quantize_mx4(x[..., :48], 32, 4)
 
