@@ -248,12 +248,22 @@ int mslk_b200_f4f4bf16_ws(const void *xq, const void *wq, const void *x_scale,
  * Replaces: mslk/quantize/triton/quantize_kernels/mx4.py:28-355 (quantize_mx4_kernel + quantize_mx4) with
  *           fp4_primitives/scale.py:96-265 (shared exponent, normalize, e8m0 encode).
  * x is bf16 or fp16 [M, K] with row stride `row_stride` elements, K % group_size == 0.  rounding_mode follows the
- * reference's RoundingMode: 0 nearest (floor(log2(max) + 0.5)), 1 floor, 2 even, 4 ceil (its default); stochastic (3) is
- * rejected.
+ * reference's RoundingMode: 0 nearest (floor(log2(max) + 0.5)), 1 floor, 2 even, 4 ceil (its default); stochastic (3)
+ * needs a seed and goes through the _seeded entry point below.
  * q is [M, K/2] bytes; scales is [ceil(M/128)*128 * ceil(K/group_size/4)*4] bytes, written completely (padding = 0).
  */
 int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, int group_size,
                            int rounding_mode, void *q, void *scales, void *stream);
+
+/*
+ * The same with the seed of the stochastic mode (rounding_mode 3; the other modes ignore it): the shared exponent and the
+ * conversion of every element are perturbed by two Philox-4x32-7 streams keyed by `seed`, counter = the group's /
+ * element's index (mslk/quantize/triton/fp4_primitives/scale.py:213-261, tl.randint(seed, offset, n_rounds=7)); the
+ * reference passes the caller's seed masked to 63 bits, or the CUDA generator's initial seed
+ * (mslk/quantize/triton/quantize_kernels/__init__.py:20-44).  Same seed, same bytes as the reference's kernel.
+ */
+int mslk_b200_quantize_mx4_seeded(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, int group_size,
+                                  int rounding_mode, uint64_t seed, void *q, void *scales, void *stream);
 
 /*
  * MXFP4 quantization of stacked segments (MoE activations): segment g owns m_sizes[g] (device int64 [G]) consecutive
@@ -266,6 +276,12 @@ int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t K, int64
 int mslk_b200_quantize_mx4_stacked(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
                                    const int64_t *m_sizes, int64_t G, int group_size, int rounding_mode, void *q,
                                    void *scales, void *stream);
+
+/* Stacked form with the seed of the stochastic mode; the random streams are indexed by the row of the padded scale
+ * matrix, as in the reference's kernel (mslk/quantize/triton/quantize_kernels/mx4_stacked.py:128-146). */
+int mslk_b200_quantize_mx4_stacked_seeded(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                          const int64_t *m_sizes, int64_t G, int group_size, int rounding_mode,
+                                          uint64_t seed, void *q, void *scales, void *stream);
 
 /*
  * MXFP4 GEMMs:  y = bf16(sum_blocks 2^(sx-127) * 2^(sw-127) * sum_block x^ * w^), the forms of f4f4bf16,

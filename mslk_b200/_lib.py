@@ -57,6 +57,11 @@ lib.mslk_b200_quantize_mx4.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _int, 
 lib.mslk_b200_quantize_mx4.restype = _int
 lib.mslk_b200_quantize_mx4_stacked.argtypes = [_vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _int, _vp, _vp, _vp]
 lib.mslk_b200_quantize_mx4_stacked.restype = _int
+lib.mslk_b200_quantize_mx4_seeded.argtypes = [_vp, _int, _i64, _i64, _i64, _int, _int, ctypes.c_uint64, _vp, _vp, _vp]
+lib.mslk_b200_quantize_mx4_seeded.restype = _int
+lib.mslk_b200_quantize_mx4_stacked_seeded.argtypes = [_vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _int, ctypes.c_uint64,
+                                                      _vp, _vp, _vp]
+lib.mslk_b200_quantize_mx4_stacked_seeded.restype = _int
 lib.mslk_b200_f4f4bf16_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]
 lib.mslk_b200_f4f4bf16_mx.restype = _int
 lib.mslk_b200_f4f4bf16_grouped_stacked_mx.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp]

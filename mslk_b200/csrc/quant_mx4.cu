@@ -10,6 +10,15 @@
 //     x^     = e2m1_rn_satfinite(x * 2^-e)          (the factor built from its exponent bits)
 // Padded scale slots (rows up to a multiple of 128, groups up to a multiple of 4 per row) are written as 0.
 //
+// Stochastic rounding (rounding mode 3, fp4_primitives/scale.py:213-261): two counter-based random streams, Philox-4x32
+// with 7 rounds, key = the 64-bit seed (low word first), counter = (offset, 0, 0, 0), first output word:
+//     group stream    seed,               offset = row * (K / group) + group index:
+//                     e = exponent of bits(max |x|) + (rand & (2^22 - 1)), then as above
+//     element stream  seed ^ 0x5A5A5A5A,  offset = row * K + column:
+//                     bits(x * 2^-e) + (rand & (2^22 - 1)) - (2^21 - 1) before the round-to-nearest conversion
+// with 32-bit wrapping offsets; `row` is the row of X (dense) or of the padded scale matrix (stacked).  Integer work
+// again, so the same seed gives the reference's bytes.
+//
 // Work unit = one warp's share of a 128-row x 4-group tile (one 512-byte scale atom): warp w of the tile takes rows
 // {2w, 2w+1} + {0, 32, 64, 96} and the 4 groups of each, one group (64 or 32 input bytes) per lane.  With
 // lane = (row & 1) * 16 + (row / 32) * 4 + group, the 32 scale bytes of a unit are the contiguous bytes [32w, 32w + 32)
@@ -26,6 +35,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 #include "../../include/mslk_b200.h"
 #include "host.h"
@@ -46,6 +57,24 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&v)[8]) {
   return r;
 }
 
+// Philox-4x32, `kRounds` rounds, counter (c0, 0, 0, 0), key (k0, k1); returns the first word of the output block.
+template <int kRounds>
+__device__ __forceinline__ uint32_t philox_first_word(uint32_t k0, uint32_t k1, uint32_t c0) {
+  constexpr uint32_t kMulA = 0xD2511F53u, kMulB = 0xCD9E8D57u, kKeyA = 0x9E3779B9u, kKeyB = 0xBB67AE85u;
+  uint32_t c1 = 0, c2 = 0, c3 = 0;
+#pragma unroll
+  for (int r = 0; r < kRounds; ++r) {
+    const uint64_t pa = static_cast<uint64_t>(kMulA) * c0, pb = static_cast<uint64_t>(kMulB) * c2;   // one wide multiply each
+    c0 = static_cast<uint32_t>(pb >> 32) ^ c1 ^ k0;
+    c2 = static_cast<uint32_t>(pa >> 32) ^ c3 ^ k1;
+    c1 = static_cast<uint32_t>(pb);
+    c3 = static_cast<uint32_t>(pa);
+    k0 += kKeyA;
+    k1 += kKeyB;
+  }
+  return c0;
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>
@@ -64,6 +93,7 @@ struct Mx4Params {
   int padded_cols;          // scale slots per padded row, multiple of 4
   int scale_cols;           // K / group
   int round_add;            // added to the fp32 bits of the group maximum before its exponent is taken; -1: nearest
+  uint32_t seed_lo, seed_hi;   // stochastic rounding only
   const int64_t *m_sizes;   // stacked form: rows per segment (device), else null
   int G;
 };
@@ -102,8 +132,8 @@ struct GroupIn {
   uint4 v[kGroup / 8];   // 32 or 16 two-byte elements
 };
 
-template <typename T, int kGroup, bool kStacked>
-__global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Params p) {
+template <typename T, int kGroup, bool kStacked, bool kSr>
+__global__ void __launch_bounds__(kThreadsMx, kSr ? 2 : 4) quant_mx4_kernel(const Mx4Params p) {
   __shared__ int s_row_end[kStacked ? kMaxSegments : 1];
   __shared__ int s_pad_end[kStacked ? kMaxSegments : 1];
   const int tid = threadIdx.x, lane = tid & 31;
@@ -124,8 +154,9 @@ __global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Param
   const int d_tile = stride / kWarpsPerTile, d_w = stride - d_tile * kWarpsPerTile;
   const int d_tr = d_tile / n_col_tiles, d_tc = d_tile - d_tr * n_col_tiles;
   int g = 0;
+  auto padded_row = [&]() { return tr * 128 + row_in_tile + 2 * w; };   // row of the padded scale matrix
   auto locate_here = [&](int64_t &row, int &col) {
-    const int pr = tr * 128 + row_in_tile + 2 * w;   // row of the padded scale matrix
+    const int pr = padded_row();
     col = tc * 4 + c;
     bool live = pr < p.M;
     row = pr;
@@ -159,17 +190,19 @@ __global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Param
   int64_t row;
   int col;
   bool live = locate_here(row, col);
+  int prow = padded_row();
   GroupIn<kGroup> cur{};
   if (live) load(row, col, cur);
   while (unit < total_units) {
     const int nunit = unit + stride;
     int64_t nrow = 0;
-    int ncol = 0;
+    int ncol = 0, nprow = 0;
     bool nlive = false;
     GroupIn<kGroup> nxt{};
     if (nunit < total_units) {
       advance();
       nlive = locate_here(nrow, ncol);
+      nprow = padded_row();
       if (nlive) load(nrow, ncol, nxt);
     }
     uint8_t s8 = 0;
@@ -186,7 +219,13 @@ __global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Param
         }
       }
       int e;
-      if (p.round_add < 0) {
+      // row of the random streams' offsets: the row of X, or of the padded scale matrix for stacked segments
+      const uint32_t sr_row = kStacked ? static_cast<uint32_t>(prow) : static_cast<uint32_t>(row);
+      if constexpr (kSr) {
+        const uint32_t off = sr_row * static_cast<uint32_t>(p.scale_cols) + static_cast<uint32_t>(col);
+        const uint32_t rnd = philox_first_word<7>(p.seed_lo, p.seed_hi, off) & 0x3fffffu;
+        e = static_cast<int>(((__float_as_uint(amax) + rnd) & 0x7f800000u) >> 23) - 127 - 2;
+      } else if (p.round_add < 0) {
         // nearest: floor(log2(max) + 0.5), a zero maximum standing in as the smallest normal bf16 (2^-126)
         e = static_cast<int>(floorf(log2f(amax == 0.f ? 1.17549435e-38f : amax) + 0.5f)) - 2;
       } else {
@@ -202,7 +241,15 @@ __global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Param
         for (int h = 0; h < 2; ++h) {
           float y[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) y[k] = v[16 * j + 8 * h + k] * inv;
+          for (int k = 0; k < 8; ++k) {
+            y[k] = v[16 * j + 8 * h + k] * inv;
+            if constexpr (kSr) {
+              const uint32_t off = sr_row * static_cast<uint32_t>(p.K) +
+                                   static_cast<uint32_t>(col * kGroup + 16 * j + 8 * h + k);
+              const uint32_t rnd = philox_first_word<7>(p.seed_lo ^ 0x5A5A5A5Au, p.seed_hi, off) & 0x3fffffu;
+              y[k] = __uint_as_float(__float_as_uint(y[k]) + rnd - 0x1fffffu);
+            }
+          }
           wd[h] = cvt_e2m1x8(y);
         }
         *reinterpret_cast<uint2 *>(dst + 8 * j) = make_uint2(wd[0], wd[1]);
@@ -214,13 +261,14 @@ __global__ void __launch_bounds__(kThreadsMx, 4) quant_mx4_kernel(const Mx4Param
     unit = nunit;
     row = nrow;
     col = ncol;
+    prow = nprow;
     live = nlive;
     cur = nxt;
   }
 }
 
 int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride, const int64_t *m_sizes,
-            int64_t G, int group_size, int rounding_mode, void *q, void *scales, cudaStream_t st) {
+            int64_t G, int group_size, int rounding_mode, uint64_t seed, void *q, void *scales, cudaStream_t st) {
   const bool stacked = m_sizes != nullptr;
   if (M < 0 || K < 0) return fail(1, "%s: bad shape", name);
   if (group_size != 32 && group_size != 16) return fail(1, "%s: group_size must be 32 or 16 (got %d)", name, group_size);
@@ -232,10 +280,11 @@ int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, in
     case 0: round_add = -1; break;                // nearest: floor(log2(max) + 0.5)
     case 1: round_add = 0; break;                 // floor
     case 2: round_add = (1 << 21) - 1; break;     // even: pre-round at the e2m1 mantissa
+    case 3: round_add = 0; break;                 // stochastic: random bits take its place
     case 4: round_add = (1 << 23) - 1; break;     // ceil (the reference's default)
     default:
-      return fail(1, "%s: rounding mode %d is not implemented (nearest = 0, floor = 1, even = 2, ceil = 4 are; stochastic "
-                     "depends on a Philox stream)", name, rounding_mode);
+      return fail(1, "%s: rounding mode %d does not exist (nearest = 0, floor = 1, even = 2, stochastic = 3, ceil = 4)",
+                  name, rounding_mode);
   }
   if (K == 0 || (M == 0 && !stacked)) return 0;
   if (!scales || (M > 0 && (!x || !q))) return fail(1, "%s: null pointer argument", name);
@@ -254,6 +303,8 @@ int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, in
   p.scale_cols = static_cast<int>(K / group_size);
   p.padded_cols = (p.scale_cols + 3) / 4 * 4;
   p.round_add = round_add;
+  p.seed_lo = static_cast<uint32_t>(seed);
+  p.seed_hi = static_cast<uint32_t>(seed >> 32);
   p.m_sizes = m_sizes;
   p.G = static_cast<int>(G);
   const int64_t units = ((p.scale_rows + 127) / 128) * (p.padded_cols / 4) * kWarpsPerTile;
@@ -262,13 +313,18 @@ int run_mx4(const char *name, const void *x, int dtype, int64_t M, int64_t K, in
   const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
   const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
   auto go = [&](auto kernel) { kernel<<<blocks, kThreadsMx, 0, st>>>(p); };
-  const bool bf = dtype == MSLK_B200_BF16;
-  if (stacked) {
-    if (bf) group_size == 32 ? go(quant_mx4_kernel<__nv_bfloat16, 32, true>) : go(quant_mx4_kernel<__nv_bfloat16, 16, true>);
-    else group_size == 32 ? go(quant_mx4_kernel<__half, 32, true>) : go(quant_mx4_kernel<__half, 16, true>);
+  auto pick = [&](auto type_tag, auto group_tag) {
+    using T = decltype(type_tag);
+    constexpr int kG = decltype(group_tag)::value;
+    if (rounding_mode == 3) stacked ? go(quant_mx4_kernel<T, kG, true, true>) : go(quant_mx4_kernel<T, kG, false, true>);
+    else stacked ? go(quant_mx4_kernel<T, kG, true, false>) : go(quant_mx4_kernel<T, kG, false, false>);
+  };
+  if (dtype == MSLK_B200_BF16) {
+    if (group_size == 32) pick(__nv_bfloat16{}, std::integral_constant<int, 32>{});
+    else pick(__nv_bfloat16{}, std::integral_constant<int, 16>{});
   } else {
-    if (bf) group_size == 32 ? go(quant_mx4_kernel<__nv_bfloat16, 32, false>) : go(quant_mx4_kernel<__nv_bfloat16, 16, false>);
-    else group_size == 32 ? go(quant_mx4_kernel<__half, 32, false>) : go(quant_mx4_kernel<__half, 16, false>);
+    if (group_size == 32) pick(__half{}, std::integral_constant<int, 32>{});
+    else pick(__half{}, std::integral_constant<int, 16>{});
   }
   return check_cuda(cudaGetLastError(), name);
 }
@@ -280,7 +336,17 @@ MSLK_API int mslk_b200_quantize_mx4(const void *x, int dtype, int64_t M, int64_t
                                     int rounding_mode, void *q, void *scales, void *stream) {
   using namespace mslk_b200;
   clear_error();
-  return run_mx4("quantize_mx4", x, dtype, M, K, row_stride, nullptr, 1, group_size, rounding_mode, q, scales,
+  if (rounding_mode == 3) return fail(1, "quantize_mx4: stochastic rounding takes a seed: call mslk_b200_quantize_mx4_seeded");
+  return run_mx4("quantize_mx4", x, dtype, M, K, row_stride, nullptr, 1, group_size, rounding_mode, 0, q, scales,
+                 static_cast<cudaStream_t>(stream));
+}
+
+MSLK_API int mslk_b200_quantize_mx4_seeded(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                           int group_size, int rounding_mode, uint64_t seed, void *q, void *scales,
+                                           void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  return run_mx4("quantize_mx4", x, dtype, M, K, row_stride, nullptr, 1, group_size, rounding_mode, seed, q, scales,
                  static_cast<cudaStream_t>(stream));
 }
 
@@ -290,6 +356,18 @@ MSLK_API int mslk_b200_quantize_mx4_stacked(const void *x, int dtype, int64_t M,
   using namespace mslk_b200;
   clear_error();
   if (!m_sizes) return fail(1, "quantize_mx4_stacked: m_sizes is null");
-  return run_mx4("quantize_mx4_stacked", x, dtype, M, K, row_stride, m_sizes, G, group_size, rounding_mode, q, scales,
+  if (rounding_mode == 3)
+    return fail(1, "quantize_mx4_stacked: stochastic rounding takes a seed: call mslk_b200_quantize_mx4_stacked_seeded");
+  return run_mx4("quantize_mx4_stacked", x, dtype, M, K, row_stride, m_sizes, G, group_size, rounding_mode, 0, q, scales,
                  static_cast<cudaStream_t>(stream));
+}
+
+MSLK_API int mslk_b200_quantize_mx4_stacked_seeded(const void *x, int dtype, int64_t M, int64_t K, int64_t row_stride,
+                                                   const int64_t *m_sizes, int64_t G, int group_size, int rounding_mode,
+                                                   uint64_t seed, void *q, void *scales, void *stream) {
+  using namespace mslk_b200;
+  clear_error();
+  if (!m_sizes) return fail(1, "quantize_mx4_stacked: m_sizes is null");
+  return run_mx4("quantize_mx4_stacked", x, dtype, M, K, row_stride, m_sizes, G, group_size, rounding_mode, seed, q,
+                 scales, static_cast<cudaStream_t>(stream));
 }

@@ -293,9 +293,20 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: Optional[torch.Tensor]):
     return q.view(*lead, -1, K // 2), s.view(*lead, -1, pc)
 
 
-def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
+def _mx4_seed(seed, rounding_mode: int, dev) -> int:
+    """The seed the reference hands its kernel (``mslk/quantize/triton/quantize_kernels/__init__.py:20-44``): 0 unless
+    the mode is stochastic; else the caller's seed, or the CUDA generator's initial seed, masked to 63 bits."""
+    if int(rounding_mode) != 3:
+        return 0
+    if seed is None:
+        seed = torch.cuda.default_generators[dev.index].initial_seed()
+    return int(seed) & ((1 << 63) - 1)
+
+
+def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4, seed=None):
     """MXFP4 quantize (``mslk/quantize/triton/quantize_kernels/mx4.py:216-355``): ``(xq uint8 [..., K/2], scales int8,
-    flattened swizzled [roundup(M,128) * roundup(K/group,4)])``.  ``rounding_mode``: 0 nearest, 1 floor, 2 even, 4 ceil."""
+    flattened swizzled [roundup(M,128) * roundup(K/group,4)])``.  ``rounding_mode``: 0 nearest, 1 floor, 2 even,
+    3 stochastic (``seed``, default the CUDA generator's initial seed), 4 ceil."""
     name = "quantize_mx4"
     dev = _require_cuda(name, x)
     if x.dtype not in (torch.bfloat16, torch.float16):
@@ -310,12 +321,13 @@ def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
     q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
     s = torch.empty((pr * pc,), dtype=torch.int8, device=dev)
     with torch.cuda.device(dev):
-        check(lib.mslk_b200_quantize_mx4(_ptr(x2), _DTYPE_CODE[x.dtype], M, K, x2.stride(0), int(group_size),
-                                         int(rounding_mode), _ptr(q), _ptr(s), _stream(dev)), name)
+        check(lib.mslk_b200_quantize_mx4_seeded(_ptr(x2), _DTYPE_CODE[x.dtype], M, K, x2.stride(0), int(group_size),
+                                                int(rounding_mode), _mx4_seed(seed, rounding_mode, dev), _ptr(q), _ptr(s),
+                                                _stream(dev)), name)
     return q.view(*lead, -1, K // 2), s
 
 
-def quantize_mx4_stacked(m_sizes: torch.Tensor, x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
+def quantize_mx4_stacked(m_sizes: torch.Tensor, x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4, seed=None):
     """MXFP4 quantize of stacked MoE segments (``mslk/quantize/triton/quantize_kernels/mx4_stacked.py:221-360``):
     ``(xq uint8 [M, K/2], scales int8 flattened [(M + 127 G) * roundup(K/group, 4)])`` with every segment's scale rows
     starting on a 128-row boundary; padding is zero."""
@@ -334,9 +346,10 @@ def quantize_mx4_stacked(m_sizes: torch.Tensor, x: torch.Tensor, group_size: int
     q = torch.empty((M, K // 2), dtype=torch.uint8, device=dev)
     s = torch.empty(((M + 127 * G) * pc,), dtype=torch.int8, device=dev)
     with torch.cuda.device(dev):
-        check(lib.mslk_b200_quantize_mx4_stacked(_ptr(x2), _DTYPE_CODE[x.dtype], M, K, x2.stride(0),
-                                                 _ptr(m_sizes.contiguous()), G, int(group_size), int(rounding_mode),
-                                                 _ptr(q), _ptr(s), _stream(dev)), name)
+        check(lib.mslk_b200_quantize_mx4_stacked_seeded(_ptr(x2), _DTYPE_CODE[x.dtype], M, K, x2.stride(0),
+                                                        _ptr(m_sizes.contiguous()), G, int(group_size), int(rounding_mode),
+                                                        _mx4_seed(seed, rounding_mode, dev), _ptr(q), _ptr(s),
+                                                        _stream(dev)), name)
     return q, s
 
 

@@ -14,4 +14,4 @@ def quantize_mx4_stacked(m_sizes: torch.Tensor, x: torch.Tensor, group_size: int
     flattened scale buffer of ``(M + 127 * num_segments) * roundup(N / group_size, 4)`` bytes in which every segment
     starts on a 128-row boundary (padding is zero)."""
     from .... import ops as _ops
-    return _ops.quantize_mx4_stacked(m_sizes, x, group_size, int(rounding_mode))
+    return _ops.quantize_mx4_stacked(m_sizes, x, group_size, int(rounding_mode), seed)

@@ -73,6 +73,10 @@ def lib() -> ctypes.CDLL:
         L.oracle_quantize_nvfp4_dt.restype = None
         L.oracle_quantize_mx4.argtypes = [vp, i32, i64, i64, i32, i32, vp, vp]
         L.oracle_quantize_mx4.restype = None
+        L.oracle_quantize_mx4_stochastic.argtypes = [vp, i32, i64, i64, i32, ctypes.c_uint64, vp, vp, vp]
+        L.oracle_quantize_mx4_stochastic.restype = None
+        L.oracle_philox7_first_word.argtypes = [ctypes.c_uint64, ctypes.c_uint32]
+        L.oracle_philox7_first_word.restype = ctypes.c_uint32
         L.oracle_gemm_nvfp4.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, vp]
         L.oracle_gemm_nvfp4.restype = None
         L.oracle_check_fma_division.argtypes = [vp, vp, i64]
@@ -337,15 +341,24 @@ def gemm_nvfp4(xq, wq, x_scale, w_scale, global_scale):
 MX_ROUND_ADD = {0: -1, 1: 0, 2: (1 << 21) - 1, 4: (1 << 23) - 1}     # nearest / floor / even / ceil of the shared exponent
 
 
-def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4):
+def quantize_mx4(x: torch.Tensor, group_size: int = 32, rounding_mode: int = 4, seed: Optional[int] = None,
+                 stream_rows: Optional[torch.Tensor] = None):
     """MXFP4 quantize (``mslk/quantize/triton/quantize_kernels/mx4.py:28-355``): returns
-    ``(xq uint8 [M, K/2], scales uint8, flattened swizzled [ceil(M/128)*128 * ceil(K/group/4)*4])``."""
+    ``(xq uint8 [M, K/2], scales uint8, flattened swizzled [ceil(M/128)*128 * ceil(K/group/4)*4])``.  Rounding mode 3
+    (stochastic) needs ``seed``; ``stream_rows`` (int32 per row) replaces the row index its random streams use."""
     x2 = _cpu(x).reshape(-1, x.shape[-1]).contiguous()
     M, K = x2.shape
     assert K % group_size == 0 and x2.dtype in (torch.bfloat16, torch.float16)
     pr, pc = (M + 127) // 128 * 128, (K // group_size + 3) // 4 * 4
     q = torch.empty((M, K // 2), dtype=torch.uint8)
     s = torch.empty((pr * pc,), dtype=torch.uint8)
+    if int(rounding_mode) == 3:
+        assert seed is not None, "stochastic rounding needs a seed"
+        rows = None if stream_rows is None else stream_rows.to(torch.int32).contiguous()
+        lib().oracle_quantize_mx4_stochastic(_p(x2.view(torch.int16)), 1 if x2.dtype == torch.bfloat16 else 2, M, K,
+                                             group_size, int(seed) & 0x7FFFFFFFFFFFFFFF,
+                                             None if rows is None else _p(rows), _p(q), _p(s))
+        return q, s
     lib().oracle_quantize_mx4(_p(x2.view(torch.int16)), 1 if x2.dtype == torch.bfloat16 else 2, M, K, group_size,
                               MX_ROUND_ADD[int(rounding_mode)], _p(q), _p(s))
     return q, s

@@ -113,7 +113,7 @@ ORACLE_API uint8_t oracle_f32_to_e2m1(float f) {
   uint8_t sign = (f32_to_bits(f) >> 28) & 0x8u;
   float a = fabsf(f);
   uint8_t m;
-  if (a != a) return (uint8_t)(sign | 7u); /* NaN saturates to max magnitude */
+  if (a != a) return 7u;       /* NaN of either sign: +6, what cvt.rn.satfinite.e2m1x2.f32 returns on sm_100a */
   if (a <= 0.25f) m = 0;       /* tie 0.25 -> 0   (code 0 even) */
   else if (a < 0.75f) m = 1;   /* tie 0.75 -> 1.0 (code 2 even) */
   else if (a <= 1.25f) m = 2;  /* tie 1.25 -> 1.0 (code 2 even) */
@@ -391,6 +391,73 @@ ORACLE_API void oracle_quantize_mx4(const uint16_t *x, int dtype, int64_t M, int
         volatile float a = (dtype == 2 ? f16_to_f32(xb[i]) : bf16_to_f32(xb[i])) * inv;
         volatile float b = (dtype == 2 ? f16_to_f32(xb[i + 1]) : bf16_to_f32(xb[i + 1])) * inv;
         q[m * (K / 2) + (j * group + i) / 2] = (uint8_t)(oracle_f32_to_e2m1(a) | (oracle_f32_to_e2m1(b) << 4));
+      }
+    }
+  }
+}
+
+/*
+ * Philox-4x32 with 7 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", 2011), the generator behind
+ * the reference's tl.randint(seed, offset, n_rounds=7) for 32-bit offsets: key = (seed low word, seed high word),
+ * counter = (offset, 0, 0, 0), result = first word of the output block.
+ */
+ORACLE_API uint32_t oracle_philox7_first_word(uint64_t seed, uint32_t offset) {
+  const uint32_t MA = 0xD2511F53u, MB = 0xCD9E8D57u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32), c0 = offset, c1 = 0, c2 = 0, c3 = 0;
+  for (int r = 0; r < 7; ++r) {
+    uint64_t pa = (uint64_t)MA * c0, pb = (uint64_t)MB * c2;
+    uint32_t n0 = (uint32_t)(pb >> 32) ^ c1 ^ k0, n2 = (uint32_t)(pa >> 32) ^ c3 ^ k1;
+    c1 = (uint32_t)pb;
+    c3 = (uint32_t)pa;
+    c0 = n0;
+    c2 = n2;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c0;
+}
+
+/*
+ * MXFP4 quantize with stochastic rounding (rounding mode 3; mslk/quantize/triton/fp4_primitives/scale.py:141-143 and
+ * 213-261): as oracle_quantize_mx4 with
+ *   e        from bits(max|x|) + (philox(seed, row * (K / group) + j) & (2^22 - 1))
+ *   x * 2^-e perturbed in its bits by (philox(seed ^ 0x5A5A5A5A, row * K + column) & (2^22 - 1)) - (2^21 - 1)
+ * before the round-to-nearest conversion (a bit pattern that became a NaN saturates to +-6 like the GPU's
+ * cvt.rn.satfinite does), offsets in wrapping 32-bit arithmetic.  `stream_rows` gives the row index the random streams
+ * use for each row of x (the stacked kernel counts rows of the padded scale matrix); NULL = the row itself.
+ */
+ORACLE_API void oracle_quantize_mx4_stochastic(const uint16_t *x, int dtype, int64_t M, int64_t K, int group,
+                                               uint64_t seed, const int32_t *stream_rows, uint8_t *q,
+                                               uint8_t *scales_swizzled) {
+  int64_t nblk = K / group;
+  int64_t ncb = (nblk + 3) / 4;
+  int64_t nrb = (M + 127) / 128;
+  memset(scales_swizzled, 0, (size_t)(nrb * ncb * 512));
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    uint32_t srow = stream_rows ? (uint32_t)stream_rows[m] : (uint32_t)m;
+    for (int64_t j = 0; j < nblk; ++j) {
+      const uint16_t *xb = x + m * K + j * group;
+      float amax = 0.f;
+      for (int i = 0; i < group; ++i) {
+        float v = fabsf(dtype == 2 ? f16_to_f32(xb[i]) : bf16_to_f32(xb[i]));
+        if (v > amax) amax = v;
+      }
+      uint32_t rg = oracle_philox7_first_word(seed, srow * (uint32_t)nblk + (uint32_t)j) & 0x3FFFFFu;
+      int e = (int)(((f32_to_bits(amax) + rg) & 0x7F800000u) >> 23) - 127 - 2;
+      if (e > 125) e = 125;
+      if (e < -127) e = -127;
+      scales_swizzled[oracle_nvfp4_scale_offset(m, j, ncb)] = (uint8_t)(e + 127);
+      float inv = bits_to_f32((uint32_t)(127 - e) << 23);
+      uint8_t nib[2];
+      for (int i = 0; i < group; i += 2) {
+        for (int h = 0; h < 2; ++h) {
+          volatile float a = (dtype == 2 ? f16_to_f32(xb[i + h]) : bf16_to_f32(xb[i + h])) * inv;
+          uint32_t re = oracle_philox7_first_word(seed ^ 0x5A5A5A5Aull,
+                                                  srow * (uint32_t)K + (uint32_t)(j * group + i + h)) & 0x3FFFFFu;
+          nib[h] = oracle_f32_to_e2m1(bits_to_f32(f32_to_bits(a) + re - 0x1FFFFFu));
+        }
+        q[m * (K / 2) + (j * group + i) / 2] = (uint8_t)(nib[0] | (nib[1] << 4));
       }
     }
   }

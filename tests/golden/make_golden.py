@@ -410,6 +410,11 @@ MX4_CASES = [("r128_k64", (128, 64), "bf16"), ("r5_k128", (5, 128), "bf16"), ("r
 MX4_NEAREST_CASES = ("r128_k64", "r129_k96", "r64_k512_f16", "r256_k256_wide")   # rounding mode 0 is captured for these
 
 
+MX4_STOCHASTIC_CASES = ("r128_k64", "r129_k96", "r64_k512_f16", "r256_k256_wide")    # rounding mode 3 likewise
+MX4_SEEDS = (0x12345678, (1 << 62) + 12345)
+MX4_STACKED_STOCHASTIC_CASES = [("st_50_30_48", [50, 30, 48], 64), ("st_130_0_7", [130, 0, 7], 256)]
+
+
 def mx4_inputs(name, shape, dtype, seed):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(shape, generator=g, dtype=torch.float32)
@@ -422,7 +427,8 @@ def mx4_inputs(name, shape, dtype, seed):
 
 
 def leg_gpu_mx4(ref_root: str):
-    """quantize_mx4 of the reference (Triton) on a B200: group sizes 32 / 16, rounding floor / even / ceil."""
+    """quantize_mx4 of the reference (Triton) on a B200: group sizes 32 / 16, every rounding mode (stochastic with
+    fixed seeds, dense and stacked)."""
     _import_reference(ref_root)
     from mslk.quantize.triton.quantize_kernels.mx4 import quantize_mx4
     out = {}
@@ -436,6 +442,21 @@ def leg_gpu_mx4(ref_root: str):
                 torch.cuda.synchronize()
                 out[f"{name}.g{group}.m{mode}.q"] = _raw(q.view(torch.uint8))
                 out[f"{name}.g{group}.m{mode}.s"] = _raw(s.view(torch.uint8))
+            if name in MX4_STOCHASTIC_CASES:
+                for seed in MX4_SEEDS:
+                    q, s = quantize_mx4(x, group_size=group, rounding_mode=3, seed=seed)
+                    torch.cuda.synchronize()
+                    out[f"{name}.g{group}.m3.seed{seed}.q"] = _raw(q.view(torch.uint8))
+                    out[f"{name}.g{group}.m3.seed{seed}.s"] = _raw(s.view(torch.uint8))
+    # stacked segments with stochastic rounding: the random streams count rows of the padded scale matrix
+    from mslk.quantize.triton.quantize_kernels.mx4_stacked import quantize_mx4_stacked
+    for name, m_sizes, K in MX4_STACKED_STOCHASTIC_CASES:
+        x = mx4_inputs(name, (sum(m_sizes), K), "bf16", 900 + K).cuda()
+        ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+        q, s = quantize_mx4_stacked(ms, x, group_size=32, rounding_mode=3, seed=MX4_SEEDS[0])
+        torch.cuda.synchronize()
+        out[f"{name}.m3.q"] = _raw(q.view(torch.uint8))
+        out[f"{name}.m3.s"] = _raw(s.view(torch.uint8))
     np.savez_compressed(os.path.join(HERE, "mx4_triton_b200.npz"), **out)
     print("gpu mx4 leg written")
 

@@ -7,7 +7,8 @@ import torch
 
 import oracle
 from helpers import assert_sharp_bf16, load_golden
-from golden.make_golden import MX4_CASES, MX4_NEAREST_CASES, mx4_inputs
+from golden.make_golden import (MX4_CASES, MX4_NEAREST_CASES, MX4_SEEDS, MX4_STACKED_STOCHASTIC_CASES, MX4_STOCHASTIC_CASES,
+                                mx4_inputs)
 
 pytestmark = pytest.mark.gpu
 
@@ -60,6 +61,85 @@ def test_quantizer_matches_reference_triton_fixture(ops):
     assert _status() == 0
 
 
+@pytest.mark.parametrize("group", [32, 16])
+def test_stochastic_rounding_bit_exact_vs_oracle(ops, group):
+    """Rounding mode 3 (the reference's tl.randint streams, mslk/quantize/triton/fp4_primitives/scale.py:213-261): same
+    seed, same bytes as the C restatement -- integer work on both sides -- including zero groups, whose perturbed bit
+    patterns turn into NaNs that the conversion saturates."""
+    for i, (name, shape, dtype) in enumerate(MX4_CASES):
+        x = mx4_inputs(name, shape, dtype, 700 + i)
+        for seed in MX4_SEEDS + (0, 7):
+            q_ref, s_ref = oracle.quantize_mx4(x, group, 3, seed=seed)
+            q, s = ops.quantize_mx4(x.cuda(), group, 3, seed=seed)
+            assert torch.equal(s.cpu().view(torch.uint8), s_ref), (name, group, seed)
+            assert torch.equal(q.cpu(), q_ref), (name, group, seed)
+    assert _status() == 0
+
+
+def test_stochastic_rounding_matches_reference_triton_fixture(ops):
+    gold = load_golden("mx4_triton_b200.npz")
+    if gold is None or not any(".m3." in k for k in gold.keys()):
+        pytest.skip("fixture of the stochastic mode captured from the reference's Triton kernel not present")
+    for i, (name, shape, dtype) in enumerate(MX4_CASES):
+        if name not in MX4_STOCHASTIC_CASES:
+            continue
+        x = mx4_inputs(name, shape, dtype, 700 + i).cuda()
+        for group in (32, 16):
+            for seed in MX4_SEEDS:
+                key = f"{name}.g{group}.m3.seed{seed}"
+                q, s = ops.quantize_mx4(x, group, 3, seed=seed)
+                assert torch.equal(s.cpu().view(torch.uint8), torch.from_numpy(gold[key + ".s"]).reshape(-1)), key
+                assert torch.equal(q.cpu(), torch.from_numpy(gold[key + ".q"])), key
+    for name, m_sizes, K in MX4_STACKED_STOCHASTIC_CASES:
+        x = mx4_inputs(name, (sum(m_sizes), K), "bf16", 900 + K).cuda()
+        ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+        q, s = ops.quantize_mx4_stacked(ms, x, 32, 3, seed=MX4_SEEDS[0])
+        assert torch.equal(s.cpu().view(torch.uint8), torch.from_numpy(gold[f"{name}.m3.s"]).reshape(-1)), name
+        assert torch.equal(q.cpu(), torch.from_numpy(gold[f"{name}.m3.q"])), name
+    assert _status() == 0
+
+
+def test_stochastic_rounding_properties(ops):
+    """What the reference's tests ask of the mode (test/quantize/triton/test_quantize_mx4.py:118-145,168-213): a seed
+    replays, another seed differs, a zero group keeps scale byte 0, +inf saturates the scale at 252; and the point of it:
+    averaged over seeds the dequantized values approach x more closely than one round-to-nearest pass does."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((64, 128), generator=g, device="cuda").bfloat16()
+    q0, s0 = ops.quantize_mx4(x, 32, 3, seed=0x12345678)
+    q1, s1 = ops.quantize_mx4(x, 32, 3, seed=0x12345678)
+    q2, _ = ops.quantize_mx4(x, 32, 3, seed=0x12345679)
+    assert torch.equal(q0, q1) and torch.equal(s0, s1) and not torch.equal(q0, q2)
+    torch.manual_seed(99)
+    qa, sa = ops.quantize_mx4(x, 32, 3)                                        # the CUDA generator's initial seed
+    qb, sb = ops.quantize_mx4(x, 32, 3, seed=torch.cuda.default_generators[0].initial_seed())
+    assert torch.equal(qa, qb) and torch.equal(sa, sb)
+    z = torch.zeros((1, 32), device="cuda", dtype=torch.bfloat16)
+    _, sz = ops.quantize_mx4(z, 32, 3, seed=0x12345678)
+    assert int(sz.view(torch.uint8)[0]) == 0
+    xi = x.clone()
+    xi[0, 0] = float("inf")
+    _, si = ops.quantize_mx4(xi, 32, 3, seed=0x12345678)
+    assert int(si.view(torch.uint8)[0]) == 252
+
+    # unbiasedness of the element rounding: every group's maximum is 3.0 (mantissa 0.5, which the group stream's 22 random
+    # bits cannot carry into the exponent), so every scale is 2^-1 and x / scale lies in (4.1, 6): between two e2m1 values
+    from oracle import fp4_to_float
+    xs = (torch.rand((32, 64), generator=g, device="cuda") * 0.9 + 2.05).bfloat16()
+    xs[:, ::32] = 3.0
+    acc = torch.zeros(xs.shape, device="cuda")
+    n = 64
+    for seed in range(n):
+        q, s = ops.quantize_mx4(xs, 32, 3, seed=seed)
+        sc = s.view(torch.uint8)[:512].reshape(32, 16)[:, :2]    # one 128 x 4 atom: row r < 32, column c at r * 16 + c
+        assert bool((sc == 126).all())
+        acc += fp4_to_float(q).to(acc.device) * 0.5
+    err_sr = (acc / n - xs.float()).abs().mean()
+    qn, sn = ops.quantize_mx4(xs, 32, 1)
+    err_rn = (fp4_to_float(qn).to(acc.device) * 0.5 - xs.float()).abs().mean()
+    assert float(err_sr) < 0.5 * float(err_rn), (float(err_sr), float(err_rn), n)
+    assert _status() == 0
+
+
 def test_quantizer_python_symbols_and_errors(ops):
     from mslk_b200 import compat
     compat.install()
@@ -70,7 +150,7 @@ def test_quantizer_python_symbols_and_errors(ops):
     q2, s2 = triton_quantize_mx4(x)
     assert torch.equal(q, q2) and torch.equal(s, s2)
     with pytest.raises(RuntimeError, match="rounding mode"):
-        ops.quantize_mx4(x, 32, 3)
+        ops.quantize_mx4(x, 32, 5)
     with pytest.raises(AssertionError):
         ops.quantize_mx4(x[..., :48], 32, 4)
 
@@ -294,6 +374,33 @@ def test_quantize_mx4_stacked_equals_per_segment(ops, m_sizes, K, group):
     for m in m_sizes:
         if m:
             q_ref, s_ref = oracle.quantize_mx4(x[r:r + m], group, 4)
+            assert torch.equal(q[r:r + m].cpu(), q_ref), (m_sizes, r)
+            want[pad * pc:pad * pc + s_ref.numel()] = s_ref.reshape(-1)
+        r += m
+        pad += (m + 127) // 128 * 128
+    assert torch.equal(s.cpu().view(torch.uint8), want)
+    assert _status() == 0
+
+
+@pytest.mark.parametrize("m_sizes,K,group", [([50, 30, 48], 64, 32), ([130, 0, 7], 256, 32), ([5, 11, 19], 64, 16),
+                                             ([300, 0, 1000, 129], 512, 32)])
+def test_quantize_mx4_stacked_stochastic(ops, m_sizes, K, group):
+    """Stochastic mode on stacked segments: the random streams are indexed by the row of the padded scale matrix
+    (mslk/quantize/triton/fp4_primitives/scale.py:200-201), so segment g equals the oracle run on its rows with the
+    stream rows shifted to the segment's 128-row-aligned start."""
+    M, G = sum(m_sizes), len(m_sizes)
+    g = torch.Generator().manual_seed(M + K)
+    x = (torch.randn((M, K), generator=g) * torch.exp2(torch.randint(-8, 8, (M, 1), generator=g).float())).bfloat16()
+    ms = torch.tensor(m_sizes, dtype=torch.int64, device="cuda")
+    seed = 0x12345678
+    q, s = ops.quantize_mx4_stacked(ms, x.cuda(), group, 3, seed=seed)
+    pc = (K // group + 3) // 4 * 4
+    want = torch.zeros_like(s, device="cpu").view(torch.uint8)
+    r = pad = 0
+    for m in m_sizes:
+        if m:
+            rows = torch.arange(pad, pad + m, dtype=torch.int32)
+            q_ref, s_ref = oracle.quantize_mx4(x[r:r + m], group, 3, seed=seed, stream_rows=rows)
             assert torch.equal(q[r:r + m].cpu(), q_ref), (m_sizes, r)
             want[pad * pc:pad * pc + s_ref.numel()] = s_ref.reshape(-1)
         r += m

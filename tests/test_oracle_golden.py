@@ -8,7 +8,8 @@ import torch
 
 import oracle
 from helpers import bf16, fp8, load_golden, u8, randn_bf16
-from golden.make_golden import FP8_ROW_CASES, MX4_CASES, NVFP4_CASES, mx4_inputs
+from golden.make_golden import (FP8_ROW_CASES, MX4_CASES, MX4_SEEDS, MX4_STACKED_STOCHASTIC_CASES, MX4_STOCHASTIC_CASES,
+                                NVFP4_CASES, mx4_inputs)
 
 
 def test_e4m3_encode_matches_torch_exhaustive_grid():
@@ -217,6 +218,79 @@ def test_mx4_triton_fixture_pins_the_mx4_oracle():
                 q, s = oracle.quantize_mx4(x, group, 0)
                 diff = s.reshape(-1) != torch.from_numpy(gold[key + ".s"]).reshape(-1)
                 assert float(diff.float().mean()) < 1e-3, key
+
+
+def test_mx4_stochastic_fixture_pins_the_oracle():
+    """Rounding mode 3 of the reference's kernel captured on a B200 with fixed seeds (dense and stacked) against the C
+    restatement with its own Philox, bit for bit."""
+    gold = load_golden("mx4_triton_b200.npz")
+    if gold is None or not any(".m3." in k for k in gold.keys()):
+        pytest.skip("fixture of the stochastic mode not present")
+    for i, (name, shape, dtype) in enumerate(MX4_CASES):
+        if name not in MX4_STOCHASTIC_CASES:
+            continue
+        x = mx4_inputs(name, shape, dtype, 700 + i)
+        for group in (32, 16):
+            for seed in MX4_SEEDS:
+                key = f"{name}.g{group}.m3.seed{seed}"
+                q, s = oracle.quantize_mx4(x, group, 3, seed=seed)
+                assert torch.equal(s.reshape(-1), torch.from_numpy(gold[key + ".s"]).reshape(-1)), key
+                assert torch.equal(q, torch.from_numpy(gold[key + ".q"])), key
+    for name, m_sizes, K in MX4_STACKED_STOCHASTIC_CASES:
+        x = mx4_inputs(name, (sum(m_sizes), K), "bf16", 900 + K)
+        gq, gs = torch.from_numpy(gold[f"{name}.m3.q"]), torch.from_numpy(gold[f"{name}.m3.s"]).reshape(-1)
+        pc = (K // 32 + 3) // 4 * 4
+        r = pad = 0
+        for m in m_sizes:
+            if m:
+                rows = torch.arange(pad, pad + m, dtype=torch.int32)
+                q, s = oracle.quantize_mx4(x[r:r + m], 32, 3, seed=MX4_SEEDS[0], stream_rows=rows)
+                assert torch.equal(q, gq[r:r + m]), (name, r)
+                assert torch.equal(s.reshape(-1), gs[pad * pc:pad * pc + s.numel()]), (name, r)
+            r += m
+            pad += (m + 127) // 128 * 128
+
+
+# First output word of Philox-4x32 with 7 rounds for (seed, offset), computed with Triton's own tl.randint in its
+# interpreter mode (no GPU needed); the test below recomputes them when Triton is importable.
+PHILOX7_KNOWN = [(1234, 0xFFFFFFF9, 0xCCFEFD1A), (0x12345678, 0xFFFFFFF9, 0x89980EC0),
+                 (0x7FFFFFFFFFFFFFF1, 0xFFFFFFF9, 0x018C5499)]
+
+_PHILOX_SCRIPT = """
+import os
+os.environ["TRITON_INTERPRET"] = "1"
+import torch, triton, triton.language as tl
+
+@triton.jit
+def k(out_ptr, seed, n: tl.constexpr):
+    offs = tl.arange(0, n) * 1000003 - 7
+    tl.store(out_ptr + tl.arange(0, n), tl.randint(seed, offs, n_rounds=7))
+
+out = torch.zeros(16, dtype=torch.int32)
+for seed in (1234, 0x12345678, 0x7FFFFFFFFFFFFFF1):
+    k[(1,)](out, seed, 16)
+    print(" ".join(str(int(v) & 0xFFFFFFFF) for v in out.tolist()))
+"""
+
+
+def test_philox_restatement_known_answers_and_triton_interpreter():
+    import subprocess
+    import sys
+    L = oracle.lib()
+    for seed, off, want in PHILOX7_KNOWN:
+        assert L.oracle_philox7_first_word(seed, off) == want
+    try:
+        import triton  # noqa: F401
+    except ImportError:
+        return
+    res = subprocess.run([sys.executable, "-c", _PHILOX_SCRIPT], capture_output=True, text=True, timeout=300)
+    if res.returncode != 0:
+        pytest.skip("Triton's interpreter mode did not run here: " + res.stderr[-200:])
+    lines = res.stdout.strip().splitlines()[-3:]
+    for seed, line in zip((1234, 0x12345678, 0x7FFFFFFFFFFFFFF1), lines):
+        got = [int(v) for v in line.split()]
+        mine = [L.oracle_philox7_first_word(seed, (i * 1000003 - 7) & 0xFFFFFFFF) for i in range(16)]
+        assert got == mine, seed
 
 
 def test_mx4_oracle_against_a_plain_statement():
