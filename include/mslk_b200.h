@@ -301,13 +301,13 @@ int mslk_b200_f4f4bf16_grouped_mm_mx(const void *xq, const void *wq, const void 
                                      int block_size, void *y, void *stream);
 
 /*
- * Diagnostics of the CTA-pair NVFP4 kernel's pipeline.  `dev_counters` is a device array of six 64-bit
+ * Diagnostics of the CTA-pair NVFP4 kernel's pipeline.  `dev_counters` is a device array of seven 64-bit
  * counters (zeroed by the caller) or NULL to switch the measurement off; while set, every launch of the pair
  * kernel adds SM clock cycles summed over its CTA pairs: [0] the MMA-issuing lane waiting for operand stages
  * to arrive, [1] the same lane waiting for the epilogue to hand back the accumulator, [2] that lane's whole
  * loop, [3] the leader's TMA-issuing lane waiting for free stages, [4] the leader's first epilogue warp between the
- * accumulator becoming ready and handing it back (the drain), [5] that warp waiting for the accumulator.  No counterpart
- * in the reference.
+ * accumulator becoming ready and handing it back (reading the columns the next tile's accumulator overlaps), [5] that
+ * warp waiting for the accumulator, [6] the same warp reading its remaining columns.  No counterpart in the reference.
  */
 int mslk_b200_debug_nvfp4_pair_timers(unsigned long long *dev_counters);
 

@@ -255,9 +255,13 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// arrive on an mbarrier that may live in the peer CTA (shared::cluster address)
+// Arrive on an mbarrier that may live in the peer CTA (shared::cluster address).  Used to hand an accumulator back to
+// the MMA-issuing CTA: what must be ordered before it are tensor-memory reads, which tcgen05.wait::ld has completed and
+// tcgen05.fence::before_thread_sync has fenced, so the default release at CTA scope is enough.  A cluster-scope
+// release (.release.cluster) makes the thread wait for all its earlier global stores as well: about 1 200 cycles per
+// tile, measured in the epilogue of the NVFP4 pair kernel.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // TMA load issued by either CTA of a pair; the bytes are counted on `bar_cluster_addr`,

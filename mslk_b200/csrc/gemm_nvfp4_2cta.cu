@@ -18,9 +18,11 @@
 //           pair-wide MMAs; commits to both CTAs' barriers
 //                                                       (idle; takes part in TMEM alloc)
 //   warps 2..9 epilogue on the CTA's own 128 accumulator rows: two warps per 32-lane quadrant, each draining
-//           128 of the 256 columns into registers (the next load in flight while a chunk is packed), handing
-//           the accumulator back, then staging 32 x 64 bf16 slabs in swizzled shared memory for TMA stores
-//           (128-byte row segments); all sixteen warps of the pair arrive on the leader's tmem_empty barrier
+//           four 32-column chunks of the accumulator into registers -- first the chunks the NEXT tile's accumulator
+//           overlaps (tiles alternate between two accumulators that share 96 columns), handing the accumulator
+//           back as soon as those have landed -- then staging 32 x 64 bf16 slabs in swizzled shared memory for
+//           TMA stores (128-byte row segments); all sixteen warps of the pair arrive on the leader's tmem_empty
+//           barrier
 //
 // Waits are bounded as everywhere else (common.cuh); cluster-wide hardware barriers only at start-up
 // and teardown, reached on every path.
@@ -44,8 +46,7 @@ constexpr int kMmaKBytes = 32;           // 64 K-elements per instruction
 constexpr int kAtomBytes = 512;          // 128 rows x 4 scales = the scales of one instruction
 constexpr int kNumEpilogueWarps = 8;
 constexpr int kNumThreads = 64 + 32 * kNumEpilogueWarps;
-constexpr int kAccCols = kPairBN;        // one accumulator
-constexpr int kSfBase = kAccCols;
+constexpr int kAccCols = kPairBN;        // columns of an accumulator
 constexpr int kTmemCols = 512;
 // block-scaled instruction descriptor: e2m1 x e2m1, ue4m3 scales, K-major, N = 256, M = 256 over the pair
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kPairBN >> 3) << 17) | (0u << 23) |
@@ -64,13 +65,22 @@ constexpr int kStageBytes = kStageA + kStageB + kStageSFA + kStageSFB;
 static_assert(kStageBytes % 1024 == 0, "stages keep the alignment of the swizzled tiles");
 constexpr int kStages = 5;
 constexpr int kSfCols = 12 * kMmasPerStage;   // one set of scale columns: A (4 per instruction) + B (8)
-static_assert(kSfBase + 2 * kSfCols <= 512, "tensor memory budget");
+// Tensor memory: the two sets of scale columns sit at the top; two accumulators of 256 columns share the 416 columns
+// below them, [0, 256) and [160, 416), tiles alternating between them.  They overlap in [160, 256): the epilogue of a
+// tile drains those 96 columns first and hands the accumulator back at once, so the next tile's instructions wait for
+// 3/8 of a drain instead of a whole one while the other 160 columns are read under them.
+constexpr int kSfBase = kTmemCols - 2 * kSfCols;
+constexpr int kAcc1Base = kSfBase - kAccCols;
+constexpr int kChunkCols = 32;                              // columns of one tensor-memory load
+static_assert(kAcc1Base >= 0 && kAcc1Base % kChunkCols == 0 && (kAccCols - kAcc1Base) == 3 * kChunkCols,
+              "the epilogue's chunk order assumes an overlap of three 32-column chunks");
 
 struct SmemTail {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   uint64_t tmem_full;
   uint64_t tmem_empty;
+  uint64_t early_done;   // this CTA's epilogue warps: the overlapped chunks of the current tile are in registers
   uint32_t tmem_base;
   int abort_flag;
   int row_start[kPairMaxGroups + 2];    // first stacked row of every group
@@ -162,6 +172,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     }
     mbar_init(&S.tmem_full, 1);
     mbar_init(&S.tmem_empty, 2 * kNumEpilogueWarps);   // the epilogue warps of both CTAs
+    mbar_init(&S.early_done, kNumEpilogueWarps);
     S.abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async_smem();
@@ -312,6 +323,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           if (timed) t_acc += clock_now() - t0;
         }
         tc_fence_after();
+        const uint32_t acc_t = tmem_base + ((local & 1) ? kAcc1Base : 0);
         int kbs = k_blocks, k_len = p.K, ncb = p.ncb;
         if constexpr (KG) {
           next_tile(tile);
@@ -346,7 +358,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
               }
 #pragma unroll
               for (int k = 0; k < kMmasPerStage; ++k)
-                mma_mxf4_2x_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                mma_mxf4_2x_pair(acc_t, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
                                  db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
                                  kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
                                  sfb_t + 8 * (k >> 1), (kb | k) != 0 ? 1u : 0u);
@@ -358,7 +370,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
                                           dsfb + static_cast<uint64_t>((kMmasPerStage + a) * (kAtomBytes >> 4)));
               }
               for (int k = 0; k < mmas; ++k)
-                mma_mxf4_2x_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+                mma_mxf4_2x_pair(acc_t, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
                                  db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
                                  kIdesc | kIdescScaleE8M0 | idesc_scale_ids((k & 1) * 2), sfa_t + 4 * (k >> 1),
                                  sfb_t + 8 * (k >> 1), (kb | k) != 0 ? 1u : 0u);
@@ -384,7 +396,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             }
 #pragma unroll
             for (int k = 0; k < kMmasPerStage; ++k)
-              mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+              mma_nvfp4_pair(acc_t, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
                              db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), idesc, sfa_t + 4 * k, sfb_t + 8 * k,
                              (kb | k) != 0 ? 1u : 0u);
           } else {
@@ -395,7 +407,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
                                         dsfb + static_cast<uint64_t>((kMmasPerStage + k) * (kAtomBytes >> 4)));
             }
             for (int k = 0; k < atoms; ++k)
-              mma_nvfp4_pair(tmem_base, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
+              mma_nvfp4_pair(acc_t, da + static_cast<uint64_t>(k * (kMmaKBytes >> 4)),
                              db + static_cast<uint64_t>(k * (kMmaKBytes >> 4)), idesc, sfa_t + 4 * k, sfb_t + 8 * k,
                              (kb | k) != 0 ? 1u : 0u);
           }
@@ -422,7 +434,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
     const int quad = warp & 3;                 // tensor-memory lanes this warp may read: 32 * (warp % 4) ...
-    const int half = (warp - 2) >> 2;          // which 128 of the tile's 256 columns
+    const int half = (warp - 2) >> 2;          // the two warps of a quadrant
     uint8_t *buf = out_stage + (warp - 2) * kOutSlabBytes;
     int local = 0;
     for (int tile = pair_id; next_tile(tile); tile += num_pairs, ++local) {
@@ -430,30 +442,48 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       const bool empty_group = KG && t.k_len == 0;   // nothing was accumulated: the tile is zero
       const int slab0 = static_cast<int>(rank) * kBM + quad * 32;   // first row of this warp's slab inside the tile
       const int row0 = t.row0 + slab0;
-      const int col0 = t.n0 + half * 128;
       const int slab_rows = min(32, t.rows - slab0);                // rows of the slab that belong to the tile's group (<= 0: none)
+      // This warp's two 64-column slabs (as 32-column chunks of the accumulator) and which of its four chunks the
+      // next tile's accumulator overlaps.  Accumulator 0 is overlapped in its chunks 5..7, accumulator 1 in 0..2:
+      //   accumulator 0: warp A slabs {6,7} (both early), {0,1};  warp B slabs {4,5} (5 early), {2,3}
+      //   accumulator 1: warp A slabs {0,1} (both early), {6,7};  warp B slabs {2,3} (2 early), {4,5}
+      const int acc = local & 1;
+      const int slab_a = acc ? (half ? 2 : 0) : (half ? 4 : 6);     // first chunk of the slab with the early chunks
+      const int slab_b = acc ? (half ? 4 : 6) : (half ? 2 : 0);
+      const bool early0 = half == 0 || acc == 1, early1 = half == 0 || acc == 0;
       const long long te0 = timed ? clock_now() : 0;
       const bool got = mbar_wait(&S.tmem_full, local & 1, abort_flag, p.status, kStatusEpilogueTimeout);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
       const long long te1 = timed ? clock_now() : 0;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(half * 128);
-      // drain this warp's 128 columns (scaled, packed to bf16) with the next load in flight while a chunk is
-      // packed, and hand the accumulator back before anything is stored
-      // drain this warp's 128 columns with all four loads in flight at once, hand the accumulator back as soon as
-      // they have landed, and only then scale and pack (two fp32 registers become one packed pair in place)
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc ? kAcc1Base : 0);
+      const uint32_t ta = taddr + static_cast<uint32_t>(slab_a * kChunkCols), tb = taddr + static_cast<uint32_t>(slab_b * kChunkCols);
+      // the overlapped chunks first; the accumulator goes back as soon as they have landed, the rest is read while
+      // the next tile's instructions already run; only then scale and pack (two fp32 registers become one packed pair)
       uint32_t r0[32], r1[32], r2[32], r3[32];
-      tmem_ld_32x32(taddr, r0);
-      tmem_ld_32x32(taddr + 32, r1);
-      tmem_ld_32x32(taddr + 64, r2);
-      tmem_ld_32x32(taddr + 96, r3);
+      if (early0) tmem_ld_32x32(ta, r0);
+      if (early1) tmem_ld_32x32(ta + kChunkCols, r1);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty), 0));
+      if (lane == 0) {
+        mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty), 0));
+        mbar_arrive(&S.early_done);
+      }
+      const long long te2 = timed ? clock_now() : 0;
+      // the other chunks are read only once every warp of this CTA has its overlapped chunks: tensor-memory reads
+      // are served in order, and a fast warp's remaining chunks would otherwise hold up a slow warp's early ones
+      const bool all_early = mbar_wait(&S.early_done, local & 1, abort_flag, p.status, kStatusEpilogueTimeout);
+      if (!__all_sync(0xffffffffu, all_early)) break;
+      if (!early0) tmem_ld_32x32(ta, r0);
+      if (!early1) tmem_ld_32x32(ta + kChunkCols, r1);
+      tmem_ld_32x32(tb, r2);
+      tmem_ld_32x32(tb + kChunkCols, r3);
+      tmem_ld_wait();
       if (timed && leader && warp == 2 && lane == 0) {
-        atomicAdd(p.timers + 4, static_cast<unsigned long long>(clock_now() - te1));   // drain: accumulator ready -> handed back
-        atomicAdd(p.timers + 5, static_cast<unsigned long long>(te1 - te0));           // waiting for the accumulator
+        atomicAdd(p.timers + 4, static_cast<unsigned long long>(te2 - te1));   // accumulator ready -> handed back
+        atomicAdd(p.timers + 5, static_cast<unsigned long long>(te1 - te0));   // waiting for the accumulator
+        atomicAdd(p.timers + 6, static_cast<unsigned long long>(clock_now() - te2));   // the rest of the drain
       }
       uint32_t packed[64];
       auto pack = [&](const uint32_t (&r)[32], int c) {
@@ -469,7 +499,8 @@ __global__ void __launch_bounds__(kNumThreads, 1)
       if (p.tma_store && slab_rows == 32) {
 #pragma unroll
         for (int s2 = 0; s2 < 2; ++s2) {
-          if (col0 + s2 * kOutCols >= p.N) break;     // slab entirely outside the matrix (warp-uniform)
+          const int col = t.n0 + (s2 ? slab_b : slab_a) * kChunkCols;
+          if (col >= p.N) continue;                   // slab entirely outside the matrix (warp-uniform)
           if (lane == 0) tma_store_wait_read<0>();   // the store that last read this buffer is done with it
           __syncwarp();
 #pragma unroll
@@ -482,17 +513,18 @@ __global__ void __launch_bounds__(kNumThreads, 1)
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_y, buf, col0 + s2 * kOutCols, row0);   // columns past the matrix are clipped
+            tma_store_2d(&tmap_y, buf, col, row0);   // columns past the matrix are clipped
             tma_store_commit();
           }
         }
       } else if (lane < slab_rows) {
         // ragged slab (the group or the matrix ends inside it) or unaligned output: rows of this group only
-        __nv_bfloat16 *yrow = p.y + static_cast<size_t>(row0 + lane) * p.N + col0;
+        __nv_bfloat16 *yrow = p.y + static_cast<size_t>(row0 + lane) * p.N;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const int cols_left = p.N - (col0 + c * 32);
-          uint16_t *d = reinterpret_cast<uint16_t *>(yrow + c * 32);
+          const int col = t.n0 + ((c < 2 ? slab_a : slab_b) + (c & 1)) * kChunkCols;
+          const int cols_left = p.N - col;
+          uint16_t *d = reinterpret_cast<uint16_t *>(yrow + col);
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (j < cols_left) d[j] = static_cast<uint16_t>(packed[c * 16 + j / 2] >> ((j & 1) * 16));

@@ -36,7 +36,8 @@ struct PairParams {
   int alpha_per_group;
   unsigned long long *timers;   // optional SM-cycle counters (sums over pairs): [0] the MMA lane waiting for operand stages,
                                 // [1] for a free accumulator, [2] its whole loop, [3] the leader's producer waiting for free
-                                // stages, [4] the leader's first epilogue warp draining the accumulator, [5] waiting for it
+                                // stages, [4] the leader's first epilogue warp from "accumulator ready" to handing it back
+                                // (the chunks the next accumulator overlaps), [5] waiting for it, [6] reading the other chunks
 };
 
 // Dense problems and grouped ones with at most kPairMaxGroups groups.  Returns 0 on success, a non-zero code after recording an error, or -1 when
@@ -44,7 +45,7 @@ struct PairParams {
 int launch_pair_kernel(const void *xq, const void *wq, const void *x_scale, const void *w_scale, const PairParams &p,
                        cudaStream_t st);
 
-// Diagnostics: device array of six 64-bit counters the kernel adds its wait cycles to (nullptr = off).
+// Diagnostics: device array of seven 64-bit counters the kernel adds its wait cycles to (nullptr = off).
 void set_pipe_timers(unsigned long long *dev_counters);
 
 }  // namespace nvfp4_pair
