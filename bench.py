@@ -797,8 +797,8 @@ def time_cpu_baseline(tokens, repeats):
 def e2e_run(tp, dd, steps):
     """The step through the public operators with HOST buffers: every step copies the bf16 activation of gate+up and
     this rank's fp8 slice of the down activation from pinned host memory, and copies the results back (this rank's
-    rows of the gathered gate+up output and its rows of the down output).  Three streams (copies in, kernels,
-    copies out) ordered by events."""
+    rows of the gathered gate+up output and its rows of the down output) to pinned host memory.  Three streams (copies
+    in, kernels, copies out) ordered by events; steps overlap as in a serving loop, every step's bytes cross PCIe."""
     import torch.distributed as dist
     device, P, r = tp.device, tp.world, tp.rank
     rows = tp.rows
@@ -809,16 +809,26 @@ def e2e_run(tp, dd, steps):
     x1_slice = torch.empty((rows, tp.x1.shape[1]), dtype=torch.bfloat16, device=device) if P > 1 else None
     hx2 = torch.empty(tp.xq2_k.shape, dtype=torch.uint8).pin_memory()
     hx2.copy_(tp.xq2_k.view(torch.uint8))
-    hy1 = torch.empty((rows, GATE_UP[0]), dtype=torch.bfloat16).pin_memory()
-    hy2 = torch.empty((rows, DOWN[0]), dtype=torch.bfloat16).pin_memory()
+    hy1 = [torch.empty((rows, GATE_UP[0]), dtype=torch.bfloat16).pin_memory() for _ in range(2)]   # results alternate, so
+    hy2 = [torch.empty((rows, DOWN[0]), dtype=torch.bfloat16).pin_memory() for _ in range(2)]      # a reader has a step's time
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     s_main = torch.cuda.current_stream(device)
-    ev_in, ev_used, ev_done1, ev_done2, ev_out = (torch.cuda.Event() for _ in range(5))
+    ev_in, ev_used, ev_done1, ev_done2 = (torch.cuda.Event() for _ in range(4))
     ev_used.record(s_main)
-    ev_out.record(s_main)
+    # The results leave through two alternating pairs of device staging buffers: a device-to-device copy on the compute
+    # stream frees the operators' output buffers for the next step at once, and the copies to the host (the slowest part
+    # of the step: PCIe) run back to back on their own stream under the next steps' kernels.
+    stage1 = [torch.empty((rows, GATE_UP[0]), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    stage2 = [torch.empty((rows, DOWN[0]), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    for e in ev_out:
+        e.record(s_main)
     x2_u8 = tp.xq2_k.view(torch.uint8)
+    count = [0]
 
     def step():
+        b = count[0] & 1
+        count[0] += 1
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_used)             # the previous step has consumed the device copies
             if P > 1:
@@ -829,25 +839,27 @@ def e2e_run(tp, dd, steps):
             x2_u8.copy_(hx2, non_blocking=True)
             ev_in.record(s_in)
         s_main.wait_event(ev_in)
-        s_main.wait_event(ev_out)                # the previous results have left the output buffers
         if P > 1:
-            tp.h1.barrier()                      # ... on every rank, before any peer stores into them again
+            tp.h1.barrier()                      # every rank is past its copies out of the buffers the peers store into
         xq, xs = tp.quantize()
         tp.gate_up_fused(xq, xs)
+        s_main.wait_event(ev_out[b])             # the results of two steps ago have left this pair of staging buffers
+        stage1[b].copy_(tp.y1[r * rows:(r + 1) * rows])
         ev_done1.record(s_main)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done1)
-            hy1.copy_(tp.y1[r * rows:(r + 1) * rows], non_blocking=True)
+            hy1[b].copy_(stage1[b], non_blocking=True)
         if tp.fused_down:
             tp.down_fused()
         else:
             tp.down_nccl()
         ev_used.record(s_main)
+        stage2[b].copy_(tp.y2)
         ev_done2.record(s_main)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_done2)
-            hy2.copy_(tp.y2, non_blocking=True)
-            ev_out.record(s_out)
+            hy2[b].copy_(stage2[b], non_blocking=True)
+            ev_out[b].record(s_out)
 
     def join():
         s_main.wait_stream(s_in)
@@ -865,8 +877,14 @@ def e2e_run(tp, dd, steps):
     s1.record()
     dd.barrier()
     ms = dd.max(s0.elapsed_time(s1) / e_steps)
-    return {"value": ffn_flops() / ms / 1e9, "unit": "TFLOP/s", "ms_per_step": ms,
-            "h2d_bytes_per_step": hx1.numel() * 2 + hx2.numel(), "d2h_bytes_per_step": (hy1.numel() + hy2.numel()) * 2,
+    # the last step's results on the host are the device's (the inputs are the same every step, so both pairs hold them)
+    torch.cuda.synchronize(device)
+    last = (count[0] - 1) & 1
+    arrived = bool(torch.equal(hy2[last], tp.y2.cpu())) and \
+        bool(torch.equal(hy1[last][:64], tp.y1[r * rows:r * rows + 64].cpu())) and \
+        bool(torch.equal(hy1[last][-64:], tp.y1[(r + 1) * rows - 64:(r + 1) * rows].cpu()))
+    return {"value": ffn_flops() / ms / 1e9, "unit": "TFLOP/s", "ms_per_step": ms, "results_on_host_match_device": arrived,
+            "h2d_bytes_per_step": hx1.numel() * 2 + hx2.numel(), "d2h_bytes_per_step": (hy1[0].numel() + hy2[0].numel()) * 2,
             "note": "bytes are per rank; every rank copies its 1/P of the rows of the replicated activation in (an NCCL "
                     "all-gather completes it on every GPU), its K slice of the down operand in, and its own rows of both "
                     "results out"}
