@@ -48,6 +48,7 @@ GATE_UP = (57344, 8192)
 DOWN = (8192, 28672)
 CPU_SAMPLE_TOKENS = 256
 LLAMA8B_PROJECTIONS = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
+SM_INGEST_TBS = 13.0           # TB/s from L2 into the SMs: what ncu counted on the FP8 and both FP4 pair kernels at 8192^3
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_FP4_TFLOPS = 9000.0
 NOMINAL_HBM_GBS = 8000.0
@@ -962,6 +963,10 @@ def run_ours(args, rank, world, local_rank):
         n1l, k2l = GATE_UP[0] // world, DOWN[1] // world      # operands + output once, per rank
         alg_bytes = [FFN_TOKENS * GATE_UP[1] + n1l * GATE_UP[1] + 2 * FFN_TOKENS * n1l,
                      FFN_TOKENS * k2l + DOWN[0] * k2l + 2 * FFN_TOKENS * DOWN[0]]
+        # bytes the two launches bring into the SMs' shared memory: every 256 x 256 pair tile takes 2 x 32 KB per K block of 128
+        def _sm_bytes(m, n, k):
+            return ((m + 255) // 256) * ((n + 255) // 256) * ((k + 127) // 128) * 2 * 32768
+        sm_bytes = _sm_bytes(FFN_TOKENS, n1l, GATE_UP[1]) + _sm_bytes(FFN_TOKENS, DOWN[0], k2l)
         line.update({
             "value": value, "ms_per_step": per_step_ms, "gpu_launches": tp.launches_per_step() * args.steps,
             "roofline": {"bound": "tensor", "kernel": "gemm_f8_rowwise_pair_kernel", "achieved": achieved,
@@ -972,7 +977,14 @@ def run_ours(args, rank, world, local_rank):
                          "peak_source": f"2 x bf16_tflops (burst) of {peaks['source']} peaks (the fp8 tensor rate is twice the bf16 rate; "
                                         "the peaks file holds no fp8 figure)",
                          "frac_of_nominal_4500": achieved / NOMINAL_FP8_TFLOPS,
-                         "flops_per_step_per_gpu": ffn_flops() / world, "ms_in_kernel": gemm_only},
+                         "flops_per_step_per_gpu": ffn_flops() / world, "ms_in_kernel": gemm_only,
+                         "operand_delivery": {
+                             "achieved_tbs": sm_bytes / gemm_only / 1e9, "ceiling_tbs": SM_INGEST_TBS,
+                             "frac": sm_bytes / gemm_only / 1e9 / SM_INGEST_TBS, "bytes_per_step_per_gpu": sm_bytes,
+                             "note": "operand bytes landing in the SMs' shared memory (2 x 32 KB per pair tile and K block) over "
+                                     "the same kernel time; the ceiling is the L2 -> SM rate ncu counted on this kernel and on "
+                                     "both FP4 pair kernels at 8192^3 (l1tex__m_xbar2l1tex_read_bytes per second, whatever the "
+                                     "SM clock): with 256 x 256 pair tiles it caps FP8 at 3.33 PFLOP/s"}},
             "in_step_intervals_ms": {"gate_up_gemm_with_collective": g1_ms, "down_gemm_with_collective": g2_ms,
                                      "quantize_and_gaps": per_step_ms - g1_ms - g2_ms,
                                      "note": "rank 0's event intervals inside the timed region"},
