@@ -164,6 +164,32 @@ def _mx_case(ops, M, N, K, group, seed=0):
     return x, w, xq, wq, sx, sw
 
 
+@pytest.mark.parametrize("M,N,K", [(2321, 2608, 1312), (2560, 2816, 544), (3100, 2304, 256)])
+@pytest.mark.parametrize("fmt", ["mx32", "mx16", "nvfp4"])
+def test_pair_kernel_ragged_shapes_both_accumulators(ops, M, N, K, fmt):
+    """More than 74 tiles of 256 x 256, so CTA pairs take the problem and every pair runs several tiles, alternating
+    between its two overlapping accumulators: ragged last row block, a last column block that ends inside a 64-column
+    slab, a partial last K block, a single K block (the next tile's first instruction follows the hand-back at once)."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = (torch.randn((M, K), generator=g, device="cuda") * 0.1).bfloat16()
+    w = (torch.randn((N, K), generator=g, device="cuda") * 0.01).bfloat16()
+    if fmt == "nvfp4":
+        gx, gw = 2688.0 / x.abs().amax().float(), 2688.0 / w.abs().amax().float()
+        xq, sx = ops.quantize_nvfp4(x, gx)
+        wq, sw = ops.quantize_nvfp4(w, gw)
+        alpha = (1.0 / (gx * gw)).reshape(1)
+        y = ops.f4f4bf16(xq, wq, sx, sw, global_scale=alpha)
+        y_ref = oracle.gemm_nvfp4_torch(xq, wq, sx, sw, alpha)
+    else:
+        group = 32 if fmt == "mx32" else 16
+        xq, sx = ops.quantize_mx4(x, group)
+        wq, sw = ops.quantize_mx4(w, group)
+        y = ops.f4f4bf16(xq, wq, sx, sw, mxfp4_block_size=group)
+        y_ref = oracle.gemm_mx4_torch(xq, wq, sx, sw, group)
+    assert_sharp_bf16(y, y_ref, f"pair kernel {fmt} {M}x{N}x{K}")
+    assert _status() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 256, 2048), (250, 512, 2048), (250, 1024, 3584), (128, 128, 128), (130, 144, 96),
                                    (300, 272, 320), (2048, 4096, 4096), (512, 2048, 1056)])
 @pytest.mark.parametrize("group", [32, 16])
